@@ -1,0 +1,79 @@
+/* kyb.h - C ABI of the B200 (sm_100a) dequant-fused quantized linear.
+ *
+ * This is the drop-in boundary for the quantized-linear / routed-expert path of kyojin-mac. The reference has no
+ * FFI for this path: its operators are Python functions that hand Metal kernel text to MLX
+ * (kyojin_mlx/kernels.py:40-44 `_kern` -> mx.fast.metal_kernel). Each entry point below names the reference
+ * function(s) whose device work it replaces; the Python mirror of those functions lives in kyojin_mac_b200/.
+ *
+ * Conventions
+ *   - every pointer is a caller-owned DEVICE pointer unless it is named host_*; nothing here allocates device
+ *     memory (scratch is passed in; sizes come from the *_workspace_bytes functions);
+ *   - `stream` is a cudaStream_t passed as void*; calls are asynchronous on it and re-entrant across streams;
+ *   - weights W are [n out rows, k inputs], activations x are row-major fp16 [m, k] with row stride ldx (elements),
+ *     y = x W^T is fp16 [m, n] (row stride ldy), accumulated in fp32 and saturated to +-65504 (never inf), as the
+ *     reference kernels do (kyojin_mlx/foreign_metal.py:344, :1076);
+ *   - return value: KYB_OK or a negative status; kyb_last_error() gives the message of the calling thread's last
+ *     failure. Shape or alignment violations are reported, never silently fixed.
+ */
+#ifndef KYB_H
+#define KYB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KYB_OK            0
+#define KYB_EINVAL       -1   /* bad shape, alignment, format or null pointer */
+#define KYB_ECUDA        -2   /* a CUDA runtime call failed (message in kyb_last_error) */
+#define KYB_ETIMEOUT     -3   /* a bounded device-side wait expired (reported through the status word) */
+#define KYB_EUNSUPPORTED -4   /* valid request outside what this build implements */
+#define KYB_EWORKSPACE   -5   /* scratch buffer missing or too small */
+
+/* weight formats (GGUF block types of kyojin_mlx/foreign_gguf.py:27-35 TYPES; NVFP4 also in the qs/meta pack form) */
+#define KYB_FMT_Q4_K  0
+#define KYB_FMT_Q6_K  1
+#define KYB_FMT_Q3_K  2
+#define KYB_FMT_NVFP4 3
+
+#define KYB_DT_F32 0
+#define KYB_DT_F16 1
+
+int kyb_version(void);
+const char* kyb_status_string(int status);
+const char* kyb_last_error(void);
+
+/* ---- T16 layout (load time). Replaces kyojin_mlx/foreign_gguf.py:634-789 `to_pack` (lossless repack of the stored
+ * blocks into the order the kernels read) and kyojin_mlx/fp4tile.py:72-134 `to_tile` / `from_tile`.
+ * raw: GGUF rows [n, k / block_elems * block_bytes]; t16: kyb_t16_nbytes bytes (n padded to 16 rows with zero blocks). */
+size_t kyb_t16_nbytes(int fmt, int64_t n, int64_t k);
+size_t kyb_raw_row_bytes(int fmt, int64_t k);
+int kyb_repack_raw_to_t16(int fmt, const void* raw, int64_t n, int64_t k, void* t16, void* stream);
+int kyb_repack_t16_to_raw(int fmt, const void* t16, int64_t n, int64_t k, void* raw, void* stream);
+
+/* ---- dequantise a T16 matrix to row-major [n, k] (ld elements per row), fp32 (bit-equal to
+ * kyojin_mlx/foreign_gguf.py:376-394 `dequant` / foreign_pack.py:179-215 `dequant`) or fp16 (= that fp32 value rounded
+ * to nearest, saturated). Replaces kyojin_mlx/foreign_linear.py:1050-1065 `DevPack.dequant` (kernels
+ * foreign_metal.py:291-312 `dequant_source`, :1130-1146 `dequantk_source`). gscale: NVFP4 per-tensor scale (1 otherwise),
+ * applied as one fp32 multiply (foreign_pack.py:213). Rows [row0, row0 + nrows) only (row0 % 16 == 0). */
+int kyb_dequant_t16(int fmt, const void* t16, int64_t n, int64_t k, int64_t row0, int64_t nrows, float gscale,
+                    int out_dtype, void* out, int64_t ld, void* stream);
+
+/* ---- decode GEMV, m <= 32 activation rows. Replaces kyojin_mlx/foreign_linear.py:846-857 `DevPack._gemv` /
+ * `_gemvk` (kernels foreign_metal.py:115-202 `gemv_source`, :1004-1099 `_gemvk_source`) and the few-row products
+ * :1025-1048 `_fmma` / `_mma` / :859-863 `_mmak`. The result of an activation row does not depend on m.
+ * workspace: kyb_gemv_workspace_bytes bytes (may be 0 -> workspace may be NULL); split-k partial sums live there. */
+size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m);
+int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
+                 void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
+
+/* device status word of the calling thread's current device: nonzero after a bounded wait expired inside a kernel.
+ * kyb_check_device_status synchronises `stream`, reads and clears it. */
+int kyb_check_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KYB_H */

@@ -1,0 +1,106 @@
+"""Loader and ctypes signatures of libkyb.so, the C-ABI CUDA library (include/kyb.h).
+
+The library is built in-tree (kyojin_mac_b200/libkyb.so) by `build()` with nvcc for sm_100a. There is no fallback: if the
+library cannot be loaded every operator raises KybUnavailable."""
+from __future__ import annotations
+
+import ctypes as C
+import glob
+import os
+import subprocess
+import threading
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+SO_PATH = os.path.join(HERE, "libkyb.so")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
+
+OK, EINVAL, ECUDA, ETIMEOUT, EUNSUPPORTED, EWORKSPACE = 0, -1, -2, -3, -4, -5
+
+
+class KybError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"kyb status {status}: {msg}")
+        self.status = status
+
+
+class KybUnavailable(RuntimeError):
+    pass
+
+
+def _nvcc() -> str:
+    for p in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc"):
+        if p and os.path.exists(p):
+            return p
+    return "nvcc"
+
+
+def sources() -> list[str]:
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+
+
+def _stale() -> bool:
+    if not os.path.exists(SO_PATH):
+        return True
+    t = os.path.getmtime(SO_PATH)
+    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(os.path.dirname(HERE), "include", "kyb.h")]
+    return any(os.path.getmtime(d) > t for d in deps)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compiles every .cu under csrc/ into libkyb.so for sm_100a (cross-compiles without a GPU)."""
+    if not force and not _stale():
+        return SO_PATH
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", SO_PATH + ".tmp"] + sources() + ["-lcuda"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+    os.replace(SO_PATH + ".tmp", SO_PATH)
+    if verbose:
+        print(r.stderr)
+    return SO_PATH
+
+
+_lock = threading.Lock()
+_lib = None
+
+_vp, _i64, _sz, _int, _f32 = C.c_void_p, C.c_int64, C.c_size_t, C.c_int, C.c_float
+SIGNATURES = {
+    "kyb_version": (_int, []),
+    "kyb_status_string": (C.c_char_p, [_int]),
+    "kyb_last_error": (C.c_char_p, []),
+    "kyb_t16_nbytes": (_sz, [_int, _i64, _i64]),
+    "kyb_raw_row_bytes": (_sz, [_int, _i64]),
+    "kyb_repack_raw_to_t16": (_int, [_int, _vp, _i64, _i64, _vp, _vp]),
+    "kyb_repack_t16_to_raw": (_int, [_int, _vp, _i64, _i64, _vp, _vp]),
+    "kyb_dequant_t16": (_int, [_int, _vp, _i64, _i64, _i64, _i64, _f32, _int, _vp, _i64, _vp]),
+    "kyb_gemv_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
+    "kyb_gemv_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _vp]),
+    "kyb_check_device_status": (_int, [_vp]),
+}
+
+
+def lib():
+    """The loaded library (ctypes.CDLL with typed entry points). Raises KybUnavailable when it is missing: no CPU path exists."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(SO_PATH):
+                raise KybUnavailable(f"{SO_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                                     "(kyojin_mac_b200 has no CPU fallback)")
+            try:
+                h = C.CDLL(SO_PATH)
+            except OSError as e:
+                raise KybUnavailable(f"cannot load {SO_PATH}: {e}") from e
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(h, name)
+                fn.restype, fn.argtypes = res, args
+            _lib = h
+    return _lib
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise KybError(status, lib().kyb_last_error().decode("utf-8", "replace") or lib().kyb_status_string(status).decode())

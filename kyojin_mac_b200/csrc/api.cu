@@ -1,0 +1,79 @@
+// Status plumbing of the kyb C ABI: thread-local error text, status strings, the per-device status word.
+#include <stdarg.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "kyb_common.cuh"
+
+static thread_local char g_err[512] = "";
+
+void kyb_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+static std::mutex g_status_mu;
+static unsigned int* g_status_words[64] = {nullptr};
+
+unsigned int* kyb_device_status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(g_status_mu);
+    if (!g_status_words[dev]) {
+        unsigned int* p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;      // one-time, 256 bytes per device, never freed
+        if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
+        g_status_words[dev] = p;
+    }
+    return g_status_words[dev];
+}
+
+extern "C" {
+
+int kyb_version(void) { return 100; }
+
+const char* kyb_status_string(int status) {
+    switch (status) {
+        case KYB_OK: return "ok";
+        case KYB_EINVAL: return "invalid argument";
+        case KYB_ECUDA: return "CUDA runtime error";
+        case KYB_ETIMEOUT: return "a bounded device-side wait expired";
+        case KYB_EUNSUPPORTED: return "unsupported request";
+        case KYB_EWORKSPACE: return "workspace missing or too small";
+        default: return "unknown status";
+    }
+}
+
+const char* kyb_last_error(void) { return g_err; }
+
+int kyb_check_device_status(void* stream) {
+    unsigned int* w = kyb_device_status_word();
+    if (!w) {
+        kyb_set_error("no device status word (no CUDA device?)");
+        return KYB_ECUDA;
+    }
+    unsigned int v = 0;
+    KYB_CUDA(cudaMemcpyAsync(&v, w, sizeof(v), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    KYB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    if (v) {
+        KYB_CUDA(cudaMemsetAsync(w, 0, sizeof(v), (cudaStream_t)stream));
+        kyb_set_error("device status 0x%x: a kernel gave up a bounded wait", v);
+        return KYB_ETIMEOUT;
+    }
+    return KYB_OK;
+}
+
+size_t kyb_t16_nbytes(int fmt, int64_t n, int64_t k) {
+    if (fmt < 0 || fmt > 3 || n <= 0 || k <= 0 || k % 256) return 0;
+    return (size_t)((n + 15) / 16) * (size_t)(k / 256) * (size_t)kyb_tile_bytes(fmt);
+}
+
+size_t kyb_raw_row_bytes(int fmt, int64_t k) {
+    if (fmt < 0 || fmt > 3 || k <= 0 || k % kyb_raw_block_elems(fmt)) return 0;
+    return (size_t)(k / kyb_raw_block_elems(fmt)) * (size_t)kyb_raw_block_bytes(fmt);
+}
+
+}  // extern "C"
