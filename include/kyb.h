@@ -69,6 +69,10 @@ size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m);
 int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
                  void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
 
+/* launch plan the GEMV would use (diagnostics and launch counting): out8 = {column tiles, stored x rows per tile, warps per CTA,
+ * ring stages, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. ksplit > 1 means two launches. */
+int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);
+
 /* device status word of the calling thread's current device: nonzero after a bounded wait expired inside a kernel.
  * kyb_check_device_status synchronises `stream`, reads and clears it. */
 int kyb_check_device_status(void* stream);

@@ -13,6 +13,8 @@
 // result of an activation row does not depend on how many rows ride along.
 #include <algorithm>
 #include <atomic>
+#include <mutex>
+#include <unordered_map>
 
 #include "t16_decode.cuh"
 
@@ -53,18 +55,21 @@ __device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int
     const int r = lane >> 1, hf = lane & 1;
     if constexpr (FMT == KYB_FMT_Q4_K) {
         const uint4 mt = *reinterpret_cast<const uint4*>(tile + 2048 + r * 16);
-        const uint32_t scw = hf ? ((mt.w & 0x0f0f0f0fu) | ((mt.y >> 2) & 0x30303030u)) : (mt.y & 0x3f3f3f3fu);
+        // 6-bit scales of sub-blocks 4 hf .. 4 hf + 3 as four bytes (kyojin_mlx/foreign_gguf.py:340-346)
+        const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const float d = half_bits_to_float(mt.x & 0xffffu);
 #if KYB_Q4K_SUBNORMAL
         const float dlo = d * 16777216.0f, dhi = d * 1048576.0f;     // even sub-blocks: code * 2^-24, odd: code * 2^-20
 #else
         const float dlo = d, dhi = d * 0.0625f;
 #endif
+        // byte b -> float without a convert: 0x4B0000bb is 2^23 + b, and fma((2^23 + b), d, -2^23 d) = b d exactly
+        const float nlo = dlo * -8388608.0f, nhi = dhi * -8388608.0f;
         float4 o;
-        o.x = dlo * (float)(scw & 255u);
-        o.y = dhi * (float)((scw >> 8) & 255u);
-        o.z = dlo * (float)((scw >> 16) & 255u);
-        o.w = dhi * (float)(scw >> 24);
+        o.x = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7440u)), dlo, nlo);
+        o.y = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7441u)), dhi, nhi);
+        o.z = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7442u)), dlo, nlo);
+        o.w = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7443u)), dhi, nhi);
         *reinterpret_cast<float4*>(scl + r * 16 + 4 * hf) = o;
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         const uint2 sw = *reinterpret_cast<const uint2*>(tile + 3072 + r * 16 + 8 * hf);
@@ -118,13 +123,6 @@ struct Acc {
     float v[NT][4];
 };
 
-// B fragments of one 16-input chunk for column tile nt (zero for lanes whose activation row is not stored)
-__device__ __forceinline__ uint2 load_b(const uint8_t* xfrag, int chunk, int nt, int NT_, int mst, int g, int t) {
-    uint2 b = make_uint2(0u, 0u);
-    if (g < mst) b = *reinterpret_cast<const uint2*>(xfrag + ((size_t)(chunk * NT_ + nt) * mst + g) * 32 + t * 8);
-    return b;
-}
-
 template <int NT>
 __device__ __forceinline__ void scale_acc(Acc<NT>& acc, const float (&c)[NT][4], float s_lo, float s_hi) {
 #pragma unroll
@@ -137,11 +135,13 @@ __device__ __forceinline__ void scale_acc(Acc<NT>& acc, const float (&c)[NT][4],
 }
 
 // ---- one tile (16 rows x 256 inputs) ----------------------------------------------------------------------------------
-template <int FMT, int NT>
-__device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* scl, const uint8_t* xfrag, const uint8_t* xaux, int blk, int mst, int lane,
-                                             Acc<NT>& acc) {
+// xb: this lane's B-fragment pointer for the tile's k-block (chunk c, column tile nt at xb + c * CS + nt * MST * 32, all
+// compile-time offsets); xa: this lane's word of the Q4_K sub-block sums of the k-block.
+template <int FMT, int NT, int MST>
+__device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* scl, const uint8_t* xb, const uint32_t* xa, int lane, Acc<NT>& acc) {
+    constexpr int CS = NT * MST * 32;
     const int g = lane >> 2, t = lane & 3;
-    const int chunk0 = blk * 16;
+    auto ldb = [&](int chunk, int nt) -> uint2 { return *reinterpret_cast<const uint2*>(xb + chunk * CS + nt * MST * 32); };
     if constexpr (FMT == KYB_FMT_Q4_K) {
         // scales of rows g and g + 8 for the 8 sub-blocks
         const float4 s0a = *reinterpret_cast<const float4*>(scl + g * 16), s0b = *reinterpret_cast<const float4*>(scl + g * 16 + 4);
@@ -152,10 +152,6 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
         for (int G = 0; G < 4; ++G) {
             const uint4 u = *reinterpret_cast<const uint4*>(tile + (G * 32 + lane) * 16);
             float clo[NT][4], chi[NT][4];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) clo[nt][i] = 0.f, chi[nt][i] = 0.f;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const uint32_t wg = c ? u.z : u.x, wh = c ? u.w : u.y;
@@ -171,10 +167,15 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
 #endif
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    const uint2 bl = load_b(xfrag, chunk0 + 4 * G + c, nt, NT, mst, g, t);
-                    mma16816(clo[nt], l0, l1, l2, l3, bl.x, bl.y);
-                    const uint2 bh = load_b(xfrag, chunk0 + 4 * G + 2 + c, nt, NT, mst, g, t);
-                    mma16816(chi[nt], h0, h1, h2, h3, bh.x, bh.y);
+                    const uint2 bl = ldb(4 * G + c, nt);
+                    const uint2 bh = ldb(4 * G + 2 + c, nt);
+                    if (c == 0) {
+                        mma16816_z(clo[nt], l0, l1, l2, l3, bl.x, bl.y);
+                        mma16816_z(chi[nt], h0, h1, h2, h3, bh.x, bh.y);
+                    } else {
+                        mma16816(clo[nt], l0, l1, l2, l3, bl.x, bl.y);
+                        mma16816(chi[nt], h0, h1, h2, h3, bh.x, bh.y);
+                    }
                 }
             }
             scale_acc<NT>(acc, clo, sg[2 * G], sh[2 * G]);
@@ -182,8 +183,10 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
         }
         // minus dmin * sum_j mn_j * (sum of x over sub-block j): an m16n8k8 product of the 6-bit mins with the staged sums (fp16 hi + lo)
         const uint4 mg = *reinterpret_cast<const uint4*>(tile + 2048 + g * 16), mh = *reinterpret_cast<const uint4*>(tile + 2048 + (g + 8) * 16);
-        const uint32_t mng = (t & 2) ? (((mg.w >> 4) & 0x0f0f0f0fu) | ((mg.z >> 2) & 0x30303030u)) : (mg.z & 0x3f3f3f3fu);
-        const uint32_t mnh = (t & 2) ? (((mh.w >> 4) & 0x0f0f0f0fu) | ((mh.z >> 2) & 0x30303030u)) : (mh.z & 0x3f3f3f3fu);
+        const bool up = (t & 2) != 0;                  // lanes t = 2, 3 own sub-blocks 4..7
+        const uint32_t mka = up ? 0x0f0f0f0fu : 0x3f3f3f3fu, mkb = up ? 0x30303030u : 0u;
+        const uint32_t mng = ((up ? mg.w >> 4 : mg.z) & mka) | ((mg.z >> 2) & mkb);
+        const uint32_t mnh = ((up ? mh.w >> 4 : mh.z) & mka) | ((mh.z >> 2) & mkb);
         const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
 #if KYB_Q4K_SUBNORMAL
         const uint32_t a0 = prmt(mng, 0u, sel), a1 = prmt(mnh, 0u, sel);
@@ -194,28 +197,22 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
 #endif
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            float tt[4] = {0.f, 0.f, 0.f, 0.f};
-            const uint32_t* xa = reinterpret_cast<const uint32_t*>(xaux + (size_t)blk * 256 * NT);
-            mma1688(tt, a0, a1, xa[(0 * NT + nt) * 32 + lane]);
-            mma1688(tt, a0, a1, xa[(1 * NT + nt) * 32 + lane]);
+            float tt[4];
+            mma1688_z(tt, a0, a1, xa[(0 * NT + nt) * 32]);
+            mma1688(tt, a0, a1, xa[(1 * NT + nt) * 32]);
             acc.v[nt][0] = fmaf(-dmg, tt[0], acc.v[nt][0]);
             acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
             acc.v[nt][2] = fmaf(-dmh, tt[2], acc.v[nt][2]);
             acc.v[nt][3] = fmaf(-dmh, tt[3], acc.v[nt][3]);
         }
     } else {
-        // one scale per MMA slice s = 0..15
-        float sg[16], sh[16];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 a = *reinterpret_cast<const float4*>(scl + g * 16 + 4 * q), b = *reinterpret_cast<const float4*>(scl + (g + 8) * 16 + 4 * q);
-            sg[4 * q] = a.x, sg[4 * q + 1] = a.y, sg[4 * q + 2] = a.z, sg[4 * q + 3] = a.w;
-            sh[4 * q] = b.x, sh[4 * q + 1] = b.y, sh[4 * q + 2] = b.z, sh[4 * q + 3] = b.w;
-        }
         uint4 hi = make_uint4(0, 0, 0, 0), hb = make_uint4(0, 0, 0, 0);
         if constexpr (FMT == KYB_FMT_Q3_K) hb = *reinterpret_cast<const uint4*>(tile + 1024 + lane * 16);
 #pragma unroll
         for (int P = 0; P < 4; ++P) {
+            // one scale per MMA slice s = 4 P + i
+            const float4 sg4 = *reinterpret_cast<const float4*>(scl + g * 16 + 4 * P), sh4 = *reinterpret_cast<const float4*>(scl + (g + 8) * 16 + 4 * P);
+            const float sg[4] = {sg4.x, sg4.y, sg4.z, sg4.w}, sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
             uint4 u;
             if constexpr (FMT == KYB_FMT_Q6_K) {
                 u = *reinterpret_cast<const uint4*>(tile + (P * 32 + lane) * 16);
@@ -227,7 +224,7 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
                 u = *reinterpret_cast<const uint4*>(tile + (P * 32 + lane) * 16);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {                                 // s = 4 P + i
+            for (int i = 0; i < 4; ++i) {
                 const int s = 4 * P + i;
                 uint32_t a0, a1, a2, a3;
                 if constexpr (FMT == KYB_FMT_Q6_K) {
@@ -271,87 +268,111 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
                 float c[NT][4];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
-                    const uint2 b = load_b(xfrag, chunk0 + s, nt, NT, mst, g, t);
-                    mma16816(c[nt], a0, a1, a2, a3, b.x, b.y);
+                    const uint2 b = ldb(s, nt);
+                    mma16816_z(c[nt], a0, a1, a2, a3, b.x, b.y);
                 }
-                scale_acc<NT>(acc, c, sg[s], sh[s]);
+                scale_acc<NT>(acc, c, sg[i], sh[i]);
             }
         }
     }
 }
 
-template <int FMT, int NT>
-__global__ void __launch_bounds__(512) gemv_t16_kernel(const GemvParams p) {
+// Persistent kernel: one CTA per SM. CTA c works on k-part c % ksplit (its activations are staged once); its warps take the row tiles
+// ws, ws + TS, ... of that part (ws = warp slot among the TS warps of the part) and stream them back to back through one ring.
+template <int FMT, int NT, int MST>
+__global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TB = kyb_tile_bytes(FMT);
+    constexpr int CS = NT * MST * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kp = blockIdx.y;
+    const int kp = blockIdx.x % p.ksplit, cgi = blockIdx.x / p.ksplit;
     const int kb0 = kp * p.kbp, nblk = min(p.nb, kb0 + p.kbp) - kb0;
-    const int mst = p.mst;
+    const int nparts_ctas = ((int)gridDim.x - kp + p.ksplit - 1) / p.ksplit;      // CTAs working on this k-part
+    const int TS = nparts_ctas * p.warps, ws = cgi * p.warps + warp;
+    const int ntiles = p.npad >> 4;
+    const int nitems = ws < ntiles ? (ntiles - ws + TS - 1) / TS : 0;
+    const int total = nitems * nblk;
 
     // ---- shared memory carve-up
-    const size_t xfrag_bytes = (size_t)p.kbp * 16 * NT * mst * 32;
     uint8_t* xfrag = smem;
-    uint8_t* xaux = xfrag + xfrag_bytes;
-    const size_t xaux_bytes = (size_t)p.kbp * xaux_bytes_per_block<FMT>(NT);
-    const size_t warp_bytes = (size_t)p.stages * TB + SCL_BYTES + 8 * (size_t)p.stages + 8;
-    uint8_t* wbase = xaux + xaux_bytes + (size_t)warp * ((warp_bytes + 15) & ~(size_t)15);
+    uint8_t* xaux = xfrag + (size_t)p.kbp * 16 * CS;
+    const size_t warp_bytes = ((size_t)p.stages * TB + SCL_BYTES + 8 * (size_t)p.stages + 8 + 15) & ~(size_t)15;
+    uint8_t* wbase = xaux + (size_t)p.kbp * xaux_bytes_per_block<FMT>(NT) + (size_t)warp * warp_bytes;
     uint8_t* ring = wbase;
     float* scl = reinterpret_cast<float*>(wbase + (size_t)p.stages * TB);
     uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + (size_t)p.stages * TB + SCL_BYTES);
 
-    const int rt = blockIdx.x * p.warps + warp;
-    const bool active = rt < p.npad / 16 && nblk > 0;
-    const uint8_t* src = p.t16 + ((size_t)rt * p.nb + kb0) * TB;
+    // producer state (lane 0): next tile to request. Tiles of one row tile are contiguous; the next row tile of this warp is TS row tiles further.
+    int p_left = total, p_blk = nblk;                       // tiles still to request, tiles left in the current row tile
+    const uint8_t* p_src = p.t16 + (((size_t)ws * (size_t)p.nb) + (size_t)kb0) * TB;
+    const size_t p_jump = ((size_t)TS * (size_t)p.nb - (size_t)nblk) * TB;       // from the end of a row tile's part to the start of the next one
+    uint32_t p_dst = smem_u32(ring), p_bar = smem_u32(bars);
+    const uint32_t ring_end = p_dst + (uint32_t)p.stages * TB, ring0 = p_dst, bar0 = p_bar;
+    auto issue = [&]() {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p_bar), "r"((uint32_t)TB) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(p_dst), "l"(p_src), "r"((uint32_t)TB), "r"(p_bar)
+                     : "memory");
+        --p_left;
+        p_src += TB;
+        if (--p_blk == 0) p_blk = nblk, p_src += p_jump;
+        p_dst += TB, p_bar += 8;
+        if (p_dst == ring_end) p_dst = ring0, p_bar = bar0;
+    };
 
     // ---- start the weight stream before staging x: the copies run while the CTA prepares the activations
     if (lane == 0) {
         for (int s = 0; s < p.stages; ++s) mbar_init(&bars[s], 1);
         mbar_fence_init();
-        if (active) {
-            const int pre = min(p.stages, nblk);
-            for (int s = 0; s < pre; ++s) {
-                mbar_expect_tx(&bars[s], TB);
-                bulk_g2s(ring + (size_t)s * TB, src + (size_t)s * TB, TB, &bars[s]);
-            }
-        }
+        const int pre = min(p.stages, total);
+        for (int s = 0; s < pre; ++s) issue();
     }
 
-    // ---- stage activations of this k-part as B fragments: [chunk][nt][row < mst][lane t][4 halves permuted (0, 2, 1, 3)]
+    // ---- stage activations of this k-part as B fragments: [chunk][nt][row < MST][lane t][4 halves permuted (0, 2, 1, 3)]
     {
-        const int nchunk = nblk * 16;
-        const int items = nchunk * NT * mst;
-        for (int it = threadIdx.x; it < items; it += blockDim.x) {
-            const int row = it % mst, nt = (it / mst) % NT, c = it / (mst * NT);
-            const int m = nt * 8 + row;
-            uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
-            if (m < p.m) {
-                const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c * 16);
-                a = __ldg(xp), b = __ldg(xp + 1);
+        const int items = nblk * 16 * NT * MST;
+        constexpr int U = 4;                                   // loads of U items are in flight together (x comes from L2: ~1 us latency each)
+        for (int it0 = threadIdx.x; it0 < items; it0 += U * blockDim.x) {
+            uint4 a[U], b[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int it = it0 + u * blockDim.x;
+                a[u] = make_uint4(0, 0, 0, 0), b[u] = make_uint4(0, 0, 0, 0);
+                if (it < items) {
+                    const int row = it % MST, nt = (it / MST) % NT, c = it / (MST * NT);
+                    const int m = nt * 8 + row;
+                    if (m < p.m) {
+                        const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c * 16);
+                        a[u] = __ldg(xp), b[u] = __ldg(xp + 1);
+                    }
+                }
             }
-            uint4 oa, ob;
-            oa.x = prmt(a.x, a.y, 0x5410u), oa.y = prmt(a.x, a.y, 0x7632u), oa.z = prmt(a.z, a.w, 0x5410u), oa.w = prmt(a.z, a.w, 0x7632u);
-            ob.x = prmt(b.x, b.y, 0x5410u), ob.y = prmt(b.x, b.y, 0x7632u), ob.z = prmt(b.z, b.w, 0x5410u), ob.w = prmt(b.z, b.w, 0x7632u);
-            uint4* dst = reinterpret_cast<uint4*>(xfrag + ((size_t)(c * NT + nt) * mst + row) * 32);
-            dst[0] = oa, dst[1] = ob;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int it = it0 + u * blockDim.x;
+                if (it < items) {
+                    const int row = it % MST, nt = (it / MST) % NT, c = it / (MST * NT);
+                    uint4 oa, ob;
+                    oa.x = prmt(a[u].x, a[u].y, 0x5410u), oa.y = prmt(a[u].x, a[u].y, 0x7632u), oa.z = prmt(a[u].z, a[u].w, 0x5410u), oa.w = prmt(a[u].z, a[u].w, 0x7632u);
+                    ob.x = prmt(b[u].x, b[u].y, 0x5410u), ob.y = prmt(b[u].x, b[u].y, 0x7632u), ob.z = prmt(b[u].z, b[u].w, 0x5410u), ob.w = prmt(b[u].z, b[u].w, 0x7632u);
+                    uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)c * CS + (nt * MST + row) * 32);
+                    dst[0] = oa, dst[1] = ob;
+                }
+            }
         }
         if constexpr (FMT == KYB_FMT_Q4_K) {
             __syncthreads();
-            // sums of x over each 32-input sub-block, split into fp16 hi + lo, laid out as m16n8k8 B fragments
+            // sums of x over each 32-input sub-block, split into fp16 hi + lo, laid out as m16n8k8 B fragments (lane 4 g + t: sub-blocks 2t, 2t + 1 of row g)
             const int items2 = nblk * 8 * NT * 8;
             for (int it = threadIdx.x; it < items2; it += blockDim.x) {
                 const int g_ = it & 7, nt = (it >> 3) % NT, j = (it / (8 * NT)) & 7, blk = it / (64 * NT);
                 float sum = 0.f;
-                if (g_ < mst) {
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        const __half2* hp = reinterpret_cast<const __half2*>(xfrag + ((size_t)((blk * 16 + 2 * j + c) * NT + nt) * mst + g_) * 32);
+                for (int c = 0; c < 2; ++c) {
+                    const __half2* hp = reinterpret_cast<const __half2*>(xfrag + (size_t)(blk * 16 + 2 * j + c) * CS + (nt * MST + (g_ & (MST - 1))) * 32);
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const float2 f = __half22float2(hp[q]);
-                            sum += f.x + f.y;
-                        }
+                    for (int q = 0; q < 8; ++q) {
+                        const float2 f = __half22float2(hp[q]);
+                        sum += f.x + f.y;
                     }
                 }
                 const __half hi = __float2half_rn(sum);
@@ -364,54 +385,52 @@ __global__ void __launch_bounds__(512) gemv_t16_kernel(const GemvParams p) {
         }
     }
     __syncthreads();
-    if (!active) return;
+    if (total == 0) return;
+
+    const int g = lane >> 2, t = lane & 3;
+    // lanes whose activation row is not staged read a staged row instead: their output columns are never stored
+    const uint8_t* xlane = xfrag + (g & (MST - 1)) * 32 + t * 8;
+    const uint32_t* xalane = reinterpret_cast<const uint32_t*>(xaux) + lane;
 
     Acc<NT> acc;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc.v[nt][0] = acc.v[nt][1] = acc.v[nt][2] = acc.v[nt][3] = 0.f;
 
-    bool alive = true;
-    int bi = 0;
-    for (; bi < nblk; ++bi) {
-        const int st = bi % p.stages;
-        const uint32_t parity = (uint32_t)(bi / p.stages) & 1u;
-        const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[st], parity));
-        if (!ok) {
-            alive = false;
-            break;
-        }
+    int st = 0, blk = 0, rt = ws;
+    uint32_t parity = 0;
+    bool failed = false;
+    for (int i = 0; i < total; ++i) {
+        // a wait that gives up is remembered; the tile is then consumed as it is (its values do not matter any more) and the kernel reports at the end
+        if (!mbar_wait_bounded(&bars[st], parity)) failed = true;
         const uint8_t* tile = ring + (size_t)st * TB;
         prep_scales<FMT>(tile, scl, lane);
         __syncwarp();
-        consume_tile<FMT, NT>(tile, scl, xfrag, xaux, bi, mst, lane, acc);
+        consume_tile<FMT, NT, MST>(tile, scl, xlane + (size_t)blk * 16 * CS, xalane + blk * 64 * NT, lane, acc);
         __syncwarp();
-        if (lane == 0 && bi + p.stages < nblk) {
-            mbar_expect_tx(&bars[st], TB);
-            bulk_g2s(ring + (size_t)st * TB, src + (size_t)(bi + p.stages) * TB, TB, &bars[st]);
-        }
-    }
-    if (!alive) {
-        // record the failure, then give the copies still in flight a bounded chance to land before leaving
-        if (lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
-        for (int b2 = bi + 1; b2 < min(nblk, bi + p.stages); ++b2) mbar_wait_bounded(&bars[b2 % p.stages], (uint32_t)(b2 / p.stages) & 1u, 1u << 16);
-        return;
-    }
-
-    // ---- epilogue: lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
-    const int g = lane >> 2, t = lane & 3;
+        if (lane == 0 && p_left > 0) issue();
+        if (++st == p.stages) st = 0, parity ^= 1u;
+        if (++blk == nblk) {
+            // ---- item epilogue: lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int nrow = rt * 16 + g + 8 * (i >> 1), m = nt * 8 + 2 * t + (i & 1);
-            if (m >= p.m) continue;
-            if (p.ksplit == 1) {
-                if (nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(acc.v[nt][i] * p.gscale);
-            } else {
-                p.partial[((size_t)kp * p.m + m) * p.npad + nrow] = acc.v[nt][i];
+                for (int q = 0; q < 4; ++q) {
+                    const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
+                    if (m < p.m) {
+                        if (p.ksplit == 1) {
+                            if (nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(acc.v[nt][q] * p.gscale);
+                        } else {
+                            p.partial[((size_t)kp * p.m + m) * p.npad + nrow] = acc.v[nt][q];
+                        }
+                    }
+                    acc.v[nt][q] = 0.f;
+                }
             }
+            blk = 0, rt += TS;
         }
     }
+    // every requested tile was waited for above (bounded), so no copy of this warp is in flight here
+    if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
 }
 
 __global__ void gemv_finalize_kernel(const float* __restrict__ partial, int ksplit, int m, int n, int npad, float gscale, __half* __restrict__ y, int64_t ldy) {
@@ -429,7 +448,7 @@ __global__ void gemv_finalize_kernel(const float* __restrict__ partial, int kspl
 namespace {
 
 struct GemvPlan {
-    int nt, mst, warps, stages, kbp, ksplit;
+    int nt, mst, warps, stages, kbp, ksplit, grid;
     size_t smem;
 };
 
@@ -446,97 +465,134 @@ size_t plan_smem(int fmt, int nt, int mst, int kbp, int warps, int stages) {
     return xfrag + xaux + warps * wb;
 }
 
-// Picks warps per CTA, ring depth and the k split from a small cost model: whole waves of CTAs, >= 64 KB of bulk copies in
-// flight per SM, split-k traffic counted. Environment overrides (KYB_GEMV_WARPS / _STAGES / _KSPLIT) exist for sweeps.
-const void* gemv_kernel_ptr(int fmt, int nt) {
-    static const void* tab[4][3] = {
-        {(const void*)kyb::gemv_t16_kernel<KYB_FMT_Q4_K, 1>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q4_K, 2>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q4_K, 4>},
-        {(const void*)kyb::gemv_t16_kernel<KYB_FMT_Q6_K, 1>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q6_K, 2>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q6_K, 4>},
-        {(const void*)kyb::gemv_t16_kernel<KYB_FMT_Q3_K, 1>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q3_K, 2>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_Q3_K, 4>},
-        {(const void*)kyb::gemv_t16_kernel<KYB_FMT_NVFP4, 1>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_NVFP4, 2>, (const void*)kyb::gemv_t16_kernel<KYB_FMT_NVFP4, 4>}};
-    return tab[fmt][nt == 1 ? 0 : nt == 2 ? 1 : 2];
-}
+// kernel variants: (column tiles, staged activation rows per tile)
+constexpr int NVAR = 6;
+constexpr int VAR_NT[NVAR] = {1, 1, 1, 1, 2, 4}, VAR_MST[NVAR] = {1, 2, 4, 8, 8, 8};
 
-// registers per thread of a kernel instantiation (cached; 128 = the launch bound, used when the query fails, e.g. without a device)
-int gemv_kernel_regs(int fmt, int nt) {
-    static int cache[4][3] = {{0}};
-    int& c = cache[fmt][nt == 1 ? 0 : nt == 2 ? 1 : 2];
-    if (!c) {
-        cudaFuncAttributes a;
-        c = cudaFuncGetAttributes(&a, gemv_kernel_ptr(fmt, nt)) == cudaSuccess && a.numRegs > 0 ? a.numRegs : 128;
-        (void)cudaGetLastError();
+int variant_of(int64_t m) { return m <= 1 ? 0 : m <= 2 ? 1 : m <= 4 ? 2 : m <= 8 ? 3 : m <= 16 ? 4 : 5; }
+
+template <int FMT>
+const void* kernel_of_fmt(int v) {
+    switch (v) {
+        case 0: return (const void*)kyb::gemv_t16_kernel<FMT, 1, 1>;
+        case 1: return (const void*)kyb::gemv_t16_kernel<FMT, 1, 2>;
+        case 2: return (const void*)kyb::gemv_t16_kernel<FMT, 1, 4>;
+        case 3: return (const void*)kyb::gemv_t16_kernel<FMT, 1, 8>;
+        case 4: return (const void*)kyb::gemv_t16_kernel<FMT, 2, 8>;
+        default: return (const void*)kyb::gemv_t16_kernel<FMT, 4, 8>;
     }
-    return c;
 }
 
-GemvPlan make_plan(int fmt, int64_t n, int64_t k, int64_t m) {
+const void* gemv_kernel_ptr(int fmt, int v) {
+    switch (fmt) {
+        case KYB_FMT_Q4_K: return kernel_of_fmt<KYB_FMT_Q4_K>(v);
+        case KYB_FMT_Q6_K: return kernel_of_fmt<KYB_FMT_Q6_K>(v);
+        case KYB_FMT_Q3_K: return kernel_of_fmt<KYB_FMT_Q3_K>(v);
+        default: return kernel_of_fmt<KYB_FMT_NVFP4>(v);
+    }
+}
+
+int device_sms() {
     static int sms = 0;
     if (!sms) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
         (void)cudaGetLastError();
     }
-    GemvPlan best{};
-    const int nt = m <= 8 ? 1 : m <= 16 ? 2 : 4;
-    const int regs = (gemv_kernel_regs(fmt, nt) + 7) / 8 * 8;
-    const int mst = m >= 8 ? 8 : m > 2 ? 4 : m > 1 ? 2 : 1;
-    const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
-    const double tb = kyb_tile_bytes(fmt), sm_bw = 6.8e12 / sms;          // bytes/s one SM can expect
-    const size_t smem_cap = 227 * 1024, smem_sm = 228 * 1024;
-    double best_t = 1e30;
-    const int fw = env_int("KYB_GEMV_WARPS", 0), fs = env_int("KYB_GEMV_STAGES", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
-    for (int ksplit = 1; ksplit <= nb; ++ksplit) {
-        if (fk && ksplit != fk) continue;
-        const int kbp = (nb + ksplit - 1) / ksplit;
-        if ((nb + kbp - 1) / kbp != ksplit) continue;                      // skip splits that leave an empty part
-        for (int warps = 1; warps <= 16; ++warps) {
-            if (fw && warps != fw) continue;
-            for (int stages = 2; stages <= 8; ++stages) {
-                if (fs && stages != fs) continue;
-                if (stages > kbp && stages > 2) continue;
-                const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, stages);
-                if (smem > smem_cap) continue;
-                int conc = (int)std::min<size_t>(smem_sm / (smem + 1024), (size_t)(64 / warps));
-                conc = std::min(conc, std::min(16, 65536 / (regs * warps * 32)));
-                if (conc < 1) continue;
-                const int64_t ctas = (int64_t)((ntiles + warps - 1) / warps) * ksplit;
-                const double waves = (double)((ctas + (int64_t)sms * conc - 1) / ((int64_t)sms * conc));
-                const double cta_bytes = (double)warps * kbp * tb;
-                const double inflight = (double)conc * warps * std::min(stages, kbp) * tb;
-                const double bw_eff = sm_bw * std::min(1.0, inflight / 65536.0);
-                double tsec = waves * (cta_bytes * conc / bw_eff + 1.0e-6 / conc);
-                if (ksplit > 1) tsec += 2.0 * ksplit * m * (double)n * 4.0 / 6.8e12 + 1.5e-6;
-                tsec += 1e-9 * stages;                                      // tie-break: shallower ring
-                if (tsec < best_t) best_t = tsec, best = GemvPlan{nt, mst, warps, stages, kbp, ksplit, smem};
-            }
-        }
-    }
-    return best;
+    return sms;
 }
 
-template <int FMT>
-int launch_gemv(const kyb::GemvParams& p, const GemvPlan& pl, cudaStream_t st) {
-    dim3 grid((unsigned)((p.npad / 16 + pl.warps - 1) / pl.warps), (unsigned)pl.ksplit), block((unsigned)pl.warps * 32);
-    auto go = [&](auto kern) -> int {
-        // opt in to large dynamic shared memory once per device and kernel instantiation (the attribute is per device)
-        static std::atomic<unsigned> configured{0};
-        int dev = 0;
-        KYB_CUDA(cudaGetDevice(&dev));
-        if (!(configured.load() & (1u << (dev & 31)))) {
-            KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
-            configured.fetch_or(1u << (dev & 31));
+// Cost model of one configuration. The kernel is persistent with one CTA per SM, so the model is per warp: the busiest warp's tile count times the time a
+// warp needs per tile (latency floor, or its share of the SM's issue slots), against the bandwidth floor, plus the split-k traffic.
+double plan_cost(int fmt, int sms, int ntiles, int nb, int nt, int64_t n, int64_t m, int warps, int stages, int kbp, int ksplit, int* grid_out) {
+    const double tb = kyb_tile_bytes(fmt);
+    const double lat0 = env_int("KYB_GEMV_LAT0", 900), issue_per_tile = env_int("KYB_GEMV_ISSUE", fmt == KYB_FMT_Q4_K ? 60 : 80) * nt;   // cycles
+    const int grid = (int)std::min<int64_t>(sms, std::max<int64_t>(ksplit, ((int64_t)ntiles * ksplit + warps - 1) / warps));
+    const int64_t slots = (int64_t)(grid / ksplit) * warps;                       // warps of the part with the fewest CTAs
+    const double busiest = (double)((ntiles + slots - 1) / slots) * kbp;
+    const double active = std::min<double>(warps, (double)ntiles * ksplit / grid);   // busy warps per SM
+    const double per_tile = std::max(lat0 * (stages >= 3 ? 1.0 : 1.15), active * issue_per_tile);
+    const double t_lat = busiest * per_tile / 1.9e9 + 1.5e-6;
+    const double t_bw = (double)ntiles * nb * tb / 6.6e12 + 1.0e-6;
+    double tsec = std::max(t_lat, t_bw);
+    if (ksplit > 1) tsec += 2.0 * ksplit * m * (double)n * 4.0 / 6.6e12 + 2.0e-6;
+    *grid_out = grid;
+    return tsec + 1e-9 * stages + 1e-10 * warps;
+}
+
+constexpr int KBP_MAX = 10;   // k-blocks per part: the 32-row variant stages 16 KB of activations per block
+
+// The k split depends on (format, n, k) only - never on m - so that the partial sums of an activation row are formed in the same order whatever the
+// number of rows in the call (bit-identical rows across m). It is chosen for the 8-row variant; warps and ring depth are then chosen per m.
+// Environment overrides (KYB_GEMV_WARPS / _STAGES / _KSPLIT) exist for sweeps.
+GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
+    const int sms = device_sms();
+    const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
+    const size_t smem_cap = 227 * 1024;
+    const int fw = env_int("KYB_GEMV_WARPS", 0), fs = env_int("KYB_GEMV_STAGES", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
+    auto best_for = [&](int v, int only_ksplit) {
+        GemvPlan best{};
+        double best_t = 1e30;
+        const int nt = VAR_NT[v], mst = VAR_MST[v];
+        const int max_warps = nt == 1 ? 32 : 16;
+        for (int ksplit = 1; ksplit <= nb && ksplit <= sms; ++ksplit) {
+            if (only_ksplit && ksplit != only_ksplit) continue;
+            const int kbp = (nb + ksplit - 1) / ksplit;
+            if (kbp > KBP_MAX || (nb + kbp - 1) / kbp != ksplit) continue;     // skip splits that leave an empty part
+            for (int warps = 4; warps <= max_warps; warps += 4) {
+                if (fw && warps != fw && warps + 4 <= max_warps) continue;
+                for (int stages = 2; stages <= 4; ++stages) {
+                    if (fs && stages != fs) continue;
+                    const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, stages);
+                    if (smem > smem_cap) continue;
+                    int grid = 0;
+                    const double tsec = plan_cost(fmt, sms, ntiles, nb, nt, n, VAR_NT[v] * 8, warps, stages, kbp, ksplit, &grid);
+                    if (tsec < best_t) best_t = tsec, best = GemvPlan{nt, mst, warps, stages, kbp, ksplit, grid, smem};
+                }
+            }
         }
-        kern<<<grid, block, pl.smem, st>>>(p);
-        return kyb_launch_check("gemv_t16");
+        return best;
     };
-    switch (pl.nt) {
-        case 1: return go(kyb::gemv_t16_kernel<FMT, 1>);
-        case 2: return go(kyb::gemv_t16_kernel<FMT, 2>);
-        default: return go(kyb::gemv_t16_kernel<FMT, 4>);
+    const int ksplit = fk ? fk : best_for(3, 0).ksplit;                          // variant 3 = one column tile, 8 staged rows
+    return best_for(variant_of(m), ksplit);
+}
+
+// plans are cached per (format, n, k, m): the search costs tens of microseconds, a decode step calls this per linear
+GemvPlan make_plan(int fmt, int64_t n, int64_t k, int64_t m) {
+    static std::mutex mu;
+    static std::unordered_map<uint64_t, GemvPlan> cache;
+    const uint64_t key = ((uint64_t)fmt << 62) ^ ((uint64_t)m << 56) ^ ((uint64_t)n << 28) ^ (uint64_t)k;
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    const GemvPlan pl = search_plan(fmt, n, k, m);
+    cache.emplace(key, pl);
+    return pl;
+}
+
+// opt in to large dynamic shared memory once per device and kernel (the attribute is per device and per function)
+int ensure_smem_attr(const void* kern) {
+    static std::mutex mu;
+    static std::unordered_map<const void*, unsigned> done;
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lk(mu);
+    unsigned& mask = done[kern];
+    if (!(mask & (1u << (dev & 31)))) {
+        KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
+        mask |= 1u << (dev & 31);
     }
+    return KYB_OK;
 }
 
 }  // namespace
+
+extern "C" int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3 && n > 0 && k > 0 && k % 256 == 0 && m >= 1 && m <= 32 && out8, "bad arguments");
+    const GemvPlan pl = make_plan(fmt, n, k, m);
+    out8[0] = pl.nt, out8[1] = pl.mst, out8[2] = pl.warps, out8[3] = pl.stages, out8[4] = pl.kbp, out8[5] = pl.ksplit, out8[6] = (int)pl.smem, out8[7] = pl.grid;
+    return KYB_OK;
+}
 
 extern "C" size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m) {
     if (fmt < 0 || fmt > 3 || n <= 0 || k <= 0 || k % 256 || m <= 0 || m > 32) return 0;
@@ -569,14 +625,10 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
     p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale;
     cudaStream_t st = (cudaStream_t)stream;
-    int rc;
-    switch (fmt) {
-        case KYB_FMT_Q4_K: rc = launch_gemv<KYB_FMT_Q4_K>(p, pl, st); break;
-        case KYB_FMT_Q6_K: rc = launch_gemv<KYB_FMT_Q6_K>(p, pl, st); break;
-        case KYB_FMT_Q3_K: rc = launch_gemv<KYB_FMT_Q3_K>(p, pl, st); break;
-        default: rc = launch_gemv<KYB_FMT_NVFP4>(p, pl, st); break;
-    }
-    if (rc) return rc;
+    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
+    if (int rc = ensure_smem_attr(kern)) return rc;
+    void* args[] = {(void*)&p};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, st));
     if (pl.ksplit > 1) {
         const int64_t tot = m * n;
         kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>((const float*)workspace, pl.ksplit, (int)m, (int)n, npad, gscale, (__half*)y, ldy);

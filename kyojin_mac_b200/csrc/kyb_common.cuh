@@ -112,6 +112,18 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t a0, const
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// D(16x8, f32) = A(16x16, f16 row) * B(16x8, f16 col)   (zero accumulator input: no register initialisation needed)
+__device__ __forceinline__ void mma16816_z(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t a2, const uint32_t a3, const uint32_t b0,
+                                           const uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void mma1688_z(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "f"(0.f));
+}
 // D(16x8, f32) += A(16x8, f16 row) * B(8x8, f16 col)
 __device__ __forceinline__ void mma1688(float (&d)[4], const uint32_t a0, const uint32_t a1, const uint32_t b0) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"

@@ -91,6 +91,13 @@ def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float 
     return y
 
 
+def gemv_plan(fmt, n: int, k: int, m: int) -> dict:
+    import ctypes
+    out = (ctypes.c_int * 8)()
+    _lib.check(_lib.lib().kyb_gemv_plan(_fmt(fmt), n, k, m, out))
+    return dict(zip(("nt", "mst", "warps", "stages", "kbp", "ksplit", "smem", "grid"), list(out)))
+
+
 def check_device_status() -> None:
     _lib.check(_lib.lib().kyb_check_device_status(_stream()))
 
