@@ -39,6 +39,7 @@ struct GemvParams {
 };
 
 constexpr int SCL_BYTES = 16 * 16 * 4;   // per-warp scale scratch: 16 rows x 16 floats
+constexpr int GEMV_STAGES = 2;           // ring depth per warp: a stage is handed back as soon as its tile sits in registers, so two stages keep two copies in flight
 
 template <int FMT>
 __host__ __device__ constexpr int xaux_bytes_per_block(int nt) { return FMT == KYB_FMT_Q4_K ? 256 * nt : 0; }
@@ -51,10 +52,10 @@ __device__ __forceinline__ uint32_t magic_sub(uint32_t h2_with_magic, uint32_t s
 
 // ---- per-format: scale preparation (all lanes cooperate, results in scl[16][16] floats) ----------------------------------
 template <int FMT>
-__device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int lane) {
+__device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lane) {
     const int r = lane >> 1, hf = lane & 1;
     if constexpr (FMT == KYB_FMT_Q4_K) {
-        const uint4 mt = *reinterpret_cast<const uint4*>(tile + 2048 + r * 16);
+        const uint4 mt = lds128(tile + 2048 + r * 16);
         // 6-bit scales of sub-blocks 4 hf .. 4 hf + 3 as four bytes (kyojin_mlx/foreign_gguf.py:340-346)
         const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const float d = half_bits_to_float(mt.x & 0xffffu);
@@ -70,10 +71,10 @@ __device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int
         o.y = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7441u)), dhi, nhi);
         o.z = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7442u)), dlo, nlo);
         o.w = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7443u)), dhi, nhi);
-        *reinterpret_cast<float4*>(scl + r * 16 + 4 * hf) = o;
+        sts128f(scl + 4 * (r * 16 + 4 * hf), o);
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
-        const uint2 sw = *reinterpret_cast<const uint2*>(tile + 3072 + r * 16 + 8 * hf);
-        const float d = ldh(tile + 3328 + r * 2);
+        const uint2 sw = lds64(tile + 3072 + r * 16 + 8 * hf);
+        const float d = half_bits_to_float(lds16(tile + 3328 + r * 2));
         float4 a, b;
         a.x = d * (float)(int)(int8_t)(sw.x & 255u);
         a.y = d * (float)(int)(int8_t)((sw.x >> 8) & 255u);
@@ -83,14 +84,14 @@ __device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int
         b.y = d * (float)(int)(int8_t)((sw.y >> 8) & 255u);
         b.z = d * (float)(int)(int8_t)((sw.y >> 16) & 255u);
         b.w = d * (float)(int)(int8_t)(sw.y >> 24);
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf) = a;
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf + 4) = b;
+        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
+        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
     } else if constexpr (FMT == KYB_FMT_Q3_K) {
-        const uint8_t* sp = tile + 1536 + r * 12;
-        const uint32_t w0 = ldw(sp), w1 = ldw(sp + 4), w2 = ldw(sp + 8);
+        const uint32_t sp = tile + 1536 + r * 12;
+        const uint32_t w0 = lds32(sp), w1 = lds32(sp + 4), w2 = lds32(sp + 8);
         const uint32_t ga = hf ? (((w0 >> 4) & 0x0f0f0f0fu) | (w2 & 0x30303030u)) : ((w0 & 0x0f0f0f0fu) | ((w2 << 4) & 0x30303030u));
         const uint32_t gb = hf ? (((w1 >> 4) & 0x0f0f0f0fu) | ((w2 >> 2) & 0x30303030u)) : ((w1 & 0x0f0f0f0fu) | ((w2 << 2) & 0x30303030u));
-        const float d = ldh(tile + 1728 + r * 2);
+        const float d = half_bits_to_float(lds16(tile + 1728 + r * 2));
         float4 a, b;
         a.x = d * (float)((int)(ga & 255u) - 32);
         a.y = d * (float)((int)((ga >> 8) & 255u) - 32);
@@ -100,10 +101,10 @@ __device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int
         b.y = d * (float)((int)((gb >> 8) & 255u) - 32);
         b.z = d * (float)((int)((gb >> 16) & 255u) - 32);
         b.w = d * (float)((int)(gb >> 24) - 32);
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf) = a;
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf + 4) = b;
+        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
+        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
     } else {
-        const uint2 sw = *reinterpret_cast<const uint2*>(tile + 2048 + r * 16 + 8 * hf);
+        const uint2 sw = lds64(tile + 2048 + r * 16 + 8 * hf);
         float4 a, b;                                                   // e2m1 operands carry 2^-14: fold 2^14 here
         a.x = e4m3_unsigned(sw.x) * 16384.0f;
         a.y = e4m3_unsigned(sw.x >> 8) * 16384.0f;
@@ -113,8 +114,8 @@ __device__ __forceinline__ void prep_scales(const uint8_t* tile, float* scl, int
         b.y = e4m3_unsigned(sw.y >> 8) * 16384.0f;
         b.z = e4m3_unsigned(sw.y >> 16) * 16384.0f;
         b.w = e4m3_unsigned(sw.y >> 24) * 16384.0f;
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf) = a;
-        *reinterpret_cast<float4*>(scl + r * 16 + 8 * hf + 4) = b;
+        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
+        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
     }
 }
 
@@ -134,23 +135,65 @@ __device__ __forceinline__ void scale_acc(Acc<NT>& acc, const float (&c)[NT][4],
     }
 }
 
+// ---- the part of a tile one lane keeps in registers, so that the ring stage can be handed back to the copy engine before the arithmetic starts
+template <int FMT>
+struct TileRegs {
+    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : 4];
+    uint32_t a0, a1;      // q4_k: 6-bit mins of rows g, g + 8 as m16n8k8 A operands
+    float dmg, dmh;       // q4_k: dmin of rows g, g + 8 (scaled to the operand convention)
+};
+
+template <int FMT>
+__device__ __forceinline__ void load_tile(uint32_t tile, int lane, TileRegs<FMT>& tr) {
+    const int g = lane >> 2, t = lane & 3;
+    if constexpr (FMT == KYB_FMT_Q4_K) {
+#pragma unroll
+        for (int G = 0; G < 4; ++G) tr.q[G] = lds128(tile + (G * 32 + lane) * 16);
+        const uint4 mg = lds128(tile + 2048 + g * 16), mh = lds128(tile + 2048 + (g + 8) * 16);
+        const bool up = (t & 2) != 0;                  // lanes t = 2, 3 own sub-blocks 4..7
+        const uint32_t mka = up ? 0x0f0f0f0fu : 0x3f3f3f3fu, mkb = up ? 0x30303030u : 0u;
+        const uint32_t mng = ((up ? mg.w >> 4 : mg.z) & mka) | ((mg.z >> 2) & mkb);
+        const uint32_t mnh = ((up ? mh.w >> 4 : mh.z) & mka) | ((mh.z >> 2) & mkb);
+        const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+#if KYB_Q4K_SUBNORMAL
+        tr.a0 = prmt(mng, 0u, sel), tr.a1 = prmt(mnh, 0u, sel);
+        tr.dmg = half_bits_to_float(mg.x >> 16) * 16777216.0f, tr.dmh = half_bits_to_float(mh.x >> 16) * 16777216.0f;
+#else
+        tr.a0 = magic_sub(prmt(mng, 0x64646464u, sel), 0x64006400u), tr.a1 = magic_sub(prmt(mnh, 0x64646464u, sel), 0x64006400u);
+        tr.dmg = half_bits_to_float(mg.x >> 16), tr.dmh = half_bits_to_float(mh.x >> 16);
+#endif
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = lds128(tile + (P * 32 + lane) * 16);
+        tr.q[4] = lds128(tile + 2048 + lane * 16);
+        tr.q[5] = lds128(tile + 2048 + (32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q3_K) {
+        tr.q[0] = lds128(tile + lane * 16);
+        tr.q[1] = lds128(tile + (32 + lane) * 16);
+        tr.q[2] = lds128(tile + 1024 + lane * 16);
+    } else {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = lds128(tile + (P * 32 + lane) * 16);
+    }
+}
+
 // ---- one tile (16 rows x 256 inputs) ----------------------------------------------------------------------------------
 // xb: this lane's B-fragment pointer for the tile's k-block (chunk c, column tile nt at xb + c * CS + nt * MST * 32, all
 // compile-time offsets); xa: this lane's word of the Q4_K sub-block sums of the k-block.
 template <int FMT, int NT, int MST>
-__device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* scl, const uint8_t* xb, const uint32_t* xa, int lane, Acc<NT>& acc) {
+__device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t scl, uint32_t xb, uint32_t xa, int lane, Acc<NT>& acc) {
     constexpr int CS = NT * MST * 32;
     const int g = lane >> 2, t = lane & 3;
-    auto ldb = [&](int chunk, int nt) -> uint2 { return *reinterpret_cast<const uint2*>(xb + chunk * CS + nt * MST * 32); };
+    auto ldb = [&](int chunk, int nt) -> uint2 { return lds64(xb + chunk * CS + nt * MST * 32); };
     if constexpr (FMT == KYB_FMT_Q4_K) {
         // scales of rows g and g + 8 for the 8 sub-blocks
-        const float4 s0a = *reinterpret_cast<const float4*>(scl + g * 16), s0b = *reinterpret_cast<const float4*>(scl + g * 16 + 4);
-        const float4 s1a = *reinterpret_cast<const float4*>(scl + (g + 8) * 16), s1b = *reinterpret_cast<const float4*>(scl + (g + 8) * 16 + 4);
+        const float4 s0a = lds128f(scl + 4 * (g * 16)), s0b = lds128f(scl + 4 * (g * 16 + 4));
+        const float4 s1a = lds128f(scl + 4 * ((g + 8) * 16)), s1b = lds128f(scl + 4 * ((g + 8) * 16 + 4));
         const float sg[8] = {s0a.x, s0a.y, s0a.z, s0a.w, s0b.x, s0b.y, s0b.z, s0b.w};
         const float sh[8] = {s1a.x, s1a.y, s1a.z, s1a.w, s1b.x, s1b.y, s1b.z, s1b.w};
 #pragma unroll
         for (int G = 0; G < 4; ++G) {
-            const uint4 u = *reinterpret_cast<const uint4*>(tile + (G * 32 + lane) * 16);
+            const uint4 u = tr.q[G];
             float clo[NT][4], chi[NT][4];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
@@ -182,24 +225,13 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
             scale_acc<NT>(acc, chi, sg[2 * G + 1], sh[2 * G + 1]);
         }
         // minus dmin * sum_j mn_j * (sum of x over sub-block j): an m16n8k8 product of the 6-bit mins with the staged sums (fp16 hi + lo)
-        const uint4 mg = *reinterpret_cast<const uint4*>(tile + 2048 + g * 16), mh = *reinterpret_cast<const uint4*>(tile + 2048 + (g + 8) * 16);
-        const bool up = (t & 2) != 0;                  // lanes t = 2, 3 own sub-blocks 4..7
-        const uint32_t mka = up ? 0x0f0f0f0fu : 0x3f3f3f3fu, mkb = up ? 0x30303030u : 0u;
-        const uint32_t mng = ((up ? mg.w >> 4 : mg.z) & mka) | ((mg.z >> 2) & mkb);
-        const uint32_t mnh = ((up ? mh.w >> 4 : mh.z) & mka) | ((mh.z >> 2) & mkb);
-        const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
-#if KYB_Q4K_SUBNORMAL
-        const uint32_t a0 = prmt(mng, 0u, sel), a1 = prmt(mnh, 0u, sel);
-        const float dmg = half_bits_to_float(mg.x >> 16) * 16777216.0f, dmh = half_bits_to_float(mh.x >> 16) * 16777216.0f;
-#else
-        const uint32_t a0 = magic_sub(prmt(mng, 0x64646464u, sel), 0x64006400u), a1 = magic_sub(prmt(mnh, 0x64646464u, sel), 0x64006400u);
-        const float dmg = half_bits_to_float(mg.x >> 16), dmh = half_bits_to_float(mh.x >> 16);
-#endif
+        const uint32_t a0 = tr.a0, a1 = tr.a1;
+        const float dmg = tr.dmg, dmh = tr.dmh;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             float tt[4];
-            mma1688_z(tt, a0, a1, xa[(0 * NT + nt) * 32]);
-            mma1688(tt, a0, a1, xa[(1 * NT + nt) * 32]);
+            mma1688_z(tt, a0, a1, lds32(xa + (0 * NT + nt) * 128));
+            mma1688(tt, a0, a1, lds32(xa + (1 * NT + nt) * 128));
             acc.v[nt][0] = fmaf(-dmg, tt[0], acc.v[nt][0]);
             acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
             acc.v[nt][2] = fmaf(-dmh, tt[2], acc.v[nt][2]);
@@ -207,21 +239,21 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
         }
     } else {
         uint4 hi = make_uint4(0, 0, 0, 0), hb = make_uint4(0, 0, 0, 0);
-        if constexpr (FMT == KYB_FMT_Q3_K) hb = *reinterpret_cast<const uint4*>(tile + 1024 + lane * 16);
+        if constexpr (FMT == KYB_FMT_Q3_K) hb = tr.q[2];
 #pragma unroll
         for (int P = 0; P < 4; ++P) {
             // one scale per MMA slice s = 4 P + i
-            const float4 sg4 = *reinterpret_cast<const float4*>(scl + g * 16 + 4 * P), sh4 = *reinterpret_cast<const float4*>(scl + (g + 8) * 16 + 4 * P);
+            const float4 sg4 = lds128f(scl + 4 * (g * 16 + 4 * P)), sh4 = lds128f(scl + 4 * ((g + 8) * 16 + 4 * P));
             const float sg[4] = {sg4.x, sg4.y, sg4.z, sg4.w}, sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
             uint4 u;
             if constexpr (FMT == KYB_FMT_Q6_K) {
-                u = *reinterpret_cast<const uint4*>(tile + (P * 32 + lane) * 16);
-                if ((P & 1) == 0) hi = *reinterpret_cast<const uint4*>(tile + 2048 + ((P >> 1) * 32 + lane) * 16);
+                u = tr.q[P];
+                hi = tr.q[4 + (P >> 1)];
             } else if constexpr (FMT == KYB_FMT_Q3_K) {
-                if ((P & 1) == 0) hi = *reinterpret_cast<const uint4*>(tile + ((P >> 1) * 32 + lane) * 16);     // 2-bit plane
+                hi = tr.q[P >> 1];                                                       // 2-bit plane
                 u = hi;
             } else {
-                u = *reinterpret_cast<const uint4*>(tile + (P * 32 + lane) * 16);
+                u = tr.q[P];
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -280,7 +312,7 @@ __device__ __forceinline__ void consume_tile(const uint8_t* tile, const float* s
 // Persistent kernel: one CTA per SM. CTA c works on k-part c % ksplit (its activations are staged once); its warps take the row tiles
 // ws, ws + TS, ... of that part (ws = warp slot among the TS warps of the part) and stream them back to back through one ring.
 template <int FMT, int NT, int MST>
-__global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t16_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TB = kyb_tile_bytes(FMT);
     constexpr int CS = NT * MST * 32;
@@ -296,53 +328,56 @@ __global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const
     // ---- shared memory carve-up
     uint8_t* xfrag = smem;
     uint8_t* xaux = xfrag + (size_t)p.kbp * 16 * CS;
-    const size_t warp_bytes = ((size_t)p.stages * TB + SCL_BYTES + 8 * (size_t)p.stages + 8 + 15) & ~(size_t)15;
+    constexpr int STAGES = GEMV_STAGES;
+    constexpr size_t warp_bytes = ((size_t)STAGES * TB + SCL_BYTES + 8 * (size_t)STAGES + 8 + 15) & ~(size_t)15;
     uint8_t* wbase = xaux + (size_t)p.kbp * xaux_bytes_per_block<FMT>(NT) + (size_t)warp * warp_bytes;
     uint8_t* ring = wbase;
-    float* scl = reinterpret_cast<float*>(wbase + (size_t)p.stages * TB);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + (size_t)p.stages * TB + SCL_BYTES);
+    float* scl = reinterpret_cast<float*>(wbase + (size_t)STAGES * TB);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + (size_t)STAGES * TB + SCL_BYTES);
 
     // producer state (lane 0): next tile to request. Tiles of one row tile are contiguous; the next row tile of this warp is TS row tiles further.
     int p_left = total, p_blk = nblk;                       // tiles still to request, tiles left in the current row tile
     const uint8_t* p_src = p.t16 + (((size_t)ws * (size_t)p.nb) + (size_t)kb0) * TB;
     const size_t p_jump = ((size_t)TS * (size_t)p.nb - (size_t)nblk) * TB;       // from the end of a row tile's part to the start of the next one
-    uint32_t p_dst = smem_u32(ring), p_bar = smem_u32(bars);
-    const uint32_t ring_end = p_dst + (uint32_t)p.stages * TB, ring0 = p_dst, bar0 = p_bar;
-    auto issue = [&]() {
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p_bar), "r"((uint32_t)TB) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(p_dst), "l"(p_src), "r"((uint32_t)TB), "r"(p_bar)
+    const uint32_t ring_a = smem_u32(ring), bar_a = smem_u32(bars), scl_a = smem_u32(scl);
+    auto issue = [&](int stage) {
+        const uint32_t bar = bar_a + 8 * stage, dst = ring_a + stage * TB;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TB) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p_src), "r"((uint32_t)TB), "r"(bar)
                      : "memory");
         --p_left;
         p_src += TB;
         if (--p_blk == 0) p_blk = nblk, p_src += p_jump;
-        p_dst += TB, p_bar += 8;
-        if (p_dst == ring_end) p_dst = ring0, p_bar = bar0;
     };
 
     // ---- start the weight stream before staging x: the copies run while the CTA prepares the activations
     if (lane == 0) {
-        for (int s = 0; s < p.stages; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
         mbar_fence_init();
-        const int pre = min(p.stages, total);
-        for (int s = 0; s < pre; ++s) issue();
+        const int pre = min(STAGES, total);
+        for (int s = 0; s < pre; ++s) issue(s);
     }
 
-    // ---- stage activations of this k-part as B fragments: [chunk][nt][row < MST][lane t][4 halves permuted (0, 2, 1, 3)]
+    // ---- stage activations of this k-part as B fragments: [chunk][nt][row < MST][lane t][4 halves permuted (0, 2, 1, 3)].
+    // One item = 32 inputs of one activation row (two chunks = one Q4_K sub-block); q4_k also gets the sum of the 32 inputs, split into
+    // fp16 hi + lo and laid out as m16n8k8 B fragments (lane 4 g + t: sub-blocks 2t, 2t + 1 of row g).
     {
-        const int items = nblk * 16 * NT * MST;
-        constexpr int U = 4;                                   // loads of U items are in flight together (x comes from L2: ~1 us latency each)
+        const int items = nblk * 8 * NT * MST;
+        constexpr int U = 2;                                   // loads of U items are in flight together (x comes from L2)
         for (int it0 = threadIdx.x; it0 < items; it0 += U * blockDim.x) {
-            uint4 a[U], b[U];
+            uint4 v[U][4];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int it = it0 + u * blockDim.x;
-                a[u] = make_uint4(0, 0, 0, 0), b[u] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v[u][q] = make_uint4(0, 0, 0, 0);
                 if (it < items) {
-                    const int row = it % MST, nt = (it / MST) % NT, c = it / (MST * NT);
+                    const int row = it % MST, nt = (it / MST) % NT, c2 = it / (MST * NT);
                     const int m = nt * 8 + row;
                     if (m < p.m) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c * 16);
-                        a[u] = __ldg(xp), b[u] = __ldg(xp + 1);
+                        const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c2 * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) v[u][q] = __ldg(xp + q);
                     }
                 }
             }
@@ -350,37 +385,36 @@ __global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const
             for (int u = 0; u < U; ++u) {
                 const int it = it0 + u * blockDim.x;
                 if (it < items) {
-                    const int row = it % MST, nt = (it / MST) % NT, c = it / (MST * NT);
-                    uint4 oa, ob;
-                    oa.x = prmt(a[u].x, a[u].y, 0x5410u), oa.y = prmt(a[u].x, a[u].y, 0x7632u), oa.z = prmt(a[u].z, a[u].w, 0x5410u), oa.w = prmt(a[u].z, a[u].w, 0x7632u);
-                    ob.x = prmt(b[u].x, b[u].y, 0x5410u), ob.y = prmt(b[u].x, b[u].y, 0x7632u), ob.z = prmt(b[u].z, b[u].w, 0x5410u), ob.w = prmt(b[u].z, b[u].w, 0x7632u);
-                    uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)c * CS + (nt * MST + row) * 32);
-                    dst[0] = oa, dst[1] = ob;
-                }
-            }
-        }
-        if constexpr (FMT == KYB_FMT_Q4_K) {
-            __syncthreads();
-            // sums of x over each 32-input sub-block, split into fp16 hi + lo, laid out as m16n8k8 B fragments (lane 4 g + t: sub-blocks 2t, 2t + 1 of row g)
-            const int items2 = nblk * 8 * NT * 8;
-            for (int it = threadIdx.x; it < items2; it += blockDim.x) {
-                const int g_ = it & 7, nt = (it >> 3) % NT, j = (it / (8 * NT)) & 7, blk = it / (64 * NT);
-                float sum = 0.f;
+                    const int row = it % MST, nt = (it / MST) % NT, c2 = it / (MST * NT);
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const __half2* hp = reinterpret_cast<const __half2*>(xfrag + (size_t)(blk * 16 + 2 * j + c) * CS + (nt * MST + (g_ & (MST - 1))) * 32);
+                    for (int c = 0; c < 2; ++c) {
+                        const uint4 a = v[u][2 * c], b = v[u][2 * c + 1];
+                        uint4 oa, ob;
+                        oa.x = prmt(a.x, a.y, 0x5410u), oa.y = prmt(a.x, a.y, 0x7632u), oa.z = prmt(a.z, a.w, 0x5410u), oa.w = prmt(a.z, a.w, 0x7632u);
+                        ob.x = prmt(b.x, b.y, 0x5410u), ob.y = prmt(b.x, b.y, 0x7632u), ob.z = prmt(b.z, b.w, 0x5410u), ob.w = prmt(b.z, b.w, 0x7632u);
+                        uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)(2 * c2 + c) * CS + (nt * MST + row) * 32);
+                        dst[0] = oa, dst[1] = ob;
+                    }
+                    if constexpr (FMT == KYB_FMT_Q4_K) {
+                        float sum = 0.f;
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const float2 f = __half22float2(hp[q]);
-                        sum += f.x + f.y;
+                        for (int q = 0; q < 4; ++q) {
+                            const __half2* hp = reinterpret_cast<const __half2*>(&v[u][q]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 f = __half22float2(hp[e]);
+                                sum += f.x + f.y;
+                            }
+                        }
+                        const __half hi = __float2half_rn(sum);
+                        const __half lo = __float2half_rn(sum - __half2float(hi));
+                        const int blk = c2 >> 3, j = c2 & 7;
+                        __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * 256 * NT);
+                        const int idx = (row * 4 + (j >> 1)) * 2 + (j & 1);
+                        xa[((0 * NT + nt) * 32) * 2 + idx] = hi;
+                        xa[((1 * NT + nt) * 32) * 2 + idx] = lo;
                     }
                 }
-                const __half hi = __float2half_rn(sum);
-                const __half lo = __float2half_rn(sum - __half2float(hi));
-                __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * 256 * NT);
-                const int idx = (g_ * 4 + (j >> 1)) * 2 + (j & 1);
-                xa[((0 * NT + nt) * 32) * 2 + idx] = hi;
-                xa[((1 * NT + nt) * 32) * 2 + idx] = lo;
             }
         }
     }
@@ -389,26 +423,30 @@ __global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const
 
     const int g = lane >> 2, t = lane & 3;
     // lanes whose activation row is not staged read a staged row instead: their output columns are never stored
-    const uint8_t* xlane = xfrag + (g & (MST - 1)) * 32 + t * 8;
-    const uint32_t* xalane = reinterpret_cast<const uint32_t*>(xaux) + lane;
+    const uint32_t xb0 = smem_u32(xfrag) + (g & (MST - 1)) * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
+    uint32_t xb = xb0, xa = xa0;                                  // this lane's fragment addresses for the current k-block
 
     Acc<NT> acc;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc.v[nt][0] = acc.v[nt][1] = acc.v[nt][2] = acc.v[nt][3] = 0.f;
 
-    int st = 0, blk = 0, rt = ws;
+    int blk = 0, rt = ws;
     uint32_t parity = 0;
     bool failed = false;
-    for (int i = 0; i < total; ++i) {
+    auto step = [&](const int stage) {                            // stage is a literal at every call: all shared addresses are base + immediate
+        const uint32_t tile = ring_a + stage * TB;
         // a wait that gives up is remembered; the tile is then consumed as it is (its values do not matter any more) and the kernel reports at the end
-        if (!mbar_wait_bounded(&bars[st], parity)) failed = true;
-        const uint8_t* tile = ring + (size_t)st * TB;
-        prep_scales<FMT>(tile, scl, lane);
+        if (!mbar_wait_fast(bar_a + 8 * stage, parity)) failed = true;
+        // phase A: everything this warp needs from the stage goes to registers / the scale scratch, then the stage is handed back and refilled
+        TileRegs<FMT> tr;
+        load_tile<FMT>(tile, lane, tr);
+        prep_scales<FMT>(tile, scl_a, lane);
         __syncwarp();
-        consume_tile<FMT, NT, MST>(tile, scl, xlane + (size_t)blk * 16 * CS, xalane + blk * 64 * NT, lane, acc);
-        __syncwarp();
-        if (lane == 0 && p_left > 0) issue();
-        if (++st == p.stages) st = 0, parity ^= 1u;
+        if (lane == 0 && p_left > 0) issue(stage);
+        // phase B: arithmetic from registers
+        consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
+        __syncwarp();                                             // the scale scratch is rewritten by the next tile
+        xb += 16 * CS, xa += 256 * NT;
         if (++blk == nblk) {
             // ---- item epilogue: lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
 #pragma unroll
@@ -426,9 +464,17 @@ __global__ void __launch_bounds__(NT == 1 ? 1024 : 512, 1) gemv_t16_kernel(const
                     acc.v[nt][q] = 0.f;
                 }
             }
-            blk = 0, rt += TS;
+            blk = 0, rt += TS, xb = xb0, xa = xa0;
         }
+    };
+    static_assert(STAGES == 2, "the tile loop is unrolled over a two-stage ring");
+    int i = 0;
+    for (; i + 1 < total; i += 2) {
+        step(0);
+        step(1);
+        parity ^= 1u;
     }
+    if (i < total) step(0);
     // every requested tile was waited for above (bounded), so no copy of this warp is in flight here
     if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
 }
@@ -529,20 +575,19 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     const int sms = device_sms();
     const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
     const size_t smem_cap = 227 * 1024;
-    const int fw = env_int("KYB_GEMV_WARPS", 0), fs = env_int("KYB_GEMV_STAGES", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
+    const int fw = env_int("KYB_GEMV_WARPS", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
     auto best_for = [&](int v, int only_ksplit) {
         GemvPlan best{};
         double best_t = 1e30;
         const int nt = VAR_NT[v], mst = VAR_MST[v];
-        const int max_warps = nt == 1 ? 32 : 16;
+        const int max_warps = nt == 1 ? 24 : nt == 2 ? 16 : 8;
         for (int ksplit = 1; ksplit <= nb && ksplit <= sms; ++ksplit) {
             if (only_ksplit && ksplit != only_ksplit) continue;
             const int kbp = (nb + ksplit - 1) / ksplit;
             if (kbp > KBP_MAX || (nb + kbp - 1) / kbp != ksplit) continue;     // skip splits that leave an empty part
             for (int warps = 4; warps <= max_warps; warps += 4) {
                 if (fw && warps != fw && warps + 4 <= max_warps) continue;
-                for (int stages = 2; stages <= 4; ++stages) {
-                    if (fs && stages != fs) continue;
+                for (int stages = kyb::GEMV_STAGES; stages <= kyb::GEMV_STAGES; ++stages) {
                     const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, stages);
                     if (smem > smem_cap) continue;
                     int grid = 0;

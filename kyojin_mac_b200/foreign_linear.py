@@ -1,0 +1,157 @@
+"""Quantized linear modules on the device: torch mirror of kyojin_mlx/foreign_linear.py (`DevPack` :464-1167, `ForeignLinear`
+:1211-1247, `SplitLinear` :1251-1268, `make_linear` :1271). Same names, argument order and shape conventions; tensors are torch CUDA
+tensors, kernels are the sm_100a kernels behind include/kyb.h. There is no CPU path."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import flags as F
+from . import foreign_pack as FP
+from . import ops
+
+
+class Split:
+    """Members of a fused linear whose GGUF types differ (role of kyojin_mlx/foreign_linear.py `Split`): packs with one input width."""
+
+    def __init__(self, packs):
+        self.packs = list(packs)
+        self.k = self.packs[0].k
+        self.n = sum(p.n for p in self.packs)
+        if any(p.k != self.k for p in self.packs):
+            raise ValueError("Split: members differ in input width")
+
+
+class DevPack:
+    """The device arrays of one weight matrix, or of a stack of E expert matrices (E * n rows, expert e = rows [e n, (e + 1) n)),
+    as kyojin_mlx/foreign_linear.py:493-559. One resident copy: the T16 bytes (same size as the stored blocks)."""
+
+    def __init__(self, packs, device="cuda"):
+        ps = packs if isinstance(packs, list) else [packs]
+        p0 = ps[0]
+        if any((p.fmt, p.n, p.k) != (p0.fmt, p0.n, p0.k) for p in ps):
+            raise ValueError("experts differ in format / shape")
+        self.fmt, self.n, self.k = p0.fmt, p0.n, p0.k
+        self.E = len(ps) if isinstance(packs, list) else None
+        if self.E and self.n % 16:
+            raise ValueError("expert stacks need n % 16 == 0 (a 16-row tile must not straddle two experts)")
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise ValueError("DevPack lives on a CUDA device (there is no CPU path)")
+        parts = []
+        for p in ps:                                                        # repack on the device, one expert at a time
+            if p.fmt == "nvfp4":
+                parts.append(torch.from_numpy(FP.to_t16(p)).to(dev))
+            else:
+                parts.append(ops.raw_to_t16(p.fmt, torch.from_numpy(np.ascontiguousarray(p.qs)).to(dev), p.n, p.k))
+        self.t16 = parts[0] if len(parts) == 1 else torch.cat(parts)
+        gs = [float(np.asarray(p.gscale, np.float32).reshape(-1)[0]) for p in ps]
+        self.gscale = gs[0]
+        self.gs = torch.tensor(gs, dtype=torch.float32, device=dev)       # one scale per expert (per-tensor scale of a single matrix)
+        self.rows = self.n * (self.E or 1)
+
+    @classmethod
+    def from_t16(cls, fmt: str, t16: torch.Tensor, n: int, k: int, E: int | None = None, gscale=1.0):
+        """Wraps T16 bytes that are already on the device (synthetic benchmark weights, shards)."""
+        self = cls.__new__(cls)
+        self.fmt, self.n, self.k, self.E, self.t16 = fmt, n, k, E, t16
+        self.gscale = float(gscale)
+        self.gs = torch.full((E or 1,), float(gscale), dtype=torch.float32, device=t16.device)
+        self.rows = n * (E or 1)
+        if t16.numel() != ops.t16_nbytes(fmt, self.rows, k):
+            raise ValueError(f"T16 buffer of {t16.numel()} bytes does not hold [{self.rows}, {k}] {fmt}")
+        return self
+
+    @property
+    def nbytes(self) -> int:
+        return self.t16.numel()
+
+    # ---- one matrix, x2 [R, k] fp16 -> [R, n] fp16 (row-count dispatch of foreign_linear.py:672-737)
+    def apply(self, x2: torch.Tensor) -> torch.Tensor:
+        if self.E:
+            raise ValueError("apply() is for one matrix; expert stacks go through gather / ForeignSwitchGLU")
+        R = x2.shape[0]
+        if R == 0:
+            return torch.empty((0, self.n), dtype=torch.float16, device=x2.device)
+        if R <= F.GEMV_ROWS:
+            return ops.gemv(self.fmt, self.t16, self.n, self.k, x2, self.gscale)
+        return self._rows_chunked(x2)
+
+    def _rows_chunked(self, x2):
+        """More rows than the few-row kernel takes: 32-row slices, one weight read each (the tcgen05 prefill GEMM replaces this above
+        GEMM_MIN_ROWS once it serves the format)."""
+        y = torch.empty((x2.shape[0], self.n), dtype=torch.float16, device=x2.device)
+        for i in range(0, x2.shape[0], 32):
+            ops.gemv(self.fmt, self.t16, self.n, self.k, x2[i:i + 32], self.gscale, out=y[i:i + 32])
+        return y
+
+    def dequant(self, dtype=torch.float16) -> torch.Tensor:
+        """[rows, k] weights (fp16 saturated as foreign_linear.py:1050-1065, or float32 bit-equal to the reference decoder)."""
+        if self.E and self.fmt == "nvfp4" and len(set(self.gs.tolist())) > 1:
+            out = torch.empty((self.rows, self.k), dtype=dtype, device=self.t16.device)
+            for e in range(self.E):
+                out[e * self.n:(e + 1) * self.n] = ops.dequant(self.fmt, self.t16, self.rows, self.k, dtype, float(self.gs[e]), e * self.n, self.n)
+            return out
+        return ops.dequant(self.fmt, self.t16, self.rows, self.k, dtype, self.gscale)
+
+    def expert(self, e: int) -> "DevPack":
+        """Row-range view of expert e (no copy), as foreign_linear.py:637-660."""
+        if not self.E:
+            raise ValueError("not an expert stack")
+        tb = ops.t16_nbytes(self.fmt, self.n, self.k)
+        return DevPack.from_t16(self.fmt, self.t16[e * tb:(e + 1) * tb], self.n, self.k, None, float(self.gs[e]))
+
+
+class ForeignLinear(torch.nn.Module):
+    """y = layer(x) for x (..., in_features); output fp16 by default, bias added when present. Arrays are private (not parameters).
+    Mirrors kyojin_mlx/foreign_linear.py:1211-1247."""
+
+    def __init__(self, pack, bias=None, out_dtype=torch.float16, in_perm=None, device="cuda"):
+        super().__init__()
+        if isinstance(pack, Split):
+            raise TypeError("a Split (mixed GGUF types) is served by SplitLinear: build it with make_linear")
+        self.dev = pack if isinstance(pack, DevPack) else DevPack(pack, device)
+        self._in_perm = None if in_perm is None else torch.as_tensor(np.asarray(in_perm).astype(np.int64), device=self.dev.t16.device)
+        self.in_features, self.out_features, self.fmt = self.dev.k, self.dev.n, self.dev.fmt
+        self.out_dtype = out_dtype
+        self._bias = None if bias is None else torch.as_tensor(bias).to(self.dev.t16.device, out_dtype)
+
+    def forward(self, x: torch.Tensor, permuted: bool = False) -> torch.Tensor:
+        shape = x.shape
+        if shape[-1] != self.in_features:
+            raise ValueError(f"input width {shape[-1]} != in_features {self.in_features}")
+        x2 = x.reshape(-1, shape[-1])
+        if x2.dtype != torch.float16:
+            x2 = x2.to(torch.float16)
+        if self._in_perm is not None and not permuted:
+            x2 = x2.index_select(1, self._in_perm)
+        y = self.dev.apply(x2)
+        if y.dtype != self.out_dtype:
+            y = y.to(self.out_dtype)
+        if self._bias is not None:
+            y = y + self._bias
+        return y.reshape(*shape[:-1], self.out_features)
+
+
+class SplitLinear(torch.nn.Module):
+    """A fused linear whose members have different GGUF types: one ForeignLinear per member, outputs concatenated on the last axis
+    (kyojin_mlx/foreign_linear.py:1251-1268)."""
+
+    def __init__(self, split: Split, bias=None, out_dtype=torch.float16, in_perm=None, device="cuda"):
+        super().__init__()
+        if in_perm is not None:
+            raise ValueError("SplitLinear: a column permutation over mixed-type members is not supported")
+        cuts = np.cumsum([0] + [p.n for p in split.packs])
+        self.members = torch.nn.ModuleList(ForeignLinear(p, None if bias is None else bias[a:b], out_dtype, None, device)
+                                           for p, a, b in zip(split.packs, cuts[:-1], cuts[1:]))
+        self.in_features, self.out_features, self.fmt, self.out_dtype = split.k, split.n, "split", out_dtype
+
+    def forward(self, x, permuted: bool = False):
+        if permuted:
+            raise ValueError("SplitLinear: no permuted input")
+        return torch.cat([m(x) for m in self.members], dim=-1)
+
+
+def make_linear(pack, bias=None, out_dtype=torch.float16, in_perm=None, device="cuda"):
+    """ForeignLinear for a Pack, SplitLinear for a Split (kyojin_mlx/foreign_linear.py:1271)."""
+    return (SplitLinear if isinstance(pack, Split) else ForeignLinear)(pack, bias, out_dtype, in_perm, device)
