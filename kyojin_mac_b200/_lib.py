@@ -12,7 +12,7 @@ import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SO_PATH = os.path.join(HERE, "libkyb.so")
+SO_PATH = os.environ.get("KYB_LIB_PATH") or os.path.join(HERE, "libkyb.so")     # KYB_LIB_PATH: load another build of the library (experiments)
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
 
 OK, EINVAL, ECUDA, ETIMEOUT, EUNSUPPORTED, EWORKSPACE = 0, -1, -2, -3, -4, -5

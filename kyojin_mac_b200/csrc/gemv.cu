@@ -18,6 +18,9 @@
 
 #include "t16_decode.cuh"
 
+#ifndef KYB_ABL
+#define KYB_ABL 0             // experiment switches (instruction-count ablations); 0 in every shipped build
+#endif
 #ifndef KYB_Q4K_SUBNORMAL
 #define KYB_Q4K_SUBNORMAL 1   // 1: 4-bit codes enter the MMA as fp16 subnormals (code * 2^-24), 0: as 1024 + code minus 1024
 #endif
@@ -28,12 +31,13 @@ struct GemvParams {
     const uint8_t* t16;
     const __half* x;
     __half* y;
-    float* partial;          // [ksplit][mpad][npad] when ksplit > 1
+    float* partial;          // [nchunks][m][npad] when ksplit > 1: one partial sum per canonical k-chunk
     unsigned int* status;
     int64_t ldx, ldy;
     int n, npad, nb;         // rows, rows padded to 16, k-blocks of 256
     int m, mst;              // activation rows, rows stored per column tile (1, 2, 4, 8)
-    int kbp, ksplit;         // k-blocks per part, parts
+    int kbp, ksplit;         // k-blocks per part (a multiple of kc), parts
+    int kc;                  // k-blocks per canonical chunk: sums are formed per chunk and chunks are added in k order, whatever the split
     int warps, stages;
     float gscale;
 };
@@ -430,41 +434,62 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc.v[nt][0] = acc.v[nt][1] = acc.v[nt][2] = acc.v[nt][3] = 0.f;
 
-    int blk = 0, rt = ws;
+    Acc<NT> tot;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) tot.v[nt][0] = tot.v[nt][1] = tot.v[nt][2] = tot.v[nt][3] = 0.f;
+    const int chunk0 = kb0 / p.kc;                                // parts start on chunk boundaries
+    int blk = 0, rt = ws, chunk = chunk0, cleft = min(p.kc, nblk);
     uint32_t parity = 0;
     bool failed = false;
     auto step = [&](const int stage) {                            // stage is a literal at every call: all shared addresses are base + immediate
         const uint32_t tile = ring_a + stage * TB;
         // a wait that gives up is remembered; the tile is then consumed as it is (its values do not matter any more) and the kernel reports at the end
+#if !(KYB_ABL & 2)
         if (!mbar_wait_fast(bar_a + 8 * stage, parity)) failed = true;
+#endif
         // phase A: everything this warp needs from the stage goes to registers / the scale scratch, then the stage is handed back and refilled
         TileRegs<FMT> tr;
         load_tile<FMT>(tile, lane, tr);
+#if !(KYB_ABL & 1)
         prep_scales<FMT>(tile, scl_a, lane);
+#endif
         __syncwarp();
+#if !(KYB_ABL & 2)
         if (lane == 0 && p_left > 0) issue(stage);
+#endif
         // phase B: arithmetic from registers
+#if !(KYB_ABL & 4)
         consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
+#else
+        acc.v[0][0] += __uint_as_float(tr.q[0].x ^ tr.q[1].y ^ tr.q[2].z ^ tr.q[3].w ^ tr.a0 ^ tr.a1) + tr.dmg + tr.dmh;
+#endif
         __syncwarp();                                             // the scale scratch is rewritten by the next tile
         xb += 16 * CS, xa += 256 * NT;
-        if (++blk == nblk) {
-            // ---- item epilogue: lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
+        ++blk;
+        if (--cleft == 0) {
+            // ---- end of a canonical chunk: its sum joins the running total (one part holds the whole k range) or goes to the workspace
+            // lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
+            const bool last = blk == nblk;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
-                    if (m < p.m) {
-                        if (p.ksplit == 1) {
-                            if (nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(acc.v[nt][q] * p.gscale);
-                        } else {
-                            p.partial[((size_t)kp * p.m + m) * p.npad + nrow] = acc.v[nt][q];
+                    if (p.ksplit == 1) {
+                        tot.v[nt][q] += acc.v[nt][q];
+                        if (last) {
+                            if (m < p.m && nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(tot.v[nt][q] * p.gscale);
+                            tot.v[nt][q] = 0.f;
                         }
+                    } else if (m < p.m) {
+                        p.partial[((size_t)chunk * p.m + m) * p.npad + nrow] = acc.v[nt][q];
                     }
                     acc.v[nt][q] = 0.f;
                 }
             }
-            blk = 0, rt += TS, xb = xb0, xa = xa0;
+            ++chunk;
+            cleft = min(p.kc, nblk - blk);
+            if (last) blk = 0, rt += TS, xb = xb0, xa = xa0, chunk = chunk0, cleft = min(p.kc, nblk);
         }
     };
     static_assert(STAGES == 2, "the tile loop is unrolled over a two-stage ring");
@@ -484,7 +509,7 @@ __global__ void gemv_finalize_kernel(const float* __restrict__ partial, int kspl
     if (i >= (int64_t)m * n) return;
     const int row = (int)(i / n), col = (int)(i % n);
     float s = 0.f;
-    for (int kp = 0; kp < ksplit; ++kp) s += partial[((size_t)kp * m + row) * npad + col];
+    for (int c = 0; c < ksplit; ++c) s += partial[((size_t)c * m + row) * npad + col];     // ksplit = number of canonical chunks here
     y[(size_t)row * ldy + col] = sat_half(s * gscale);
 }
 
@@ -496,6 +521,7 @@ namespace {
 struct GemvPlan {
     int nt, mst, warps, stages, kbp, ksplit, grid;
     size_t smem;
+    int kc, nchunks;
 };
 
 int env_int(const char* name, int dflt) {
@@ -561,45 +587,45 @@ double plan_cost(int fmt, int sms, int ntiles, int nb, int nt, int64_t n, int64_
     const double t_lat = busiest * per_tile / 1.9e9 + 1.5e-6;
     const double t_bw = (double)ntiles * nb * tb / 6.6e12 + 1.0e-6;
     double tsec = std::max(t_lat, t_bw);
-    if (ksplit > 1) tsec += 2.0 * ksplit * m * (double)n * 4.0 / 6.6e12 + 2.0e-6;
+    if (ksplit > 1) tsec += 2.0 * ((nb + kbp - 1) / kbp) * m * (double)n * 4.0 / 6.6e12 + 3.0e-6;      // partial traffic + the finalize launch
     *grid_out = grid;
     return tsec + 1e-9 * stages + 1e-10 * warps;
 }
 
-constexpr int KBP_MAX = 10;   // k-blocks per part: the 32-row variant stages 16 KB of activations per block
+// Canonical k-chunk of a matrix: depends on (n, k) only - never on m or on the launch shape - so the partial sums of an activation row are always
+// formed chunk by chunk and added in k order (bit-identical rows whatever m and however the chunks are spread over CTAs). Small-n matrices get short
+// chunks so that row tiles x chunks still give every SM a full set of warps.
+int canonical_chunk(int ntiles, int nb) {
+    const int want_chunks = (2400 + ntiles - 1) / ntiles;               // ~16 warps on each of 148 SMs
+    return std::max(1, std::min(10, nb / std::max(1, want_chunks)));
+}
 
-// The k split depends on (format, n, k) only - never on m - so that the partial sums of an activation row are formed in the same order whatever the
-// number of rows in the call (bit-identical rows across m). It is chosen for the 8-row variant; warps and ring depth are then chosen per m.
-// Environment overrides (KYB_GEMV_WARPS / _STAGES / _KSPLIT) exist for sweeps.
+// Warps per CTA, chunks per part (k split) and grid are chosen per m. Environment overrides (KYB_GEMV_WARPS / _KSPLIT) exist for sweeps.
 GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     const int sms = device_sms();
     const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
     const size_t smem_cap = 227 * 1024;
     const int fw = env_int("KYB_GEMV_WARPS", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
-    auto best_for = [&](int v, int only_ksplit) {
-        GemvPlan best{};
-        double best_t = 1e30;
-        const int nt = VAR_NT[v], mst = VAR_MST[v];
-        const int max_warps = nt == 1 ? 24 : nt == 2 ? 16 : 8;
-        for (int ksplit = 1; ksplit <= nb && ksplit <= sms; ++ksplit) {
-            if (only_ksplit && ksplit != only_ksplit) continue;
-            const int kbp = (nb + ksplit - 1) / ksplit;
-            if (kbp > KBP_MAX || (nb + kbp - 1) / kbp != ksplit) continue;     // skip splits that leave an empty part
-            for (int warps = 4; warps <= max_warps; warps += 4) {
-                if (fw && warps != fw && warps + 4 <= max_warps) continue;
-                for (int stages = kyb::GEMV_STAGES; stages <= kyb::GEMV_STAGES; ++stages) {
-                    const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, stages);
-                    if (smem > smem_cap) continue;
-                    int grid = 0;
-                    const double tsec = plan_cost(fmt, sms, ntiles, nb, nt, n, VAR_NT[v] * 8, warps, stages, kbp, ksplit, &grid);
-                    if (tsec < best_t) best_t = tsec, best = GemvPlan{nt, mst, warps, stages, kbp, ksplit, grid, smem};
-                }
-            }
+    const int kc = canonical_chunk(ntiles, nb), nchunks = (nb + kc - 1) / kc;
+    const int v = variant_of(m), nt = VAR_NT[v], mst = VAR_MST[v];
+    const int max_warps = nt == 1 ? 24 : nt == 2 ? 16 : 8;
+    GemvPlan best{};
+    double best_t = 1e30;
+    for (int cpp = 1; cpp <= nchunks; ++cpp) {                           // chunks per part
+        const int ksplit = (nchunks + cpp - 1) / cpp, kbp = cpp * kc;
+        if ((nchunks + ksplit - 1) / ksplit != cpp) continue;            // one representative per distinct split
+        if (fk && ksplit != fk) continue;
+        if (ksplit > sms) continue;
+        for (int warps = 4; warps <= max_warps; warps += 4) {
+            if (fw && warps != std::min(fw, max_warps)) continue;
+            const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, kyb::GEMV_STAGES);
+            if (smem > smem_cap) continue;
+            int grid = 0;
+            const double tsec = plan_cost(fmt, sms, ntiles, nb, nt, n, m, warps, kyb::GEMV_STAGES, kbp, ksplit, &grid);
+            if (tsec < best_t) best_t = tsec, best = GemvPlan{nt, mst, warps, kyb::GEMV_STAGES, kbp, ksplit, grid, smem, kc, nchunks};
         }
-        return best;
-    };
-    const int ksplit = fk ? fk : best_for(3, 0).ksplit;                          // variant 3 = one column tile, 8 staged rows
-    return best_for(variant_of(m), ksplit);
+    }
+    return best;
 }
 
 // plans are cached per (format, n, k, m): the search costs tens of microseconds, a decode step calls this per linear
@@ -642,7 +668,7 @@ extern "C" int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8
 extern "C" size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m) {
     if (fmt < 0 || fmt > 3 || n <= 0 || k <= 0 || k % 256 || m <= 0 || m > 32) return 0;
     const GemvPlan pl = make_plan(fmt, n, k, m);
-    return pl.ksplit > 1 ? (size_t)pl.ksplit * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float) : 0;
+    return pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float) : 0;
 }
 
 extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
@@ -658,7 +684,7 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     const GemvPlan pl = make_plan(fmt, n, k, m);
     KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
     const int npad = (int)((n + 15) / 16 * 16);
-    const size_t need = pl.ksplit > 1 ? (size_t)pl.ksplit * (size_t)m * (size_t)npad * sizeof(float) : 0;
+    const size_t need = pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
     if (need && (!workspace || workspace_bytes < need)) {
         kyb_set_error("gemv needs %zu bytes of workspace, got %zu", need, workspace ? workspace_bytes : (size_t)0);
         return KYB_EWORKSPACE;
@@ -668,7 +694,7 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     kyb::GemvParams p;
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = (float*)workspace, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc;
     cudaStream_t st = (cudaStream_t)stream;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
@@ -676,7 +702,7 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, st));
     if (pl.ksplit > 1) {
         const int64_t tot = m * n;
-        kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>((const float*)workspace, pl.ksplit, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
+        kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>((const float*)workspace, pl.nchunks, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
         return kyb_launch_check("gemv_finalize");
     }
     return KYB_OK;
