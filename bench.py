@@ -1,0 +1,340 @@
+"""Benchmark of the dequant-fused quantized linear on B200: decode GEMV sweep over the layer shapes of a 32B-class dense transformer.
+
+Workload (the benchmark's second configuration): hidden 5120, 64 query / 8 KV heads of dim 128, MLP 27648. Projections q 5120->8192,
+k and v 5120->1024, o 8192->5120, gate/up 5120->27648 in Q4_K, down 27648->5120 in Q6_K; activations fp16 N(0, 1) at batch
+M = 1, 2, 4, 8. One step = one pass over the layer at each of the four batch sizes. Weights are seeded synthetic blocks (random
+payload bytes, fp16 d/dmin = |N(0, 1e-3)|, Q6_K scales U[-32, 31]) because no model file is available offline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-group]
+
+Prints ONE JSON line (rank 0). `value` = GGUF weight bytes + activation bytes moved per second with everything resident in HBM (one
+CUDA graph per step); `e2e` = the same through the module API with host activations (pinned h2d, d2h of the results inside the timed
+region). N > 1: every rank holds a full layer-sized shard of an N-times wider layer (output dimension column-sharded) and all-gathers
+its output slices over NCCL; value is the whole-job aggregate (weak scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HID, QDIM, KVDIM, MLP = 5120, 8192, 1024, 27648
+# name, format, n (out), k (in), same-input group
+MATRICES = [("q", "q4_k", QDIM, HID, "qkv"), ("k", "q4_k", KVDIM, HID, "qkv"), ("v", "q4_k", KVDIM, HID, "qkv"), ("o", "q4_k", HID, QDIM, "o"),
+            ("gate", "q4_k", MLP, HID, "gateup"), ("up", "q4_k", MLP, HID, "gateup"), ("down", "q6_k", HID, MLP, "down")]
+BATCHES = (1, 2, 4, 8)
+BPW = {"q4_k": 144 / 256, "q6_k": 210 / 256, "q3_k": 110 / 256, "nvfp4": 144 / 256}
+METRIC = "quant GEMV GB/s (% HBM peak)"
+
+
+def alg_bytes(fmt, n, k, m):
+    """Algorithmic bytes of one GEMV: stored weight bytes + fp16 activations in + fp16 results out."""
+    return n * k * BPW[fmt] + 2 * m * k + 2 * m * n
+
+
+def layer_list(group: bool):
+    """[(name, fmt, n, k)] of the launches of one layer pass; same-input projections concatenated along n when `group`
+    (the reference runs q|k|v and gate|up as one product: kyojin_mlx/foreign_linear.py:1617-1655 group_same_input)."""
+    if not group:
+        return [(nm, f, n, k) for nm, f, n, k, _ in MATRICES]
+    out, seen = [], {}
+    for nm, f, n, k, g in MATRICES:
+        if g in seen:
+            i = seen[g]
+            out[i] = (out[i][0] + "|" + nm, f, out[i][2] + n, k)
+        else:
+            seen[g] = len(out)
+            out.append((nm, f, n, k))
+    return out
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thr = threading.Thread(target=self._read, daemon=True)
+            self.thr.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()                      # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            sm.append(int(f[0]))
+            mx = max(mx, int(f[1]) if f[1].isdigit() else 0)
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample(threads=None, row_frac=4, m=8, seed=1):
+    """The reference's CPU path (numpy dequant on min(8, cores) threads, then a float32 matmul: kyojin_mlx/foreign_gguf.py:376-394 +
+    foreign_linear.py:710) on a bounded sample of the workload: every matrix of the layer with 1/row_frac of its rows, batch m."""
+    from oracle import kq_numpy as O                       # CPU baseline leg: the oracle port is what is timed here
+    from kyojin_mac_b200 import synth
+    rng = np.random.default_rng(seed)
+    cases = []
+    for nm, f, n, k, _ in MATRICES:
+        ns = max(16, n // row_frac)
+        cases.append((f, ns, k, synth.raw_blocks(f, ns, k, rng), synth.activations(m, k, rng)))
+    nbytes = sum(alg_bytes(f, ns, k, m) for f, ns, k, _, _ in cases)
+    T = {"q4_k": "Q4_K", "q6_k": "Q6_K"}
+
+    def one_pass():
+        t0 = time.perf_counter()
+        for f, ns, k, raw, x in cases:
+            O.linear_cpu(T[f], raw, k, x, threads)
+        return time.perf_counter() - t0
+
+    return one_pass, nbytes, f"every matrix of the layer at 1/{row_frac} of its rows, M={m}, dequant-then-matmul per call"
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    one_pass, nbytes, sample = cpu_sample()
+    for _ in range(min(args.warmup, 1)):
+        one_pass()
+    steps = min(args.steps, 5)
+    ts = [one_pass() for _ in range(steps)]
+    t = float(np.mean(ts))
+    gbs = nbytes / t / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1),
+            "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cfg1: 32B-class layer decode GEMV sweep (Q4_K, down Q6_K), CPU sample", "sample": sample},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": min(8, cores), "kind": "port", "sample": sample,
+                             "note": "numpy restatement of the reference's CPU path (oracle/kq_numpy.py); dequant threads = min(8, cores) as the reference, BLAS threads = numpy default"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from kyojin_mac_b200 import ops, synth
+    from kyojin_mac_b200.foreign_linear import DevPack, ForeignLinear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    mats = layer_list(not args.no_group)
+    copies = 2                                                   # two layer copies alternate; one layer (328 MB) already exceeds the 126 MB L2
+    layers = []
+    for c in range(copies):
+        layers.append([DevPack.from_t16(f, synth.t16_random_device(f, n, k, seed=1000 * rank + 10 * c + i, device=dev), n, k) for i, (nm, f, n, k) in enumerate(mats)])
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    xs = {(m, k): torch.randn((m, k), device=dev, generator=gen).to(torch.float16) for m in BATCHES for k in sorted({k for _, _, _, k in mats})}
+    ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)}
+    yg = {(m, i): torch.empty((world, m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)} if world > 1 else None
+    step_bytes = sum(alg_bytes(f, n, k, m) for m in BATCHES for _, f, n, k in mats)
+    launches_per_step = sum(1 + (ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
+
+    def one_step(layer, timed=None):
+        for m in BATCHES:
+            for i, (nm, f, n, k) in enumerate(mats):
+                if timed is not None and i == timed[0]:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                ops.gemv(f, layer[i].t16, n, k, xs[(m, k)], 1.0, out=ys[(m, i)])
+                if timed is not None and i == timed[0]:
+                    e1.record()
+                    timed[1].append((m, e0, e1))
+                if world > 1:
+                    dist.all_gather_into_tensor(yg[(m, i)], ys[(m, i)])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: one CUDA graph per layer copy (launch-bound inner loop captured), device-timed
+    for c in range(copies):
+        one_step(layers[c])
+    torch.cuda.synchronize()
+    graphs = None
+    try:
+        graphs = []
+        for c in range(copies):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                one_step(layers[c])
+            graphs.append(g)
+    except Exception as e:                                        # collectives that cannot be captured: time eager launches instead
+        graphs = None
+        if rank == 0:
+            print(f"[bench] CUDA graph capture unavailable ({type(e).__name__}); timing eager launches", file=sys.stderr)
+        torch.cuda.synchronize()
+
+    def run_step(s):
+        if graphs is not None:
+            graphs[s % copies].replay()
+        else:
+            one_step(layers[s % copies])
+
+    for s in range(args.warmup):
+        run_step(s)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        time.sleep(0.25)
+        barrier()
+        e0.record()
+        for s in range(args.steps):
+            run_step(s)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        time.sleep(0.25)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ops.check_device_status()
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (the largest Q4_K product of the layer), timed per launch with events on the launching stream
+    dom = max(range(len(mats)), key=lambda i: mats[i][2] * mats[i][3] * BPW[mats[i][1]])
+    rec = []
+    for s in range(max(3, min(args.steps, 10))):
+        one_step(layers[s % copies], timed=(dom, rec))
+    torch.cuda.synchronize()
+    nm, f, n, k = mats[dom]
+    per_m = {}
+    for m, a, b in rec:
+        per_m.setdefault(m, []).append(a.elapsed_time(b))
+    dom_ms = float(np.mean([np.mean(v) for v in per_m.values()]))
+    dom_bytes = float(np.mean([alg_bytes(f, n, k, m) for m in per_m]))
+    peak, peak_src = peaks()
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": f"gemv_t16_kernel<{f}> on {nm} [{n} x {k}]", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": peak_src, "traffic": None, "alg_bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3,
+                "us_per_launch_by_m": {str(m): float(np.mean(v)) * 1e3 for m, v in per_m.items()},
+                "whole_step_frac_of_peak": value / world / peak}
+
+    # ---- e2e: the module API with host activations (pinned h2d each step, d2h of every result)
+    mods = [[ForeignLinear(dp) for dp in layer] for layer in layers]
+    ks = sorted({k for _, _, _, k in mats})
+    hx = {(m, k): xs[(m, k)].cpu().pin_memory() for m in BATCHES for k in ks}
+    hy = {(m, i): torch.empty((m, n), dtype=torch.float16).pin_memory() for m in BATCHES for i, (_, _, n, _) in enumerate(mats)}
+    h2d = sum(2 * m * k for m in BATCHES for k in ks)
+    d2h = sum(2 * m * n for m in BATCHES for _, _, n, _ in mats)
+
+    def e2e_step(s):
+        layer = mods[s % copies]
+        for m in BATCHES:
+            dx = {k: hx[(m, k)].to(dev, non_blocking=True) for k in ks}
+            for i, (nm_, f_, n_, k_) in enumerate(mats):
+                y = layer[i](dx[k_])
+                if world > 1:
+                    dist.all_gather_into_tensor(yg[(m, i)], y)
+                hy[(m, i)].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for s in range(args.warmup):
+        e2e_step(s)
+    barrier()
+    t0 = time.perf_counter()
+    e0.record()
+    for s in range(args.steps):
+        e2e_step(s)
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 * 0.0)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = world * step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            one_pass, nbytes, sample = cpu_sample()
+            one_pass()
+            ts = [one_pass() for _ in range(3)]
+            cpu = {"value": nbytes / float(np.mean(ts)) / 1e9, "unit": "GB/s", "cores": min(8, os.cpu_count() or 1), "kind": "port", "sample": sample,
+                   "host_cores": os.cpu_count()}
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate (u8 stored blocks)", "data": "synthetic",
+                "config": {"workload": "cfg1: decode GEMV sweep over a 32B-class layer (q,k,v,o,gate,up Q4_K; down Q6_K), M=1,2,4,8 per step",
+                           "launch_list": [f"{nm}:{f}:{n}x{k}" for nm, f, n, k in mats], "same_input_groups": not args.no_group,
+                           "l2": "two layer copies alternate; one layer (328 MB) exceeds the 126 MB L2", "timing": "CUDA graph per step, CUDA events, max over ranks" if graphs is not None else "eager launches, CUDA events, max over ranks",
+                           "parallelism": f"n-sharded x{world} + NCCL all-gather of output slices" if world > 1 else "single GPU",
+                           "bytes_per_step": step_bytes},
+                "roofline": roofline, "cpu_baseline": cpu,
+                "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-group", action="store_true", help="launch q, k, v and gate, up separately instead of as same-input groups")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

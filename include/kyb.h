@@ -69,6 +69,13 @@ size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m);
 int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
                  void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- prefill GEMM on tcgen05 (UMMA 128 x 256 x 16, kind::f16, fp32 accumulation in tensor memory), fp16 operands:
+ * d [m, n] = sat_f16(gscale * a [m, k] b [n, k]^T), k % 64 == 0, lda / ldb / ldd in elements. Replaces the library matmul of the
+ * reference's large-row path, kyojin_mlx/foreign_linear.py:710 and :737 (`x2 @ self.dequant().T`), which the reference takes for
+ * more rows than its stored kernels serve (thresholds at foreign_linear.py:38-81); b is the fp16 output of kyb_dequant_t16. */
+int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale,
+                    void* d, int64_t ldd, void* stream);
+
 /* launch plan the GEMV would use (diagnostics and launch counting): out8 = {column tiles, stored x rows per tile, warps per CTA,
  * ring stages, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. ksplit > 1 means two launches. */
 int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);

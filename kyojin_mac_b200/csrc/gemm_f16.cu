@@ -1,0 +1,168 @@
+// Prefill GEMM on tcgen05: D[m, n] = sat_f16(gscale * sum_k A[m, k] * B[n, k]) with fp16 operands and fp32 accumulation in tensor memory.
+// A = activations [M, K], B = dequantised weights [N, K] (fp16 exactly as the reference stages them: kyojin_mlx/foreign_metal.py:1130-1146),
+// both K-major, so this is the x W^T contraction of kyojin_mlx/foreign_linear.py:710/:737 (`x2 @ self.dequant().T`).
+//
+// One CTA per 128 x BN output tile. Warp 0 feeds a ring of shared-memory stages with TMA tiled loads (128-byte swizzle), warp 1 issues
+// tcgen05.mma (UMMA 128 x BN x 16, kind::f16) from one elected thread and hands stages back through tcgen05.commit, warps 2-5 read the accumulator
+// from tensor memory with tcgen05.ld and store fp16 rows. Every mbarrier wait is bounded: a wait that gives up sets the device status word and
+// the CTA drains and frees its tensor memory.
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace kyb {
+
+constexpr int GM_BM = 128, GM_BK = 64, GM_THREADS = 192;
+
+struct GemmParams {
+    __half* d;
+    int64_t ldd;
+    int m, n, k;
+    float gscale;
+    unsigned int* status;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr uint32_t A_BYTES = GM_BM * GM_BK * 2, B_BYTES = BN * GM_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;                 // 1024-byte alignment for the 128-byte swizzle atoms
+    const uint32_t bars = smem0 + STAGES * STAGE_BYTES;                            // full[STAGES], empty[STAGES], accum, tmem slot
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accum_bar = bars + 16 * STAGES, tmem_slot = accum_bar + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GM_BM;
+    const int kblocks = p.k / GM_BK;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
+        mbar_init_a(accum_bar, 1);
+        mbar_fence_init();
+        prefetch_tmap(&tma_a);
+        prefetch_tmap(&tma_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (elect_one()) {
+            uint32_t parity = 1;                                                    // a fresh barrier passes a wait on the previous phase
+            int s = 0;
+            for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                const uint32_t a_dst = smem0 + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                mbar_expect_tx_a(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(a_dst, &tma_a, kb * GM_BK, m0, full0 + 8 * s);
+                tma_load_2d(b_dst, &tma_b, kb * GM_BK, n0, full0 + 8 * s);
+                if (++s == STAGES) s = 0, parity ^= 1u;
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_f16(GM_BM, BN);
+            uint32_t parity = 0;
+            int s = 0;
+            for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                tc_fence_after();
+                const uint64_t adesc = umma_desc_sw128(smem0 + s * STAGE_BYTES), bdesc = umma_desc_sw128(smem0 + s * STAGE_BYTES + A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < GM_BK / 16; ++kk)                             // 16 fp16 = 32 bytes along K inside the swizzle atom: +2 in the address field
+                    umma_f16(tmem_base, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
+                umma_commit(empty0 + 8 * s);                                        // stage free once these MMAs have read it
+                if (++s == STAGES) s = 0, parity ^= 1u;
+            }
+            umma_commit(accum_bar);                                                 // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32)
+        const int q = warp & 3;
+        if (!mbar_wait_fast(accum_bar, 0)) failed = true;
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        __half* drow = p.d + (size_t)row * p.ldd + n0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+            tmem_ld_wait();
+            if (row < p.m && !failed) {
+                if (n0 + c + 32 <= p.n && (p.ldd & 7) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 o;
+                        __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * p.gscale), sat_half(__uint_as_float(v[j + 1]) * p.gscale));
+                        __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * p.gscale), sat_half(__uint_as_float(v[j + 3]) * p.gscale));
+                        __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * p.gscale), sat_half(__uint_as_float(v[j + 5]) * p.gscale));
+                        __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * p.gscale), sat_half(__uint_as_float(v[j + 7]) * p.gscale));
+                        o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(drow + c + j) = o;
+                    }
+                } else {
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + c + j < p.n) drow[c + j] = sat_half(__uint_as_float(v[j]) * p.gscale);
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace kyb
+
+namespace {
+
+template <int BN, int STAGES>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const kyb::GemmParams& p, cudaStream_t st) {
+    constexpr size_t smem = (size_t)STAGES * (kyb::GM_BM * kyb::GM_BK * 2 + BN * kyb::GM_BK * 2) + 16 * STAGES + 16 + 1024;
+    auto kern = kyb::gemm_f16_tn_kernel<BN, STAGES>;
+    static std::mutex mu;
+    static unsigned done = 0;
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!(done & (1u << (dev & 31)))) {
+            KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done |= 1u << (dev & 31);
+        }
+    }
+    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + kyb::GM_BM - 1) / kyb::GM_BM));
+    kern<<<grid, kyb::GM_THREADS, smem, st>>>(ta, tb, p);
+    return kyb_launch_check("gemm_f16_tn");
+}
+
+}  // namespace
+
+// D fp16 [m, n] (row stride ldd) = sat(gscale * A [m, k] (row stride lda) x B [n, k]^T (row stride ldb)), all fp16, k % 64 == 0.
+extern "C" int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale, void* d, int64_t ldd,
+                               void* stream) {
+    KYB_REQUIRE(a && b && d, "null pointer");
+    KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 64 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 64", (long long)m, (long long)n, (long long)k);
+    KYB_REQUIRE(lda >= k && ldb >= k && lda % 8 == 0 && ldb % 8 == 0 && ldd >= n, "leading dimensions: lda, ldb >= k and multiples of 8, ldd >= n");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0 && ((uintptr_t)d & 1) == 0, "a and b must be 16-byte aligned");
+    KYB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "dimension too large");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    const bool wide = n >= 256;
+    CUtensorMap ta, tb;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda * 2, kyb::GM_BM, kyb::GM_BK)) return rc;
+    if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
+    kyb::GemmParams p;
+    p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale, p.status = status;
+    cudaStream_t st = (cudaStream_t)stream;
+    return wide ? launch_gemm<256, 4>(ta, tb, p, st) : launch_gemm<128, 6>(ta, tb, p, st);
+}

@@ -9,6 +9,6 @@ def _int(name: str, default: int) -> int:
 
 
 GEMV_ROWS = _int("KYB_GEMV_ROWS", 32)        # rows served by the decode GEMV / few-row tensor-core kernel (one weight read per 32 rows)
-GEMM_MIN_ROWS = _int("KYB_GEMM_MIN_ROWS", 33)  # from here the prefill GEMM (tcgen05) runs
+GEMM_MIN_ROWS = _int("KYB_GEMM_MIN_ROWS", 65)  # from here the prefill GEMM (tcgen05) runs
 GATHER_MAX = _int("KYB_GATHER_MAX", 256)     # routed-expert slots up to here take the gathered GEMV path (reference: 128, foreign_linear.py:87)
 KQ_MT = _int("KYB_KQ_GMM_MT", 128)           # rows of one expert per grouped-GEMM tile (reference: 32 on its 32-wide matmul2d, foreign_linear.py:83)

@@ -75,15 +75,23 @@ class DevPack:
             return torch.empty((0, self.n), dtype=torch.float16, device=x2.device)
         if R <= F.GEMV_ROWS:
             return ops.gemv(self.fmt, self.t16, self.n, self.k, x2, self.gscale)
-        return self._rows_chunked(x2)
+        if R < F.GEMM_MIN_ROWS:
+            return self._rows_chunked(x2)
+        return self._prefill(x2)
 
     def _rows_chunked(self, x2):
-        """More rows than the few-row kernel takes: 32-row slices, one weight read each (the tcgen05 prefill GEMM replaces this above
-        GEMM_MIN_ROWS once it serves the format)."""
+        """A few more rows than one few-row launch takes: 32-row slices, one weight read each."""
         y = torch.empty((x2.shape[0], self.n), dtype=torch.float16, device=x2.device)
         for i in range(0, x2.shape[0], 32):
             ops.gemv(self.fmt, self.t16, self.n, self.k, x2[i:i + 32], self.gscale, out=y[i:i + 32])
         return y
+
+    def _prefill(self, x2):
+        """Prefill: weights staged as fp16 exactly like the reference's large-row path (foreign_linear.py:710 `x2 @ self.dequant().T`, fp16 staging
+        at foreign_metal.py:1130-1146), then one tcgen05 GEMM with fp32 accumulation. The NVFP4 per-tensor scale is applied to the fp32
+        accumulator, not folded into the fp16 weights."""
+        w16 = ops.dequant(self.fmt, self.t16, self.n, self.k, torch.float16, 1.0)
+        return ops.gemm_f16(x2, w16, self.gscale)
 
     def dequant(self, dtype=torch.float16) -> torch.Tensor:
         """[rows, k] weights (fp16 saturated as foreign_linear.py:1050-1065, or float32 bit-equal to the reference decoder)."""

@@ -91,6 +91,22 @@ def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float 
     return y
 
 
+def gemm_f16(a: torch.Tensor, b: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """d fp16 [m, n] = a fp16 [m, k] @ b fp16 [n, k]^T on tcgen05 (fp32 accumulation in tensor memory, saturated fp16 result)."""
+    _need_cuda(a, b)
+    if a.dtype != torch.float16 or b.dtype != torch.float16 or a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"gemm_f16 takes float16 [m, k] and [n, k], got {a.dtype} {tuple(a.shape)} and {b.dtype} {tuple(b.shape)}")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[0]
+    d = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_gemm_f16_tn(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), m, n, k, float(gscale), d.data_ptr(), d.stride(0), _stream()))
+    return d
+
+
 def gemv_plan(fmt, n: int, k: int, m: int) -> dict:
     import ctypes
     out = (ctypes.c_int * 8)()

@@ -1,0 +1,68 @@
+"""Prefill GEMM parity (GPU): tcgen05 fp16 GEMM against torch fp32 / the fp64 dequant-then-matmul oracle; mirrors the reference's large-row checks
+(tests/test_foreign_formats.py:321-339: R = 24, 70 through dequant + matmul, max-abs <= 4e-3 max|ref|) with the benchmark's 1e-3 Frobenius bound."""
+import numpy as np
+import pytest
+import torch
+
+from kyojin_mac_b200 import foreign_pack as FP, ops, synth
+from kyojin_mac_b200.foreign_linear import ForeignLinear
+from oracle import kq_numpy as O
+
+pytestmark = pytest.mark.gpu
+T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4"}
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 256), (256, 512, 1024), (70, 200, 320), (1000, 1300, 2048), (2048, 3072, 3072)])
+def test_gemm_f16_vs_fp32(m, n, k):
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+    b = (torch.randn((n, k), device="cuda", generator=g) * 0.05).to(torch.float16)
+    d = ops.gemm_f16(a, b)
+    ops.check_device_status()
+    want = a.double() @ b.double().T
+    err = (torch.linalg.norm(d.double() - want) / torch.linalg.norm(want)).item()
+    assert err < 5e-4, err                                    # fp16 output rounding only (2^-11 relative per element)
+    assert (d.double() - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+
+
+def test_gemm_f16_exact_small_integers():
+    """Integer-valued operands: every product and partial sum is exact in fp32, so the result must be exact."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randint(-3, 4, (256, 512), device="cuda", generator=g).to(torch.float16)
+    b = torch.randint(-3, 4, (384, 512), device="cuda", generator=g).to(torch.float16)
+    d = ops.gemm_f16(a, b)
+    assert torch.equal(d.float(), a.float() @ b.float().T)
+
+
+def test_gemm_saturates_and_scales():
+    a = torch.full((128, 64), 100.0, dtype=torch.float16, device="cuda")
+    b = torch.full((128, 64), 100.0, dtype=torch.float16, device="cuda")
+    d = ops.gemm_f16(a, b)
+    assert torch.isfinite(d).all() and (d == 65504).all()
+    d2 = ops.gemm_f16(a, b, gscale=1e-3)
+    torch.testing.assert_close(d2.float(), torch.full((128, 128), 640.0, device="cuda"), rtol=1e-3, atol=0)
+
+
+@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4"])
+@pytest.mark.parametrize("rows", [70, 300])
+def test_linear_prefill_vs_fp64(fmt, rows):
+    n, k = 384, 1024
+    rng = np.random.default_rng(rows)
+    raw = synth.raw_blocks(fmt, n, k, rng)
+    x = synth.activations(rows, k, rng)
+    w = O.dequant(T[fmt], raw, k)
+    lin = ForeignLinear(FP.to_pack(T[fmt], raw, k))
+    y = lin(torch.from_numpy(x).cuda()).cpu().numpy()
+    ops.check_device_status()
+    want = O.matmul_f64(x, w)
+    err, ref_err = O.rel_fro(y, want), O.rel_fro(O.matmul_ref_path(x, w), want)
+    assert err <= 1e-3 and err <= 2 * ref_err + 1e-6, (err, ref_err)
+    assert np.abs(y.astype(np.float64) - want).max() <= 4e-3 * np.abs(want).max()
+
+
+def test_gemm_errors():
+    a = torch.zeros((128, 96), dtype=torch.float16, device="cuda")
+    with pytest.raises(Exception):
+        ops.gemm_f16(a, a)                                     # k % 64 != 0
+    with pytest.raises(ValueError):
+        ops.gemm_f16(a.float(), a.float())
