@@ -76,6 +76,38 @@ int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, 
 int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale,
                     void* d, int64_t ldd, void* stream);
 
+/* grouped form: rows of a sorted by expert, b = expert stack [experts * n, k] in fp16, tile list on the device (tb, off from kyb_moe_plan with mt = 128),
+ * optional scatter of the output rows (row_map) and per-expert output scale (gs). Replaces kyojin_mlx/foreign_kqgmm.py:225-239 `gmm` (tile lookup
+ * :23-30 `_TILE`, scatter epilogue `orow`) and the `mx.gather_mm` fallback foreign_linear.py:1389-1407 `_sorted_gmm`. n % 128 == 0. */
+int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t s, int64_t n, int64_t k, int experts, const void* tb,
+                         const void* off, const void* row_map, const void* gs, void* d, int64_t ldd, void* stream);
+
+/* ---- routed experts (MoE). Expert stacks are E matrices of n rows concatenated along rows (kyojin_mlx/foreign_linear.py:504-527).
+ *
+ * kyb_moe_select: router softmax + top-k + renormalise (+ sigmoid of the shared-expert gate logit at column E), one warp per token.
+ *   Replaces kyojin_mlx/foreign_moe.py:77-104 `_SELECT` (launched by `_select` :132-135). logits fp32 [T, ld]; inds u32 [T*K]; scs f32 [T*K]; sgs f32 [T] or NULL.
+ * kyb_moe_plan: counting sort of P slots by expert. Replaces kyojin_mlx/foreign_kqgmm.py:169-196 `_CSORT` / `csort` (order, tb, off) and
+ *   kyojin_mlx/moe_sort.py:18-78 `plan_device` (tok, ids_s, wts_s, inv, cum = off). Any output may be NULL. Order inside an expert's segment is unspecified
+ *   (as in the reference: moe_sort.py:10-12). ids i32 [P]; rank u32 [E] or NULL; mt = rows per tile for tb.
+ * kyb_gather_rows: out[r] = x[src[r] / div] (optionally with a column permutation). Replaces foreign_kqgmm.py:242-268 `_GATHER_ORD` / `gather_perm`.
+ * kyb_silu_mul: h = fp16(silu(a) * b) in fp32, optional clamp `limit` (> 0) and output column permutation. Replaces foreign_kqgmm.py:249-290 `_SILU_PERM` /
+ *   `silu_perm`, foreign_moe.py:106-110 `_SILU`, foreign_linear.py:1275-1319 `glu_rows`.
+ * kyb_moe_combine: o[t] = sum_k y[t K + k] * scs[t K + k] (+ sgs[t] * shared[t]); fp16 saturated or fp32. Replaces foreign_moe.py:112-119 `_COMBINE`.
+ * kyb_moe_groups + kyb_gemv_group_t16: gathered GEMV over routed slots with expert election: slot s = expert eids[s] applied to row xrows[s] (or s / xdiv)
+ *   of x; slots of one expert are served 8 at a time so its bytes are read once per 8 slots. Replace kyojin_mlx/foreign_linear.py:1068-1095 `DevPack.gather`
+ *   (kernels foreign_metal.py:115-202 / :1004-1099 with gather=True, :1487-1557 `gemv_g2_source`, fp4tile.py:166-256) and kyojin_mlx/moe_union.py:27-129.
+ *   g_expert u32 [S], g_slots u32 [8 S], ngroups u32 [1] are scratch written by kyb_moe_groups. gs: per-expert fp32 output scale or NULL. */
+int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream);
+int kyb_moe_plan(const void* ids, const void* wts, const void* rank, int E, int64_t P, int topk, int mt, void* order, void* inv, void* tok, void* ids_s,
+                 void* wts_s, void* off, void* tb, void* stream);
+int kyb_gather_rows(const void* x, int64_t ldx, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo, void* stream);
+int kyb_silu_mul(const void* a, const void* b, int64_t ld, int64_t rows, int64_t n, float limit, const void* perm, void* h, int64_t ldh, void* stream);
+int kyb_moe_combine(const void* y, int64_t ldy, const void* scs, const void* sgs, const void* shared, int64_t lds, int64_t T, int K, int64_t H, int out_dtype,
+                    void* o, int64_t ldo, void* stream);
+int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_slots, void* ngroups, void* stream);
+int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
+                       const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream);
+
 /* launch plan the GEMV would use (diagnostics and launch counting): out8 = {column tiles, stored x rows per tile, warps per CTA,
  * ring stages, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. ksplit > 1 means two launches. */
 int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);

@@ -77,6 +77,14 @@ SIGNATURES = {
     "kyb_gemv_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "kyb_gemv_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _vp]),
     "kyb_gemm_f16_tn": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _vp]),
+    "kyb_gemm_f16_grouped": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "kyb_moe_select": (_int, [_vp, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp]),
+    "kyb_moe_plan": (_int, [_vp, _vp, _vp, _int, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "kyb_gather_rows": (_int, [_vp, _i64, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "kyb_silu_mul": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _i64, _vp]),
+    "kyb_moe_combine": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _int, _i64, _int, _vp, _i64, _vp]),
+    "kyb_moe_groups": (_int, [_vp, _i64, _int, _vp, _vp, _vp, _vp]),
+    "kyb_gemv_group_t16": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _vp, _int, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "kyb_gemv_plan": (_int, [_int, _i64, _i64, _i64, C.POINTER(C.c_int)]),
     "kyb_check_device_status": (_int, [_vp]),
 }

@@ -21,6 +21,13 @@ struct GemmParams {
     int m, n, k;
     float gscale;
     unsigned int* status;
+    // grouped mode (routed experts, rows of A sorted by expert): tile blockIdx.y belongs to the expert e with tb[e] <= tile < tb[e + 1]; its rows start at
+    // off[e] + (tile - tb[e]) * 128 and end at off[e + 1]; B rows of expert e start at e * n. row_map (optional) scatters output rows.
+    const uint32_t* tb;
+    const uint32_t* off;
+    const uint32_t* row_map;
+    const float* gs;           // per-expert output scale or null
+    int experts;
 };
 
 template <int BN, int STAGES>
@@ -31,7 +38,22 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
     const uint32_t bars = smem0 + STAGES * STAGE_BYTES;                            // full[STAGES], empty[STAGES], accum, tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accum_bar = bars + 16 * STAGES, tmem_slot = accum_bar + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * GM_BM;
+    const int n0 = blockIdx.x * BN;
+    int m0 = blockIdx.y * GM_BM, m_end = p.m, b_row0 = n0;
+    float gscale = p.gscale;
+    if (p.tb) {
+        const uint32_t ti = blockIdx.y;
+        if (ti >= p.tb[p.experts]) return;                                          // uniform for the CTA, before any barrier or TMEM allocation
+        int lo = 0, hi = p.experts;                                                 // largest e with tb[e] <= ti (empty experts repeat a value)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (p.tb[mid] <= ti) lo = mid; else hi = mid;
+        }
+        m0 = (int)(p.off[lo] + (ti - p.tb[lo]) * GM_BM);
+        m_end = (int)p.off[lo + 1];
+        b_row0 = lo * p.n + n0;
+        if (p.gs) gscale = p.gs[lo];
+    }
     const int kblocks = p.k / GM_BK;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 
@@ -59,7 +81,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
                 const uint32_t a_dst = smem0 + s * STAGE_BYTES, b_dst = a_dst + A_BYTES;
                 mbar_expect_tx_a(full0 + 8 * s, STAGE_BYTES);
                 tma_load_2d(a_dst, &tma_a, kb * GM_BK, m0, full0 + 8 * s);
-                tma_load_2d(b_dst, &tma_b, kb * GM_BK, n0, full0 + 8 * s);
+                tma_load_2d(b_dst, &tma_b, kb * GM_BK, b_row0, full0 + 8 * s);
                 if (++s == STAGES) s = 0, parity ^= 1u;
             }
         }
@@ -87,27 +109,28 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
         if (!mbar_wait_fast(accum_bar, 0)) failed = true;
         tc_fence_after();
         const int row = m0 + q * 32 + lane;
-        __half* drow = p.d + (size_t)row * p.ldd + n0;
+        const size_t orow = (p.row_map && row < m_end) ? (size_t)p.row_map[row] : (size_t)row;
+        __half* drow = p.d + orow * p.ldd + n0;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
             uint32_t v[32];
             tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
             tmem_ld_wait();
-            if (row < p.m && !failed) {
+            if (row < m_end && !failed) {
                 if (n0 + c + 32 <= p.n && (p.ldd & 7) == 0) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         uint4 o;
-                        __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * p.gscale), sat_half(__uint_as_float(v[j + 1]) * p.gscale));
-                        __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * p.gscale), sat_half(__uint_as_float(v[j + 3]) * p.gscale));
-                        __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * p.gscale), sat_half(__uint_as_float(v[j + 5]) * p.gscale));
-                        __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * p.gscale), sat_half(__uint_as_float(v[j + 7]) * p.gscale));
+                        __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * gscale), sat_half(__uint_as_float(v[j + 1]) * gscale));
+                        __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * gscale), sat_half(__uint_as_float(v[j + 3]) * gscale));
+                        __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * gscale), sat_half(__uint_as_float(v[j + 5]) * gscale));
+                        __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * gscale), sat_half(__uint_as_float(v[j + 7]) * gscale));
                         o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
                         *reinterpret_cast<uint4*>(drow + c + j) = o;
                     }
                 } else {
                     for (int j = 0; j < 32; ++j)
-                        if (n0 + c + j < p.n) drow[c + j] = sat_half(__uint_as_float(v[j]) * p.gscale);
+                        if (n0 + c + j < p.n) drow[c + j] = sat_half(__uint_as_float(v[j]) * gscale);
                 }
             }
         }
@@ -126,7 +149,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
 namespace {
 
 template <int BN, int STAGES>
-int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const kyb::GemmParams& p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const kyb::GemmParams& p, cudaStream_t st, int tiles_y) {
     constexpr size_t smem = (size_t)STAGES * (kyb::GM_BM * kyb::GM_BK * 2 + BN * kyb::GM_BK * 2) + 16 * STAGES + 16 + 1024;
     auto kern = kyb::gemm_f16_tn_kernel<BN, STAGES>;
     static std::mutex mu;
@@ -140,7 +163,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const kyb::GemmPar
             done |= 1u << (dev & 31);
         }
     }
-    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)((p.m + kyb::GM_BM - 1) / kyb::GM_BM));
+    dim3 grid((unsigned)((p.n + BN - 1) / BN), (unsigned)(tiles_y ? tiles_y : (p.m + kyb::GM_BM - 1) / kyb::GM_BM));
     kern<<<grid, kyb::GM_THREADS, smem, st>>>(ta, tb, p);
     return kyb_launch_check("gemm_f16_tn");
 }
@@ -163,6 +186,32 @@ extern "C" int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_
     if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
     kyb::GemmParams p;
     p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale, p.status = status;
+    p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
     cudaStream_t st = (cudaStream_t)stream;
-    return wide ? launch_gemm<256, 4>(ta, tb, p, st) : launch_gemm<128, 6>(ta, tb, p, st);
+    return wide ? launch_gemm<256, 4>(ta, tb, p, st, 0) : launch_gemm<128, 6>(ta, tb, p, st, 0);
+}
+
+// Grouped form for routed experts: a fp16 [s, k] rows sorted by expert (segment e = rows [off[e], off[e + 1])), b fp16 [experts * n, k] (expert stack),
+// tb / off from kyb_moe_plan with mt = 128, row_map (optional, u32 [s]) = output row of each sorted row, gs (optional) per-expert output scale.
+// d [*, n]. The grid is sized for the worst case (s / 128 + experts tiles); tiles past tb[experts] exit at once.
+extern "C" int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t s, int64_t n, int64_t k, int experts, const void* tb_, const void* off,
+                                    const void* row_map, const void* gs, void* d, int64_t ldd, void* stream) {
+    KYB_REQUIRE(a && b && d && tb_ && off, "null pointer");
+    KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 64 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 64", (long long)s, (long long)n,
+                (long long)k, experts);
+    KYB_REQUIRE(n % 128 == 0, "grouped GEMM needs n %% 128 == 0 (an output tile must not straddle two experts), got n=%lld", (long long)n);
+    KYB_REQUIRE(lda >= k && ldb >= k && lda % 8 == 0 && ldb % 8 == 0 && ldd >= n, "leading dimensions: lda, ldb >= k and multiples of 8, ldd >= n");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0, "a and b must be 16-byte aligned");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    const bool wide = n % 256 == 0;
+    CUtensorMap ta, tb;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)s, (uint64_t)k, (uint64_t)lda * 2, kyb::GM_BM, kyb::GM_BK)) return rc;
+    if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)experts * (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
+    kyb::GemmParams p;
+    p.d = (__half*)d, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.gscale = 1.0f, p.status = status;
+    p.tb = (const uint32_t*)tb_, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
+    const int max_tiles = (int)((s + kyb::GM_BM - 1) / kyb::GM_BM) + experts;
+    cudaStream_t st = (cudaStream_t)stream;
+    return wide ? launch_gemm<256, 4>(ta, tb, p, st, max_tiles) : launch_gemm<128, 6>(ta, tb, p, st, max_tiles);
 }

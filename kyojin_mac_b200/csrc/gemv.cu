@@ -504,6 +504,192 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
     if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
 }
 
+// ------------------------------------------------------------------------------------------------ routed experts: grouped GEMV with expert election
+// Slots routed to the same expert are served together: group = (expert, up to 8 of its slots), so an expert's bytes are read once per 8 slots
+// (the reference's `moe_union` election, kyojin_mlx/moe_union.py:27-63, done for 8 rows because the MMA has 8 activation columns anyway).
+struct GroupParams {
+    const uint8_t* t16;            // expert stack: E matrices of n rows
+    const __half* x;               // [*, k] source rows
+    const uint32_t* xrows;         // [S] source row of each slot, or null (slot s reads row s / xdiv)
+    const uint32_t* g_expert;      // [G]
+    const uint32_t* g_slots;       // [G * 8] slot or 0xFFFFFFFF
+    const uint32_t* ngroups;       // device scalar
+    const float* gs;               // per-expert output scale or null
+    __half* y;                     // [S, ldy]
+    unsigned int* status;
+    int64_t ldx, ldy;
+    int n, nb, kc, xdiv, rc, warps;   // rows per expert, k-blocks, canonical chunk, slot -> row divisor, row chunks per group, warps per CTA
+};
+
+// Single CTA: slots -> groups. counts per expert, groups per expert = ceil(count / 8), slot p of rank r inside its expert -> group start + r / 8.
+__global__ void moe_groups_kernel(const uint32_t* __restrict__ eids, int S, int E, uint32_t* __restrict__ g_expert, uint32_t* __restrict__ g_slots, uint32_t* __restrict__ ngroups) {
+    extern __shared__ uint32_t gsm[];
+    uint32_t* counts = gsm;          // [E]
+    uint32_t* gstart = gsm + E;      // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0u;
+    for (int i = threadIdx.x; i < S * 8; i += blockDim.x) g_slots[i] = 0xFFFFFFFFu;
+    __syncthreads();
+    for (int p = threadIdx.x; p < S; p += blockDim.x)
+        if (eids[p] < (uint32_t)E) atomicAdd(&counts[eids[p]], 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t g = 0;
+        for (int e = 0; e < E; ++e) {
+            gstart[e] = g;
+            g += (counts[e] + 7u) >> 3;
+        }
+        gstart[E] = g;
+        *ngroups = g;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (uint32_t g = gstart[e]; g < gstart[e + 1]; ++g) g_expert[g] = (uint32_t)e;
+        counts[e] = 0u;                                   // reused as the rank cursor
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < S; p += blockDim.x) {
+        const uint32_t e = eids[p];
+        if (e >= (uint32_t)E) continue;
+        const uint32_t r = atomicAdd(&counts[e], 1u);
+        g_slots[(size_t)(gstart[e] + (r >> 3)) * 8 + (r & 7u)] = (uint32_t)p;
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int TB = kyb_tile_bytes(FMT), NT = 1, MST = 8, CS = NT * MST * 32, STAGES = GEMV_STAGES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    uint8_t* xfrag = smem;
+    uint8_t* xaux = xfrag + (size_t)p.nb * 16 * CS;
+    constexpr size_t warp_bytes = ((size_t)STAGES * TB + SCL_BYTES + 8 * (size_t)STAGES + 8 + 15) & ~(size_t)15;
+    uint8_t* wbase = xaux + (size_t)p.nb * xaux_bytes_per_block<FMT>(NT) + (size_t)warp * warp_bytes;
+    const uint32_t ring_a = smem_u32(wbase), scl_a = ring_a + STAGES * TB, bar_a = scl_a + SCL_BYTES;
+    __shared__ uint32_t s_slots[8];
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init_a_local(bar_a + 8 * s);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const int ntiles = p.n >> 4;                                   // row tiles per expert (n % 16 == 0)
+    const int tpc = (ntiles + p.rc - 1) / p.rc;                    // row tiles per chunk
+    const uint32_t ngroups = *p.ngroups;
+    const uint32_t xb0 = smem_u32(xfrag) + g * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
+    uint32_t parity = 0;
+    int stage = 0;
+    bool failed = false;
+    for (uint32_t item = blockIdx.x; item < ngroups * (uint32_t)p.rc; item += gridDim.x) {
+        const uint32_t grp = item / (uint32_t)p.rc, rc = item % (uint32_t)p.rc;
+        const uint32_t e = p.g_expert[grp];
+        const int rt0 = (int)rc * tpc + warp, rt_end = min(ntiles, ((int)rc + 1) * tpc);
+        const int nrt = rt0 < rt_end ? (rt_end - rt0 + p.warps - 1) / p.warps : 0;      // row tiles of this warp: rt0, rt0 + warps, ...
+        const int total = nrt * p.nb;
+        // ---- producer (lane 0): this item's tiles of this warp
+        int p_left = total, p_blk = p.nb, p_stage = stage;
+        const uint8_t* p_src = p.t16 + (((size_t)e * ntiles + rt0) * (size_t)p.nb) * TB;
+        const size_t p_jump = ((size_t)p.warps - 1) * (size_t)p.nb * TB;
+        auto issue = [&]() {
+            const uint32_t bar = bar_a + 8 * p_stage, dst = ring_a + p_stage * TB;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)TB) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(p_src), "r"((uint32_t)TB), "r"(bar) : "memory");
+            --p_left;
+            p_src += TB;
+            if (--p_blk == 0) p_blk = p.nb, p_src += p_jump;
+            p_stage ^= 1;
+        };
+        if (lane == 0)
+            for (int s = 0; s < min(STAGES, total); ++s) issue();
+        if (threadIdx.x < 8) s_slots[threadIdx.x] = p.g_slots[(size_t)grp * 8 + threadIdx.x];
+        __syncthreads();
+        // ---- stage the group's activation rows (gathered) as B fragments, as in gemv_t16_kernel
+        {
+            const int items = p.nb * 8 * MST;
+            for (int it = threadIdx.x; it < items; it += blockDim.x) {
+                const int row = it % MST, c2 = it / MST;
+                const uint32_t slot = s_slots[row];
+                uint4 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v[q] = make_uint4(0, 0, 0, 0);
+                if (slot != 0xFFFFFFFFu) {
+                    const size_t xr = p.xrows ? p.xrows[slot] : slot / (uint32_t)p.xdiv;
+                    const uint4* xp = reinterpret_cast<const uint4*>(p.x + xr * p.ldx + (size_t)c2 * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) v[q] = __ldg(xp + q);
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const uint4 a = v[2 * c], b = v[2 * c + 1];
+                    uint4 oa, ob;
+                    oa.x = prmt(a.x, a.y, 0x5410u), oa.y = prmt(a.x, a.y, 0x7632u), oa.z = prmt(a.z, a.w, 0x5410u), oa.w = prmt(a.z, a.w, 0x7632u);
+                    ob.x = prmt(b.x, b.y, 0x5410u), ob.y = prmt(b.x, b.y, 0x7632u), ob.z = prmt(b.z, b.w, 0x5410u), ob.w = prmt(b.z, b.w, 0x7632u);
+                    uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)(2 * c2 + c) * CS + row * 32);
+                    dst[0] = oa, dst[1] = ob;
+                }
+                if constexpr (FMT == KYB_FMT_Q4_K) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __half2* hp = reinterpret_cast<const __half2*>(&v[q]);
+#pragma unroll
+                        for (int e2 = 0; e2 < 4; ++e2) {
+                            const float2 f = __half22float2(hp[e2]);
+                            sum += f.x + f.y;
+                        }
+                    }
+                    const __half hi = __float2half_rn(sum);
+                    const __half lo = __float2half_rn(sum - __half2float(hi));
+                    const int blk = c2 >> 3, j = c2 & 7;
+                    __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * 256 * NT);
+                    const int idx = (row * 4 + (j >> 1)) * 2 + (j & 1);
+                    xa[idx] = hi;
+                    xa[64 + idx] = lo;
+                }
+            }
+        }
+        __syncthreads();
+        // ---- this warp's row tiles
+        Acc<NT> acc, tot;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc.v[0][q] = 0.f, tot.v[0][q] = 0.f;
+        const float gsc = p.gs ? p.gs[e] : 1.0f;
+        uint32_t xb = xb0, xa = xa0;
+        int blk = 0, rt = rt0, cleft = min(p.kc, p.nb);
+        for (int i = 0; i < total; ++i) {
+            const uint32_t tile = ring_a + stage * TB;
+            if (!mbar_wait_fast(bar_a + 8 * stage, parity)) failed = true;
+            TileRegs<FMT> tr;
+            load_tile<FMT>(tile, lane, tr);
+            prep_scales<FMT>(tile, scl_a, lane);
+            __syncwarp();
+            if (lane == 0 && p_left > 0) issue();
+            consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
+            __syncwarp();
+            xb += 16 * CS, xa += 256 * NT;
+            ++blk;
+            if (--cleft == 0) {
+                const bool last = blk == p.nb;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    tot.v[0][q] += acc.v[0][q];
+                    acc.v[0][q] = 0.f;
+                    if (last) {
+                        const uint32_t slot = s_slots[2 * t + (q & 1)];
+                        const int nrow = rt * 16 + g + 8 * (q >> 1);
+                        if (slot != 0xFFFFFFFFu) p.y[(size_t)slot * p.ldy + nrow] = sat_half(tot.v[0][q] * gsc);
+                        tot.v[0][q] = 0.f;
+                    }
+                }
+                cleft = min(p.kc, p.nb - blk);
+                if (last) blk = 0, rt += p.warps, xb = xb0, xa = xa0, cleft = min(p.kc, p.nb);
+            }
+            stage ^= 1;
+            if (stage == 0) parity ^= 1u;
+        }
+        __syncthreads();                                          // the staged rows are replaced by the next item
+    }
+    if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
+}
+
 __global__ void gemv_finalize_kernel(const float* __restrict__ partial, int ksplit, int m, int n, int npad, float gscale, __half* __restrict__ y, int64_t ldy) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)m * n) return;
@@ -705,5 +891,51 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
         kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>((const float*)workspace, pl.nchunks, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
         return kyb_launch_check("gemv_finalize");
     }
+    return KYB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ routed experts (host side)
+extern "C" int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_slots, void* ngroups, void* stream) {
+    KYB_REQUIRE(eids && g_expert && g_slots && ngroups, "null pointer");
+    KYB_REQUIRE(S > 0 && S <= (1 << 20) && E > 0 && E <= 8192, "S=%lld E=%d out of range", (long long)S, E);
+    kyb::moe_groups_kernel<<<1, 1024, (size_t)(2 * E + 1) * sizeof(uint32_t), (cudaStream_t)stream>>>((const uint32_t*)eids, (int)S, E, (uint32_t*)g_expert, (uint32_t*)g_slots,
+                                                                                                    (uint32_t*)ngroups);
+    return kyb_launch_check("moe_groups");
+}
+
+extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
+                                  const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(n > 0 && n % 16 == 0 && k > 0 && k % 256 == 0 && E > 0, "n=%lld k=%lld: expert matrices need n %% 16 == 0 and k %% 256 == 0", (long long)n, (long long)k);
+    KYB_REQUIRE(t16 && x && y && g_expert && g_slots && ngroups, "null pointer");
+    KYB_REQUIRE(S > 0 && xdiv > 0 && ldx >= k && ldx % 8 == 0 && ldy >= n, "S=%lld xdiv=%d ldx=%lld ldy=%lld", (long long)S, xdiv, (long long)ldx, (long long)ldy);
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    const int nb = (int)(k / 256), ntiles = (int)(n / 16), sms = device_sms();
+    int warps = 0;
+    size_t smem = 0;
+    for (int w = 24; w >= 4; w -= 4) {
+        smem = plan_smem(fmt, 1, 8, nb, w, kyb::GEMV_STAGES);
+        if (smem <= 227 * 1024 - 256) {
+            warps = w;
+            break;
+        }
+    }
+    KYB_REQUIRE(warps > 0, "k=%lld: the staged activations of a group do not fit in shared memory", (long long)k);
+    warps = std::min(warps, std::max(4, (ntiles + 3) / 4 * 4));
+    const int64_t exp_groups = std::max<int64_t>(1, std::min<int64_t>(S, E));
+    int rc = (int)std::min<int64_t>(std::max<int64_t>(1, (4 * sms + exp_groups - 1) / exp_groups), std::max(1, ntiles / warps));
+    kyb::GroupParams p;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.xrows = (const uint32_t*)xrows, p.g_expert = (const uint32_t*)g_expert, p.g_slots = (const uint32_t*)g_slots;
+    p.ngroups = (const uint32_t*)ngroups, p.gs = (const float*)gs, p.y = (__half*)y, p.status = status, p.ldx = ldx, p.ldy = ldy;
+    p.n = (int)n, p.nb = nb, p.kc = canonical_chunk(ntiles, nb), p.xdiv = xdiv, p.rc = rc, p.warps = warps;
+    const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q4_K>
+                       : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q6_K>
+                       : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q3_K>
+                                             : (const void*)kyb::gemv_group_kernel<KYB_FMT_NVFP4>;
+    if (int r = ensure_smem_attr(kern)) return r;
+    void* args[] = {(void*)&p};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)sms), dim3((unsigned)warps * 32), args, smem + 64, (cudaStream_t)stream));
     return KYB_OK;
 }

@@ -1,0 +1,206 @@
+// Routed-expert plumbing around the quantized products: router softmax / top-k, slot sort by expert (counting sort), row gather, gated
+// activation, weighted combine. These are launch-bound elementwise / index kernels; the arithmetic follows the reference's Metal kernels
+// (kyojin_mlx/foreign_moe.py:77-119 _SELECT / _SILU / _COMBINE, foreign_kqgmm.py:169-188 _CSORT, :242-261 _GATHER_ORD / _SILU_PERM,
+// moe_sort.py:18-45) in float32.
+#include "kyb_common.cuh"
+
+namespace kyb {
+
+// One warp per token. logits fp32 [T, ld]: E expert logits, then (has_shared) the shared-expert gate logit at column E.
+// softmax in fp32 (exp(l - max) * (1 / sum)), k rounds of arg-max by value, lowest index on ties, weights top / sum(top) when norm.
+__global__ void moe_select_kernel(const float* __restrict__ lg, int64_t ld, int T, int E, int K, int norm, int has_shared, uint32_t* __restrict__ inds,
+                                  float* __restrict__ scs, float* __restrict__ sgs) {
+    extern __shared__ float sp[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int t = blockIdx.x * wpb + warp;
+    if (t >= T) return;
+    float* p = sp + (size_t)warp * E;
+    const float* L = lg + (size_t)t * ld;
+    float m = -INFINITY;
+    for (int i = lane; i < E; i += 32) {
+        const float v = L[i];
+        p[i] = v;
+        m = fmaxf(m, v);
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) {
+        const float e = expf(p[i] - m);
+        p[i] = e;
+        sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    for (int i = lane; i < E; i += 32) p[i] *= inv;
+    __syncwarp();
+    float ts = 0.f, mine = 0.f;                      // lane k keeps the k-th weight (K <= 32)
+    for (int k = 0; k < K; ++k) {
+        float best = -1.0f;
+        uint32_t bi = 0xFFFFFFFFu;
+        for (int i = lane; i < E; i += 32)
+            if (p[i] > best) best = p[i], bi = (uint32_t)i;
+        float gv = best;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) gv = fmaxf(gv, __shfl_xor_sync(0xffffffffu, gv, o));
+        uint32_t gi = best == gv ? bi : 0xFFFFFFFFu;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) gi = min(gi, __shfl_xor_sync(0xffffffffu, gi, o));
+        if (gi < (uint32_t)E && (gi & 31u) == (uint32_t)lane) p[gi] = -1.0f;
+        __syncwarp();
+        ts += gv;
+        if (lane == k) mine = gv;
+        if (lane == 0) inds[(size_t)t * K + k] = gi;
+    }
+    if (lane < K) scs[(size_t)t * K + lane] = norm ? mine / ts : mine;
+    if (lane == 0 && sgs) sgs[t] = has_shared ? 1.0f / (1.0f + expf(-L[E])) : 0.0f;
+}
+
+// Counting sort of P slots by expert in ONE CTA (histogram, scan, scatter with shared-memory cursors). rank (optional) maps expert -> position of
+// its segment. Outputs (any may be null): order[pos] = slot, inv[slot] = pos, tok[pos] = slot / topk, ids_s[pos] = expert, wts_s[pos] = wts[slot],
+// off[E + 1] = first row of each segment, tb[E + 1] = first tile of each segment for tiles of mt rows.
+__global__ void moe_plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, const uint32_t* __restrict__ rank, int E, int P, int topk, int mt,
+                                uint32_t* __restrict__ order, uint32_t* __restrict__ inv, uint32_t* __restrict__ tok, int32_t* __restrict__ ids_s,
+                                float* __restrict__ wts_s, uint32_t* __restrict__ off, uint32_t* __restrict__ tb) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* counts = sm;             // [E]
+    uint32_t* cursor = sm + E;         // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0u;
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[rank ? rank[e] : (uint32_t)e], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t s = 0, t = 0;
+        for (int e = 0; e < E; ++e) {
+            const uint32_t c = counts[e];
+            cursor[e] = s;
+            if (off) off[e] = s;
+            if (tb) tb[e] = t;
+            s += c;
+            t += (c + (uint32_t)mt - 1u) / (uint32_t)mt;
+        }
+        cursor[E] = s;
+        if (off) off[E] = s;
+        if (tb) tb[E] = t;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+        const int e0 = ids[p];
+        if (e0 < 0 || e0 >= E) continue;
+        const uint32_t pos = atomicAdd(&cursor[rank ? rank[e0] : (uint32_t)e0], 1u);
+        if (order) order[pos] = (uint32_t)p;
+        if (inv) inv[p] = pos;
+        if (tok) tok[pos] = (uint32_t)(p / topk);
+        if (ids_s) ids_s[pos] = e0;
+        if (wts_s && wts) wts_s[pos] = wts[p];
+    }
+}
+
+// out[r, :] = x[src[r] / div, perm ? perm[c] : c]   (fp16 rows of k columns; 8 columns per thread)
+__global__ void gather_rows_kernel(const __half* __restrict__ x, int64_t ldx, const uint32_t* __restrict__ src, int div, const uint32_t* __restrict__ perm, int R, int k,
+                                   __half* __restrict__ out, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int kv = k >> 3;
+    if (i >= (int64_t)R * kv) return;
+    const int r = (int)(i / kv), c = (int)(i % kv) * 8;
+    const __half* xr = x + (size_t)(src[r] / (uint32_t)div) * ldx;
+    if (!perm) {
+        *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = *reinterpret_cast<const uint4*>(xr + c);
+    } else {
+        __half v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = xr[perm[c + j]];
+        *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = *reinterpret_cast<uint4*>(v);
+    }
+}
+
+// h = fp16(silu(a) * b) in fp32, silu(a) = a * (1 / (1 + exp(-a))); limit > 0: a = min(a, limit), b = clamp(b, -limit, limit)
+// (kyojin_mlx/foreign_linear.py:1353-1361 `_glu`, foreign_metal.py:1107-1113). Optional column permutation of the output.
+__global__ void silu_mul_kernel(const __half* __restrict__ a, const __half* __restrict__ b, int64_t ld, int64_t total, int n, float limit, const uint32_t* __restrict__ perm,
+                                __half* __restrict__ h, int64_t ldh) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / n;
+    const int c = (int)(i % n), cs = perm ? (int)perm[c] : c;
+    float av = __half2float(a[r * ld + cs]), bv = __half2float(b[r * ld + cs]);
+    if (limit > 0.f) av = fminf(av, limit), bv = fminf(fmaxf(bv, -limit), limit);
+    h[r * ldh + c] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
+}
+
+// o[t, c] = sum_k f32(y[t K + k, c]) * scs[t K + k] (+ sgs[t] * shared[t, c]); fp16 saturated or fp32 output (foreign_moe.py:112-119)
+template <typename OUT>
+__global__ void moe_combine_kernel(const __half* __restrict__ y, int64_t ldy, const float* __restrict__ scs, const float* __restrict__ sgs, const __half* __restrict__ shared,
+                                   int64_t lds, int T, int K, int H, OUT* __restrict__ o, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)T * H) return;
+    const int t = (int)(i / H), c = (int)(i % H);
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) acc += __half2float(y[((size_t)t * K + k) * ldy + c]) * scs[(size_t)t * K + k];
+    if (shared) acc += sgs[t] * __half2float(shared[(size_t)t * lds + c]);
+    if constexpr (sizeof(OUT) == 2) o[(size_t)t * ldo + c] = sat_half(acc);
+    else o[(size_t)t * ldo + c] = acc;
+}
+
+}  // namespace kyb
+
+extern "C" int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream) {
+    KYB_REQUIRE(logits && inds && scs, "null pointer");
+    KYB_REQUIRE(T > 0 && E > 0 && E <= 4096 && K > 0 && K <= 32 && K <= E, "T=%lld E=%d K=%d: need 1 <= K <= min(32, E), E <= 4096", (long long)T, E, K);
+    KYB_REQUIRE(ld >= E + (has_shared ? 1 : 0), "ld=%lld is smaller than the row of logits", (long long)ld);
+    KYB_REQUIRE(!has_shared || sgs, "has_shared needs the sgs output");
+    const int wpb = E <= 1024 ? 4 : 1;
+    const size_t smem = (size_t)wpb * E * sizeof(float);
+    kyb::moe_select_kernel<<<(unsigned)((T + wpb - 1) / wpb), wpb * 32, smem, (cudaStream_t)stream>>>((const float*)logits, ld, (int)T, E, K, norm, has_shared, (uint32_t*)inds,
+                                                                                                   (float*)scs, (float*)sgs);
+    return kyb_launch_check("moe_select");
+}
+
+extern "C" int kyb_moe_plan(const void* ids, const void* wts, const void* rank, int E, int64_t P, int topk, int mt, void* order, void* inv, void* tok, void* ids_s,
+                            void* wts_s, void* off, void* tb, void* stream) {
+    KYB_REQUIRE(ids, "null pointer");
+    KYB_REQUIRE(E > 0 && E <= 8192 && P > 0 && P < (1ll << 31) && topk > 0 && mt > 0, "E=%d P=%lld topk=%d mt=%d out of range", E, (long long)P, topk, mt);
+    const size_t smem = (size_t)(2 * E + 1) * sizeof(uint32_t);
+    kyb::moe_plan_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>((const int32_t*)ids, (const float*)wts, (const uint32_t*)rank, E, (int)P, topk, mt, (uint32_t*)order,
+                                                                 (uint32_t*)inv, (uint32_t*)tok, (int32_t*)ids_s, (float*)wts_s, (uint32_t*)off, (uint32_t*)tb);
+    return kyb_launch_check("moe_plan");
+}
+
+extern "C" int kyb_gather_rows(const void* x, int64_t ldx, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo, void* stream) {
+    KYB_REQUIRE(x && src && out, "null pointer");
+    KYB_REQUIRE(R > 0 && k > 0 && k % 8 == 0 && div > 0 && ldx % 8 == 0 && ldo % 8 == 0, "R=%lld k=%lld: k, ldx, ldo must be multiples of 8", (long long)R, (long long)k);
+    KYB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "x and out must be 16-byte aligned");
+    const int64_t total = R * (k / 8);
+    kyb::gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, ldx, (const uint32_t*)src, div, (const uint32_t*)perm, (int)R, (int)k,
+                                                                                              (__half*)out, ldo);
+    return kyb_launch_check("gather_rows");
+}
+
+extern "C" int kyb_silu_mul(const void* a, const void* b, int64_t ld, int64_t rows, int64_t n, float limit, const void* perm, void* h, int64_t ldh, void* stream) {
+    KYB_REQUIRE(a && b && h, "null pointer");
+    KYB_REQUIRE(rows > 0 && n > 0 && ld >= n && ldh >= n, "rows=%lld n=%lld ld=%lld ldh=%lld", (long long)rows, (long long)n, (long long)ld, (long long)ldh);
+    const int64_t total = rows * n;
+    kyb::silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)a, (const __half*)b, ld, total, (int)n, limit, (const uint32_t*)perm,
+                                                                                           (__half*)h, ldh);
+    return kyb_launch_check("silu_mul");
+}
+
+extern "C" int kyb_moe_combine(const void* y, int64_t ldy, const void* scs, const void* sgs, const void* shared, int64_t lds, int64_t T, int K, int64_t H, int out_dtype,
+                               void* o, int64_t ldo, void* stream) {
+    KYB_REQUIRE(y && scs && o, "null pointer");
+    KYB_REQUIRE(T > 0 && K > 0 && H > 0 && ldy >= H && ldo >= H, "T=%lld K=%d H=%lld", (long long)T, K, (long long)H);
+    KYB_REQUIRE(!shared || sgs, "a shared-expert output needs its gate values (sgs)");
+    KYB_REQUIRE(out_dtype == KYB_DT_F32 || out_dtype == KYB_DT_F16, "out_dtype %d", out_dtype);
+    const int64_t total = T * H;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == KYB_DT_F16)
+        kyb::moe_combine_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
+                                                                                 (int)H, (__half*)o, ldo);
+    else
+        kyb::moe_combine_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
+                                                                                (int)H, (float*)o, ldo);
+    return kyb_launch_check("moe_combine");
+}

@@ -122,3 +122,99 @@ def to_device_t16(fmt: str, raw_np: np.ndarray, n: int, k: int, device="cuda") -
     """Host GGUF rows (numpy uint8 [n, row_bytes]) -> device T16, repacked on the device."""
     raw = torch.from_numpy(np.ascontiguousarray(raw_np)).to(device)
     return raw_to_t16(fmt, raw, n, k)
+
+
+# ------------------------------------------------------------------------------------------------ routed experts
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def moe_select(logits: torch.Tensor, E: int, K: int, norm: bool = True, has_shared: bool = False):
+    """logits fp32 [T, >= E (+1)] -> (inds uint32-as-int32 [T*K], scs f32 [T*K], sgs f32 [T] or None)."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("router logits must be contiguous float32 [T, E(+1)]")
+    T = logits.shape[0]
+    inds = torch.empty(T * K, dtype=torch.int32, device=logits.device)
+    scs = torch.empty(T * K, dtype=torch.float32, device=logits.device)
+    sgs = torch.empty(T, dtype=torch.float32, device=logits.device) if has_shared else None
+    _lib.check(_lib.lib().kyb_moe_select(logits.data_ptr(), logits.stride(0), T, E, K, int(norm), int(has_shared), inds.data_ptr(), scs.data_ptr(), _p(sgs), _stream()))
+    return inds, scs, sgs
+
+
+def moe_plan(ids: torch.Tensor, E: int, topk: int, mt: int = 128, wts: torch.Tensor | None = None, rank: torch.Tensor | None = None):
+    """Counting sort of the slots by expert. Returns dict(order, inv, tok, ids_s, wts_s, off, tb)."""
+    _need_cuda(ids)
+    ids = ids.reshape(-1).to(torch.int32).contiguous()
+    P, dev = ids.numel(), ids.device
+    mk = lambda n, dt: torch.empty(n, dtype=dt, device=dev)
+    out = dict(order=mk(P, torch.int32), inv=mk(P, torch.int32), tok=mk(P, torch.int32), ids_s=mk(P, torch.int32),
+               wts_s=mk(P, torch.float32) if wts is not None else None, off=mk(E + 1, torch.int32), tb=mk(E + 1, torch.int32))
+    w = None if wts is None else wts.reshape(-1).to(torch.float32).contiguous()
+    r = None if rank is None else rank.to(torch.int32).contiguous()
+    _lib.check(_lib.lib().kyb_moe_plan(ids.data_ptr(), _p(w), _p(r), E, P, topk, mt, out["order"].data_ptr(), out["inv"].data_ptr(), out["tok"].data_ptr(),
+                                       out["ids_s"].data_ptr(), _p(out["wts_s"]), out["off"].data_ptr(), out["tb"].data_ptr(), _stream()))
+    return out
+
+
+def gather_rows(x: torch.Tensor, src: torch.Tensor, div: int = 1, perm: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = x[src[r] // div] (fp16 rows), optional column permutation."""
+    _need_cuda(x, src)
+    if x.dtype != torch.float16 or x.stride(1) != 1:
+        raise ValueError("gather_rows takes float16 rows")
+    R, k = src.numel(), x.shape[1]
+    out = torch.empty((R, k), dtype=torch.float16, device=x.device)
+    _lib.check(_lib.lib().kyb_gather_rows(x.data_ptr(), x.stride(0), src.data_ptr(), div, _p(perm), R, k, out.data_ptr(), k, _stream()))
+    return out
+
+
+def silu_mul(a: torch.Tensor, b: torch.Tensor, limit: float | None = None, perm: torch.Tensor | None = None) -> torch.Tensor:
+    """fp16(silu(a) * b) computed in fp32 (optional clamp as the reference's swiglu_limit)."""
+    _need_cuda(a, b)
+    if a.shape != b.shape or a.dtype != torch.float16 or b.dtype != torch.float16 or a.stride() != b.stride() or a.stride(1) != 1:
+        raise ValueError("silu_mul takes two float16 [rows, n] tensors of the same layout")
+    rows, n = a.shape
+    h = torch.empty((rows, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_silu_mul(a.data_ptr(), b.data_ptr(), a.stride(0), rows, n, float(limit or 0.0), _p(perm), h.data_ptr(), n, _stream()))
+    return h
+
+
+def moe_combine(y: torch.Tensor, scs: torch.Tensor, K: int, sgs: torch.Tensor | None = None, shared: torch.Tensor | None = None, dtype=torch.float16) -> torch.Tensor:
+    """y fp16 [T*K, H] (slot order), scs f32 [T*K] -> [T, H] weighted sum (+ gated shared expert)."""
+    _need_cuda(y, scs)
+    S, H = y.shape
+    T = S // K
+    o = torch.empty((T, H), dtype=dtype, device=y.device)
+    _lib.check(_lib.lib().kyb_moe_combine(y.data_ptr(), y.stride(0), scs.data_ptr(), _p(sgs), _p(shared), 0 if shared is None else shared.stride(0), T, K, H,
+                                          0 if dtype == torch.float32 else 1, o.data_ptr(), H, _stream()))
+    return o
+
+
+def gemv_group(fmt, t16: torch.Tensor, n: int, k: int, E: int, x: torch.Tensor, eids: torch.Tensor, xrows: torch.Tensor | None = None, xdiv: int = 1,
+               gs: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y fp16 [S, n]: slot s = expert eids[s] applied to row xrows[s] (or s // xdiv) of x fp16 [*, k]; one weight read per expert and 8 slots."""
+    _need_cuda(t16, x, eids)
+    if x.dtype != torch.float16 or x.stride(1) != 1 or x.shape[1] != k:
+        raise ValueError(f"x must be float16 [rows, {k}]")
+    S = eids.numel()
+    eids = eids.reshape(-1).to(torch.int32).contiguous()
+    y = out if out is not None else torch.empty((S, n), dtype=torch.float16, device=x.device)
+    scratch = torch.empty(S * 9 + 1, dtype=torch.int32, device=x.device)
+    g_expert, g_slots, ngroups = scratch[:S], scratch[S:9 * S], scratch[9 * S:]
+    L = _lib.lib()
+    _lib.check(L.kyb_moe_groups(eids.data_ptr(), S, E, g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
+    xr = None if xrows is None else xrows.reshape(-1).to(torch.int32).contiguous()
+    _lib.check(L.kyb_gemv_group_t16(_fmt(fmt), t16.data_ptr(), n, k, E, x.data_ptr(), x.stride(0), _p(xr), xdiv, S, _p(gs), y.data_ptr(), y.stride(0),
+                                    g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
+    return y
+
+
+def gemm_f16_grouped(a: torch.Tensor, b: torch.Tensor, n: int, E: int, tb: torch.Tensor, off: torch.Tensor, row_map: torch.Tensor | None = None,
+                     gs: torch.Tensor | None = None, out: torch.Tensor | None = None, out_rows: int | None = None) -> torch.Tensor:
+    """d [rows, n]: sorted rows a fp16 [s, k] of expert segments (off) times the fp16 expert stack b [E*n, k]; tile list tb (tiles of 128 rows)."""
+    _need_cuda(a, b, tb, off)
+    s, k = a.shape
+    d = out if out is not None else torch.empty((out_rows or s, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_gemm_f16_grouped(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), s, n, k, E, tb.data_ptr(), off.data_ptr(), _p(row_map), _p(gs),
+                                               d.data_ptr(), d.stride(0), _stream()))
+    return d
