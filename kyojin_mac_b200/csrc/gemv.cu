@@ -790,7 +790,7 @@ int canonical_chunk(int ntiles, int nb) {
 GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     const int sms = device_sms();
     const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
-    const size_t smem_cap = 227 * 1024;
+    const size_t smem_cap = 226 * 1024;
     const int fw = env_int("KYB_GEMV_WARPS", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
     const int kc = canonical_chunk(ntiles, nb), nchunks = (nb + kc - 1) / kc;
     const int v = variant_of(m), nt = VAR_NT[v], mst = VAR_MST[v];
@@ -836,7 +836,7 @@ int ensure_smem_attr(const void* kern) {
     std::lock_guard<std::mutex> lk(mu);
     unsigned& mask = done[kern];
     if (!(mask & (1u << (dev & 31)))) {
-        KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024)));
+        KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(227 * 1024 - 1024)));   // leaves room for the few static words
         mask |= 1u << (dev & 31);
     }
     return KYB_OK;
@@ -917,7 +917,7 @@ extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k
     size_t smem = 0;
     for (int w = 24; w >= 4; w -= 4) {
         smem = plan_smem(fmt, 1, 8, nb, w, kyb::GEMV_STAGES);
-        if (smem <= 227 * 1024 - 256) {
+        if (smem <= 226 * 1024 - 256) {
             warps = w;
             break;
         }

@@ -1,0 +1,63 @@
+"""Expert-grouped GEMM on routed slots (prefill), torch mirror of kyojin_mlx/foreign_kqgmm.py: `csort` :191-196, `plan` :210-216, `gmm` :225-239,
+`gather_perm` :264-268, `silu_perm` :283-290, `mlp` :293-314, `dense` :343-354. Slots are sorted by expert on the device (no host readback), tiles of MT
+rows of ONE expert run on tcgen05 (kyb_gemm_f16_grouped), the down projection scatters its rows back to slot order.
+The weights reach the tensor cores as fp16 tiles of the dequantised stack (the reference decodes inside its NAX kernel; here the decode is a separate
+pass over the stack, fused decode is the planned next step)."""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+MT = 128                     # rows of one expert per tile = UMMA M
+
+
+def csort(e32: torch.Tensor, E: int, mt: int = MT):
+    """Slots -> (order [S] sorted position -> slot, tb [E+1] first tile of each expert, off [E+1] first row of each expert)."""
+    pl = ops.moe_plan(e32, E, 1, mt)
+    return pl["order"], pl["tb"], pl["off"]
+
+
+def plan(e32: torch.Tensor, E: int, mt: int = MT):
+    """(order, tb, off, max_tiles): max_tiles bounds the grid without reading the device (S / mt + E)."""
+    order, tb, off = csort(e32, E, mt)
+    return order, tb, off, (e32.numel() + mt - 1) // mt + E
+
+
+def gather_perm(x2: torch.Tensor, order: torch.Tensor, K: int, xperm=None) -> torch.Tensor:
+    """Rows of x2 [T, k] gathered into sorted slot order (slot s reads token s // K), optional column permutation."""
+    return ops.gather_rows(x2, order, K, xperm)
+
+
+def silu_perm(a: torch.Tensor, b: torch.Tensor, xperm=None, limit=None) -> torch.Tensor:
+    return ops.silu_mul(a, b, limit, xperm)
+
+
+def gmm(dev, xg: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, S: int, mt: int = MT, orow=None, out_rows=None, w16=None) -> torch.Tensor:
+    """Sorted grouped product: row r of xg (expert segment e) times expert e of `dev` -> [S, n] (or scattered to rows orow[r])."""
+    if mt != MT:
+        raise ValueError(f"tiles are {MT} rows (UMMA M)")
+    if w16 is None:
+        w16 = ops.dequant(dev.fmt, dev.t16, dev.rows, dev.k, torch.float16, 1.0)
+    gs = dev.gs if dev.fmt == "nvfp4" else None
+    return ops.gemm_f16_grouped(xg, w16, dev.n, dev.E, tb, off, orow, gs, out_rows=out_rows or S)
+
+
+def mlp(glu, x2: torch.Tensor, e32: torch.Tensor, K: int, mt: int = MT) -> torch.Tensor:
+    """Routed SwiGLU MLP on sorted slots -> unweighted per-slot outputs [S, H] in slot order (foreign_kqgmm.py:293-314)."""
+    S = e32.numel()
+    order, tb, off = csort(e32, glu.g.E, mt)
+    xg = gather_perm(x2, order, K)
+    a = gmm(glu.g, xg, tb, off, S, mt)
+    b = gmm(glu.u, xg, tb, off, S, mt)
+    h = silu_perm(a, b, None, glu.limit)
+    return gmm(glu.d, h, tb, off, S, mt, orow=order)
+
+
+def dense_ok(dev, R: int) -> bool:
+    return not dev.E and dev.n % 128 == 0 and R > 32
+
+
+def dense(dev, x2: torch.Tensor) -> torch.Tensor:
+    """A dense linear as ONE group of the grouped kernel (foreign_kqgmm.py:343-354): same result as DevPack.apply's prefill path."""
+    return dev._prefill(x2)

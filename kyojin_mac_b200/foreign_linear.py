@@ -102,6 +102,44 @@ class DevPack:
             return out
         return ops.dequant(self.fmt, self.t16, self.rows, self.k, dtype, self.gscale)
 
+    # ---- routed-expert slots: slot s uses expert eids[s] and row xrows[s] of x (fp16 [T, k]) -> [S, n]   (foreign_linear.py:1068-1164)
+    def gather(self, x, xrows, eids):
+        if not self.E or x.dtype != torch.float16:
+            raise ValueError("gather() needs an expert stack and fp16 rows")
+        gs = self.gs if self.fmt == "nvfp4" else None
+        return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, gs=gs)
+
+    def pair_ok(self, o) -> bool:
+        return bool(self.E) and (self.fmt, self.n, self.k, self.E) == (o.fmt, o.n, o.k, o.E)
+
+    def gather_pair(self, o, x, xrows, eids):
+        """(self.gather(...), o.gather(...)): gate | up of one expert block on the same slots (foreign_linear.py:1119-1154)."""
+        y = self.gather_pair_raw(o, x, xrows, eids)
+        S = eids.numel()
+        return y[:S], y[S:]
+
+    def gather_pair_raw(self, o, x, xrows, eids):
+        S = eids.numel()
+        y = torch.empty((2 * S, self.n), dtype=torch.float16, device=x.device)
+        gs = lambda d: d.gs if d.fmt == "nvfp4" else None
+        ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, gs=gs(self), out=y[:S])
+        ops.gemv_group(o.fmt, o.t16, o.n, o.k, o.E, x, eids, xrows=xrows, gs=gs(o), out=y[S:])
+        return y
+
+    def glu_ok(self) -> bool:
+        return bool(self.E)
+
+    def gather_glu(self, a, b, xrows, eids, act=None, limit=None):
+        """gather() of the down projection on the gated input silu(a) * b (a, b fp16 [S, k]; slot s reads row xrows[s]) (foreign_linear.py:1156-1164).
+        Bit-identical to the activation kernel followed by gather(), which is what runs here."""
+        if act is not None:
+            raise NotImplementedError("only the silu-gated activation is built")
+        return self.gather(ops.silu_mul(a, b, limit), xrows, eids)
+
+    def apply_glu(self, a, b, limit=None):
+        """One matrix on the gated input silu(a) * b (foreign_linear.py:960-977)."""
+        return self.apply(ops.silu_mul(a, b, limit))
+
     def expert(self, e: int) -> "DevPack":
         """Row-range view of expert e (no copy), as foreign_linear.py:637-660."""
         if not self.E:
@@ -163,3 +201,44 @@ class SplitLinear(torch.nn.Module):
 def make_linear(pack, bias=None, out_dtype=torch.float16, in_perm=None, device="cuda"):
     """ForeignLinear for a Pack, SplitLinear for a Split (kyojin_mlx/foreign_linear.py:1271)."""
     return (SplitLinear if isinstance(pack, Split) else ForeignLinear)(pack, bias, out_dtype, in_perm, device)
+
+
+def glu_rows(y, S: int, limit=None):
+    """Gated activation over a [2 S, n] pair output (rows [0, S) = gate, [S, 2 S) = up), one launch (foreign_linear.py:1316-1319)."""
+    return ops.silu_mul(y[:S], y[S:], limit)
+
+
+class ForeignSwitchGLU(torch.nn.Module):
+    """mlx-lm SwitchGLU drop-in: (x [.., H], inds [.., K]) -> [.., K, H] UNWEIGHTED per-slot outputs; silu(gate x) * (up x) -> down
+    (kyojin_mlx/foreign_linear.py:1333-1514). Up to GATHER_MAX slots: gathered GEMV with expert election (an expert's bytes are read once per 8 slots).
+    More slots (prefill): slots sorted by expert on the device, grouped tcgen05 GEMM over 128-row tiles of one expert, scatter back to slot order."""
+
+    def __init__(self, gate: DevPack, up: DevPack, down: DevPack, limit: float | None = None, act_kind=None):
+        super().__init__()
+        if act_kind is not None:
+            raise NotImplementedError("only the silu-gated activation is built")
+        if not (gate.E and gate.E == up.E == down.E) or (gate.n, gate.k) != (up.n, up.k) or down.k != gate.n or down.n != gate.k:
+            raise ValueError("gate / up / down must be expert stacks of matching shapes")
+        self.g, self.u, self.d = gate, up, down
+        self.limit = limit
+
+    def forward(self, x, inds):
+        lead, H = x.shape[:-1], x.shape[-1]
+        K = inds.shape[-1]
+        T = int(np.prod(lead)) if len(lead) else 1
+        x2 = x.reshape(T, H).to(torch.float16)
+        e32 = inds.reshape(-1).to(torch.int32)
+        S = T * K
+        if S <= F.GATHER_MAX:
+            y = self._gather_path(x2, e32, K)
+        else:
+            from . import foreign_kqgmm as KQ
+            y = KQ.mlp(self, x2, e32, K, F.KQ_MT)
+        return y.reshape(*lead, K, self.d.n)
+
+    def _gather_path(self, x2, e32, K):
+        gs = lambda d: d.gs if d.fmt == "nvfp4" else None
+        a = ops.gemv_group(self.g.fmt, self.g.t16, self.g.n, self.g.k, self.g.E, x2, e32, xdiv=K, gs=gs(self.g))
+        b = ops.gemv_group(self.u.fmt, self.u.t16, self.u.n, self.u.k, self.u.E, x2, e32, xdiv=K, gs=gs(self.u))
+        h = ops.silu_mul(a, b, self.limit)
+        return ops.gemv_group(self.d.fmt, self.d.t16, self.d.n, self.d.k, self.d.E, h, e32, xdiv=1, gs=gs(self.d))
