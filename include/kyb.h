@@ -108,6 +108,21 @@ int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_s
 int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
                        const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream);
 
+/* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).
+ * Meant for hosts that cannot call cudaMalloc when they need a GEMV: a server that gave all free HBM to its KV-cache pool at start-up, a decode loop that
+ * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a runtime whose plug-in rules forbid the callee to allocate.
+ * Same arithmetic and results as kyb_gemv_t16; the split-k partial sums and the bounded-wait status word live in a fixed 16 MiB + 256 B array inside the
+ * library image (held by every GPU that loads the library until the process exits) instead of a caller workspace. The call allocates nothing
+ * (no cudaMalloc / cudaFree, no allocating library routine). Limits and rules:
+ *   - shapes whose split-k scratch exceeds 16 MiB are refused with KYB_EWORKSPACE (use kyb_gemv_t16 with your own workspace);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current); make that first call
+ *     before any stream capture;
+ *   - all calls on a device share the one array: two calls that overlap on the GPU (different streams) race on it - serialise them;
+ *   - check != 0: the call also synchronises `stream`, reads the status word and returns KYB_ETIMEOUT if a bounded wait expired (the word is cleared);
+ *     check == 0: purely asynchronous, a timeout stays recorded until a later call with check != 0. */
+int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
+                        void* y, int64_t ldy, int check, void* stream);
+
 /* launch plan the GEMV would use (diagnostics and launch counting): out8 = {column tiles, stored x rows per tile, warps per CTA,
  * ring stages, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. ksplit > 1 means two launches. */
 int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);

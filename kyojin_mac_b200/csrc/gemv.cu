@@ -894,6 +894,85 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     return KYB_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ decode GEMV without any allocation
+// Some hosts may not allocate device memory at the moment they need a GEMV: a serving process that handed every free byte of HBM to its KV-cache
+// pool at start-up (a later cudaMalloc fails or fragments the pool), a latency-critical decode loop that cannot take the implicit device
+// synchronisation of cudaMalloc / cudaFree, or an embedding runtime whose plug-in contract forbids the callee to allocate. For them the split-k
+// partial sums and the timeout word of this variant live in a fixed array that is part of the library image: every GPU that loads the library
+// holds KYB_GEMV_STATIC_SCRATCH_BYTES + 256 bytes of it until the process exits.
+#define KYB_GEMV_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[KYB_GEMV_STATIC_SCRATCH_BYTES + 256];   // [0, 256): status word, then fp32 partial sums
+
+namespace {
+// In host code the array's name is only a stand-in; the device address is looked up once per device (with that device current) and cached.
+int static_scratch_address(unsigned char** out) {
+    static std::mutex mu;
+    static unsigned char* addr[64] = {nullptr};
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    KYB_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (!addr[dev]) {
+        void* ptr = nullptr;
+        KYB_CUDA(cudaGetSymbolAddress(&ptr, g_gemv_static_scratch));
+        addr[dev] = (unsigned char*)ptr;
+    }
+    *out = addr[dev];
+    return KYB_OK;
+}
+}  // namespace
+
+extern "C" int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
+                                   int check, void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
+    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
+    KYB_REQUIRE(t16 && x && y, "null pointer");
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    KYB_REQUIRE(ldy >= n, "ldy=%lld must be >= n", (long long)ldy);
+    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
+    const GemvPlan pl = make_plan(fmt, n, k, m);
+    KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
+    const int npad = (int)((n + 15) / 16 * 16);
+    const size_t need = pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
+    if (need > KYB_GEMV_STATIC_SCRATCH_BYTES) {
+        kyb_set_error("kyb_gemv_t16_static: this shape needs %zu bytes of split-k scratch, the built-in array holds %u; use kyb_gemv_t16 with a caller workspace", need,
+                      (unsigned)KYB_GEMV_STATIC_SCRATCH_BYTES);
+        return KYB_EWORKSPACE;
+    }
+    unsigned char* base = nullptr;
+    if (int rc = static_scratch_address(&base)) return rc;
+    unsigned int* status = (unsigned int*)base;
+    float* partial = (float*)(base + 256);
+    kyb::GemvParams p;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
+    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
+    if (int rc = ensure_smem_attr(kern)) return rc;
+    void* args[] = {(void*)&p};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, st));
+    if (pl.ksplit > 1) {
+        // every partial sum the finalize pass reads was written by the launch above, so nothing in the array has to start at zero
+        const int64_t tot = m * n;
+        kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(partial, pl.nchunks, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
+        if (int rc = kyb_launch_check("gemv_finalize")) return rc;
+    }
+    if (check) {
+        unsigned int v = 0;
+        KYB_CUDA(cudaMemcpyAsync(&v, status, sizeof(v), cudaMemcpyDeviceToHost, st));
+        KYB_CUDA(cudaStreamSynchronize(st));
+        if (v) {
+            KYB_CUDA(cudaMemsetAsync(status, 0, sizeof(v), st));                // the word must read zero again for the next call
+            kyb_set_error("device status 0x%x: a kernel gave up a bounded wait", v);
+            return KYB_ETIMEOUT;
+        }
+    }
+    return KYB_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ routed experts (host side)
 extern "C" int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_slots, void* ngroups, void* stream) {
     KYB_REQUIRE(eids && g_expert && g_slots && ngroups, "null pointer");
