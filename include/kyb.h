@@ -82,6 +82,22 @@ int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int6
 int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t s, int64_t n, int64_t k, int experts, const void* tb,
                          const void* off, const void* row_map, const void* gs, void* d, int64_t ldd, void* stream);
 
+/* ---- NVFP4 on the block-scaled tensor-core path.
+ * kyb_nvfp4_quant_rows: activations (x_dtype 1 = fp16, 2 = bf16) [rows, k] -> packed e2m1 codes [rows, k/2] (two per byte, low nibble first) + one e4m3 scale per
+ *   16 inputs, written plain [rows, k/16] (sf_plain) and / or in the tensor-core chunk layout (sf_swz, kyb_nvfp4_sf_bytes bytes). The rounding rule is
+ *   kyojin_mlx/fp4pack.py:30-48 `pack(x, block=16, e4m3_scale=True)`. kyb_nvfp4_unpack_rows is fp4pack.py:51-63 `unpack` (out_dtype 0 f32 / 1 f16 / 2 bf16).
+ * kyb_nvfp4_sf_swizzle: plain scale bytes <-> chunk layout (128 rows x 4 scales per 512-byte chunk), lossless except that the sign bit is dropped and the NaN
+ *   code 0x7F becomes 0, which is how the reference decodes them (kyojin_mlx/foreign_pack.py:113-117). Role of kyojin_mlx/fp4tile.py:72-134 `to_tile` / `from_tile`.
+ * kyb_gemm_nvfp4: d [m, n] (out_dtype 1 = fp16 saturated, 2 = bf16) = gscale * A B^T with A, B packed e2m1 + block scales, tcgen05.mma kind::mxf4nvf4
+ *   (block 16, fp32 accumulation in tensor memory). k % 256 == 0, n % 256 == 0. The reference has no W4A4 product (its NVFP4 linear is W4A16,
+ *   kyojin_mlx/foreign_metal.py:1487-1557); this is the benchmark's "activations quantised on the fly with the same block rule" configuration. */
+size_t kyb_nvfp4_sf_bytes(int64_t rows, int64_t k);
+int kyb_nvfp4_quant_rows(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t k, void* codes, void* sf_plain, void* sf_swz, void* stream);
+int kyb_nvfp4_unpack_rows(const void* codes, const void* sf_plain, int64_t rows, int64_t k, int out_dtype, void* out, int64_t ldo, void* stream);
+int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* swz, int to_swizzled, void* stream);
+int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                   void* d, int64_t ldd, void* stream);
+
 /* ---- routed experts (MoE). Expert stacks are E matrices of n rows concatenated along rows (kyojin_mlx/foreign_linear.py:504-527).
  *
  * kyb_moe_select: router softmax + top-k + renormalise (+ sigmoid of the shared-expert gate logit at column E), one warp per token.

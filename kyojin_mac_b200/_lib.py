@@ -79,6 +79,11 @@ SIGNATURES = {
     "kyb_gemv_t16_static": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
     "kyb_gemm_f16_tn": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _vp]),
     "kyb_gemm_f16_grouped": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "kyb_nvfp4_sf_bytes": (_sz, [_i64, _i64]),
+    "kyb_nvfp4_quant_rows": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "kyb_nvfp4_unpack_rows": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _i64, _vp]),
+    "kyb_nvfp4_sf_swizzle": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
+    "kyb_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_moe_select": (_int, [_vp, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp]),
     "kyb_moe_plan": (_int, [_vp, _vp, _vp, _int, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "kyb_gather_rows": (_int, [_vp, _i64, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),

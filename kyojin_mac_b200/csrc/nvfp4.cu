@@ -1,0 +1,304 @@
+// NVFP4 (e2m1 values, one e4m3 scale per 16 inputs) on the block-scaled tensor-core path of sm_100a.
+//   nvfp4_quant_rows   activations bf16/fp16 -> packed e2m1 codes + e4m3 block scales, the rule of kyojin_mlx/fp4pack.py:30-48 `pack(x, 16, e4m3_scale=True)`
+//   nvfp4_unpack_rows  inverse (fp4pack.py:51-63 `unpack`)
+//   sf_swizzle         plain scale bytes [rows, k/16] -> the 128-row x 4-scale chunks tcgen05 reads (and back): lossless re-layout
+//   gemm_nvfp4         D = sat(gscale * A B^T), A, B packed e2m1 [rows, k/2] K-major with block scales, tcgen05.mma kind::mxf4nvf4 block16, fp32 accumulate in TMEM
+//
+// Scale-factor chunk layout ("SF512"): rows are cut in blocks of 128, k in blocks of 64 (= 4 scales); chunk (rb, kb) holds 512 bytes at ((rb * k/64) + kb) * 512,
+// byte (r % 32) * 16 + (r / 32) * 4 + c = scale c of row r of the block. One chunk is what `tcgen05.cp 32x128b.warpx4` moves into 4 tensor-memory columns.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include <mutex>
+
+#include "tc_common.cuh"
+
+namespace kyb {
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t b) {      // unsigned e4m3 magnitude, exact (see e4m3_unsigned in t16_decode.cuh); 0x7F -> 0
+    b &= 127u;
+    const float v = __uint_as_float(b << 20) * 1.329227995784916e36f;
+    return b == 127u ? 0.0f : v;
+}
+
+__device__ __forceinline__ size_t sf512_offset(int64_t row, int64_t s, int64_t kblocks64) {     // s = scale index along k (k / 16)
+    const int64_t rb = row >> 7, r = row & 127, kb = s >> 2, c = s & 3;
+    return (size_t)((rb * kblocks64 + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4 + c);
+}
+
+// One thread per block of 16 inputs. amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6); v = clip(x / scale, -6, 6);
+// code = #(|v| > .25, 1.25, 2.5, 5) + #(|v| >= .75, 1.75, 3.5) (round to nearest even onto e2m1), sign bit 3 for v < 0; two codes per byte, low first.
+template <typename T>
+__global__ void nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain,
+                                        uint8_t* __restrict__ sf_swz) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nblk = k >> 4;
+    if (i >= rows * nblk) return;
+    const int64_t row = i / nblk, b = i % nblk;
+    const T* xp = x + row * ldx + b * 16;
+    float v[16];
+    float amax = 6.0f * 0.001953125f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        v[j] = (float)xp[j];
+        amax = fmaxf(amax, fabsf(v[j]));
+    }
+    const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3);
+    const float scale = e4m3_to_float(s8);
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float q = fminf(fmaxf(__fdiv_rn(v[j], scale), -6.0f), 6.0f);
+        const float mag = fabsf(q);
+        const uint32_t code = (uint32_t)(mag > 0.25f) + (uint32_t)(mag > 1.25f) + (uint32_t)(mag > 2.5f) + (uint32_t)(mag > 5.0f) + (uint32_t)(mag >= 0.75f) +
+                              (uint32_t)(mag >= 1.75f) + (uint32_t)(mag >= 3.5f);
+        packed[j >> 3] |= (code | (q < 0.0f ? 8u : 0u)) << (4 * (j & 7));
+    }
+    *reinterpret_cast<uint2*>(codes + row * (k >> 1) + b * 8) = make_uint2(packed[0], packed[1]);
+    if (sf_plain) sf_plain[row * nblk + b] = s8;
+    if (sf_swz) sf_swz[sf512_offset(row, b, k >> 6)] = s8;
+}
+
+template <typename T>
+__global__ void nvfp4_unpack_rows_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf_plain, int64_t rows, int64_t k, T* __restrict__ out, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nblk = k >> 4;
+    if (i >= rows * nblk) return;
+    const int64_t row = i / nblk, b = i % nblk;
+    const uint2 pk = *reinterpret_cast<const uint2*>(codes + row * (k >> 1) + b * 8);
+    const float scale = e4m3_to_float(sf_plain[row * nblk + b]);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const uint32_t c = ((j < 8 ? pk.x : pk.y) >> (4 * (j & 7))) & 15u;
+        const uint32_t hb = ((c & 8u) << 12) | ((c & 7u) << 9);                       // e2m1 as fp16 bits = value * 2^-14
+        out[row * ldo + b * 16 + j] = (T)(half_bits_to_float(hb) * 16384.0f * scale);
+    }
+}
+
+// plain [rows, k/16] <-> SF512 (rows padded to 128 with zero scales); sanitize: sign bit dropped, NaN code 0x7F -> 0 (the reference's decode rule)
+__global__ void sf_swizzle_kernel(const uint8_t* __restrict__ plain, int64_t rows, int64_t k, uint8_t* __restrict__ swz, int to_swizzled) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nblk = k >> 4, rows_pad = (rows + 127) & ~(int64_t)127;
+    if (i >= rows_pad * nblk) return;
+    const int64_t row = i / nblk, s = i % nblk;
+    const size_t o = sf512_offset(row, s, k >> 6);
+    if (to_swizzled) {
+        uint8_t v = row < rows ? (uint8_t)(plain[row * nblk + s] & 127u) : (uint8_t)0;
+        swz[o] = v == 127 ? (uint8_t)0 : v;
+    } else if (row < rows) {
+        const_cast<uint8_t*>(plain)[row * nblk + s] = swz[o];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ block-scaled GEMM
+constexpr int NV_BM = 128, NV_BN = 256, NV_BK = 256, NV_THREADS = 192, NV_STAGES = 4;
+constexpr uint32_t NV_A_BYTES = NV_BM * NV_BK / 2, NV_B_BYTES = NV_BN * NV_BK / 2, NV_SFA_BYTES = 4 * 512, NV_SFB_BYTES = 2 * 4 * 512;
+constexpr uint32_t NV_STAGE_BYTES = NV_A_BYTES + NV_B_BYTES + NV_SFA_BYTES + NV_SFB_BYTES;     // 16 K + 32 K + 2 K + 4 K
+
+struct NvGemmParams {
+    const uint8_t* sfa;      // SF512 of A [m_pad / 128][k / 64][512]
+    const uint8_t* sfb;      // SF512 of B
+    __half* d;
+    int64_t ldd;
+    int m, n, k;
+    float gscale;
+    int out_bf16;
+    unsigned int* status;
+};
+
+// kind::mxf4nvf4 instruction descriptor: A = B = e2m1 (format 1 at [7,10) and [10,13)), scales ue4m3 (bit 23 = 0), K-major, N >> 3 at [17,23), M >> 4 at [24,29)
+__host__ __device__ constexpr uint32_t umma_idesc_nvf4(int m, int n) { return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
+
+// shared-memory descriptor of one 512-byte scale chunk (32 rows of 16 bytes, no swizzle): 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const NvGemmParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem0 + NV_STAGES * NV_STAGE_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * NV_STAGES, accum_bar = bars + 16 * NV_STAGES, tmem_slot = accum_bar + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * NV_BN, m0 = blockIdx.y * NV_BM;
+    const int kblocks = p.k / NV_BK, k64 = p.k / 64;
+    constexpr uint32_t TMEM_COLS = 512, COL_SFA = 256, COL_SFB = 272;       // accumulator [0, 256), scales of A [256, 272), of B [272, 304)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NV_STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
+        mbar_init_a(accum_bar, 1);
+        mbar_fence_init();
+        prefetch_tmap(&tma_a);
+        prefetch_tmap(&tma_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    bool failed = false;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t parity = 1;
+            int s = 0;
+            for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                const uint32_t a_dst = smem0 + s * NV_STAGE_BYTES, b_dst = a_dst + NV_A_BYTES, sfa_dst = b_dst + NV_B_BYTES, sfb_dst = sfa_dst + NV_SFA_BYTES;
+                const uint32_t bar = full0 + 8 * s;
+                mbar_expect_tx_a(bar, NV_STAGE_BYTES);
+                tma_load_2d(a_dst, &tma_a, kb * (NV_BK / 2), m0, bar);                     // coordinates in bytes along k (two codes per byte)
+                tma_load_2d(b_dst, &tma_b, kb * (NV_BK / 2), n0, bar);
+                const uint8_t* sa = p.sfa + ((size_t)(m0 >> 7) * k64 + (size_t)kb * 4) * 512;
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfa_dst), "l"(sa), "r"(NV_SFA_BYTES), "r"(bar) : "memory");
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint8_t* sb = p.sfb + ((size_t)((n0 >> 7) + h) * k64 + (size_t)kb * 4) * 512;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_dst + h * 2048), "l"(sb), "r"(2048u), "r"(bar)
+                                 : "memory");
+                }
+                if (++s == NV_STAGES) s = 0, parity ^= 1u;
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_nvf4(NV_BM, NV_BN);
+            uint32_t parity = 0;
+            int s = 0;
+            for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                tc_fence_after();
+                const uint32_t a_src = smem0 + s * NV_STAGE_BYTES, b_src = a_src + NV_A_BYTES, sfa_src = b_src + NV_B_BYTES, sfb_src = sfa_src + NV_SFA_BYTES;
+                // scales of this stage into tensor memory: A 4 chunks (one per 64-wide k block), B 2 row blocks x 4 chunks; the copies and the MMAs of one
+                // thread execute in issue order, so the same columns are reused every stage
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    tmem_cp_32x128b_x4(tmem_base + COL_SFA + 4 * j, sf_desc(sfa_src + 512 * j));
+                    tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j, sf_desc(sfb_src + 512 * j));
+                    tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j + 4, sf_desc(sfb_src + 2048 + 512 * j));
+                }
+                const uint64_t adesc = umma_desc_sw128(a_src), bdesc = umma_desc_sw128(b_src);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)                                                  // 64 e2m1 = 32 bytes along k inside the swizzle atom
+                    umma_nvf4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + COL_SFA + 4 * j, tmem_base + COL_SFB + 8 * j, (kb | j) != 0);
+                umma_commit(empty0 + 8 * s);
+                if (++s == NV_STAGES) s = 0, parity ^= 1u;
+            }
+            umma_commit(accum_bar);
+        }
+    } else {
+        const int q = warp & 3;
+        if (!mbar_wait_fast(accum_bar, 0)) failed = true;
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        __half* drow = p.d + (size_t)row * p.ldd + n0;
+#pragma unroll 1
+        for (int c = 0; c < NV_BN; c += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+            tmem_ld_wait();
+            if (row < p.m && !failed) {
+                for (int j = 0; j < 32; ++j) {
+                    if (n0 + c + j >= p.n) break;
+                    const float f = __uint_as_float(v[j]) * p.gscale;
+                    if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(drow)[c + j] = __float2bfloat16_rn(f);
+                    else drow[c + j] = sat_half(f);
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace kyb
+
+// ------------------------------------------------------------------------------------------------ host side
+extern "C" size_t kyb_nvfp4_sf_bytes(int64_t rows, int64_t k) {
+    if (rows <= 0 || k <= 0 || k % 64) return 0;
+    return (size_t)((rows + 127) / 128) * (size_t)(k / 64) * 512;
+}
+
+extern "C" int kyb_nvfp4_quant_rows(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t k, void* codes, void* sf_plain, void* sf_swz, void* stream) {
+    KYB_REQUIRE(x && codes && (sf_plain || sf_swz), "null pointer");
+    KYB_REQUIRE(rows > 0 && k > 0 && k % 16 == 0 && ldx >= k, "rows=%lld k=%lld: k must be a positive multiple of 16", (long long)rows, (long long)k);
+    KYB_REQUIRE(!sf_swz || k % 64 == 0, "the tensor-core scale layout needs k %% 64 == 0");
+    KYB_REQUIRE(x_dtype == 1 || x_dtype == 2, "x_dtype: 1 = fp16, 2 = bf16");
+    KYB_REQUIRE(((uintptr_t)codes & 7) == 0, "codes must be 8-byte aligned");
+    const int64_t total = rows * (k / 16);
+    const unsigned blocks = (unsigned)((total + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (sf_swz) KYB_CUDA(cudaMemsetAsync(sf_swz, 0, kyb_nvfp4_sf_bytes(rows, k), st));            // padding rows of the last 128-row block read as zero scales
+    if (x_dtype == 1) kyb::nvfp4_quant_rows_kernel<__half><<<blocks, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+    else kyb::nvfp4_quant_rows_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+    return kyb_launch_check("nvfp4_quant_rows");
+}
+
+extern "C" int kyb_nvfp4_unpack_rows(const void* codes, const void* sf_plain, int64_t rows, int64_t k, int out_dtype, void* out, int64_t ldo, void* stream) {
+    KYB_REQUIRE(codes && sf_plain && out, "null pointer");
+    KYB_REQUIRE(rows > 0 && k > 0 && k % 16 == 0 && ldo >= k, "rows=%lld k=%lld", (long long)rows, (long long)k);
+    KYB_REQUIRE(out_dtype >= 0 && out_dtype <= 2, "out_dtype: 0 = fp32, 1 = fp16, 2 = bf16");
+    const int64_t total = rows * (k / 16);
+    const unsigned blocks = (unsigned)((total + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == 0) kyb::nvfp4_unpack_rows_kernel<float><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf_plain, rows, k, (float*)out, ldo);
+    else if (out_dtype == 1) kyb::nvfp4_unpack_rows_kernel<__half><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf_plain, rows, k, (__half*)out, ldo);
+    else kyb::nvfp4_unpack_rows_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf_plain, rows, k, (__nv_bfloat16*)out, ldo);
+    return kyb_launch_check("nvfp4_unpack_rows");
+}
+
+extern "C" int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* swz, int to_swizzled, void* stream) {
+    KYB_REQUIRE(plain && swz, "null pointer");
+    KYB_REQUIRE(rows > 0 && k > 0 && k % 64 == 0, "rows=%lld k=%lld: k must be a positive multiple of 64", (long long)rows, (long long)k);
+    const int64_t total = ((rows + 127) / 128 * 128) * (k / 16);
+    kyb::sf_swizzle_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)plain, rows, k, (uint8_t*)swz, to_swizzled);
+    return kyb_launch_check("nvfp4_sf_swizzle");
+}
+
+// D [m, n] = sat(gscale * A B^T): a_codes [m, k/2], b_codes [n, k/2] packed e2m1 (two per byte, low nibble first), sfa / sfb in the SF512 layout.
+extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                              void* d, int64_t ldd, void* stream) {
+    KYB_REQUIRE(a_codes && sfa && b_codes && sfb && d, "null pointer");
+    KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
+    KYB_REQUIRE(n % 256 == 0, "n=%lld must be a multiple of 256 (one CTA covers two 128-row scale chunks of B)", (long long)n);
+    KYB_REQUIRE(ldd >= n && (out_dtype == 1 || out_dtype == 2), "ldd >= n, out_dtype 1 = fp16 or 2 = bf16");
+    KYB_REQUIRE(((uintptr_t)a_codes & 15) == 0 && ((uintptr_t)b_codes & 15) == 0 && ((uintptr_t)sfa & 15) == 0 && ((uintptr_t)sfb & 15) == 0, "operands must be 16-byte aligned");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    CUtensorMap ta, tb;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, (uint64_t)m, (uint64_t)(k / 2), (uint64_t)(k / 2), kyb::NV_BM, 128)) return rc;
+    if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_codes, (uint64_t)n, (uint64_t)(k / 2), (uint64_t)(k / 2), kyb::NV_BN, 128)) return rc;
+    kyb::NvGemmParams p;
+    p.sfa = (const uint8_t*)sfa, p.sfb = (const uint8_t*)sfb, p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale;
+    p.out_bf16 = out_dtype == 2, p.status = status;
+    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 16 * kyb::NV_STAGES + 16 + 1024;
+    static std::mutex mu;
+    static unsigned done = 0;
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!(done & (1u << (dev & 31)))) {
+            KYB_CUDA(cudaFuncSetAttribute(kyb::gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done |= 1u << (dev & 31);
+        }
+    }
+    dim3 grid((unsigned)((n + kyb::NV_BN - 1) / kyb::NV_BN), (unsigned)((m + kyb::NV_BM - 1) / kyb::NV_BM));
+    kyb::gemm_nvfp4_kernel<<<grid, kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, p);
+    return kyb_launch_check("gemm_nvfp4");
+}

@@ -218,3 +218,57 @@ def gemm_f16_grouped(a: torch.Tensor, b: torch.Tensor, n: int, E: int, tb: torch
     _lib.check(_lib.lib().kyb_gemm_f16_grouped(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), s, n, k, E, tb.data_ptr(), off.data_ptr(), _p(row_map), _p(gs),
                                                d.data_ptr(), d.stride(0), _stream()))
     return d
+
+
+# ------------------------------------------------------------------------------------------------ NVFP4 tensor-core path
+_DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+
+def nvfp4_sf_bytes(rows: int, k: int) -> int:
+    return _lib.lib().kyb_nvfp4_sf_bytes(rows, k)
+
+
+def nvfp4_quant_rows(x: torch.Tensor, swizzled: bool = True, plain: bool = True):
+    """x fp16 / bf16 [rows, k] -> (codes uint8 [rows, k/2], plain scales uint8 [rows, k/16] or None, chunk-layout scales uint8 or None)."""
+    _need_cuda(x)
+    if x.dtype not in (torch.float16, torch.bfloat16) or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("nvfp4_quant_rows takes fp16 / bf16 [rows, k]")
+    rows, k = x.shape
+    codes = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    sp = torch.empty((rows, k // 16), dtype=torch.uint8, device=x.device) if plain else None
+    ss = torch.empty(nvfp4_sf_bytes(rows, k), dtype=torch.uint8, device=x.device) if swizzled else None
+    _lib.check(_lib.lib().kyb_nvfp4_quant_rows(x.data_ptr(), _DT[x.dtype], x.stride(0), rows, k, codes.data_ptr(), _p(sp), _p(ss), _stream()))
+    return codes, sp, ss
+
+
+def nvfp4_unpack_rows(codes: torch.Tensor, scales: torch.Tensor, dtype=torch.float16) -> torch.Tensor:
+    _need_cuda(codes, scales)
+    rows, k = codes.shape[0], codes.shape[1] * 2
+    out = torch.empty((rows, k), dtype=dtype, device=codes.device)
+    _lib.check(_lib.lib().kyb_nvfp4_unpack_rows(codes.data_ptr(), scales.data_ptr(), rows, k, _DT[dtype], out.data_ptr(), k, _stream()))
+    return out
+
+
+def nvfp4_sf_swizzle(plain: torch.Tensor, k: int) -> torch.Tensor:
+    """plain scale bytes [rows, k/16] -> chunk layout."""
+    _need_cuda(plain)
+    plain = plain.contiguous()
+    rows = plain.shape[0]
+    out = torch.empty(nvfp4_sf_bytes(rows, k), dtype=torch.uint8, device=plain.device)
+    _lib.check(_lib.lib().kyb_nvfp4_sf_swizzle(plain.data_ptr(), rows, k, out.data_ptr(), 1, _stream()))
+    return out
+
+
+def nvfp4_sf_unswizzle(swz: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    out = torch.empty((rows, k // 16), dtype=torch.uint8, device=swz.device)
+    _lib.check(_lib.lib().kyb_nvfp4_sf_swizzle(out.data_ptr(), rows, k, swz.data_ptr(), 0, _stream()))
+    return out
+
+
+def gemm_nvfp4(a_codes, sfa, b_codes, sfb, m: int, n: int, k: int, gscale: float = 1.0, dtype=torch.float16, out=None) -> torch.Tensor:
+    """d [m, n] = gscale * dequant(A) dequant(B)^T on block-scaled tcgen05 (scales in the chunk layout)."""
+    _need_cuda(a_codes, sfa, b_codes, sfb)
+    d = out if out is not None else torch.empty((m, n), dtype=dtype, device=a_codes.device)
+    _lib.check(_lib.lib().kyb_gemm_nvfp4(a_codes.data_ptr(), sfa.data_ptr(), b_codes.data_ptr(), sfb.data_ptr(), m, n, k, float(gscale), _DT[d.dtype], d.data_ptr(),
+                                         d.stride(0), _stream()))
+    return d

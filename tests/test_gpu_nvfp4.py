@@ -1,0 +1,60 @@
+"""NVFP4 tensor-core path parity (GPU): activation quantiser == the numpy restatement of kyojin_mlx/fp4pack.py bit for bit (codes and scale bytes, incl. an
+all-zero row; reference test tests/test_fp4pack.py:8-18), scale re-layout round trip exact incl. zero / subnormal / 0x7F codes (tests/test_fp4tile.py:29-40),
+block-scaled GEMM vs the fp64 product of the dequantised operands < 1e-3 (tests/test_fp4tile.py:58, tests/test_foreign_g2a.py:27-70)."""
+import numpy as np
+import pytest
+import torch
+
+from kyojin_mac_b200 import fp4pack, layout as L, ops, synth
+from oracle import fp4_numpy as F4, kq_numpy as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_quantiser_equals_restatement(dtype):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn((96, 512), device="cuda", generator=g) * torch.exp(torch.rand((96, 1), device="cuda", generator=g) * 6 - 3)).to(dtype)
+    x[3] = 0
+    x[4, :16] = 1e4 if dtype == torch.float16 else 3e4                    # large block: scale near the top of e4m3
+    codes, sc = fp4pack.pack(x, 16, True)
+    wc, ws = F4.pack(x.float().cpu().numpy())
+    np.testing.assert_array_equal(sc.cpu().numpy(), ws)
+    np.testing.assert_array_equal(codes.cpu().numpy(), wc)
+    y = fp4pack.unpack(codes, sc, 16, True, torch.float32)
+    np.testing.assert_array_equal(y.cpu().numpy(), F4.unpack(wc, ws))
+
+
+def test_sf_layout_round_trip():
+    rng = np.random.default_rng(1)
+    rows, k = 200, 512
+    sc = rng.integers(0, 127, (rows, k // 16), dtype=np.uint8)
+    sc[0, :6] = (0x00, 0x01, 0x07, 0x08, 0x7E, 0x7F)
+    swz = ops.nvfp4_sf_swizzle(torch.from_numpy(sc).cuda(), k)
+    back = ops.nvfp4_sf_unswizzle(swz, rows, k).cpu().numpy()
+    want = sc.copy()
+    want[want == 0x7F] = 0                                               # the NaN code decodes as 0 in the reference and is stored as 0
+    np.testing.assert_array_equal(back, want)
+    s = swz.cpu().numpy().reshape(-1, k // 64, 512)                       # chunk layout: byte (r % 32) * 16 + (r / 32) * 4 + c
+    r, j = 77, 13
+    assert s[r // 128, j // 4, (r % 128 % 32) * 16 + (r % 128 // 32) * 4 + j % 4] == want[r, j]
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (256, 512, 1024), (200, 256, 768), (1024, 1024, 2048)])
+def test_gemm_nvfp4_vs_fp64(m, n, k):
+    rng = np.random.default_rng(m + n)
+    wcodes = rng.integers(0, 16, (n, k), dtype=np.uint8)
+    wsc = synth.nvfp4_scale_bytes(rng, (n, k // 16))                      # e4m3 nearest to 2^U[-8, 0]: mantissa bits and subnormals
+    qs, meta = L.nvfp4_codes_to_pack(wcodes, wsc)
+    w = O.dequant_nvfp4_pack(qs, meta)
+    x = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).cuda().to(torch.bfloat16)
+    acodes, asp, asw = ops.nvfp4_quant_rows(x)
+    xq = F4.unpack(acodes.cpu().numpy(), asp.cpu().numpy())
+    sfb = ops.nvfp4_sf_swizzle(torch.from_numpy(wsc).cuda(), k)
+    d = ops.gemm_nvfp4(acodes, asw, torch.from_numpy(qs).cuda(), sfb, m, n, k, 1.0, torch.float16)
+    ops.check_device_status()
+    want = xq.astype(np.float64) @ w.astype(np.float64).T
+    err = O.rel_fro(d.cpu().numpy(), want)
+    assert err < 1e-3, err
+    d2 = ops.gemm_nvfp4(acodes, asw, torch.from_numpy(qs).cuda(), sfb, m, n, k, 0.25, torch.bfloat16)
+    assert O.rel_fro(d2.float().cpu().numpy(), want * 0.25) < 5e-3       # bf16 output rounding
