@@ -124,19 +124,22 @@ __device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint6
         : "memory");
 }
 
-__global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const NvGemmParams p) {
+// Persistent: CTA c works on tiles c, c + gridDim.x, ... (n tile fastest). Tensor memory: accumulator 256 columns + scale columns; the producer runs ahead
+// into the next tile while the epilogue drains the accumulator.
+__global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const NvGemmParams p,
+                                                                   const int tiles_n, const int num_tiles) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = smem0 + NV_STAGES * NV_STAGE_BYTES;
-    const uint32_t full0 = bars, empty0 = bars + 8 * NV_STAGES, accum_bar = bars + 16 * NV_STAGES, tmem_slot = accum_bar + 8;
+    const uint32_t full0 = bars, empty0 = bars + 8 * NV_STAGES, accf = bars + 16 * NV_STAGES, acce = accf + 8, tmem_slot = acce + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * NV_BN, m0 = blockIdx.y * NV_BM;
     const int kblocks = p.k / NV_BK, k64 = p.k / 64;
     constexpr uint32_t TMEM_COLS = 512, COL_SFA = 256, COL_SFB = 272;       // accumulator [0, 256), scales of A [256, 272), of B [272, 304)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NV_STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
-        mbar_init_a(accum_bar, 1);
+        mbar_init_a(accf, 1);
+        mbar_init_a(acce, 4);
         mbar_fence_init();
         prefetch_tmap(&tma_a);
         prefetch_tmap(&tma_b);
@@ -152,69 +155,102 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
         if (elect_one()) {
             uint32_t parity = 1;
             int s = 0;
-            for (int kb = 0; kb < kblocks && !failed; ++kb) {
-                if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
-                const uint32_t a_dst = smem0 + s * NV_STAGE_BYTES, b_dst = a_dst + NV_A_BYTES, sfa_dst = b_dst + NV_B_BYTES, sfb_dst = sfa_dst + NV_SFA_BYTES;
-                const uint32_t bar = full0 + 8 * s;
-                mbar_expect_tx_a(bar, NV_STAGE_BYTES);
-                tma_load_2d(a_dst, &tma_a, kb * (NV_BK / 2), m0, bar);                     // coordinates in bytes along k (two codes per byte)
-                tma_load_2d(b_dst, &tma_b, kb * (NV_BK / 2), n0, bar);
-                const uint8_t* sa = p.sfa + ((size_t)(m0 >> 7) * k64 + (size_t)kb * 4) * 512;
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfa_dst), "l"(sa), "r"(NV_SFA_BYTES), "r"(bar) : "memory");
+            for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
+                const int n0 = (t % tiles_n) * NV_BN, m0 = (t / tiles_n) * NV_BM;
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                    const uint32_t a_dst = smem0 + s * NV_STAGE_BYTES, b_dst = a_dst + NV_A_BYTES, sfa_dst = b_dst + NV_B_BYTES, sfb_dst = sfa_dst + NV_SFA_BYTES;
+                    const uint32_t bar = full0 + 8 * s;
+                    mbar_expect_tx_a(bar, NV_STAGE_BYTES);
+                    tma_load_2d(a_dst, &tma_a, kb * (NV_BK / 2), m0, bar);                 // coordinates in bytes along k (two codes per byte)
+                    tma_load_2d(b_dst, &tma_b, kb * (NV_BK / 2), n0, bar);
+                    const uint8_t* sa = p.sfa + ((size_t)(m0 >> 7) * k64 + (size_t)kb * 4) * 512;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfa_dst), "l"(sa), "r"(NV_SFA_BYTES), "r"(bar) : "memory");
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint8_t* sb = p.sfb + ((size_t)((n0 >> 7) + h) * k64 + (size_t)kb * 4) * 512;
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_dst + h * 2048), "l"(sb), "r"(2048u), "r"(bar)
-                                 : "memory");
+                    for (int h = 0; h < 2; ++h) {
+                        const uint8_t* sb = p.sfb + ((size_t)((n0 >> 7) + h) * k64 + (size_t)kb * 4) * 512;
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_dst + h * 2048), "l"(sb), "r"(2048u), "r"(bar)
+                                     : "memory");
+                    }
+                    if (++s == NV_STAGES) s = 0, parity ^= 1u;
                 }
-                if (++s == NV_STAGES) s = 0, parity ^= 1u;
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc = umma_idesc_nvf4(NV_BM, NV_BN);
             uint32_t parity = 0;
-            int s = 0;
-            for (int kb = 0; kb < kblocks && !failed; ++kb) {
-                if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+            int s = 0, it = 0;
+            for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x, ++it) {
+                if (!mbar_wait_fast(acce, ((uint32_t)it & 1u) ^ 1u)) failed = true;         // the epilogue has drained the accumulator
                 tc_fence_after();
-                const uint32_t a_src = smem0 + s * NV_STAGE_BYTES, b_src = a_src + NV_A_BYTES, sfa_src = b_src + NV_B_BYTES, sfb_src = sfa_src + NV_SFA_BYTES;
-                // scales of this stage into tensor memory: A 4 chunks (one per 64-wide k block), B 2 row blocks x 4 chunks; the copies and the MMAs of one
-                // thread execute in issue order, so the same columns are reused every stage
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                    tc_fence_after();
+                    const uint32_t a_src = smem0 + s * NV_STAGE_BYTES, b_src = a_src + NV_A_BYTES, sfa_src = b_src + NV_B_BYTES, sfb_src = sfa_src + NV_SFA_BYTES;
+                    // scales of this stage into tensor memory: A 4 chunks (one per 64-wide k block), B 2 row blocks x 4 chunks; the copies and the MMAs of one
+                    // thread execute in issue order, so the same columns are reused every stage
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    tmem_cp_32x128b_x4(tmem_base + COL_SFA + 4 * j, sf_desc(sfa_src + 512 * j));
-                    tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j, sf_desc(sfb_src + 512 * j));
-                    tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j + 4, sf_desc(sfb_src + 2048 + 512 * j));
+                    for (int j = 0; j < 4; ++j) {
+                        tmem_cp_32x128b_x4(tmem_base + COL_SFA + 4 * j, sf_desc(sfa_src + 512 * j));
+                        tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j, sf_desc(sfb_src + 512 * j));
+                        tmem_cp_32x128b_x4(tmem_base + COL_SFB + 8 * j + 4, sf_desc(sfb_src + 2048 + 512 * j));
+                    }
+                    const uint64_t adesc = umma_desc_sw128(a_src), bdesc = umma_desc_sw128(b_src);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)                                              // 64 e2m1 = 32 bytes along k inside the swizzle atom
+                        umma_nvf4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + COL_SFA + 4 * j, tmem_base + COL_SFB + 8 * j, (kb | j) != 0);
+                    umma_commit(empty0 + 8 * s);
+                    if (++s == NV_STAGES) s = 0, parity ^= 1u;
                 }
-                const uint64_t adesc = umma_desc_sw128(a_src), bdesc = umma_desc_sw128(b_src);
-#pragma unroll
-                for (int j = 0; j < 4; ++j)                                                  // 64 e2m1 = 32 bytes along k inside the swizzle atom
-                    umma_nvf4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + COL_SFA + 4 * j, tmem_base + COL_SFB + 8 * j, (kb | j) != 0);
-                umma_commit(empty0 + 8 * s);
-                if (++s == NV_STAGES) s = 0, parity ^= 1u;
+                umma_commit(accf);
             }
-            umma_commit(accum_bar);
         }
     } else {
         const int q = warp & 3;
-        if (!mbar_wait_fast(accum_bar, 0)) failed = true;
-        tc_fence_after();
-        const int row = m0 + q * 32 + lane;
-        __half* drow = p.d + (size_t)row * p.ldd + n0;
+        int it = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const int n0 = (t % tiles_n) * NV_BN, m0 = (t / tiles_n) * NV_BM;
+            if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            __half* drow = p.d + (size_t)row * p.ldd + n0;
+            const bool vec = (p.ldd & 7) == 0;
 #pragma unroll 1
-        for (int c = 0; c < NV_BN; c += 32) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-            tmem_ld_wait();
-            if (row < p.m && !failed) {
-                for (int j = 0; j < 32; ++j) {
-                    if (n0 + c + j >= p.n) break;
-                    const float f = __uint_as_float(v[j]) * p.gscale;
-                    if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(drow)[c + j] = __float2bfloat16_rn(f);
-                    else drow[c + j] = sat_half(f);
+            for (int c = 0; c < NV_BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (row < p.m && !failed) {
+                    if (vec && n0 + c + 32 <= p.n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float f0 = __uint_as_float(v[j + 2 * e]) * p.gscale, f1 = __uint_as_float(v[j + 2 * e + 1]) * p.gscale;
+                                if (p.out_bf16) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                                } else {
+                                    __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                                    w[e] = *reinterpret_cast<uint32_t*>(&h);
+                                }
+                            }
+                            *reinterpret_cast<uint4*>(drow + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && n0 + c + j < p.n; ++j) {
+                            const float f = __uint_as_float(v[j]) * p.gscale;
+                            if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(drow)[c + j] = __float2bfloat16_rn(f);
+                            else drow[c + j] = sat_half(f);
+                        }
+                    }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_a(acce);
         }
     }
     if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
@@ -286,7 +322,7 @@ extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* 
     kyb::NvGemmParams p;
     p.sfa = (const uint8_t*)sfa, p.sfb = (const uint8_t*)sfb, p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale;
     p.out_bf16 = out_dtype == 2, p.status = status;
-    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 16 * kyb::NV_STAGES + 16 + 1024;
+    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
     static std::mutex mu;
     static unsigned done = 0;
     int dev = 0;
@@ -298,7 +334,9 @@ extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* 
             done |= 1u << (dev & 31);
         }
     }
-    dim3 grid((unsigned)((n + kyb::NV_BN - 1) / kyb::NV_BN), (unsigned)((m + kyb::NV_BM - 1) / kyb::NV_BM));
-    kyb::gemm_nvfp4_kernel<<<grid, kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, p);
+    int sms = 148;
+    KYB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int tiles_n = (int)((n + kyb::NV_BN - 1) / kyb::NV_BN), num_tiles = tiles_n * (int)((m + kyb::NV_BM - 1) / kyb::NV_BM);
+    kyb::gemm_nvfp4_kernel<<<(unsigned)(num_tiles < sms ? num_tiles : sms), kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, p, tiles_n, num_tiles);
     return kyb_launch_check("gemm_nvfp4");
 }

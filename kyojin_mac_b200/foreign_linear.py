@@ -93,6 +93,29 @@ class DevPack:
         w16 = ops.dequant(self.fmt, self.t16, self.n, self.k, torch.float16, 1.0)
         return ops.gemm_f16(x2, w16, self.gscale)
 
+    # ---- NVFP4 W4A4: activations quantised on the fly with the weights' block rule, block-scaled tcgen05 GEMM (no counterpart kernel in the reference, whose
+    # NVFP4 linear is W4A16; this serves the benchmark's NVFP4 prefill configuration)
+    def _a4_operands(self):
+        if getattr(self, "_a4", None) is None:
+            if self.fmt != "nvfp4" or self.E:
+                raise ValueError("apply_a4() is for one NVFP4 matrix")
+            raw = ops.t16_to_raw("nvfp4", self.t16, self.n, self.k)                       # GGUF NVFP4 rows, back from T16 on the device
+            blk = raw.reshape(self.n, self.k // 64, 36)
+            sc = blk[:, :, 0:4].reshape(self.n, self.k // 16).contiguous()
+            q = blk[:, :, 4:36].reshape(self.n, self.k // 64, 4, 8)
+            codes = torch.cat([q & 15, q >> 4], dim=-1).reshape(self.n, self.k)          # byte j of a 16-sub-block = inputs j and j + 8
+            qs = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+            self._a4 = (qs, ops.nvfp4_sf_swizzle(sc, self.k))
+        return self._a4
+
+    def apply_a4(self, x2: torch.Tensor, out_dtype=torch.float16) -> torch.Tensor:
+        """y = quant_nvfp4(x) W^T on the block-scaled tensor-core path; x fp16 / bf16 [R, k]. Needs n % 256 == 0 and k % 256 == 0."""
+        qs, sfb = self._a4_operands()
+        if x2.dtype not in (torch.float16, torch.bfloat16):
+            x2 = x2.to(torch.bfloat16)
+        acodes, _, asw = ops.nvfp4_quant_rows(x2.contiguous(), swizzled=True, plain=False)
+        return ops.gemm_nvfp4(acodes, asw, qs, sfb, x2.shape[0], self.n, self.k, self.gscale, out_dtype)
+
     def dequant(self, dtype=torch.float16) -> torch.Tensor:
         """[rows, k] weights (fp16 saturated as foreign_linear.py:1050-1065, or float32 bit-equal to the reference decoder)."""
         if self.E and self.fmt == "nvfp4" and len(set(self.gs.tolist())) > 1:
