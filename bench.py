@@ -175,7 +175,7 @@ def run_ours(args):
     gen = torch.Generator(device=dev).manual_seed(7 + rank)
     xs = {(m, k): torch.randn((m, k), device=dev, generator=gen).to(torch.float16) for m in BATCHES for k in sorted({k for _, _, _, k in mats})}
     ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)}
-    yg = {(m, i): torch.empty((world, m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)} if world > 1 else None
+    yg = {(m, i): torch.empty((world * m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)} if world > 1 else None
     step_bytes = sum(alg_bytes(f, n, k, m) for m in BATCHES for _, f, n, k in mats)
     launches_per_step = sum(1 + (ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
 

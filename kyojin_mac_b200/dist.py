@@ -1,0 +1,99 @@
+"""Multi-GPU plumbing of the quantized linear over torch.distributed (NCCL on GPUs; the index / split logic is backend-agnostic and runs on gloo for tests).
+The reference is single-device; this is new design for an 8 x B200 box:
+
+* dense linears: the output dimension n is column-sharded in whole 16-row tiles (a T16 shard is a contiguous byte range), activations are replicated, every
+  rank runs its shard and the output slices are all-gathered;
+* routed experts: expert-parallel. Experts are split in contiguous ranges, tokens stay data-parallel; routed slots are sent to the rank that owns their expert
+  with one all-to-all, run through that rank's local expert stack, and sent back with the mirrored all-to-all; the owner combines them with the routing weights.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+# ------------------------------------------------------------------------------------------------ dense: n-sharding
+def shard_rows(n: int, world: int, rank: int, align: int = 16):
+    """Rows [row0, row0 + rows) of rank `rank`: contiguous, whole `align`-row tiles, sizes differ by at most one tile."""
+    tiles = (n + align - 1) // align
+    base, extra = divmod(tiles, world)
+    t0 = rank * base + min(rank, extra)
+    nt = base + (1 if rank < extra else 0)
+    row0 = t0 * align
+    return row0, max(0, min(n, (t0 + nt) * align) - row0)
+
+
+def shard_t16(fmt: str, t16: torch.Tensor, n: int, k: int, world: int, rank: int):
+    """The byte range of a T16 matrix that holds rank's rows (no copy): returns (view, row0, rows)."""
+    from .layout import TILE_BYTES
+    row0, rows = shard_rows(n, world, rank)
+    per_tile_row = (k // 256) * TILE_BYTES[fmt]
+    return t16[(row0 // 16) * per_tile_row:((row0 + rows + 15) // 16) * per_tile_row], row0, rows
+
+
+class ShardedLinear:
+    """y [m, n] = all-gather over ranks of x @ W[shard]^T. `local` is any callable x -> y_local (a ForeignLinear on this rank's shard)."""
+
+    def __init__(self, local, n: int, group=None):
+        self.local, self.n, self.group = local, n, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.splits = [shard_rows(n, self.world, r)[1] for r in range(self.world)]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.local(x)
+        m = y.shape[0]
+        if len(set(self.splits)) == 1:                                      # equal shards: one all-gather into [world, m, n / world]
+            out = torch.empty((self.world * m, self.splits[0]), dtype=y.dtype, device=y.device)
+            dist.all_gather_into_tensor(out, y.contiguous(), group=self.group)
+            return out.view(self.world, m, -1).permute(1, 0, 2).reshape(m, self.n)
+        mx = max(self.splits)                                               # uneven shards: pad the slices to the widest, gather, cut
+        pad = torch.zeros((m, mx), dtype=y.dtype, device=y.device)
+        pad[:, :y.shape[1]] = y
+        out = torch.empty((self.world * m, mx), dtype=y.dtype, device=y.device)
+        dist.all_gather_into_tensor(out, pad, group=self.group)
+        out = out.view(self.world, m, mx)
+        return torch.cat([out[r, :, :s] for r, s in enumerate(self.splits)], dim=1)
+
+
+# ------------------------------------------------------------------------------------------------ routed experts: expert parallelism
+def expert_range(E: int, world: int, rank: int):
+    base, extra = divmod(E, world)
+    e0 = rank * base + min(rank, extra)
+    return e0, base + (1 if rank < extra else 0)
+
+
+def owner_of(e: torch.Tensor, E: int, world: int) -> torch.Tensor:
+    """Rank that owns each expert id (contiguous ranges, the first E % world ranks hold one more)."""
+    base, extra = divmod(E, world)
+    cut = extra * (base + 1)
+    return torch.where(e < cut, e // (base + 1), extra + (e - cut) // max(base, 1))
+
+
+def ep_moe(x: torch.Tensor, inds: torch.Tensor, scs: torch.Tensor, E: int, local_experts, group=None, out_dtype=torch.float32) -> torch.Tensor:
+    """Expert-parallel routed layer. x [T, H] (this rank's tokens), inds [T, K] global expert ids, scs [T, K] routing weights.
+    local_experts(rows [S, H], local_ids [S]) -> [S, H_out]: this rank's expert stack applied slot by slot (unweighted), e.g. a ForeignSwitchGLU with K = 1.
+    Returns [T, H_out] = sum_k scs[t, k] * expert(inds[t, k])(x[t]). Split sizes are exchanged first (one small all-to-all; the sizes are read on the host)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    T, K = inds.shape
+    e = inds.reshape(-1).to(torch.int64)
+    dest = owner_of(e, E, world)
+    order = torch.argsort(dest, stable=True)                                # slots grouped by destination rank
+    send_counts = torch.bincount(dest, minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()
+    e0_of = torch.tensor([expert_range(E, world, r)[0] for r in range(world)], device=e.device)
+    send_rows = x[order // K].contiguous()
+    send_ids = (e[order] - e0_of[dest[order]]).to(torch.int32).contiguous()
+    recv_rows = torch.empty((sum(rc), x.shape[1]), dtype=x.dtype, device=x.device)
+    recv_ids = torch.empty(sum(rc), dtype=torch.int32, device=x.device)
+    dist.all_to_all_single(recv_rows, send_rows, rc, sc, group=group)
+    dist.all_to_all_single(recv_ids, send_ids, rc, sc, group=group)
+    y_recv = local_experts(recv_rows, recv_ids) if recv_rows.shape[0] else torch.empty((0, x.shape[1]), dtype=x.dtype, device=x.device)
+    y_back = torch.empty((send_rows.shape[0], y_recv.shape[1]), dtype=y_recv.dtype, device=x.device)
+    dist.all_to_all_single(y_back, y_recv.contiguous(), sc, rc, group=group)
+    y_slots = torch.empty_like(y_back)
+    y_slots[order] = y_back                                                  # back to slot order (t K + k)
+    w = scs.reshape(T, K, 1).to(torch.float32)
+    return (y_slots.reshape(T, K, -1).to(torch.float32) * w).sum(1).to(out_dtype)
