@@ -180,6 +180,7 @@ def run_ours(args):
     launches_per_step = sum(1 + (ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
 
     def one_step(layer, timed=None):
+        works = []
         for m in BATCHES:
             for i, (nm, f, n, k) in enumerate(mats):
                 if timed is not None and i == timed[0]:
@@ -189,8 +190,10 @@ def run_ours(args):
                 if timed is not None and i == timed[0]:
                     e1.record()
                     timed[1].append((m, e0, e1))
-                if world > 1:
-                    dist.all_gather_into_tensor(yg[(m, i)], ys[(m, i)])
+                if world > 1:                                    # gathers run on NCCL's stream and overlap the following products; joined at the end of the step
+                    works.append(dist.all_gather_into_tensor(yg[(m, i)], ys[(m, i)], async_op=True))
+        for w in works:
+            w.wait()
 
     def barrier():
         if world > 1:
@@ -317,7 +320,13 @@ def run_ours(args):
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing NCCL down: captured collectives keep communicator resources alive and a destroy can block at exit
+        graphs = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():
