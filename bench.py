@@ -177,7 +177,8 @@ def run_ours(args):
     ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)}
     yg = {(m, i): torch.empty((world * m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)} if world > 1 else None
     step_bytes = sum(alg_bytes(f, n, k, m) for m in BATCHES for _, f, n, k in mats)
-    launches_per_step = sum(1 + (ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
+    two = ops.TWO_LAUNCH                                              # split-k shapes: gemv_t16_kernel + gemv_finalize_kernel
+    launches_per_step = sum(1 + (two and ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
 
     def one_step(layer, timed=None):
         works = []

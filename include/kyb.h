@@ -124,6 +124,14 @@ int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_s
 int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
                        const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream);
 
+/* single-launch form of kyb_gemv_t16: split-k partial sums are reduced inside the kernel by the last part that finishes a row tile. The workspace holds
+ * kyb_gemv_counter_bytes(n) bytes of arrival counters (must be ZERO before the first call; every call leaves them zero) followed by
+ * kyb_gemv_workspace_bytes(...) bytes of partial sums. Same results, bit for bit, as kyb_gemv_t16. flags bit 0: programmatic dependent launch (the kernel's
+ * set-up and weight prefetch overlap the tail of the preceding kernel on the stream; it waits for that kernel before touching x, y or the workspace). */
+size_t kyb_gemv_counter_bytes(int64_t n);
+int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
+                       void* workspace, size_t workspace_bytes, int flags, void* stream);
+
 /* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).
  * Meant for hosts that cannot call cudaMalloc when they need a GEMV: a server that gave all free HBM to its KV-cache pool at start-up, a decode loop that
  * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a runtime whose plug-in rules forbid the callee to allocate.

@@ -38,6 +38,9 @@ struct GemvParams {
     int m, mst;              // activation rows, rows stored per column tile (1, 2, 4, 8)
     int kbp, ksplit;         // k-blocks per part (a multiple of kc), parts
     int kc;                  // k-blocks per canonical chunk: sums are formed per chunk and chunks are added in k order, whatever the split
+    int nchunks;             // canonical chunks along k
+    int pdl;                 // launched with programmatic stream serialization
+    unsigned int* counters;  // split k: one arrival counter per row tile (zero before the call, zero again after it); null = a finalize kernel sums the partials
     int warps, stages;
     float gscale;
 };
@@ -355,12 +358,15 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
     };
 
     // ---- start the weight stream before staging x: the copies run while the CTA prepares the activations
+    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may start its own weight prefetch as SMs free up
     if (lane == 0) {
         for (int s = 0; s < STAGES; ++s) mbar_init(&bars[s], 1);
         mbar_fence_init();
         const int pre = min(STAGES, total);
         for (int s = 0; s < pre; ++s) issue(s);
     }
+    // weights are never written by a preceding kernel, activations and outputs may be: everything below waits for the launch this one depends on
+    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- stage activations of this k-part as B fragments: [chunk][nt][row < MST][lane t][4 halves permuted (0, 2, 1, 3)].
     // One item = 32 inputs of one activation row (two chunks = one Q4_K sub-block); q4_k also gets the sum of the 32 inputs, split into
@@ -489,6 +495,38 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
             }
             ++chunk;
             cleft = min(p.kc, nblk - blk);
+            if (last && p.ksplit > 1 && p.counters) {
+                // ---- split k without a second launch: the last part to finish a row tile adds the chunk sums in k order and stores the result
+                __threadfence();                                            // this warp's partial sums are visible before it counts itself in
+                unsigned int arrived = 0;
+                if (lane == 0) arrived = atomicAdd(&p.counters[rt], 1u);
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (arrived == (unsigned int)p.ksplit - 1u) {
+                    __threadfence();
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
+                            if (m < p.m && nrow < p.n) {
+                                float sum = 0.f;
+                                const float* pp = p.partial + (size_t)m * p.npad + nrow;
+                                const size_t cstride = (size_t)p.m * p.npad;
+                                for (int c0 = 0; c0 < p.nchunks; c0 += 8) {                  // loads of 8 chunks in flight, added in k order
+                                    float v[8];
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c) v[c] = c0 + c < p.nchunks ? __ldcg(pp + (size_t)(c0 + c) * cstride) : 0.f;
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c)
+                                        if (c0 + c < p.nchunks) sum += v[c];
+                                }
+                                p.y[(size_t)m * p.ldy + nrow] = sat_half(sum * p.gscale);
+                            }
+                        }
+                    }
+                    if (lane == 0) p.counters[rt] = 0u;                     // ready for the next call
+                }
+            }
             if (last) blk = 0, rt += TS, xb = xb0, xa = xa0, chunk = chunk0, cleft = min(p.kc, nblk);
         }
     };
@@ -857,6 +895,9 @@ extern "C" size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_
     return pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float) : 0;
 }
 
+// Bytes at the START of the workspace that hold the row-tile arrival counters of the single-launch split-k reduction (kyb_gemv_t16_fused).
+extern "C" size_t kyb_gemv_counter_bytes(int64_t n) { return n > 0 ? (size_t)(((n + 15) / 16 * 4 + 255) / 256 * 256) : 0; }
+
 extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
                             void* workspace, size_t workspace_bytes, void* stream) {
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
@@ -880,7 +921,7 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     kyb::GemvParams p;
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = (float*)workspace, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
@@ -891,6 +932,50 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
         kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>((const float*)workspace, pl.nchunks, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
         return kyb_launch_check("gemv_finalize");
     }
+    return KYB_OK;
+}
+
+// Single-launch form: split-k partial sums are reduced inside the kernel by the last part that finishes a row tile (arrival counters in the first
+// kyb_gemv_counter_bytes(n) bytes of the workspace, then the partial sums). The counter bytes must be zero before the first call; every call leaves them zero.
+// flags bit 0: launch with programmatic stream serialization, so that in a chain of GEMVs on one stream the next kernel's set-up and weight prefetch overlap
+// the tail of this one (the kernel itself waits for its predecessor before it touches activations or outputs).
+extern "C" int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
+                                  void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
+    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
+    KYB_REQUIRE(t16 && x && y, "null pointer");
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    KYB_REQUIRE(ldy >= n, "ldy=%lld must be >= n", (long long)ldy);
+    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
+    const GemvPlan pl = make_plan(fmt, n, k, m);
+    KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
+    const int npad = (int)((n + 15) / 16 * 16);
+    const size_t cbytes = kyb_gemv_counter_bytes(n);
+    const size_t need = pl.ksplit > 1 ? cbytes + (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
+    if (need && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) {
+        kyb_set_error("fused gemv needs %zu bytes of 16-byte aligned workspace (counters first, zeroed once), got %zu", need, workspace ? workspace_bytes : (size_t)0);
+        return KYB_EWORKSPACE;
+    }
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    kyb::GemvParams p;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.status = status;
+    p.counters = need ? (unsigned int*)workspace : nullptr;
+    p.partial = need ? (float*)((unsigned char*)workspace + cbytes) : nullptr;
+    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.pdl = flags & 1;
+    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
+    if (int rc = ensure_smem_attr(kern)) return rc;
+    void* args[] = {(void*)&p};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.grid), cfg.blockDim = dim3((unsigned)pl.warps * 32), cfg.dynamicSmemBytes = pl.smem, cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = (flags & 1) ? 1 : 0;
+    KYB_CUDA(cudaLaunchKernelExC(&cfg, kern, args));
     return KYB_OK;
 }
 
@@ -948,7 +1033,7 @@ extern "C" int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t 
     kyb::GemvParams p;
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0;
     cudaStream_t st = (cudaStream_t)stream;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
