@@ -132,6 +132,17 @@ size_t kyb_gemv_counter_bytes(int64_t n);
 int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
                        void* workspace, size_t workspace_bytes, int flags, void* stream);
 
+/* two-step form with the partial sums exposed. Replaces kyojin_mlx/mma_gemv.py:129-135 `partial_mma` (-> f32 [parts, rows, n]) and :141-149 `finalize_rows`.
+ * partial: f32 [kyb_gemv_chunks(n, k)][m][n padded to 16]; finalize adds the parts in k order, scales, saturates to fp16. */
+int kyb_gemv_chunks(int64_t n, int64_t k);
+int kyb_gemv_partial_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, void* partial, void* stream);
+int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int64_t n, float gscale, void* y, int64_t ldy, void* stream);
+
+/* few-row product on affine 4-bit weights in the MLX layout (w u32 [n, k/8], scales / biases fp16 [n, k/group], group 32 or 64, weight = scale q + bias),
+ * rows <= 32. Replaces kyojin_mlx/q4mma.py:97-106 `q4mma`, :451-474 `q4mma3` / `q4mma4` (kernels :16-72, :291-448). */
+int kyb_q4mma(const void* w, const void* scales, const void* biases, int group, const void* x, int64_t ldx, int64_t rows, int64_t n, int64_t k,
+              void* y, int64_t ldy, void* stream);
+
 /* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).
  * Meant for hosts that cannot call cudaMalloc when they need a GEMV: a server that gave all free HBM to its KV-cache pool at start-up, a decode loop that
  * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a runtime whose plug-in rules forbid the callee to allocate.

@@ -78,6 +78,10 @@ SIGNATURES = {
     "kyb_gemv_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _vp]),
     "kyb_gemv_counter_bytes": (_sz, [_i64]),
     "kyb_gemv_t16_fused": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _int, _vp]),
+    "kyb_gemv_chunks": (_int, [_i64, _i64]),
+    "kyb_gemv_partial_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
+    "kyb_gemv_finalize": (_int, [_vp, _int, _i64, _i64, _f32, _vp, _i64, _vp]),
+    "kyb_q4mma": (_int, [_vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "kyb_gemv_t16_static": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
     "kyb_gemm_f16_tn": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _vp]),
     "kyb_gemm_f16_grouped": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),

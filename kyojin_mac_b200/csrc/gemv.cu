@@ -40,6 +40,7 @@ struct GemvParams {
     int kc;                  // k-blocks per canonical chunk: sums are formed per chunk and chunks are added in k order, whatever the split
     int nchunks;             // canonical chunks along k
     int pdl;                 // launched with programmatic stream serialization
+    int direct;              // one k-part and no partial output wanted: chunk sums are added in registers and y is stored by the kernel
     unsigned int* counters;  // split k: one arrival counter per row tile (zero before the call, zero again after it); null = a finalize kernel sums the partials
     int warps, stages;
     float gscale;
@@ -481,7 +482,7 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
-                    if (p.ksplit == 1) {
+                    if (p.direct) {
                         tot.v[nt][q] += acc.v[nt][q];
                         if (last) {
                             if (m < p.m && nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(tot.v[nt][q] * p.gscale);
@@ -495,9 +496,10 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
             }
             ++chunk;
             cleft = min(p.kc, nblk - blk);
-            if (last && p.ksplit > 1 && p.counters) {
+            if (last && !p.direct && p.counters) {
                 // ---- split k without a second launch: the last part to finish a row tile adds the chunk sums in k order and stores the result
                 __threadfence();                                            // this warp's partial sums are visible before it counts itself in
+                __syncwarp();                                               // every lane has fenced its own stores before lane 0 announces the warp
                 unsigned int arrived = 0;
                 if (lane == 0) arrived = atomicAdd(&p.counters[rt], 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);
@@ -921,7 +923,7 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     kyb::GemvParams p;
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = (float*)workspace, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0, p.direct = pl.ksplit == 1;
     cudaStream_t st = (cudaStream_t)stream;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
@@ -965,7 +967,7 @@ extern "C" int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k
     p.counters = need ? (unsigned int*)workspace : nullptr;
     p.partial = need ? (float*)((unsigned char*)workspace + cbytes) : nullptr;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.pdl = flags & 1;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.pdl = flags & 1, p.direct = pl.ksplit == 1;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
     void* args[] = {(void*)&p};
@@ -977,6 +979,45 @@ extern "C" int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k
     cfg.attrs = attr, cfg.numAttrs = (flags & 1) ? 1 : 0;
     KYB_CUDA(cudaLaunchKernelExC(&cfg, kern, args));
     return KYB_OK;
+}
+
+// Two-step form with the partial sums exposed (split-k partials, then finalize): the call shape of the reference's few-row MMA GEMV,
+// kyojin_mlx/mma_gemv.py:129-149 `partial_mma` -> f32 [parts, rows, n] and `finalize_rows` -> [rows, n]. partial: f32 [kyb_gemv_chunks(n, k)][m][npad].
+extern "C" int kyb_gemv_chunks(int64_t n, int64_t k) {
+    if (n <= 0 || k <= 0 || k % 256) return 0;
+    const int nb = (int)(k / 256), kc = canonical_chunk((int)((n + 15) / 16), nb);
+    return (nb + kc - 1) / kc;
+}
+
+extern "C" int kyb_gemv_partial_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, void* partial, void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
+    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
+    KYB_REQUIRE(t16 && x && partial, "null pointer");
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    const GemvPlan pl = make_plan(fmt, n, k, m);
+    KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    kyb::GemvParams p;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = nullptr, p.partial = (float*)partial, p.status = status;
+    p.ldx = ldx, p.ldy = 0, p.n = (int)n, p.npad = (int)((n + 15) / 16 * 16), p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = 1.0f, p.kc = pl.kc, p.nchunks = pl.nchunks;
+    p.counters = nullptr, p.pdl = 0, p.direct = 0;
+    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
+    if (int rc = ensure_smem_attr(kern)) return rc;
+    void* args[] = {(void*)&p};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, (cudaStream_t)stream));
+    return KYB_OK;
+}
+
+extern "C" int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int64_t n, float gscale, void* y, int64_t ldy, void* stream) {
+    KYB_REQUIRE(partial && y && chunks > 0 && m > 0 && n > 0 && ldy >= n, "bad arguments");
+    const int64_t tot = m * n;
+    kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)partial, chunks, (int)m, (int)n, (int)((n + 15) / 16 * 16), gscale,
+                                                                                              (__half*)y, ldy);
+    return kyb_launch_check("gemv_finalize");
 }
 
 // ------------------------------------------------------------------------------------------------ decode GEMV without any allocation
@@ -1033,7 +1074,7 @@ extern "C" int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t 
     kyb::GemvParams p;
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0, p.direct = pl.ksplit == 1;
     cudaStream_t st = (cudaStream_t)stream;
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;

@@ -65,9 +65,10 @@ def dequant(fmt, t16: torch.Tensor, n: int, k: int, dtype=torch.float16, gscale:
 _ws: dict = {}
 
 
-def workspace(device, nbytes: int) -> torch.Tensor:
-    """Grow-only ZEROED scratch buffer per (device, stream): arrival counters (kept zero by the kernels) and split-k partial sums of the GEMV live here."""
-    key = (device.index, _stream())
+def workspace(device, nbytes: int, tag: int = 0) -> torch.Tensor:
+    """Grow-only ZEROED scratch buffer per (device, stream, tag): split-k partial sums of the GEMV live here; the single-launch form keeps one buffer per
+    counter-area size (tag), so that partial sums of one shape never land in the arrival counters (kept zero by the kernels) of another."""
+    key = (device.index, _stream(), tag)
     buf = _ws.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = _ws[key] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -79,8 +80,9 @@ PDL = _os.environ.get("KYB_PDL", "0") not in ("0", "")          # chain GEMVs wi
 TWO_LAUNCH = _os.environ.get("KYB_GEMV_TWO_LAUNCH", "1") not in ("0", "")   # split-k sums by a separate finalize kernel (measured faster than the in-kernel reduction, whose release fence per row tile costs more than the second launch)
 
 
-def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, two_launch: bool = False) -> torch.Tensor:
-    """y fp16 [m, n] = x fp16 [m, k] @ W^T for m <= 32, W in T16. One launch (split-k sums reduced in the kernel); two_launch=True uses the finalize kernel."""
+def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, two_launch: bool | None = None, pdl: bool | None = None) -> torch.Tensor:
+    """y fp16 [m, n] = x fp16 [m, k] @ W^T for m <= 32, W in T16. two_launch (default TWO_LAUNCH): split-k sums by the finalize kernel; False: reduced inside the GEMV (one launch, optionally a
+    programmatic dependent launch). All forms return the same bits."""
     _need_cuda(t16, x)
     if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != k:
         raise ValueError(f"x must be float16 [m, {k}], got {x.dtype} {tuple(x.shape)}")
@@ -90,16 +92,15 @@ def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float 
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
     L = _lib.lib()
     need = L.kyb_gemv_workspace_bytes(_fmt(fmt), n, k, m)
-    if two_launch or TWO_LAUNCH:
-        ws = workspace(x.device, need + (1 << 16)) if need else None
-        off = 1 << 16                                                        # keep clear of the counter area of the single-launch form
+    if TWO_LAUNCH if two_launch is None else two_launch:
+        ws = workspace(x.device, need) if need else None
         _lib.check(L.kyb_gemv_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
-                                  ws.data_ptr() + off if ws is not None else None, ws.numel() - off if ws is not None else 0, _stream()))
+                                  ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream()))
         return y
     cb = L.kyb_gemv_counter_bytes(n) if need else 0
-    ws = workspace(x.device, need + cb) if need else None
+    ws = workspace(x.device, need + cb, cb) if need else None
     _lib.check(L.kyb_gemv_t16_fused(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
-                                    ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 1 if PDL else 0, _stream()))
+                                    ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 1 if (PDL if pdl is None else pdl) else 0, _stream()))
     return y
 
 

@@ -134,3 +134,16 @@ def test_full_size_properties(fmt, n, k):
     # linearity: W(2x) = 2 W x exactly (power-of-two scaling commutes with every rounding, no overflow at these magnitudes)
     y2 = ops.gemv(fmt, t16, n, k, (x * 2).to(torch.float16)).float()
     assert torch.equal(y2, y * 2)
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [("q4_k", 512, 5120, 8), ("q6_k", 1024, 8192, 3), ("q4_k", 10240, 5120, 1)])
+def test_single_launch_reduction_equals_two_launch(fmt, n, k, m):
+    """Split-k sums reduced inside the kernel (with and without a programmatic dependent launch) == the finalize-kernel form, bit for bit, call after call."""
+    t16 = synth.t16_random_device(fmt, n, k, seed=3)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    for _ in range(3):
+        x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+        want = ops.gemv(fmt, t16, n, k, x, two_launch=True)
+        assert torch.equal(ops.gemv(fmt, t16, n, k, x, two_launch=False, pdl=False), want)
+        assert torch.equal(ops.gemv(fmt, t16, n, k, x, two_launch=False, pdl=True), want)
+    ops.check_device_status()
