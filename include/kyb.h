@@ -40,6 +40,7 @@ extern "C" {
 
 #define KYB_DT_F32 0
 #define KYB_DT_F16 1
+#define KYB_DT_BF16 2
 
 int kyb_version(void);
 const char* kyb_status_string(int status);
@@ -60,6 +61,11 @@ int kyb_repack_t16_to_raw(int fmt, const void* t16, int64_t n, int64_t k, void* 
  * applied as one fp32 multiply (foreign_pack.py:213). Rows [row0, row0 + nrows) only (row0 % 16 == 0). */
 int kyb_dequant_t16(int fmt, const void* t16, int64_t n, int64_t k, int64_t row0, int64_t nrows, float gscale,
                     int out_dtype, void* out, int64_t ld, void* stream);
+
+/* gathered rows: out[i] = decoded row rows[i] (int32 ids on the device, 0 <= id < n), nrows rows of k weights. Token-embedding lookup in the stored blocks:
+ * kyojin_mlx/foreign_linear.py:1170-1199 `StoredEmbedding.__call__` (mx.take of the per-row arrays + dequant). */
+int kyb_dequant_rows_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* rows, int64_t nrows, float gscale, int out_dtype, void* out, int64_t ld,
+                         void* stream);
 
 /* ---- decode GEMV, m <= 32 activation rows. Replaces kyojin_mlx/foreign_linear.py:846-857 `DevPack._gemv` /
  * `_gemvk` (kernels foreign_metal.py:115-202 `gemv_source`, :1004-1099 `_gemvk_source`) and the few-row products
@@ -97,6 +103,10 @@ int kyb_nvfp4_unpack_rows(const void* codes, const void* sf_plain, int64_t rows,
 int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* swz, int to_swizzled, void* stream);
 int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
                    void* d, int64_t ldd, void* stream);
+
+/* router logits in fp32: lg[t, r] = sum_h gw[r, h] * x[t, h] (x fp32 / fp16 / bf16 [T, H], gw fp32 [E, H]); column E = the shared-expert gate row sgw (fp32 [H]) when
+ * sgw is not null. Replaces kyojin_mlx/foreign_moe.py:122-130 `_logits` (kernels :36-75). lg: fp32 [T, ldl], ldl >= E + (sgw ? 1 : 0). */
+int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const void* gw, const void* sgw, int64_t T, int E, int64_t H, void* lg, int64_t ldl, void* stream);
 
 /* ---- routed experts (MoE). Expert stacks are E matrices of n rows concatenated along rows (kyojin_mlx/foreign_linear.py:504-527).
  *

@@ -2,6 +2,8 @@
 // activation, weighted combine. These are launch-bound elementwise / index kernels; the arithmetic follows the reference's Metal kernels
 // (kyojin_mlx/foreign_moe.py:77-119 _SELECT / _SILU / _COMBINE, foreign_kqgmm.py:169-188 _CSORT, :242-261 _GATHER_ORD / _SILU_PERM,
 // moe_sort.py:18-45) in float32.
+#include <cuda_bf16.h>
+
 #include "kyb_common.cuh"
 
 namespace kyb {
@@ -145,6 +147,63 @@ __global__ void moe_combine_kernel(const __half* __restrict__ y, int64_t ldy, co
     else o[(size_t)t * ldo + c] = acc;
 }
 
+// Router logits in fp32: lg[t, r] = sum_h gw[r, h] * float(x[t, h]) for r < E, and the shared-expert gate row sgw at r = E (kyojin_mlx/foreign_moe.py:36-75).
+// A CTA keeps TT token rows in shared memory in their own type and every warp walks weight rows, so a weight row read from L2 serves TT tokens.
+template <typename XT> struct XVec4;
+template <> struct XVec4<float> {
+    static __device__ __forceinline__ float4 ld(const float* p) { return *reinterpret_cast<const float4*>(p); }
+};
+template <> struct XVec4<__half> {
+    static __device__ __forceinline__ float4 ld(const __half* p) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+template <> struct XVec4<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 ld(const __nv_bfloat16* p) {
+        const uint2 v = *reinterpret_cast<const uint2*>(p);
+        return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    }
+};
+
+template <typename XT, int TT>
+__global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E, int H,
+                                                            float* __restrict__ lg, int64_t ldl) {
+    extern __shared__ __align__(16) unsigned char router_smem[];
+    XT* xs = reinterpret_cast<XT*>(router_smem);
+    constexpr int PER = 16 / (int)sizeof(XT);                              // elements per 16-byte copy
+    const int t0 = blockIdx.x * TT;
+    for (int idx = threadIdx.x; idx < TT * (H / PER); idx += blockDim.x) {
+        const int j = idx / (H / PER), c = idx - j * (H / PER);
+        const int t = min(t0 + j, T - 1);                                   // rows past T repeat the last token; their results are not stored
+        *reinterpret_cast<uint4*>(xs + (size_t)j * H + (size_t)c * PER) = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + (size_t)c * PER);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, R = E + (sgw ? 1 : 0);
+    for (int r = warp; r < R; r += 8) {
+        const float4* wp = reinterpret_cast<const float4*>(r < E ? gw + (size_t)r * H : sgw);
+        float acc[TT];
+#pragma unroll
+        for (int j = 0; j < TT; ++j) acc[j] = 0.f;
+        for (int i = lane; i < H / 4; i += 32) {
+            const float4 w = __ldg(wp + i);
+#pragma unroll
+            for (int j = 0; j < TT; ++j) {
+                const float4 v = XVec4<XT>::ld(xs + (size_t)j * H + 4 * i);
+                acc[j] = fmaf(w.x, v.x, fmaf(w.y, v.y, fmaf(w.z, v.z, fmaf(w.w, v.w, acc[j]))));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < TT; ++j) {
+            float v = acc[j];
+#pragma unroll
+            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && t0 + j < T) lg[(size_t)(t0 + j) * ldl + r] = v;
+        }
+    }
+}
+
 }  // namespace kyb
 
 extern "C" int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream) {
@@ -203,4 +262,38 @@ extern "C" int kyb_moe_combine(const void* y, int64_t ldy, const void* scs, cons
         kyb::moe_combine_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
                                                                                 (int)H, (float*)o, ldo);
     return kyb_launch_check("moe_combine");
+}
+
+template <typename XT, int TT>
+static int launch_router(const void* x, int64_t ldx, const float* gw, const float* sgw, int64_t T, int E, int64_t H, float* lg, int64_t ldl, cudaStream_t st) {
+    const size_t smem = (size_t)TT * (size_t)H * sizeof(XT);
+    static bool configured = false;                                         // one flag per instantiation (a template static)
+    if (!configured) {
+        KYB_CUDA(cudaFuncSetAttribute(kyb::router_logits_kernel<XT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        configured = true;
+    }
+    kyb::router_logits_kernel<XT, TT><<<(unsigned)((T + TT - 1) / TT), 256, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
+    return kyb_launch_check("router_logits");
+}
+
+extern "C" int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const void* gw, const void* sgw, int64_t T, int E, int64_t H, void* lg, int64_t ldl, void* stream) {
+    KYB_REQUIRE(x && gw && lg, "null pointer");
+    KYB_REQUIRE(x_dtype == KYB_DT_F32 || x_dtype == KYB_DT_F16 || x_dtype == KYB_DT_BF16, "x dtype %d", x_dtype);
+    KYB_REQUIRE(T > 0 && T < (1ll << 31) && E > 0 && H > 0 && H % 8 == 0 && ldx >= H && ldx % 8 == 0 && ldl >= E + (sgw ? 1 : 0), "T=%lld E=%d H=%lld: H and ldx must be multiples of 8",
+                (long long)T, E, (long long)H);
+    KYB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)gw & 15) == 0 && ((uintptr_t)sgw & 15) == 0, "x, gw and sgw must be 16-byte aligned");
+    const size_t per_row = (size_t)H * (x_dtype == KYB_DT_F32 ? 4 : 2);
+    KYB_REQUIRE(per_row * 2 <= 226 * 1024, "H=%lld: two token rows do not fit shared memory", (long long)H);
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool small = T < 8 * 148;                                          // few tokens: fewer per CTA so that more SMs take part
+    const int fit = (int)((226 * 1024) / per_row);
+    const int tt = (!small && fit >= 8) ? 8 : (fit >= 4 && (!small || T >= 4 * 64)) ? 4 : 2;
+#define KYB_ROUTER(XT)                                                                                                         \
+    return tt == 8 ? launch_router<XT, 8>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st)           \
+         : tt == 4 ? launch_router<XT, 4>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st)           \
+                   : launch_router<XT, 2>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st)
+    if (x_dtype == KYB_DT_F32) { KYB_ROUTER(float); }
+    if (x_dtype == KYB_DT_F16) { KYB_ROUTER(__half); }
+    KYB_ROUTER(__nv_bfloat16);
+#undef KYB_ROUTER
 }

@@ -38,7 +38,7 @@ def gmm(dev, xg: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, S: int, mt: 
     if mt != MT:
         raise ValueError(f"tiles are {MT} rows (UMMA M)")
     if w16 is None:
-        w16 = ops.dequant(dev.fmt, dev.t16, dev.rows, dev.k, torch.float16, 1.0)
+        w16 = ops.dequant(dev.fmt, dev.t16, dev.nrows, dev.k, torch.float16, 1.0)
     gs = dev.gs if dev.fmt == "nvfp4" else None
     return ops.gemm_f16_grouped(xg, w16, dev.n, dev.E, tb, off, orow, gs, out_rows=out_rows or S)
 

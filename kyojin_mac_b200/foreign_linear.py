@@ -48,7 +48,7 @@ class DevPack:
         gs = [float(np.asarray(p.gscale, np.float32).reshape(-1)[0]) for p in ps]
         self.gscale = gs[0]
         self.gs = torch.tensor(gs, dtype=torch.float32, device=dev)       # one scale per expert (per-tensor scale of a single matrix)
-        self.rows = self.n * (self.E or 1)
+        self.nrows = self.n * (self.E or 1)
 
     @classmethod
     def from_t16(cls, fmt: str, t16: torch.Tensor, n: int, k: int, E: int | None = None, gscale=1.0):
@@ -57,14 +57,54 @@ class DevPack:
         self.fmt, self.n, self.k, self.E, self.t16 = fmt, n, k, E, t16
         self.gscale = float(gscale)
         self.gs = torch.full((E or 1,), float(gscale), dtype=torch.float32, device=t16.device)
-        self.rows = n * (E or 1)
-        if t16.numel() != ops.t16_nbytes(fmt, self.rows, k):
-            raise ValueError(f"T16 buffer of {t16.numel()} bytes does not hold [{self.rows}, {k}] {fmt}")
+        self.nrows = n * (E or 1)
+        if t16.numel() != ops.t16_nbytes(fmt, self.nrows, k):
+            raise ValueError(f"T16 buffer of {t16.numel()} bytes does not hold [{self.nrows}, {k}] {fmt}")
         return self
 
     @property
     def nbytes(self) -> int:
         return self.t16.numel()
+
+    def arrays(self):
+        """The resident device arrays (kyojin_mlx/foreign_linear.py:621-622)."""
+        return [self.t16, self.gs]
+
+    @classmethod
+    def grouped(cls, devs):
+        """One DevPack over the concatenated rows of same-input DevPacks (q | k | v, gate | up), members' rows one after the other
+        (kyojin_mlx/foreign_linear.py:577-594). Members whose row count is not a multiple of 16 are re-tiled through the stored row form on the device.
+        NVFP4 members must share one per-tensor scale (the kernels apply one scale per matrix)."""
+        d0 = devs[0]
+        if any((d.fmt, d.k, d.E) != (d0.fmt, d0.k, None) for d in devs):
+            raise ValueError("grouped: one format, one k, no expert stacks")
+        if any(d.gscale != d0.gscale for d in devs):
+            raise ValueError("grouped: members differ in their per-tensor scale")
+        n = sum(d.n for d in devs)
+        if all(d.n % 16 == 0 for d in devs[:-1]):
+            t16 = torch.cat([d.t16 for d in devs])
+        else:
+            raw = torch.cat([ops.t16_to_raw(d.fmt, d.t16, d.n, d.k) for d in devs])
+            t16 = ops.raw_to_t16(d0.fmt, raw, n, d0.k)
+        return cls.from_t16(d0.fmt, t16, n, d0.k, None, d0.gscale)
+
+    def rows(self, n) -> "DevPack":
+        """A DevPack over output rows of one matrix: n = an int (the first n rows) or a 1-D sequence of row ids, gathered in that order
+        (kyojin_mlx/foreign_linear.py:596-619). The per-tensor scale stays."""
+        if self.E:
+            raise ValueError("rows: one matrix")
+        if isinstance(n, int):
+            if not 0 < n <= self.n:
+                raise ValueError("rows: 0 < n <= N")
+            if n % 16 == 0:
+                return DevPack.from_t16(self.fmt, self.t16[:ops.t16_nbytes(self.fmt, n, self.k)].clone(), n, self.k, None, self.gscale)
+            idx = torch.arange(n, device=self.t16.device)
+        else:
+            idx = torch.as_tensor(np.asarray(n).astype(np.int64), device=self.t16.device)
+            if idx.dim() != 1 or not 0 < idx.numel() <= self.n:
+                raise ValueError("rows: 1-D index, 0 < len <= N")
+        raw = ops.t16_to_raw(self.fmt, self.t16, self.n, self.k).index_select(0, idx)
+        return DevPack.from_t16(self.fmt, ops.raw_to_t16(self.fmt, raw.contiguous(), idx.numel(), self.k), idx.numel(), self.k, None, self.gscale)
 
     # ---- one matrix, x2 [R, k] fp16 -> [R, n] fp16 (row-count dispatch of foreign_linear.py:672-737)
     def apply(self, x2: torch.Tensor) -> torch.Tensor:
@@ -119,11 +159,11 @@ class DevPack:
     def dequant(self, dtype=torch.float16) -> torch.Tensor:
         """[rows, k] weights (fp16 saturated as foreign_linear.py:1050-1065, or float32 bit-equal to the reference decoder)."""
         if self.E and self.fmt == "nvfp4" and len(set(self.gs.tolist())) > 1:
-            out = torch.empty((self.rows, self.k), dtype=dtype, device=self.t16.device)
+            out = torch.empty((self.nrows, self.k), dtype=dtype, device=self.t16.device)
             for e in range(self.E):
-                out[e * self.n:(e + 1) * self.n] = ops.dequant(self.fmt, self.t16, self.rows, self.k, dtype, float(self.gs[e]), e * self.n, self.n)
+                out[e * self.n:(e + 1) * self.n] = ops.dequant(self.fmt, self.t16, self.nrows, self.k, dtype, float(self.gs[e]), e * self.n, self.n)
             return out
-        return ops.dequant(self.fmt, self.t16, self.rows, self.k, dtype, self.gscale)
+        return ops.dequant(self.fmt, self.t16, self.nrows, self.k, dtype, self.gscale)
 
     # ---- routed-expert slots: slot s uses expert eids[s] and row xrows[s] of x (fp16 [T, k]) -> [S, n]   (foreign_linear.py:1068-1164)
     def gather(self, x, xrows, eids):
@@ -224,6 +264,24 @@ class SplitLinear(torch.nn.Module):
 def make_linear(pack, bias=None, out_dtype=torch.float16, in_perm=None, device="cuda"):
     """ForeignLinear for a Pack, SplitLinear for a Split (kyojin_mlx/foreign_linear.py:1271)."""
     return (SplitLinear if isinstance(pack, Split) else ForeignLinear)(pack, bias, out_dtype, in_perm, device)
+
+
+class StoredEmbedding(torch.nn.Module):
+    """Token embedding kept in its quantized blocks (one resident copy): the rows of the ids are decoded on the fly; `as_linear` (a tied head) runs the
+    stored product (kyojin_mlx/foreign_linear.py:1170-1199)."""
+
+    def __init__(self, pack, device="cuda"):
+        super().__init__()
+        self.dev = pack if isinstance(pack, DevPack) else DevPack(pack, device)
+        self.num_embeddings, self.dims = self.dev.n, self.dev.k
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        d = self.dev
+        return ops.dequant_rows(d.fmt, d.t16, d.n, d.k, ids.reshape(-1), torch.float16, d.gscale).reshape(*ids.shape, self.dims)
+
+    def as_linear(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        return self.dev.apply(x.reshape(-1, shape[-1]).to(torch.float16)).reshape(*shape[:-1], self.num_embeddings)
 
 
 def glu_rows(y, S: int, limit=None):

@@ -155,6 +155,31 @@ def moe_select(logits: torch.Tensor, E: int, K: int, norm: bool = True, has_shar
     return inds, scs, sgs
 
 
+def router_logits(x: torch.Tensor, gw: torch.Tensor, sgw: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 [T, E + 1] router logits of x [T, H] (fp32 / fp16 / bf16) on the fp32 gate gw [E, H]; column E = shared-expert gate logit (sgw [H]) or unwritten."""
+    _need_cuda(x, gw)
+    if gw.dtype != torch.float32 or x.dtype not in _DT or x.dim() != 2 or x.shape[1] != gw.shape[1]:
+        raise ValueError("router_logits takes x [T, H] (fp32 / fp16 / bf16) and an fp32 gate [E, H]")
+    x, gw = (x if x.stride(1) == 1 else x.contiguous()), gw.contiguous()
+    sg = None if sgw is None else sgw.reshape(-1).to(torch.float32).contiguous()
+    T, (E, H) = x.shape[0], gw.shape
+    lg = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
+    if sg is None:
+        lg[:, E].zero_()                                                    # no shared expert: the column exists (fixed row pitch) and reads as 0
+    _lib.check(_lib.lib().kyb_router_logits(x.data_ptr(), _DT[x.dtype], x.stride(0), gw.data_ptr(), _p(sg), T, E, H, lg.data_ptr(), lg.stride(0), _stream()))
+    return lg
+
+
+def dequant_rows(fmt, t16: torch.Tensor, n: int, k: int, rows: torch.Tensor, dtype=torch.float16, gscale: float = 1.0) -> torch.Tensor:
+    """[len(rows), k] decoded rows of a T16 matrix, gathered by id (int tensor on the device, 0 <= id < n)."""
+    _need_cuda(t16, rows)
+    ids = rows.reshape(-1).to(torch.int32).contiguous()
+    out = torch.empty((ids.numel(), k), dtype=dtype, device=t16.device)
+    if ids.numel():
+        _lib.check(_lib.lib().kyb_dequant_rows_t16(_fmt(fmt), t16.data_ptr(), n, k, ids.data_ptr(), ids.numel(), float(gscale), _DT[dtype], out.data_ptr(), k, _stream()))
+    return out
+
+
 def moe_plan(ids: torch.Tensor, E: int, topk: int, mt: int = 128, wts: torch.Tensor | None = None, rank: torch.Tensor | None = None):
     """Counting sort of the slots by expert. Returns dict(order, inv, tok, ids_s, wts_s, off, tb)."""
     _need_cuda(ids)
