@@ -1,0 +1,547 @@
+// Prefill GEMM with the dequantisation fused into the operand producer: D[m, n] = sat_f16(gscale * sum_k A[m, k] * W[n, k]), W read as T16 tiles
+// (Q4_K / Q6_K / Q3_K / NVFP4) and never written to HBM as fp16. Replaces the two-step large-row path of kyojin_mlx/foreign_linear.py:710 / :737
+// (`x2 @ self.dequant().T`) and, in grouped form, the sorted grouped product of kyojin_mlx/foreign_kqgmm.py:225-239 (`gmm`).
+//
+// One persistent CTA per SM, 22 warps:
+//   warp 0      TMA: activation tiles (128 rows x 64 inputs, 128-byte swizzle) into the stage ring
+//   warp 1      tcgen05.mma issuer (UMMA 128 x 256 x 16, kind::f16, fp32 accumulators in tensor memory), stages handed back by tcgen05.commit
+//   warps 2-5   epilogue: tcgen05.ld, output scale, saturating fp16 stores
+//   warps 6-21  decoders: warp w owns the 16-row T16 row tile w of the CTA's 256 weight rows. It keeps one T16 tile (256 inputs) in registers (the next one
+//               is already in flight), and for each 64-input quarter unpacks the codes with LOP3 / PRMT into fp16 pairs, applies the block scales with
+//               half2 arithmetic (scale and min rounded to fp16, then one fma per pair: the rounding points of the reference's few-row kernels,
+//               kyojin_mlx/foreign_metal.py:1357-1358, :1382-1383) and writes the pairs into the stage's B tile in the swizzled K-major layout the UMMA
+//               descriptor expects, followed by a proxy fence and one mbarrier arrival per warp.
+// A work item is a 256-row block of W times one or two 128-row blocks of A (msub): with two, a decoded weight serves 256 activation rows, which halves the
+// decode work per flop; with one, the two tensor-memory accumulators alternate and the epilogue overlaps the next item's MMAs (grouped form: an expert's
+// segment is cut into 128-row tiles). Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA drains.
+#include <algorithm>
+#include <mutex>
+
+#include "t16_decode.cuh"
+#include "tc_common.cuh"
+
+#ifndef KYB_KQ_ABL
+#define KYB_KQ_ABL 0          // experiment switches (what limits the decoders); 0 in every shipped build
+#endif
+
+namespace kyb {
+
+constexpr int KQ_BN = 256, KQ_BK = 64, KQ_DW = 16, KQ_THREADS = (6 + KQ_DW) * 32;
+constexpr uint32_t KQ_A_SUB = 128 * KQ_BK * 2, KQ_B_BYTES = KQ_BN * KQ_BK * 2;
+constexpr uint32_t KQ_SCR = 1280;                       // per decoder warp: block scales of one T16 tile as half2 pairs
+
+struct KqParams {
+    const uint8_t* t16;
+    __half* d;
+    int64_t ldd;
+    int m, n, k, nb;            // rows of A, rows of one W matrix, inputs, 256-input blocks
+    int rt_total;               // 16-row tiles in the whole T16 buffer (row tiles past it are clamped; their columns are never stored)
+    float gscale;
+    unsigned int* status;
+    const uint32_t* tb;         // grouped form: first 128-row tile of every expert (E + 1 entries), else null
+    const uint32_t* off;        // grouped form: first sorted row of every expert (E + 1 entries)
+    const uint32_t* row_map;    // optional: output row of every sorted row
+    const float* gs;            // optional: per-expert output scale
+    int experts;
+    int tiles_m, tiles_n;
+    int msub, stages;
+};
+
+struct KqItem {
+    int m0, m_end, n0, b_rt0, nsub;
+    float gscale;
+    bool valid;
+};
+
+__device__ __forceinline__ KqItem kq_item(const KqParams& p, int t) {
+    KqItem it;
+    it.valid = true, it.gscale = p.gscale, it.m_end = p.m;
+    if (!p.tb) {
+        const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;                         // m fastest: CTAs running together share the weight rows
+        it.n0 = tn * KQ_BN, it.m0 = tm * 128 * p.msub, it.b_rt0 = it.n0 >> 4;
+        it.nsub = min(p.msub, (p.m - it.m0 + 127) >> 7);
+        return it;
+    }
+    const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;                              // n fastest: CTAs running together share the activation rows
+    it.n0 = tn * KQ_BN, it.nsub = 1;
+    if ((uint32_t)tm >= p.tb[p.experts]) {
+        it.valid = false;
+        return it;
+    }
+    int lo = 0, hi = p.experts;                                                          // largest e with tb[e] <= tm (empty experts repeat a value)
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (p.tb[mid] <= (uint32_t)tm) lo = mid; else hi = mid;
+    }
+    it.m0 = (int)(p.off[lo] + ((uint32_t)tm - p.tb[lo]) * 128u);
+    it.m_end = (int)p.off[lo + 1];
+    it.b_rt0 = (lo * p.n + it.n0) >> 4;
+    if (p.gs) it.gscale = p.gs[lo];
+    return it;
+}
+
+// ------------------------------------------------------------------------------------------------ decoder: tile registers, scales, quarters
+__device__ __forceinline__ uint4 ldg128s(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg64s(const uint8_t* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg32s(const uint8_t* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t ldg16s(const uint8_t* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) { asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory"); }
+__device__ __forceinline__ void sts128(uint32_t a, uint4 v) { asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
+
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
+    __half2 r = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b), *reinterpret_cast<__half2*>(&c));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t h2_splat(float v) {
+    __half2 r = __half2half2(sat_half(v));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// What one lane holds of a T16 tile: its 16-byte units of the code planes (the lane's MMA-fragment bytes, see kyojin_mac_b200/layout.py) and the scale bytes
+// of row lane / 2 (half lane % 2) for the scale preparation.
+template <int FMT>
+struct KqTile {
+    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : 4];
+    uint4 sc;
+    uint32_t d16;
+};
+
+template <int FMT>
+__device__ __forceinline__ void kq_load(const uint8_t* tile, int lane, KqTile<FMT>& tr) {
+    const int r = lane >> 1, hf = lane & 1;
+    if constexpr (FMT == KYB_FMT_Q4_K) {
+#pragma unroll
+        for (int G = 0; G < 4; ++G) tr.q[G] = ldg128s(tile + (G * 32 + lane) * 16);
+        tr.sc = ldg128s(tile + 2048 + r * 16);
+        tr.d16 = 0;
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
+        tr.q[4] = ldg128s(tile + 2048 + lane * 16);
+        tr.q[5] = ldg128s(tile + 2048 + (32 + lane) * 16);
+        const uint2 s = ldg64s(tile + 3072 + r * 16 + 8 * hf);
+        tr.sc = make_uint4(s.x, s.y, 0, 0);
+        tr.d16 = ldg16s(tile + 3328 + r * 2);
+    } else if constexpr (FMT == KYB_FMT_Q3_K) {
+        tr.q[0] = ldg128s(tile + lane * 16);
+        tr.q[1] = ldg128s(tile + (32 + lane) * 16);
+        tr.q[2] = ldg128s(tile + 1024 + lane * 16);
+        const uint8_t* sp = tile + 1536 + r * 12;
+        tr.sc = make_uint4(ldg32s(sp), ldg32s(sp + 4), ldg32s(sp + 8), 0);
+        tr.d16 = ldg16s(tile + 1728 + r * 2);
+    } else {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
+        const uint2 s = ldg64s(tile + 2048 + r * 16 + 8 * hf);
+        tr.sc = make_uint4(s.x, s.y, 0, 0);
+        tr.d16 = 0;
+    }
+}
+
+// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus min of
+// the eight 32-input sub-blocks); the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte reads of 8 rows on distinct banks).
+template <int FMT>
+__device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t scr, int lane) {
+    const int r = lane >> 1, hf = lane & 1;
+    if constexpr (FMT == KYB_FMT_Q4_K) {
+        const uint4 mt = tr.sc;
+        const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
+        const uint32_t mnw = ((hf ? mt.w >> 4 : mt.z) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.z >> 2) & (hf ? 0x30303030u : 0u));
+        const float d = half_bits_to_float(mt.x & 0xffffu), dm = -half_bits_to_float(mt.x >> 16);
+        uint4 s, z;
+        s.x = h2_splat(d * (float)(scw & 255u)), s.y = h2_splat(d * (float)((scw >> 8) & 255u)), s.z = h2_splat(d * (float)((scw >> 16) & 255u)), s.w = h2_splat(d * (float)(scw >> 24));
+        z.x = h2_splat(dm * (float)(mnw & 255u)), z.y = h2_splat(dm * (float)((mnw >> 8) & 255u)), z.z = h2_splat(dm * (float)((mnw >> 16) & 255u)), z.w = h2_splat(dm * (float)(mnw >> 24));
+        sts128(scr + r * 32 + 16 * hf, s);
+        sts128(scr + 512 + r * 32 + 16 * hf, z);
+    } else {
+        float v[8];
+        if constexpr (FMT == KYB_FMT_Q6_K) {
+            const float d = half_bits_to_float(tr.d16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = d * (float)(int)(int8_t)(((j < 4 ? tr.sc.x : tr.sc.y) >> (8 * (j & 3))) & 255u);
+        } else if constexpr (FMT == KYB_FMT_Q3_K) {
+            const uint32_t w0 = tr.sc.x, w1 = tr.sc.y, w2 = tr.sc.z;
+            const uint32_t ga = hf ? (((w0 >> 4) & 0x0f0f0f0fu) | (w2 & 0x30303030u)) : ((w0 & 0x0f0f0f0fu) | ((w2 << 4) & 0x30303030u));
+            const uint32_t gb = hf ? (((w1 >> 4) & 0x0f0f0f0fu) | ((w2 >> 2) & 0x30303030u)) : ((w1 & 0x0f0f0f0fu) | ((w2 << 2) & 0x30303030u));
+            const float d = half_bits_to_float(tr.d16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = d * (float)((int)(((j < 4 ? ga : gb) >> (8 * (j & 3))) & 255u) - 32);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = e4m3_unsigned((j < 4 ? tr.sc.x : tr.sc.y) >> (8 * (j & 3)));
+        }
+        uint4 a, b;
+        a.x = h2_splat(v[0]), a.y = h2_splat(v[1]), a.z = h2_splat(v[2]), a.w = h2_splat(v[3]);
+        b.x = h2_splat(v[4]), b.y = h2_splat(v[5]), b.z = h2_splat(v[6]), b.w = h2_splat(v[7]);
+        sts128(scr + r * 80 + 32 * hf, a);
+        sts128(scr + r * 80 + 32 * hf + 16, b);
+    }
+}
+
+// Quarter P (inputs [64 P, 64 P + 64)) of the tile: fp16 weights of rows g and g + 8 into the B stage. dst_g / dst_h: this lane's row addresses (8 (t & 1) already
+// added); cx[i]: swizzled byte offset of 16-input slice i for this lane, ((2 i + (t >> 1)) ^ g) * 16.
+template <int FMT, int P>
+__device__ __forceinline__ void kq_decode_quarter(const KqTile<FMT>& tr, uint32_t scr, uint32_t dst_g, uint32_t dst_h, const uint32_t (&cx)[4], int lane) {
+    const int g = lane >> 2;
+    if constexpr (FMT == KYB_FMT_Q4_K) {
+        const uint4 u = tr.q[P];
+        const uint2 sg = lds64(scr + g * 32 + 8 * P), zg = lds64(scr + 512 + g * 32 + 8 * P);
+        const uint2 sh = lds64(scr + (g + 8) * 32 + 8 * P), zh = lds64(scr + 512 + (g + 8) * 32 + 8 * P);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t w = h ? (c ? u.w : u.y) : (c ? u.z : u.x);
+                const uint32_t s_lo = h ? sh.x : sg.x, s_hi = h ? sh.y : sg.y, z_lo = h ? zh.x : zg.x, z_hi = h ? zh.y : zg.y;
+                const uint32_t p01 = prmt(w, 0u, 0x4140u), p23 = prmt(w, 0u, 0x4342u);       // bytes (b0, 0, b1, 0), (b2, 0, b3, 0)
+                // low nibbles: 1024 + q, minus 1024; high nibbles: (1024 + 16 q) / 16 - 64; both exact
+                const uint32_t l01 = h2_sub(and_or(p01, 0x000F000Fu, 0x64006400u), 0x64006400u), l23 = h2_sub(and_or(p23, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                const uint32_t h01 = h2_fma(and_or(p01, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
+                const uint32_t h23 = h2_fma(and_or(p23, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
+                const uint32_t dst = h ? dst_h : dst_g;
+                sts64(dst + cx[c], h2_fma(l01, s_lo, z_lo), h2_fma(l23, s_lo, z_lo));
+                sts64(dst + cx[2 + c], h2_fma(h01, s_hi, z_hi), h2_fma(h23, s_hi, z_hi));
+            }
+        }
+    } else {
+        const uint4 sg4 = lds128(scr + g * 80 + 16 * P), sh4 = lds128(scr + (g + 8) * 80 + 16 * P);
+        const uint32_t sg[4] = {sg4.x, sg4.y, sg4.z, sg4.w}, sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
+        uint4 u, hi = make_uint4(0, 0, 0, 0), hb = make_uint4(0, 0, 0, 0);
+        if constexpr (FMT == KYB_FMT_Q6_K) {
+            u = tr.q[P];
+            hi = tr.q[4 + (P >> 1)];
+        } else if constexpr (FMT == KYB_FMT_Q3_K) {
+            u = tr.q[P >> 1];
+            hb = tr.q[2];
+        } else {
+            u = tr.q[P];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int s = 4 * P + i;
+            uint32_t g01, g23, h01, h23;                                                     // rows g / g + 8: weights (0, 1) and (2, 3) of the slice
+            if constexpr (FMT == KYB_FMT_Q6_K) {
+                const int p = i >> 1;
+                uint32_t wg = p ? u.z : u.x, wh = p ? u.w : u.y;
+                if (i & 1) wg >>= 4, wh >>= 4;
+                uint32_t hg = (P & 1) ? hi.z : hi.x, hh = (P & 1) ? hi.w : hi.y;
+                if (i == 0) hg <<= 4, hh <<= 4;
+                else if (i == 1) hg <<= 2, hh <<= 2;
+                else if (i == 3) hg >>= 2, hh >>= 2;
+                const uint32_t vg = and_or(wg, 0x0F0F0F0Fu, hg & 0x30303030u), vh = and_or(wh, 0x0F0F0F0Fu, hh & 0x30303030u);
+                // bytes -> fp16 (1024 + v) - 1056 = v - 32, exact
+                g01 = h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64206420u), g23 = h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64206420u);
+                h01 = h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64206420u), h23 = h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64206420u);
+            } else if constexpr (FMT == KYB_FMT_Q3_K) {
+                uint32_t wg = (P & 1) ? u.z : u.x, wh = (P & 1) ? u.w : u.y;
+                wg >>= 2 * i, wh >>= 2 * i;
+                uint32_t bg = (P & 2) ? hb.z : hb.x, bh = (P & 2) ? hb.w : hb.y;
+                const int i8 = s & 7;                                                        // bit i8 -> bit 2
+                if (i8 < 2) bg <<= (2 - i8), bh <<= (2 - i8);
+                else bg >>= (i8 - 2), bh >>= (i8 - 2);
+                const uint32_t vg = and_or(wg, 0x03030303u, bg & 0x04040404u), vh = and_or(wh, 0x03030303u, bh & 0x04040404u);
+                // (1024 + v) - 1028 = v - 4
+                g01 = h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64046404u), g23 = h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64046404u);
+                h01 = h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64046404u), h23 = h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64046404u);
+            } else {
+                const int p = i >> 1;
+                const uint32_t wg = p ? u.z : u.x, wh = p ? u.w : u.y;
+                uint32_t eg, og, eh, oh;                                                     // (w0, w2) and (w1, w3) as fp16 bits of value * 2^-14
+                if ((i & 1) == 0) {
+                    eg = wg & 0x8E008E00u, eh = wh & 0x8E008E00u;
+                    og = (wg << 3) & 0x8E008E00u, oh = (wh << 3) & 0x8E008E00u;
+                } else {
+                    eg = and_or(wg << 6, 0x0E000E00u, (wg << 2) & 0x80008000u), eh = and_or(wh << 6, 0x0E000E00u, (wh << 2) & 0x80008000u);
+                    og = and_or(wg << 9, 0x0E000E00u, (wg << 1) & 0x80008000u), oh = and_or(wh << 9, 0x0E000E00u, (wh << 1) & 0x80008000u);
+                }
+                eg = h2_mul(eg, 0x74007400u), og = h2_mul(og, 0x74007400u), eh = h2_mul(eh, 0x74007400u), oh = h2_mul(oh, 0x74007400u);   // * 2^14: the e2m1 value, exact
+                g01 = prmt(eg, og, 0x5410u), g23 = prmt(eg, og, 0x7632u);
+                h01 = prmt(eh, oh, 0x5410u), h23 = prmt(eh, oh, 0x7632u);
+            }
+            sts64(dst_g + cx[i], h2_mul(g01, sg[i]), h2_mul(g23, sg[i]));
+            sts64(dst_h + cx[i], h2_mul(h01, sh[i]), h2_mul(h23, sh[i]));
+        }
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int FMT>
+__global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_constant__ CUtensorMap tma_a, const KqParams p, const int num_items) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int TB = kyb_tile_bytes(FMT);
+    const uint32_t a_bytes = (uint32_t)p.msub * KQ_A_SUB, stage_bytes = a_bytes + KQ_B_BYTES;
+    const int STAGES = p.stages;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t scr0 = smem0 + (uint32_t)STAGES * stage_bytes;
+    const uint32_t bars = scr0 + KQ_DW * KQ_SCR;                                    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16, tmem_slot = acce0 + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kblocks = p.k / KQ_BK;
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init_a(full0 + 8 * s, KQ_DW + 1), mbar_init_a(empty0 + 8 * s, 1);
+        for (int a = 0; a < 2; ++a) mbar_init_a(accf0 + 8 * a, 1), mbar_init_a(acce0 + 8 * a, 4);
+        mbar_fence_init();
+        prefetch_tmap(&tma_a);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---- TMA producer: activation tiles
+        if (elect_one()) {
+            uint32_t parity = 1;                                                    // a fresh barrier passes a wait on the previous phase
+            int s = 0;
+            for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
+                const KqItem it = kq_item(p, t);
+                if (!it.valid) continue;
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                    const uint32_t a_dst = smem0 + s * stage_bytes;
+                    mbar_expect_tx_a(full0 + 8 * s, (uint32_t)it.nsub * KQ_A_SUB);
+                    for (int sub = 0; sub < it.nsub; ++sub) tma_load_2d(a_dst + sub * KQ_A_SUB, &tma_a, kb * KQ_BK, it.m0 + sub * 128, full0 + 8 * s);
+                    if (++s == STAGES) s = 0, parity ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_f16(128, KQ_BN);
+            uint32_t parity = 0;
+            int s = 0;
+            uint32_t cnt = 0;                                                       // accumulators used so far: number cnt lives in slot cnt & 1
+            for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
+                const KqItem it = kq_item(p, t);
+                if (!it.valid) continue;
+                for (int sub = 0; sub < it.nsub; ++sub)
+                    if (!mbar_wait_fast(acce0 + 8 * ((cnt + sub) & 1u), (((cnt + sub) >> 1) & 1u) ^ 1u)) failed = true;     // the epilogue has drained the slot
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                    tc_fence_after();
+                    const uint32_t a_src = smem0 + s * stage_bytes;
+                    const uint64_t bdesc = umma_desc_sw128(a_src + a_bytes);
+                    for (int sub = 0; sub < it.nsub; ++sub) {
+                        const uint64_t adesc = umma_desc_sw128(a_src + sub * KQ_A_SUB);
+                        const uint32_t tmem_d = tmem_base + (uint32_t)(((cnt + sub) & 1u) * KQ_BN);
+#pragma unroll
+                        for (int kk = 0; kk < KQ_BK / 16; ++kk) umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
+                    }
+                    umma_commit(empty0 + 8 * s);                                    // stage free once these MMAs have read it
+                    if (++s == STAGES) s = 0, parity ^= 1u;
+                }
+                for (int sub = 0; sub < it.nsub; ++sub) umma_commit(accf0 + 8 * ((cnt + sub) & 1u));
+                cnt += (uint32_t)it.nsub;
+            }
+        }
+    } else if (warp < 6) {
+        // ---- epilogue: warp w may touch TMEM lanes [32 (w % 4), 32 (w % 4) + 32)
+        const int q = warp & 3;
+        uint32_t cnt = 0;
+        for (int t = blockIdx.x; t < num_items; t += gridDim.x) {
+            const KqItem it = kq_item(p, t);
+            if (!it.valid) continue;
+            for (int sub = 0; sub < it.nsub; ++sub, ++cnt) {
+                const uint32_t slot = cnt & 1u;
+                if (!mbar_wait_fast(accf0 + 8 * slot, (cnt >> 1) & 1u)) failed = true;
+                tc_fence_after();
+                const int row = it.m0 + sub * 128 + q * 32 + lane;
+                const size_t orow = (p.row_map && row < it.m_end) ? (size_t)p.row_map[row] : (size_t)row;
+                __half* drow = p.d + orow * p.ldd + it.n0;
+                const float gscale = it.gscale;
+#pragma unroll 1
+                for (int c = 0; c < KQ_BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
+                    tmem_ld_wait();
+                    if (row < it.m_end && !failed) {
+                        if (it.n0 + c + 32 <= p.n && (p.ldd & 7) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 o;
+                                __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * gscale), sat_half(__uint_as_float(v[j + 1]) * gscale));
+                                __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * gscale), sat_half(__uint_as_float(v[j + 3]) * gscale));
+                                __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * gscale), sat_half(__uint_as_float(v[j + 5]) * gscale));
+                                __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * gscale), sat_half(__uint_as_float(v[j + 7]) * gscale));
+                                o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                *reinterpret_cast<uint4*>(drow + c + j) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (it.n0 + c + j < p.n) drow[c + j] = sat_half(__uint_as_float(v[j]) * gscale);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_a(acce0 + 8 * slot);                       // this warp has read its quarter of the accumulator
+            }
+        }
+    } else {
+        // ---- decoders
+        const int dw = warp - 6, g = lane >> 2, tq = lane & 3;
+        const uint32_t scr = scr0 + dw * KQ_SCR;
+        // rows 16 dw + g and 16 dw + g + 8 of the B tile: 128-byte rows in 8-row groups of 1024 bytes, 16-byte chunks XOR-swizzled with the row number (row & 7 = g)
+        const uint32_t row_off = (uint32_t)(2 * dw) * 1024u + (uint32_t)g * 128u + 8u * (uint32_t)(tq & 1);
+        uint32_t cx[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cx[i] = (uint32_t)(((2 * i + (tq >> 1)) ^ g) * 16);
+        uint32_t parity = 1;
+        int s = 0;
+        for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
+            const KqItem it = kq_item(p, t);
+            if (!it.valid) continue;
+            const int rt = min(it.b_rt0 + dw, p.rt_total - 1);
+            const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
+            KqTile<FMT> cur, nxt;
+            kq_load<FMT>(tp, lane, cur);
+            for (int kb = 0; kb < p.nb && !failed; ++kb) {
+#if KYB_KQ_ABL & 1
+                nxt = cur;
+#else
+                if (kb + 1 < p.nb) kq_load<FMT>(tp + (size_t)(kb + 1) * TB, lane, nxt);     // in flight while this tile is decoded
+#endif
+                kq_prep_scales<FMT>(cur, scr, lane);
+                __syncwarp();
+#define KYB_KQ_QUARTER(P)                                                                                         \
+    {                                                                                                             \
+        if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
+        const uint32_t b_dst = smem0 + s * stage_bytes + a_bytes + row_off;                                       \
+        if (!(KYB_KQ_ABL & 2)) kq_decode_quarter<FMT, P>(cur, scr, b_dst, b_dst + 1024u, cx, lane);               \
+        if (!(KYB_KQ_ABL & 8)) fence_proxy_async_smem();                                                          \
+        __syncwarp();                                                                                             \
+        if (lane == 0) mbar_arrive_a(full0 + 8 * s);                                                              \
+        if (++s == STAGES) s = 0, parity ^= 1u;                                                                   \
+    }
+                KYB_KQ_QUARTER(0)
+                KYB_KQ_QUARTER(1)
+                KYB_KQ_QUARTER(2)
+                KYB_KQ_QUARTER(3)
+#undef KYB_KQ_QUARTER
+                __syncwarp();                                                        // the scratch is rewritten for the next tile
+                cur = nxt;
+            }
+        }
+    }
+    if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+}  // namespace kyb
+
+namespace {
+
+int kq_launch(int fmt, const CUtensorMap& ta, kyb::KqParams p, int num_items, cudaStream_t st) {
+    static std::mutex mu;
+    static unsigned done[4] = {0, 0, 0, 0};
+    static int sms = 0;
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q4_K>
+                       : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q6_K>
+                       : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
+                                             : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
+    const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
+    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 1024 + 256;
+    const size_t cap = 226 * 1024;
+    p.stages = (int)std::min<size_t>(8, (cap - fixed) / stage_bytes);
+    const size_t smem = (size_t)p.stages * stage_bytes + fixed;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!(done[fmt] & (1u << (dev & 31)))) {
+            KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap));
+            done[fmt] |= 1u << (dev & 31);
+        }
+        if (!sms) KYB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    void* args[] = {(void*)&ta, (void*)&p, (void*)&num_items};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)std::min(num_items, sms)), dim3(kyb::KQ_THREADS), args, smem, st));
+    return kyb_launch_check("gemm_kq");
+}
+
+}  // namespace
+
+// D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub: 1 or 2 blocks of 128
+// activation rows per work item (0 = chosen here).
+extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub,
+                           void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(t16 && a && d, "null pointer");
+    KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
+    KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0 && ((uintptr_t)d & 1) == 0, "a and t16 must be 16-byte aligned");
+    KYB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 24), "dimension too large");
+    KYB_REQUIRE(msub >= 0 && msub <= 2, "msub is 0 (automatic), 1 or 2");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    CUtensorMap ta;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda * 2, 128, kyb::KQ_BK)) return rc;
+    kyb::KqParams p;
+    p.t16 = (const uint8_t*)t16, p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256), p.rt_total = (int)((n + 15) / 16);
+    p.gscale = gscale, p.status = status, p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
+    p.msub = msub ? msub : (m > 128 ? 2 : 1);
+    p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN), p.tiles_m = (int)((m + 128 * p.msub - 1) / (128 * p.msub));
+    return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+}
+
+// Grouped form for routed experts: a fp16 [s, k] rows sorted by expert (segment e = rows [off[e], off[e + 1])), T16 of the expert stack (experts * n rows),
+// tb / off from kyb_moe_plan with mt = 128, row_map (optional, u32 [s]) = output row of each sorted row, gs (optional) per-expert output scale. d [*, n].
+// The item list is sized for the worst case (s / 128 + experts tiles per 256 output columns); items past tb[experts] are skipped.
+extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
+                                   const void* row_map, const void* gs, void* d, int64_t ldd, void* stream) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
+    KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,
+                (long long)k, experts);
+    KYB_REQUIRE(n % 256 == 0, "the grouped product needs n %% 256 == 0 (an output tile must not straddle two experts), got n=%lld", (long long)n);
+    KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0, "a and t16 must be 16-byte aligned");
+    KYB_REQUIRE(s < (1ll << 31) && (int64_t)experts * n < (1ll << 31) && k < (1ll << 24), "dimension too large");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    CUtensorMap ta;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)s, (uint64_t)k, (uint64_t)lda * 2, 128, kyb::KQ_BK)) return rc;
+    kyb::KqParams p;
+    p.t16 = (const uint8_t*)t16, p.d = (__half*)d, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256);
+    p.rt_total = (int)((int64_t)experts * n / 16);
+    p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
+    p.msub = 1;
+    p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + 127) / 128) + experts;
+    return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+}

@@ -4,6 +4,8 @@
 // moe_sort.py:18-45) in float32.
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "kyb_common.cuh"
 
 namespace kyb {
@@ -173,6 +175,7 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict
     extern __shared__ __align__(16) unsigned char router_smem[];
     XT* xs = reinterpret_cast<XT*>(router_smem);
     constexpr int PER = 16 / (int)sizeof(XT);                              // elements per 16-byte copy
+    constexpr int RE = 4;                                                  // weight rows per warp pass: a token chunk read from shared memory serves 4 rows
     const int t0 = blockIdx.x * TT;
     for (int idx = threadIdx.x; idx < TT * (H / PER); idx += blockDim.x) {
         const int j = idx / (H / PER), c = idx - j * (H / PER);
@@ -181,26 +184,39 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, R = E + (sgw ? 1 : 0);
-    for (int r = warp; r < R; r += 8) {
-        const float4* wp = reinterpret_cast<const float4*>(r < E ? gw + (size_t)r * H : sgw);
-        float acc[TT];
+    // weight rows are dealt to (blockIdx.y, warp) in groups of RE
+    for (int r0 = (blockIdx.y * 8 + warp) * RE; r0 < R; r0 += gridDim.y * 8 * RE) {
+        const float4* wp[RE];
 #pragma unroll
-        for (int j = 0; j < TT; ++j) acc[j] = 0.f;
+        for (int e = 0; e < RE; ++e) {
+            const int r = min(r0 + e, R - 1);                               // a short last group repeats its last row; the repeats are not stored
+            wp[e] = reinterpret_cast<const float4*>(r < E ? gw + (size_t)r * H : sgw);
+        }
+        float acc[RE][TT];
+#pragma unroll
+        for (int e = 0; e < RE; ++e)
+#pragma unroll
+            for (int j = 0; j < TT; ++j) acc[e][j] = 0.f;
         for (int i = lane; i < H / 4; i += 32) {
-            const float4 w = __ldg(wp + i);
+            float4 w[RE];
+#pragma unroll
+            for (int e = 0; e < RE; ++e) w[e] = __ldg(wp[e] + i);
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
                 const float4 v = XVec4<XT>::ld(xs + (size_t)j * H + 4 * i);
-                acc[j] = fmaf(w.x, v.x, fmaf(w.y, v.y, fmaf(w.z, v.z, fmaf(w.w, v.w, acc[j]))));
+#pragma unroll
+                for (int e = 0; e < RE; ++e) acc[e][j] = fmaf(w[e].x, v.x, fmaf(w[e].y, v.y, fmaf(w[e].z, v.z, fmaf(w[e].w, v.w, acc[e][j]))));
             }
         }
 #pragma unroll
-        for (int j = 0; j < TT; ++j) {
-            float v = acc[j];
+        for (int e = 0; e < RE; ++e)
 #pragma unroll
-            for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && t0 + j < T) lg[(size_t)(t0 + j) * ldl + r] = v;
-        }
+            for (int j = 0; j < TT; ++j) {
+                float v = acc[e][j];
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && t0 + j < T && r0 + e < R) lg[(size_t)(t0 + j) * ldl + r0 + e] = v;
+            }
     }
 }
 
@@ -272,7 +288,10 @@ static int launch_router(const void* x, int64_t ldx, const float* gw, const floa
         KYB_CUDA(cudaFuncSetAttribute(kyb::router_logits_kernel<XT, TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
         configured = true;
     }
-    kyb::router_logits_kernel<XT, TT><<<(unsigned)((T + TT - 1) / TT), 256, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
+    const int64_t gx = (T + TT - 1) / TT;
+    const int R = E + (sgw ? 1 : 0), ymax = (R + 31) / 32;                   // 8 warps x 4 rows per pass
+    const int gy = (int)std::min<int64_t>(ymax, std::max<int64_t>(1, (2 * 148 + gx - 1) / gx));   // few tokens: spread the weight rows over more CTAs
+    kyb::router_logits_kernel<XT, TT><<<dim3((unsigned)gx, (unsigned)gy), 256, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
     return kyb_launch_check("router_logits");
 }
 
@@ -285,9 +304,8 @@ extern "C" int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const 
     const size_t per_row = (size_t)H * (x_dtype == KYB_DT_F32 ? 4 : 2);
     KYB_REQUIRE(per_row * 2 <= 226 * 1024, "H=%lld: two token rows do not fit shared memory", (long long)H);
     cudaStream_t st = (cudaStream_t)stream;
-    const bool small = T < 8 * 148;                                          // few tokens: fewer per CTA so that more SMs take part
     const int fit = (int)((226 * 1024) / per_row);
-    const int tt = (!small && fit >= 8) ? 8 : (fit >= 4 && (!small || T >= 4 * 64)) ? 4 : 2;
+    const int tt = (fit >= 8 && T >= 8) ? 8 : (fit >= 4 && T >= 4) ? 4 : 2;
 #define KYB_ROUTER(XT)                                                                                                         \
     return tt == 8 ? launch_router<XT, 8>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st)           \
          : tt == 4 ? launch_router<XT, 4>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st)           \

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import torch
 
+from . import flags as F
 from . import ops
 
 MT = 128                     # rows of one expert per tile = UMMA M
@@ -37,9 +38,11 @@ def gmm(dev, xg: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, S: int, mt: 
     """Sorted grouped product: row r of xg (expert segment e) times expert e of `dev` -> [S, n] (or scattered to rows orow[r])."""
     if mt != MT:
         raise ValueError(f"tiles are {MT} rows (UMMA M)")
+    gs = dev.gs if dev.fmt == "nvfp4" else None
+    if w16 is None and dev.n % 256 == 0 and not F.PREFILL_TWO_STEP:                 # weights decoded inside the grouped GEMM
+        return ops.gemm_kq_grouped(dev.fmt, dev.t16, dev.n, dev.k, dev.E, xg, tb, off, orow, gs, out_rows=out_rows or S)
     if w16 is None:
         w16 = ops.dequant(dev.fmt, dev.t16, dev.nrows, dev.k, torch.float16, 1.0)
-    gs = dev.gs if dev.fmt == "nvfp4" else None
     return ops.gemm_f16_grouped(xg, w16, dev.n, dev.E, tb, off, orow, gs, out_rows=out_rows or S)
 
 

@@ -127,9 +127,14 @@ class DevPack:
         return y
 
     def _prefill(self, x2):
-        """Prefill: weights staged as fp16 exactly like the reference's large-row path (foreign_linear.py:710 `x2 @ self.dequant().T`, fp16 staging
-        at foreign_metal.py:1130-1146), then one tcgen05 GEMM with fp32 accumulation. The NVFP4 per-tensor scale is applied to the fp32
-        accumulator, not folded into the fp16 weights."""
+        """Prefill: one tcgen05 GEMM whose weight operand is decoded from the T16 tiles inside the kernel (fp16 weights in shared memory only, fp32
+        accumulation); role of the reference's large-row path (foreign_linear.py:710 `x2 @ self.dequant().T`). The NVFP4 per-tensor scale is applied to the
+        fp32 accumulator, not folded into the fp16 weights. KYB_PREFILL_TWO_STEP=1 runs the staged form instead (fp16 matrix in HBM, then the fp16 GEMM)."""
+        if F.PREFILL_TWO_STEP:
+            return self._prefill_two_step(x2)
+        return ops.gemm_kq(self.fmt, self.t16, self.n, self.k, x2, self.gscale)
+
+    def _prefill_two_step(self, x2):
         w16 = ops.dequant(self.fmt, self.t16, self.n, self.k, torch.float16, 1.0)
         return ops.gemm_f16(x2, w16, self.gscale)
 
@@ -310,7 +315,7 @@ class ForeignSwitchGLU(torch.nn.Module):
         x2 = x.reshape(T, H).to(torch.float16)
         e32 = inds.reshape(-1).to(torch.int32)
         S = T * K
-        if S <= F.GATHER_MAX:
+        if S <= max(F.GATHER_MAX, F.GATHER_PER_EXPERT * self.g.E):
             y = self._gather_path(x2, e32, K)
         else:
             from . import foreign_kqgmm as KQ

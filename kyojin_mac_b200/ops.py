@@ -258,6 +258,30 @@ def gemm_f16_grouped(a: torch.Tensor, b: torch.Tensor, n: int, E: int, tb: torch
     return d
 
 
+def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, msub: int = 0) -> torch.Tensor:
+    """d fp16 [m, n] = a fp16 [m, k] @ W^T with W decoded from its T16 tiles inside the GEMM (no fp16 copy of W in HBM)."""
+    _need_cuda(t16, a)
+    if a.dtype != torch.float16 or a.dim() != 2 or a.shape[1] != k:
+        raise ValueError(f"gemm_kq takes float16 [m, {k}], got {a.dtype} {tuple(a.shape)}")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    m = a.shape[0]
+    d = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_gemm_kq(_fmt(fmt), t16.data_ptr(), n, k, a.data_ptr(), a.stride(0), m, float(gscale), d.data_ptr(), d.stride(0), msub, _stream()))
+    return d
+
+
+def gemm_kq_grouped(fmt, t16: torch.Tensor, n: int, k: int, E: int, a: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, row_map: torch.Tensor | None = None,
+                    gs: torch.Tensor | None = None, out: torch.Tensor | None = None, out_rows: int | None = None) -> torch.Tensor:
+    """d [rows, n]: sorted rows a fp16 [s, k] of expert segments (off) times the T16 expert stack (E * n rows), decoded inside the GEMM; tile list tb (128 rows)."""
+    _need_cuda(t16, a, tb, off)
+    s = a.shape[0]
+    d = out if out is not None else torch.empty((out_rows or s, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_gemm_kq_grouped(_fmt(fmt), t16.data_ptr(), n, k, E, a.data_ptr(), a.stride(0), s, tb.data_ptr(), off.data_ptr(), _p(row_map), _p(gs),
+                                              d.data_ptr(), d.stride(0), _stream()))
+    return d
+
+
 # ------------------------------------------------------------------------------------------------ NVFP4 tensor-core path
 _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 

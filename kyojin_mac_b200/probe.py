@@ -2,6 +2,7 @@
 
     python -m kyojin_mac_b200.probe gemv q4_k 27648 5120 1        # fmt n k m
     python -m kyojin_mac_b200.probe gemm q3_k 12288 3072 2048     # dequant + tcgen05 GEMM
+    python -m kyojin_mac_b200.probe gemm_kq q3_k 12288 3072 2048  # tcgen05 GEMM with the weights decoded inside (6th argument: msub 1 | 2)
     python -m kyojin_mac_b200.probe gemm_a4 nvfp4 18432 7168 4096 # activation quantiser + block-scaled tcgen05 GEMM
 """
 import sys
@@ -23,6 +24,8 @@ def main(argv):
             y = ops.gemv(fmt, t16, n, k, x)
         elif op == "gemm":
             y = ops.gemm_f16(x, ops.dequant(fmt, t16, n, k, torch.float16))
+        elif op == "gemm_kq":
+            y = ops.gemm_kq(fmt, t16, n, k, x, msub=int(argv[6]) if len(argv) > 6 else 0)
         elif op == "gemm_a4":
             from .foreign_linear import DevPack
             y = DevPack.from_t16(fmt, t16, n, k).apply_a4(x.to(torch.bfloat16))

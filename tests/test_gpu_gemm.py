@@ -60,6 +60,30 @@ def test_linear_prefill_vs_fp64(fmt, rows):
     assert np.abs(y.astype(np.float64) - want).max() <= 4e-3 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4"])
+def test_fused_decode_gemm_vs_staged(fmt):
+    """Weights decoded inside the GEMM: one and two activation blocks per work item give the same bits; NVFP4 equals the staged form bit for bit (its fp16
+    weights are exact), K-quants stay within the accuracy bound and within a few fp16 roundings of the staged form."""
+    n, k, m = 1040, 2048, 520                                               # n and m with ragged last tiles
+    t16 = synth.t16_random_device(fmt, n, k, seed=11)
+    g = torch.Generator(device="cuda").manual_seed(12)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+    y1 = ops.gemm_kq(fmt, t16, n, k, x, msub=1)
+    y2 = ops.gemm_kq(fmt, t16, n, k, x, msub=2)
+    ops.check_device_status()
+    assert torch.equal(y1, y2)
+    w16 = ops.dequant(fmt, t16, n, k, torch.float16)
+    staged = ops.gemm_f16(x, w16)
+    if fmt == "nvfp4":
+        assert torch.equal(y1, staged)
+    want = x.double() @ ops.dequant(fmt, t16, n, k, torch.float32).double().T
+    err = ((y1.double() - want).norm() / want.norm()).item()
+    err_staged = ((staged.double() - want).norm() / want.norm()).item()
+    assert err <= 1e-3 and err <= 2.5 * err_staged + 1e-6, (err, err_staged)
+    ys = ops.gemm_kq(fmt, t16, n, k, x[:3], gscale=0.5)                      # a short block of rows, output scale
+    assert torch.allclose(ys.float(), y1[:3].float() * 0.5, rtol=2e-3, atol=1e-4)
+
+
 def test_gemm_errors():
     a = torch.zeros((128, 96), dtype=torch.float16, device="cuda")
     with pytest.raises(Exception):
