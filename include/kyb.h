@@ -92,10 +92,11 @@ int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, int64_t ldb,
  * matrix never exists in HBM. d fp16 [m, n] = sat(gscale * a fp16 [m, k] x W^T). Same call sites as the two entries above
  * (kyojin_mlx/foreign_linear.py:710 / :737 dense, kyojin_mlx/foreign_kqgmm.py:225-239 `gmm` grouped). Weights are rounded to fp16 at the reference's own rounding
  * points for its few-row tensor kernels (block scale and min to fp16, one fp16 fma per weight: kyojin_mlx/foreign_metal.py:1357-1358, :1382-1383); NVFP4 weights
- * are exact in fp16. msub: 128-row blocks of a per work item, 1 or 2 (0 = chosen by the library). The grouped form needs n % 256 == 0. */
+ * are exact in fp16. msub: 128-row blocks of a per work item, 1 or 2 (0 = chosen by the library). The grouped form needs n % 256 == 0 and tb / off from
+ * kyb_moe_plan with the same mt (128 or 256 rows of one expert per work item). */
 int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub, void* stream);
 int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
-                        const void* row_map, const void* gs, void* d, int64_t ldd, void* stream);
+                        const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream);
 
 /* ---- NVFP4 on the block-scaled tensor-core path.
  * kyb_nvfp4_quant_rows: activations (x_dtype 1 = fp16, 2 = bf16) [rows, k] -> packed e2m1 codes [rows, k/2] (two per byte, low nibble first) + one e4m3 scale per

@@ -82,7 +82,7 @@ SIGNATURES = {
     "kyb_gemv_partial_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "kyb_gemv_finalize": (_int, [_vp, _int, _i64, _i64, _f32, _vp, _i64, _vp]),
     "kyb_gemm_kq": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
-    "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "kyb_dequant_rows_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_router_logits": (_int, [_vp, _int, _i64, _vp, _vp, _i64, _int, _i64, _vp, _i64, _vp]),
     "kyb_q4mma": (_int, [_vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),

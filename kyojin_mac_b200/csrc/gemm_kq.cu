@@ -23,6 +23,9 @@
 #ifndef KYB_KQ_ABL
 #define KYB_KQ_ABL 0          // experiment switches (what limits the decoders); 0 in every shipped build
 #endif
+#ifndef KYB_KQ_PF
+#define KYB_KQ_PF 2           // the next tile's loads are issued before quarter KYB_KQ_PF of the current one
+#endif
 
 namespace kyb {
 
@@ -38,7 +41,7 @@ struct KqParams {
     int rt_total;               // 16-row tiles in the whole T16 buffer (row tiles past it are clamped; their columns are never stored)
     float gscale;
     unsigned int* status;
-    const uint32_t* tb;         // grouped form: first 128-row tile of every expert (E + 1 entries), else null
+    const uint32_t* tb;         // grouped form: first (128 msub)-row tile of every expert (E + 1 entries), else null
     const uint32_t* off;        // grouped form: first sorted row of every expert (E + 1 entries)
     const uint32_t* row_map;    // optional: output row of every sorted row
     const float* gs;            // optional: per-expert output scale
@@ -63,7 +66,7 @@ __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t) {
         return it;
     }
     const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;                              // n fastest: CTAs running together share the activation rows
-    it.n0 = tn * KQ_BN, it.nsub = 1;
+    it.n0 = tn * KQ_BN;
     if ((uint32_t)tm >= p.tb[p.experts]) {
         it.valid = false;
         return it;
@@ -73,8 +76,9 @@ __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t) {
         const int mid = (lo + hi) >> 1;
         if (p.tb[mid] <= (uint32_t)tm) lo = mid; else hi = mid;
     }
-    it.m0 = (int)(p.off[lo] + ((uint32_t)tm - p.tb[lo]) * 128u);
+    it.m0 = (int)(p.off[lo] + ((uint32_t)tm - p.tb[lo]) * (uint32_t)(128 * p.msub));
     it.m_end = (int)p.off[lo + 1];
+    it.nsub = min(p.msub, (it.m_end - it.m0 + 127) >> 7);                                // a segment tail of up to 128 rows runs one block
     it.b_rt0 = (lo * p.n + it.n0) >> 4;
     if (p.gs) it.gscale = p.gs[lo];
     return it;
@@ -101,7 +105,17 @@ __device__ __forceinline__ uint32_t ldg16s(const uint8_t* p) {
     asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
 }
+#if KYB_KQ_ABL & 4
+// experiment: the values are computed and folded into one predicate-guarded store instead of being written
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    if ((x ^ y) == 0x12345678u) asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+#elif KYB_KQ_ABL & 16
+// experiment: stores without the arithmetic (the address still depends on the lane)
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) { asm volatile("st.shared.v2.b32 [%0], {%1, %1};" ::"r"(a), "r"(a) : "memory"); }
+#else
 __device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) { asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory"); }
+#endif
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) { asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
 
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
@@ -164,6 +178,23 @@ __device__ __forceinline__ void kq_load(const uint8_t* tile, int lane, KqTile<FM
 
 // Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus min of
 // the eight 32-input sub-blocks); the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte reads of 8 rows on distinct banks).
+// (lo, hi) fp16 pair -> the two (v, v) pairs, clamped to the finite fp16 range (an overflowing block scale must not turn into inf * 0)
+__device__ __forceinline__ uint32_t h2_clamp(uint32_t a) {
+    __half2 v = *reinterpret_cast<__half2*>(&a);
+    const uint32_t hi_bits = 0x7BFF7BFFu, lo_bits = 0xFBFFFBFFu;
+    v = __hmax2(__hmin2(v, *reinterpret_cast<const __half2*>(&hi_bits)), *reinterpret_cast<const __half2*>(&lo_bits));
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// four byte codes c (unsigned, as (1024 + c) - bias in fp16, exact) times the fp16 pair d2 -> four (v, v) pairs; fp16(d * code) is the single rounding of the
+// exact product, the same value as the float32 product rounded to fp16
+__device__ __forceinline__ uint4 kq_scale4(uint32_t codes, uint32_t bias2, uint32_t d2) {
+    const uint32_t a = h2_clamp(h2_mul(h2_sub(prmt(codes, 0x64646464u, 0x4140u), bias2), d2));
+    const uint32_t b = h2_clamp(h2_mul(h2_sub(prmt(codes, 0x64646464u, 0x4342u), bias2), d2));
+    return make_uint4(prmt(a, 0u, 0x1010u), prmt(a, 0u, 0x3232u), prmt(b, 0u, 0x1010u), prmt(b, 0u, 0x3232u));
+}
+
+// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus min of
+// the eight 32-input sub-blocks); the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte reads of 8 rows on distinct banks).
 template <int FMT>
 __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t scr, int lane) {
     const int r = lane >> 1, hf = lane & 1;
@@ -171,34 +202,32 @@ __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t s
         const uint4 mt = tr.sc;
         const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const uint32_t mnw = ((hf ? mt.w >> 4 : mt.z) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.z >> 2) & (hf ? 0x30303030u : 0u));
-        const float d = half_bits_to_float(mt.x & 0xffffu), dm = -half_bits_to_float(mt.x >> 16);
-        uint4 s, z;
-        s.x = h2_splat(d * (float)(scw & 255u)), s.y = h2_splat(d * (float)((scw >> 8) & 255u)), s.z = h2_splat(d * (float)((scw >> 16) & 255u)), s.w = h2_splat(d * (float)(scw >> 24));
-        z.x = h2_splat(dm * (float)(mnw & 255u)), z.y = h2_splat(dm * (float)((mnw >> 8) & 255u)), z.z = h2_splat(dm * (float)((mnw >> 16) & 255u)), z.w = h2_splat(dm * (float)(mnw >> 24));
-        sts128(scr + r * 32 + 16 * hf, s);
-        sts128(scr + 512 + r * 32 + 16 * hf, z);
+        const uint32_t d2 = prmt(mt.x, 0u, 0x1010u), dm2 = prmt(mt.x, 0u, 0x3232u) ^ 0x80008000u;           // (d, d) and (-dmin, -dmin)
+        sts128(scr + r * 32 + 16 * hf, kq_scale4(scw, 0x64006400u, d2));
+        sts128(scr + 512 + r * 32 + 16 * hf, kq_scale4(mnw, 0x64006400u, dm2));
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+        const uint32_t d2 = prmt(tr.d16, 0u, 0x1010u);
+        // int8 scale + 128 as an unsigned byte, bias 1024 + 128
+        sts128(scr + r * 80 + 32 * hf, kq_scale4(tr.sc.x ^ 0x80808080u, 0x64806480u, d2));
+        sts128(scr + r * 80 + 32 * hf + 16, kq_scale4(tr.sc.y ^ 0x80808080u, 0x64806480u, d2));
+    } else if constexpr (FMT == KYB_FMT_Q3_K) {
+        const uint32_t w0 = tr.sc.x, w1 = tr.sc.y, w2 = tr.sc.z;
+        const uint32_t ga = hf ? (((w0 >> 4) & 0x0f0f0f0fu) | (w2 & 0x30303030u)) : ((w0 & 0x0f0f0f0fu) | ((w2 << 4) & 0x30303030u));
+        const uint32_t gb = hf ? (((w1 >> 4) & 0x0f0f0f0fu) | ((w2 >> 2) & 0x30303030u)) : ((w1 & 0x0f0f0f0fu) | ((w2 << 2) & 0x30303030u));
+        const uint32_t d2 = prmt(tr.d16, 0u, 0x1010u);
+        sts128(scr + r * 80 + 32 * hf, kq_scale4(ga, 0x64206420u, d2));                                     // 6-bit scale - 32
+        sts128(scr + r * 80 + 32 * hf + 16, kq_scale4(gb, 0x64206420u, d2));
     } else {
-        float v[8];
-        if constexpr (FMT == KYB_FMT_Q6_K) {
-            const float d = half_bits_to_float(tr.d16);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = d * (float)(int)(int8_t)(((j < 4 ? tr.sc.x : tr.sc.y) >> (8 * (j & 3))) & 255u);
-        } else if constexpr (FMT == KYB_FMT_Q3_K) {
-            const uint32_t w0 = tr.sc.x, w1 = tr.sc.y, w2 = tr.sc.z;
-            const uint32_t ga = hf ? (((w0 >> 4) & 0x0f0f0f0fu) | (w2 & 0x30303030u)) : ((w0 & 0x0f0f0f0fu) | ((w2 << 4) & 0x30303030u));
-            const uint32_t gb = hf ? (((w1 >> 4) & 0x0f0f0f0fu) | ((w2 >> 2) & 0x30303030u)) : ((w1 & 0x0f0f0f0fu) | ((w2 << 2) & 0x30303030u));
-            const float d = half_bits_to_float(tr.d16);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = d * (float)((int)(((j < 4 ? ga : gb) >> (8 * (j & 3))) & 255u) - 32);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = e4m3_unsigned((j < 4 ? tr.sc.x : tr.sc.y) >> (8 * (j & 3)));
-        }
-        uint4 a, b;
-        a.x = h2_splat(v[0]), a.y = h2_splat(v[1]), a.z = h2_splat(v[2]), a.w = h2_splat(v[3]);
-        b.x = h2_splat(v[4]), b.y = h2_splat(v[5]), b.z = h2_splat(v[6]), b.w = h2_splat(v[7]);
-        sts128(scr + r * 80 + 32 * hf, a);
-        sts128(scr + r * 80 + 32 * hf + 16, b);
+        // e4m3 magnitude (7 bits) << 7 is the fp16 of value * 2^-8; code 0x7F decodes to 0
+        auto four = [](uint32_t w) -> uint4 {
+            w &= 0x7f7f7f7fu;
+            const uint32_t is7f = ((w + 0x01010101u) & 0x80808080u) >> 7;                                    // 1 in every byte that is 0x7F
+            w ^= is7f * 0x7fu;
+            const uint32_t a = h2_mul(prmt(w, 0u, 0x4140u) << 7, 0x5C005C00u), b = h2_mul(prmt(w, 0u, 0x4342u) << 7, 0x5C005C00u);   // * 2^8, exact
+            return make_uint4(prmt(a, 0u, 0x1010u), prmt(a, 0u, 0x3232u), prmt(b, 0u, 0x1010u), prmt(b, 0u, 0x3232u));
+        };
+        sts128(scr + r * 80 + 32 * hf, four(tr.sc.x));
+        sts128(scr + r * 80 + 32 * hf + 16, four(tr.sc.y));
     }
 }
 
@@ -424,16 +453,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             if (!it.valid) continue;
             const int rt = min(it.b_rt0 + dw, p.rt_total - 1);
             const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
-            KqTile<FMT> cur, nxt;
-            kq_load<FMT>(tp, lane, cur);
-            for (int kb = 0; kb < p.nb && !failed; ++kb) {
-#if KYB_KQ_ABL & 1
-                nxt = cur;
-#else
-                if (kb + 1 < p.nb) kq_load<FMT>(tp + (size_t)(kb + 1) * TB, lane, nxt);     // in flight while this tile is decoded
-#endif
-                kq_prep_scales<FMT>(cur, scr, lane);
-                __syncwarp();
+            KqTile<FMT> ta, tb_;
+            kq_load<FMT>(tp, lane, ta);
 #define KYB_KQ_QUARTER(P)                                                                                         \
     {                                                                                                             \
         if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
@@ -444,14 +465,29 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         if (lane == 0) mbar_arrive_a(full0 + 8 * s);                                                              \
         if (++s == STAGES) s = 0, parity ^= 1u;                                                                   \
     }
+#define KYB_KQ_PREFETCH(AT)                                                                                       \
+    if (KYB_KQ_PF == AT && !(KYB_KQ_ABL & 1) && kb + 1 < p.nb) kq_load<FMT>(tp + (size_t)(kb + 1) * TB, lane, nxt);
+            // one T16 tile from registers; the next tile's loads are issued part-way through so that they are in flight for two quarters, not four
+            // (a wait on a shared-memory result can share a scoreboard with loads still in flight)
+            auto tile = [&](const KqTile<FMT>& cur, KqTile<FMT>& nxt, const int kb) {
+                KYB_KQ_PREFETCH(0)
+                kq_prep_scales<FMT>(cur, scr, lane);
+                __syncwarp();
                 KYB_KQ_QUARTER(0)
+                KYB_KQ_PREFETCH(1)
                 KYB_KQ_QUARTER(1)
+                KYB_KQ_PREFETCH(2)
                 KYB_KQ_QUARTER(2)
+                KYB_KQ_PREFETCH(3)
                 KYB_KQ_QUARTER(3)
-#undef KYB_KQ_QUARTER
                 __syncwarp();                                                        // the scratch is rewritten for the next tile
-                cur = nxt;
+            };
+            for (int kb = 0; kb < p.nb && !failed; kb += 2) {                        // two register sets alternate: no copies between them
+                tile(ta, tb_, kb);
+                if (kb + 1 < p.nb && !failed) tile(tb_, ta, kb + 1);
             }
+#undef KYB_KQ_QUARTER
+#undef KYB_KQ_PREFETCH
         }
     }
     if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
@@ -521,10 +557,12 @@ extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const
 }
 
 // Grouped form for routed experts: a fp16 [s, k] rows sorted by expert (segment e = rows [off[e], off[e + 1])), T16 of the expert stack (experts * n rows),
-// tb / off from kyb_moe_plan with mt = 128, row_map (optional, u32 [s]) = output row of each sorted row, gs (optional) per-expert output scale. d [*, n].
-// The item list is sized for the worst case (s / 128 + experts tiles per 256 output columns); items past tb[experts] are skipped.
+// tb / off from kyb_moe_plan with the same mt (128 or 256 rows of one expert per work item: with 256 a decoded weight tile serves up to two 128-row blocks, so an
+// expert with 129..256 rows is decoded once, not twice), row_map (optional, u32 [s]) = output row of each sorted row, gs (optional) per-expert output scale.
+// d [*, n]. The item list is sized for the worst case (s / mt + experts tiles per 256 output columns); items past tb[experts] are skipped.
 extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
-                                   const void* row_map, const void* gs, void* d, int64_t ldd, void* stream) {
+                                   const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream) {
+    KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
     KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,
@@ -541,7 +579,7 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     p.t16 = (const uint8_t*)t16, p.d = (__half*)d, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256);
     p.rt_total = (int)((int64_t)experts * n / 16);
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
-    p.msub = 1;
-    p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + 127) / 128) + experts;
+    p.msub = mt / 128;
+    p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
     return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }

@@ -10,7 +10,13 @@ import torch
 from . import flags as F
 from . import ops
 
-MT = 128                     # rows of one expert per tile = UMMA M
+MT = 128                     # rows of one expert per tile of the staged fp16 grouped GEMM = UMMA M
+MT_FUSED = 256               # rows of one expert per work item when the weights are decoded inside the GEMM: one decode serves two 128-row blocks
+
+
+def fused_ok(dev) -> bool:
+    """The expert stack can go through the grouped GEMM that decodes its T16 tiles in the kernel."""
+    return dev.n % 256 == 0 and not F.PREFILL_TWO_STEP
 
 
 def csort(e32: torch.Tensor, E: int, mt: int = MT):
@@ -36,19 +42,23 @@ def silu_perm(a: torch.Tensor, b: torch.Tensor, xperm=None, limit=None) -> torch
 
 def gmm(dev, xg: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, S: int, mt: int = MT, orow=None, out_rows=None, w16=None) -> torch.Tensor:
     """Sorted grouped product: row r of xg (expert segment e) times expert e of `dev` -> [S, n] (or scattered to rows orow[r])."""
-    if mt != MT:
-        raise ValueError(f"tiles are {MT} rows (UMMA M)")
     gs = dev.gs if dev.fmt == "nvfp4" else None
-    if w16 is None and dev.n % 256 == 0 and not F.PREFILL_TWO_STEP:                 # weights decoded inside the grouped GEMM
-        return ops.gemm_kq_grouped(dev.fmt, dev.t16, dev.n, dev.k, dev.E, xg, tb, off, orow, gs, out_rows=out_rows or S)
+    if w16 is None and fused_ok(dev):                                                # weights decoded inside the grouped GEMM; tb counts mt-row tiles
+        if mt not in (128, 256):
+            raise ValueError("work items are 128 or 256 rows of one expert")
+        return ops.gemm_kq_grouped(dev.fmt, dev.t16, dev.n, dev.k, dev.E, xg, tb, off, orow, gs, out_rows=out_rows or S, mt=mt)
+    if mt != MT:
+        raise ValueError(f"tiles of the staged form are {MT} rows (UMMA M)")
     if w16 is None:
         w16 = ops.dequant(dev.fmt, dev.t16, dev.nrows, dev.k, torch.float16, 1.0)
     return ops.gemm_f16_grouped(xg, w16, dev.n, dev.E, tb, off, orow, gs, out_rows=out_rows or S)
 
 
-def mlp(glu, x2: torch.Tensor, e32: torch.Tensor, K: int, mt: int = MT) -> torch.Tensor:
+def mlp(glu, x2: torch.Tensor, e32: torch.Tensor, K: int, mt: int | None = None) -> torch.Tensor:
     """Routed SwiGLU MLP on sorted slots -> unweighted per-slot outputs [S, H] in slot order (foreign_kqgmm.py:293-314)."""
     S = e32.numel()
+    if mt is None:
+        mt = MT_FUSED if all(fused_ok(d) for d in (glu.g, glu.u, glu.d)) else MT
     order, tb, off = csort(e32, glu.g.E, mt)
     xg = gather_perm(x2, order, K)
     a = gmm(glu.g, xg, tb, off, S, mt)

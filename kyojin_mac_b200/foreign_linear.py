@@ -319,7 +319,7 @@ class ForeignSwitchGLU(torch.nn.Module):
             y = self._gather_path(x2, e32, K)
         else:
             from . import foreign_kqgmm as KQ
-            y = KQ.mlp(self, x2, e32, K, F.KQ_MT)
+            y = KQ.mlp(self, x2, e32, K)
         return y.reshape(*lead, K, self.d.n)
 
     def _gather_path(self, x2, e32, K):

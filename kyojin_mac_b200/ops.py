@@ -272,13 +272,14 @@ def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: flo
 
 
 def gemm_kq_grouped(fmt, t16: torch.Tensor, n: int, k: int, E: int, a: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, row_map: torch.Tensor | None = None,
-                    gs: torch.Tensor | None = None, out: torch.Tensor | None = None, out_rows: int | None = None) -> torch.Tensor:
-    """d [rows, n]: sorted rows a fp16 [s, k] of expert segments (off) times the T16 expert stack (E * n rows), decoded inside the GEMM; tile list tb (128 rows)."""
+                    gs: torch.Tensor | None = None, out: torch.Tensor | None = None, out_rows: int | None = None, mt: int = 256) -> torch.Tensor:
+    """d [rows, n]: sorted rows a fp16 [s, k] of expert segments (off) times the T16 expert stack (E * n rows), decoded inside the GEMM; tile list tb of mt-row
+    tiles (moe_plan with the same mt, 128 or 256)."""
     _need_cuda(t16, a, tb, off)
     s = a.shape[0]
     d = out if out is not None else torch.empty((out_rows or s, n), dtype=torch.float16, device=a.device)
     _lib.check(_lib.lib().kyb_gemm_kq_grouped(_fmt(fmt), t16.data_ptr(), n, k, E, a.data_ptr(), a.stride(0), s, tb.data_ptr(), off.data_ptr(), _p(row_map), _p(gs),
-                                              d.data_ptr(), d.stride(0), _stream()))
+                                              d.data_ptr(), d.stride(0), mt, _stream()))
     return d
 
 

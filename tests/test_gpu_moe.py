@@ -138,16 +138,17 @@ def test_switch_glu_block_vs_fp64(T, K):
     np.testing.assert_allclose(c16.float().cpu().numpy(), M.combine(y.reshape(T * K, H).cpu().numpy(), scs.cpu().numpy(), K).astype(np.float32), rtol=1e-3, atol=1e-3)
 
 
-def test_grouped_gemm_equals_per_expert():
+@pytest.mark.parametrize("mt", [128, 256])
+def test_grouped_gemm_equals_per_expert(mt):
     E, n, k, S = 5, 256, 512, 700
     dev, W = _stack("q3_k", E, n, k, 20)
     rng = np.random.default_rng(21)
     e = rng.integers(0, E, S).astype(np.int32)
     e[e == 1] = 0                                                             # an expert without rows
     x = synth.activations(S, k, rng)
-    order, tb, off = KQ.csort(torch.from_numpy(e).cuda(), E)
+    order, tb, off = KQ.csort(torch.from_numpy(e).cuda(), E, mt)
     xg = KQ.gather_perm(torch.from_numpy(x).cuda(), order, 1)
-    y = KQ.gmm(dev, xg, tb, off, S, orow=order)                               # scattered back to slot order
+    y = KQ.gmm(dev, xg, tb, off, S, mt, orow=order)                               # scattered back to slot order
     ops.check_device_status()
     yn = y.cpu().numpy()
     for ex in range(E):
