@@ -88,6 +88,20 @@ int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int6
 int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t s, int64_t n, int64_t k, int experts, const void* tb,
                          const void* off, const void* row_map, const void* gs, void* d, int64_t ldd, void* stream);
 
+/* ---- GEMM + all-gather in one kernel (N-sharded linear, one process per GPU): the epilogue stores every output tile into the [m, ld] output matrix of EVERY rank
+ * (plain 16-byte stores to peer-mapped addresses over NVLink, own rank included) at column col0 = first output column of this rank's shard, so the slices are
+ * gathered while the tensor cores work on the next tiles. The caller provides the peer-mapped base pointers (e.g. CUDA IPC or symmetric-memory mappings) and
+ * synchronises the ranks around the call (all ranks must have finished reading the previous contents before, all kernels must have completed after). No
+ * counterpart in the reference (it runs on one device); this is the N-sharding of the benchmark's multi-GPU configurations. */
+typedef struct kyb_peer_out {
+    void* ptr[8];   /* base address of the output matrix on rank i, as mapped into this process */
+    int count;      /* ranks, 1..8 */
+} kyb_peer_out;
+int kyb_gemm_kq_ag(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, const kyb_peer_out* out, int64_t ldd, int64_t col0,
+                   int msub, void* stream);
+int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                      const kyb_peer_out* out, int64_t ldd, int64_t col0, void* stream);
+
 /* ---- prefill GEMM with the dequantisation fused into the tensor-core operand producer: weights are read as T16 tiles and decoded into shared memory, the fp16
  * matrix never exists in HBM. d fp16 [m, n] = sat(gscale * a fp16 [m, k] x W^T). Same call sites as the two entries above
  * (kyojin_mlx/foreign_linear.py:710 / :737 dense, kyojin_mlx/foreign_kqgmm.py:225-239 `gmm` grouped). Weights are rounded to fp16 at the reference's own rounding

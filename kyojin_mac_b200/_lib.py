@@ -65,6 +65,24 @@ _lock = threading.Lock()
 _lib = None
 
 _vp, _i64, _sz, _int, _f32 = C.c_void_p, C.c_int64, C.c_size_t, C.c_int, C.c_float
+
+
+class PeerOut(C.Structure):
+    """kyb_peer_out: base address of the output matrix on every rank (peer-mapped), and the rank count."""
+    _fields_ = [("ptr", C.c_void_p * 8), ("count", C.c_int)]
+
+    @classmethod
+    def of(cls, ptrs):
+        if not 1 <= len(ptrs) <= 8:
+            raise ValueError("1..8 peer outputs")
+        o = cls()
+        for i, p in enumerate(ptrs):
+            o.ptr[i] = int(p)
+        o.count = len(ptrs)
+        return o
+
+
+_pp = C.POINTER(PeerOut)
 SIGNATURES = {
     "kyb_version": (_int, []),
     "kyb_status_string": (C.c_char_p, [_int]),
@@ -82,6 +100,8 @@ SIGNATURES = {
     "kyb_gemv_partial_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "kyb_gemv_finalize": (_int, [_vp, _int, _i64, _i64, _f32, _vp, _i64, _vp]),
     "kyb_gemm_kq": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
+    "kyb_gemm_kq_ag": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _pp, _i64, _i64, _int, _vp]),
+    "kyb_gemm_nvfp4_ag": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _pp, _i64, _i64, _vp]),
     "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "kyb_dequant_rows_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_router_logits": (_int, [_vp, _int, _i64, _vp, _vp, _i64, _int, _i64, _vp, _i64, _vp]),

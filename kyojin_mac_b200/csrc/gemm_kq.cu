@@ -35,7 +35,8 @@ constexpr uint32_t KQ_SCR = 1280;                       // per decoder warp: blo
 
 struct KqParams {
     const uint8_t* t16;
-    __half* d;
+    __half* d[8];               // output matrix on every rank that receives the tiles (one entry without sharding), already offset to this rank's first column
+    int nout;
     int64_t ldd;
     int m, n, k, nb;            // rows of A, rows of one W matrix, inputs, 256-input blocks
     int rt_total;               // 16-row tiles in the whole T16 buffer (row tiles past it are clamped; their columns are never stored)
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                 tc_fence_after();
                 const int row = it.m0 + sub * 128 + q * 32 + lane;
                 const size_t orow = (p.row_map && row < it.m_end) ? (size_t)p.row_map[row] : (size_t)row;
-                __half* drow = p.d + orow * p.ldd + it.n0;
+                const size_t doff = orow * p.ldd + it.n0;
                 const float gscale = it.gscale;
 #pragma unroll 1
                 for (int c = 0; c < KQ_BN; c += 32) {
@@ -424,11 +425,12 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                                 __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * gscale), sat_half(__uint_as_float(v[j + 5]) * gscale));
                                 __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * gscale), sat_half(__uint_as_float(v[j + 7]) * gscale));
                                 o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(drow + c + j) = o;
+                                for (int pr = 0; pr < p.nout; ++pr) *reinterpret_cast<uint4*>(p.d[pr] + doff + c + j) = o;
                             }
                         } else {
                             for (int j = 0; j < 32; ++j)
-                                if (it.n0 + c + j < p.n) drow[c + j] = sat_half(__uint_as_float(v[j]) * gscale);
+                                if (it.n0 + c + j < p.n)
+                                    for (int pr = 0; pr < p.nout; ++pr) p.d[pr][doff + c + j] = sat_half(__uint_as_float(v[j]) * gscale);
                         }
                     }
                 }
@@ -533,15 +535,13 @@ int kq_launch(int fmt, const CUtensorMap& ta, kyb::KqParams p, int num_items, cu
 
 }  // namespace
 
-// D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub: 1 or 2 blocks of 128
-// activation rows per work item (0 = chosen here).
-extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub,
-                           void* stream) {
+static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd, int msub,
+                    void* stream) {
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
-    KYB_REQUIRE(t16 && a && d, "null pointer");
+    KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
-    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0 && ((uintptr_t)d & 1) == 0, "a and t16 must be 16-byte aligned");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0, "a and t16 must be 16-byte aligned");
     KYB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 24), "dimension too large");
     KYB_REQUIRE(msub >= 0 && msub <= 2, "msub is 0 (automatic), 1 or 2");
     unsigned int* status = kyb_device_status_word();
@@ -549,11 +549,35 @@ extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const
     CUtensorMap ta;
     if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda * 2, 128, kyb::KQ_BK)) return rc;
     kyb::KqParams p;
-    p.t16 = (const uint8_t*)t16, p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256), p.rt_total = (int)((n + 15) / 16);
+    p.t16 = (const uint8_t*)t16, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256), p.rt_total = (int)((n + 15) / 16);
+    p.nout = nout;
+    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] : nullptr;
     p.gscale = gscale, p.status = status, p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
     p.msub = msub ? msub : (m > 128 ? 2 : 1);
     p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN), p.tiles_m = (int)((m + 128 * p.msub - 1) / (128 * p.msub));
     return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+}
+
+// D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub: 1 or 2 blocks of 128
+// activation rows per work item (0 = chosen here).
+extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub,
+                           void* stream) {
+    KYB_REQUIRE(d && ((uintptr_t)d & 1) == 0, "null or odd output pointer");
+    void* outs[1] = {d};
+    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, 1, ldd, msub, stream);
+}
+
+// The same product with the all-gather of an N-sharded linear folded into the epilogue: every tile goes to the output matrix of every rank, at column col0.
+extern "C" int kyb_gemm_kq_ag(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, const kyb_peer_out* out, int64_t ldd,
+                              int64_t col0, int msub, void* stream) {
+    KYB_REQUIRE(out && out->count >= 1 && out->count <= 8, "peer outputs: 1..8 ranks");
+    KYB_REQUIRE(col0 >= 0 && col0 % 8 == 0 && col0 + n <= ldd && ldd % 8 == 0, "col0=%lld: a multiple of 8 with col0 + n <= ldd, ldd a multiple of 8", (long long)col0);
+    void* outs[8];
+    for (int i = 0; i < out->count; ++i) {
+        KYB_REQUIRE(out->ptr[i] && ((uintptr_t)out->ptr[i] & 15) == 0, "peer output %d is null or not 16-byte aligned", i);
+        outs[i] = (__half*)out->ptr[i] + col0;
+    }
+    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, out->count, ldd, msub, stream);
 }
 
 // Grouped form for routed experts: a fp16 [s, k] rows sorted by expert (segment e = rows [off[e], off[e + 1])), T16 of the expert stack (experts * n rows),
@@ -576,7 +600,9 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     CUtensorMap ta;
     if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)s, (uint64_t)k, (uint64_t)lda * 2, 128, kyb::KQ_BK)) return rc;
     kyb::KqParams p;
-    p.t16 = (const uint8_t*)t16, p.d = (__half*)d, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256);
+    p.t16 = (const uint8_t*)t16, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256);
+    p.nout = 1;
+    for (int i = 0; i < 8; ++i) p.d[i] = i == 0 ? (__half*)d : nullptr;
     p.rt_total = (int)((int64_t)experts * n / 16);
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     p.msub = mt / 128;

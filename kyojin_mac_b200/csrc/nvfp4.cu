@@ -98,7 +98,8 @@ constexpr uint32_t NV_STAGE_BYTES = NV_A_BYTES + NV_B_BYTES + NV_SFA_BYTES + NV_
 struct NvGemmParams {
     const uint8_t* sfa;      // SF512 of A [m_pad / 128][k / 64][512]
     const uint8_t* sfb;      // SF512 of B
-    __half* d;
+    __half* d[8];            // output matrix on every receiving rank (one entry without sharding), already offset to this rank's first column
+    int nout;
     int64_t ldd;
     int m, n, k;
     float gscale;
@@ -214,7 +215,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
             if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
-            __half* drow = p.d + (size_t)row * p.ldd + n0;
+            const size_t doff = (size_t)row * p.ldd + n0;
             const bool vec = (p.ldd & 7) == 0;
 #pragma unroll 1
             for (int c = 0; c < NV_BN; c += 32) {
@@ -237,13 +238,15 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                                     w[e] = *reinterpret_cast<uint32_t*>(&h);
                                 }
                             }
-                            *reinterpret_cast<uint4*>(drow + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int pr = 0; pr < p.nout; ++pr) *reinterpret_cast<uint4*>(p.d[pr] + doff + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
                         for (int j = 0; j < 32 && n0 + c + j < p.n; ++j) {
                             const float f = __uint_as_float(v[j]) * p.gscale;
-                            if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(drow)[c + j] = __float2bfloat16_rn(f);
-                            else drow[c + j] = sat_half(f);
+                            for (int pr = 0; pr < p.nout; ++pr) {
+                                if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.d[pr])[doff + c + j] = __float2bfloat16_rn(f);
+                                else p.d[pr][doff + c + j] = sat_half(f);
+                            }
                         }
                     }
                 }
@@ -307,9 +310,9 @@ extern "C" int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* 
 }
 
 // D [m, n] = sat(gscale * A B^T): a_codes [m, k/2], b_codes [n, k/2] packed e2m1 (two per byte, low nibble first), sfa / sfb in the SF512 layout.
-extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
-                              void* d, int64_t ldd, void* stream) {
-    KYB_REQUIRE(a_codes && sfa && b_codes && sfb && d, "null pointer");
+static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                           void* const* d, int nout, int64_t ldd, void* stream) {
+    KYB_REQUIRE(a_codes && sfa && b_codes && sfb, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(n % 256 == 0, "n=%lld must be a multiple of 256 (one CTA covers two 128-row scale chunks of B)", (long long)n);
     KYB_REQUIRE(ldd >= n && (out_dtype == 1 || out_dtype == 2), "ldd >= n, out_dtype 1 = fp16 or 2 = bf16");
@@ -320,8 +323,9 @@ extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* 
     if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a_codes, (uint64_t)m, (uint64_t)(k / 2), (uint64_t)(k / 2), kyb::NV_BM, 128)) return rc;
     if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_codes, (uint64_t)n, (uint64_t)(k / 2), (uint64_t)(k / 2), kyb::NV_BN, 128)) return rc;
     kyb::NvGemmParams p;
-    p.sfa = (const uint8_t*)sfa, p.sfb = (const uint8_t*)sfb, p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale;
-    p.out_bf16 = out_dtype == 2, p.status = status;
+    p.sfa = (const uint8_t*)sfa, p.sfb = (const uint8_t*)sfb, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale;
+    p.out_bf16 = out_dtype == 2, p.status = status, p.nout = nout;
+    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] : nullptr;
     constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
     static std::mutex mu;
     static unsigned done = 0;
@@ -339,4 +343,24 @@ extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* 
     const int tiles_n = (int)((n + kyb::NV_BN - 1) / kyb::NV_BN), num_tiles = tiles_n * (int)((m + kyb::NV_BM - 1) / kyb::NV_BM);
     kyb::gemm_nvfp4_kernel<<<(unsigned)(num_tiles < sms ? num_tiles : sms), kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, p, tiles_n, num_tiles);
     return kyb_launch_check("gemm_nvfp4");
+}
+
+extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                              void* d, int64_t ldd, void* stream) {
+    KYB_REQUIRE(d, "null pointer");
+    void* outs[1] = {d};
+    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, 1, ldd, stream);
+}
+
+// The same product with the all-gather of an N-sharded linear folded into the epilogue: every tile goes to the output matrix of every rank, at column col0.
+extern "C" int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
+                                 const kyb_peer_out* out, int64_t ldd, int64_t col0, void* stream) {
+    KYB_REQUIRE(out && out->count >= 1 && out->count <= 8, "peer outputs: 1..8 ranks");
+    KYB_REQUIRE(col0 >= 0 && col0 % 8 == 0 && col0 + n <= ldd && ldd % 8 == 0, "col0=%lld: a multiple of 8 with col0 + n <= ldd, ldd a multiple of 8", (long long)col0);
+    void* outs[8];
+    for (int i = 0; i < out->count; ++i) {
+        KYB_REQUIRE(out->ptr[i] && ((uintptr_t)out->ptr[i] & 15) == 0, "peer output %d is null or not 16-byte aligned", i);
+        outs[i] = (__half*)out->ptr[i] + col0;
+    }
+    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, out->count, ldd, stream);
 }

@@ -56,6 +56,50 @@ class ShardedLinear:
         return torch.cat([out[r, :, :s] for r, s in enumerate(self.splits)], dim=1)
 
 
+class FusedShardedLinear:
+    """N-sharded prefill linear whose GEMM writes every output tile into the output matrix of EVERY rank (peer stores over NVLink from the epilogue), so the
+    all-gather overlaps the tensor-core work tile by tile; one device-side barrier per call tells the ranks that all tiles have landed. `dev` is this rank's DevPack
+    shard (rows [row0, row0 + dev.n) of the [n_total, k] matrix, shard_rows with whole 16-row tiles). a4 = True runs the NVFP4 W4A4 path (activations quantised on
+    the fly). Outputs live in two alternating symmetric-memory buffers of max_rows rows: the tensor returned by call c is valid until call c + 2, and the
+    consumer must read it on the stream of the call. Rows <= 32 (decode) are served by ShardedLinear (GEMV + NCCL all-gather): they are latency-bound either way."""
+
+    def __init__(self, dev, n_total: int, max_rows: int, group=None, a4: bool = False, out_dtype=torch.float16):
+        import torch.distributed._symmetric_memory as symm
+        self.dev, self.n, self.group, self.a4, self.out_dtype = dev, n_total, group or dist.group.WORLD, a4, out_dtype
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        align = 256 if a4 else 16
+        self.col0, rows = shard_rows(n_total, self.world, self.rank, align)
+        if rows != dev.n:
+            raise ValueError(f"this rank's shard has {dev.n} rows, shard_rows gives {rows}")
+        if n_total % 8:
+            raise ValueError("the gathered width must be a multiple of 8")
+        self.bufs = [symm.empty((max_rows, n_total), dtype=out_dtype, device=dev.t16.device) for _ in range(2)]
+        self.hdls = [symm.rendezvous(b, self.group) for b in self.bufs]
+        self.turn = 0
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        from . import ops
+        m = x.shape[0]
+        i, self.turn = self.turn, self.turn ^ 1
+        buf, hdl = self.bufs[i], self.hdls[i]
+        if m > buf.shape[0]:
+            raise ValueError(f"{m} rows exceed the buffer of {buf.shape[0]}")
+        ptrs = list(hdl.buffer_ptrs)
+        d = self.dev
+        if self.a4:
+            qs, sfb = d._a4_operands()
+            if x.dtype not in (torch.float16, torch.bfloat16):
+                x = x.to(torch.bfloat16)
+            codes, _, asw = ops.nvfp4_quant_rows(x.contiguous(), swizzled=True, plain=False)
+            ops.gemm_nvfp4_ag(codes, asw, qs, sfb, m, d.n, d.k, ptrs, self.n, self.col0, d.gscale, self.out_dtype)
+        else:
+            if self.out_dtype != torch.float16:
+                raise ValueError("the K-quant GEMM writes float16")
+            ops.gemm_kq_ag(d.fmt, d.t16, d.n, d.k, x.to(torch.float16), ptrs, self.n, self.col0, d.gscale)
+        hdl.barrier()                                                        # every rank's tiles have landed in every buffer
+        return buf[:m]
+
+
 # ------------------------------------------------------------------------------------------------ routed experts: expert parallelism
 def expert_range(E: int, world: int, rank: int):
     base, extra = divmod(E, world)
@@ -95,5 +139,8 @@ def ep_moe(x: torch.Tensor, inds: torch.Tensor, scs: torch.Tensor, E: int, local
     dist.all_to_all_single(y_back, y_recv.contiguous(), sc, rc, group=group)
     y_slots = torch.empty_like(y_back)
     y_slots[order] = y_back                                                  # back to slot order (t K + k)
+    if y_slots.is_cuda and y_slots.dtype == torch.float16 and out_dtype in (torch.float16, torch.float32):
+        from . import ops
+        return ops.moe_combine(y_slots, scs.reshape(-1).to(torch.float32).contiguous(), K, dtype=out_dtype)
     w = scs.reshape(T, K, 1).to(torch.float32)
     return (y_slots.reshape(T, K, -1).to(torch.float32) * w).sum(1).to(out_dtype)

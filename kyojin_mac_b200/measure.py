@@ -4,6 +4,8 @@
     python -m kyojin_mac_b200.measure cfg2            # Q3_K prefill GEMM, M = 2048, 3072 -> 12288 and 12288 -> 3072
     python -m kyojin_mac_b200.measure cfg3            # NVFP4 prefill GEMM, 4096 x 7168 -> 18432, activations quantised on the fly
     python -m kyojin_mac_b200.measure cfg4 [E]        # routed-expert layer, E (default 256) experts, top-8, hidden 7168, T = 64 and 4096
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 -m kyojin_mac_b200.measure dist
+                                                      # cfg 2 / 3 N-sharded with all-gather, cfg 4 expert-parallel with all-to-all, on N GPUs
 
 Device time by CUDA events on the current stream, after warm-up, minimum and median over the repetitions. Synthetic seeded weights."""
 import json
@@ -130,6 +132,84 @@ def cfg4(E=256):
         print(json.dumps(rec), flush=True)
 
 
+def dist_cases(E=256):
+    """Sharded configurations under torchrun (one rank per GPU, NCCL): cfg 2 and cfg 3 column-sharded over N with an all-gather of the output slices, cfg 4
+    expert-parallel with all-to-all dispatch and combine. Strong scaling (the problem is fixed, each rank holds 1 / world of the weights). Times are the maximum
+    over ranks of CUDA-event durations; rank 0 prints."""
+    import os
+    import torch.distributed as dist
+    from . import dist as D
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def tmax(fn, iters=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) * 1e3], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts.append(float(t))
+        return statistics.median(ts)
+
+    def say(**kw):
+        if rank == 0:
+            print(json.dumps(dict(n_gpus=world, **kw)), flush=True)
+
+    m = 2048
+    gen = torch.Generator(device="cuda").manual_seed(7)                      # the same activations on every rank
+    for n, k in ((12288, 3072), (3072, 12288)):
+        row0, rows = D.shard_rows(n, world, rank)
+        dp = DevPack.from_t16("q3_k", synth.t16_random_device("q3_k", rows, k, seed=100 + rank), rows, k)
+        lin = D.ShardedLinear(dp.apply, n)
+        x = torch.randn((m, k), device="cuda", generator=gen).to(torch.float16)
+        fused = D.FusedShardedLinear(dp, n, m)
+        t_local, t_all, t_fused = tmax(lambda: dp.apply(x)), tmax(lambda: lin(x)), tmax(lambda: fused(x))
+        same = bool(torch.equal(fused(x), lin(x)))
+        fl = 2.0 * m * n * k
+        say(case=f"cfg2 q3_k {k}->{n} m={m} N-sharded", local_us=t_local, nccl_allgather_us=t_all, fused_allgather_us=t_fused, local_TFLOPs=fl / t_local / 1e6,
+            nccl_allgather_TFLOPs=fl / t_all / 1e6, fused_allgather_TFLOPs=fl / t_fused / 1e6, fused_equals_nccl=same)
+    n, k, m = 18432, 7168, 4096
+    row0, rows = D.shard_rows(n, world, rank, align=256)
+    dp = DevPack.from_t16("nvfp4", synth.t16_random_device("nvfp4", rows, k, seed=200 + rank), rows, k)
+    x = torch.randn((m, k), device="cuda", generator=gen).to(torch.bfloat16)
+    lin = D.ShardedLinear(lambda v: dp.apply_a4(v, torch.bfloat16), n)
+    fused = D.FusedShardedLinear(dp, n, m, a4=True, out_dtype=torch.bfloat16)
+    t_local, t_all, t_fused = tmax(lambda: dp.apply_a4(x, torch.bfloat16)), tmax(lambda: lin(x)), tmax(lambda: fused(x))
+    same = bool(torch.equal(fused(x), lin(x)))
+    fl = 2.0 * m * n * k
+    say(case="cfg3 nvfp4 7168->18432 m=4096 N-sharded", local_us=t_local, nccl_allgather_us=t_all, fused_allgather_us=t_fused, local_TFLOPs=fl / t_local / 1e6,
+        nccl_allgather_TFLOPs=fl / t_all / 1e6, fused_allgather_TFLOPs=fl / t_fused / 1e6, fused_equals_nccl=same)
+    H, I, K = 7168, 2048, 8
+    e0, ne = D.expert_range(E, world, rank)
+    mk = lambda rows_, k_, seed: DevPack.from_t16("q4_k", synth.t16_random_device("q4_k", ne * rows_, k_, seed=seed + rank), rows_, k_, ne)
+    glu = ForeignSwitchGLU(mk(I, H, 300), mk(I, H, 400), mk(H, I, 500))
+    local_experts = lambda rows_, ids: glu(rows_, ids.reshape(-1, 1)).reshape(rows_.shape[0], H)
+    for T in (64, 4096):
+        Tl = T // world
+        g2 = torch.Generator(device="cuda").manual_seed(1000 + rank)
+        x = torch.randn((Tl, H), device="cuda", generator=g2).to(torch.float16)
+        lg = torch.randn((Tl, E + 1), device="cuda", generator=g2)
+        inds, scs, _ = ops.moe_select(lg, E, K, True)
+        t = tmax(lambda: D.ep_moe(x, inds.reshape(Tl, K), scs.reshape(Tl, K), E, local_experts, out_dtype=torch.float16), iters=6)
+        rec = dict(case=f"cfg4 moe E={E} top{K} T={T} expert-parallel", tokens_per_rank=Tl, layer_us=t)
+        if T > 64:
+            rec["TFLOPs"] = 2.0 * T * K * H * I * 3 / t / 1e6
+        say(**rec)
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    dist.barrier()
+    os._exit(0)                                                               # NCCL teardown at interpreter exit hung on the boxes this was developed on
+
+
 def main(argv):
     what = argv[0] if argv else "cfg0"
     if what == "cfg0":
@@ -140,6 +220,8 @@ def main(argv):
         cfg3()
     elif what == "cfg4":
         cfg4(int(argv[1]) if len(argv) > 1 else 256)
+    elif what == "dist":
+        dist_cases(int(argv[1]) if len(argv) > 1 else 256)
     else:
         raise SystemExit(f"unknown case {what}")
     torch.cuda.synchronize()

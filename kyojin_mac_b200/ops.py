@@ -271,6 +271,18 @@ def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: flo
     return d
 
 
+def gemm_kq_ag(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, peer_ptrs, ldd: int, col0: int, gscale: float = 1.0, msub: int = 0) -> None:
+    """gemm_kq whose epilogue stores every tile into the [m, ldd] fp16 output matrix of every rank (peer_ptrs: peer-mapped base addresses, own rank included) at
+    column col0: the all-gather of an N-sharded linear happens inside the GEMM. The caller synchronises the ranks around the call."""
+    _need_cuda(t16, a)
+    if a.dtype != torch.float16 or a.dim() != 2 or a.shape[1] != k:
+        raise ValueError(f"gemm_kq_ag takes float16 [m, {k}], got {a.dtype} {tuple(a.shape)}")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    out = _lib.PeerOut.of(peer_ptrs)
+    _lib.check(_lib.lib().kyb_gemm_kq_ag(_fmt(fmt), t16.data_ptr(), n, k, a.data_ptr(), a.stride(0), a.shape[0], float(gscale), out, ldd, col0, msub, _stream()))
+
+
 def gemm_kq_grouped(fmt, t16: torch.Tensor, n: int, k: int, E: int, a: torch.Tensor, tb: torch.Tensor, off: torch.Tensor, row_map: torch.Tensor | None = None,
                     gs: torch.Tensor | None = None, out: torch.Tensor | None = None, out_rows: int | None = None, mt: int = 256) -> torch.Tensor:
     """d [rows, n]: sorted rows a fp16 [s, k] of expert segments (off) times the T16 expert stack (E * n rows), decoded inside the GEMM; tile list tb of mt-row
@@ -326,6 +338,13 @@ def nvfp4_sf_unswizzle(swz: torch.Tensor, rows: int, k: int) -> torch.Tensor:
     out = torch.empty((rows, k // 16), dtype=torch.uint8, device=swz.device)
     _lib.check(_lib.lib().kyb_nvfp4_sf_swizzle(out.data_ptr(), rows, k, swz.data_ptr(), 0, _stream()))
     return out
+
+
+def gemm_nvfp4_ag(a_codes, sfa, b_codes, sfb, m: int, n: int, k: int, peer_ptrs, ldd: int, col0: int, gscale: float = 1.0, dtype=torch.float16) -> None:
+    """gemm_nvfp4 with the all-gather of an N-sharded linear folded into the epilogue (see gemm_kq_ag)."""
+    _need_cuda(a_codes, sfa, b_codes, sfb)
+    out = _lib.PeerOut.of(peer_ptrs)
+    _lib.check(_lib.lib().kyb_gemm_nvfp4_ag(a_codes.data_ptr(), sfa.data_ptr(), b_codes.data_ptr(), sfb.data_ptr(), m, n, k, float(gscale), _DT[dtype], out, ldd, col0, _stream()))
 
 
 def gemm_nvfp4(a_codes, sfa, b_codes, sfb, m: int, n: int, k: int, gscale: float = 1.0, dtype=torch.float16, out=None) -> torch.Tensor:

@@ -84,6 +84,35 @@ def test_fused_decode_gemm_vs_staged(fmt):
     assert torch.allclose(ys.float(), y1[:3].float() * 0.5, rtol=2e-3, atol=1e-4)
 
 
+def test_gather_epilogue_writes_every_destination():
+    """The GEMM + all-gather entry points on one GPU: two 'ranks' (two shards, two output matrices in this process), every shard's tiles land in both matrices
+    at the shard's column offset; the result equals the plain GEMM of each shard."""
+    k, m, shards = 1024, 200, [(0, 512), (512, 272)]                       # second shard with a ragged last tile
+    n_total = 784
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+    outs = [torch.zeros((m, n_total), dtype=torch.float16, device="cuda") for _ in range(2)]
+    want = torch.zeros((m, n_total), dtype=torch.float16, device="cuda")
+    for col0, n in shards:
+        t16 = synth.t16_random_device("q4_k", n, k, seed=col0 + 1)
+        ops.gemm_kq_ag("q4_k", t16, n, k, x, [o.data_ptr() for o in outs], n_total, col0)
+        want[:, col0:col0 + n] = ops.gemm_kq("q4_k", t16, n, k, x)
+    ops.check_device_status()
+    assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+    # NVFP4 W4A4 form
+    from kyojin_mac_b200.foreign_linear import DevPack
+    n_total, outs = 768, [torch.zeros((m, 768), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    want = torch.zeros((m, 768), dtype=torch.bfloat16, device="cuda")
+    codes, _, asw = ops.nvfp4_quant_rows(x.to(torch.bfloat16), swizzled=True, plain=False)
+    for col0, n in [(0, 512), (512, 256)]:
+        dp = DevPack.from_t16("nvfp4", synth.t16_random_device("nvfp4", n, k, seed=col0 + 7), n, k)
+        qs, sfb = dp._a4_operands()
+        ops.gemm_nvfp4_ag(codes, asw, qs, sfb, m, n, k, [o.data_ptr() for o in outs], n_total, col0, 1.0, torch.bfloat16)
+        want[:, col0:col0 + n] = ops.gemm_nvfp4(codes, asw, qs, sfb, m, n, k, 1.0, torch.bfloat16)
+    ops.check_device_status()
+    assert torch.equal(outs[0], want) and torch.equal(outs[1], want)
+
+
 def test_gemm_errors():
     a = torch.zeros((128, 96), dtype=torch.float16, device="cuda")
     with pytest.raises(Exception):
