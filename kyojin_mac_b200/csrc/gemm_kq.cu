@@ -15,6 +15,7 @@
 // decode work per flop; with one, the two tensor-memory accumulators alternate and the epilogue overlaps the next item's MMAs (grouped form: an expert's
 // segment is cut into 128-row tiles). Every mbarrier wait is bounded; a wait that gives up sets the device status word and the CTA drains.
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 
 #include "t16_decode.cuh"
@@ -32,6 +33,8 @@ namespace kyb {
 constexpr int KQ_BN = 256, KQ_BK = 64, KQ_DW = 16, KQ_THREADS = (6 + KQ_DW) * 32;
 constexpr uint32_t KQ_A_SUB = 128 * KQ_BK * 2, KQ_B_BYTES = KQ_BN * KQ_BK * 2;
 constexpr uint32_t KQ_SCR = 1280;                       // per decoder warp: block scales of one T16 tile as half2 pairs
+constexpr uint32_t KQ_STG = KYB_STG_BYTES;              // per epilogue warp: 32 rows x 32 fp16 columns staged for a tiled bulk store
+using KqOutMaps = KybOutMaps;                           // dense form: the [m, col0 + n] fp16 output matrix of every receiving rank
 
 struct KqParams {
     const uint8_t* t16;
@@ -49,6 +52,7 @@ struct KqParams {
     int experts;
     int tiles_m, tiles_n;
     int msub, stages;
+    int tma_out, col0;          // dense form: the epilogue stores through the tensor maps (bulk tiled stores), at column col0 + n0
 };
 
 struct KqItem {
@@ -321,14 +325,16 @@ __device__ __forceinline__ void kq_decode_quarter(const KqTile<FMT>& tr, uint32_
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 template <int FMT>
-__global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_constant__ CUtensorMap tma_a, const KqParams p, const int num_items) {
+__global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ KqOutMaps outs, const KqParams p,
+                                                                 const int num_items) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int TB = kyb_tile_bytes(FMT);
     const uint32_t a_bytes = (uint32_t)p.msub * KQ_A_SUB, stage_bytes = a_bytes + KQ_B_BYTES;
     const int STAGES = p.stages;
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t scr0 = smem0 + (uint32_t)STAGES * stage_bytes;
-    const uint32_t bars = scr0 + KQ_DW * KQ_SCR;                                    // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+    const uint32_t stg0 = scr0 + KQ_DW * KQ_SCR;                                    // epilogue staging, 4 warps
+    const uint32_t bars = stg0 + 4 * KQ_STG;                                        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16, tmem_slot = acce0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = p.k / KQ_BK;
@@ -406,10 +412,29 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                 const uint32_t slot = cnt & 1u;
                 if (!mbar_wait_fast(accf0 + 8 * slot, (cnt >> 1) & 1u)) failed = true;
                 tc_fence_after();
+                const float gscale = it.gscale;
+                if (p.tma_out) {
+                    // ---- staged tiled stores: 32 rows x 32 columns per step go to shared memory (64-byte swizzle, conflict-free 16-byte stores) and leave as one bulk
+                    // tensor store per receiving rank: full 64-byte row segments on the wire, rows / columns past the matrix are dropped by the tensor map
+                    const uint32_t stg = stg0 + (uint32_t)q * KQ_STG;
+                    const int row0 = it.m0 + sub * 128 + q * 32;
+#pragma unroll 1
+                    for (int c = 0; c < KQ_BN; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
+                        tmem_ld_wait();
+                        uint32_t w[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * j]) * gscale), sat_half(__uint_as_float(v[2 * j + 1]) * gscale));
+                            w[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + it.n0 + c, row0, !failed && row0 < it.m_end && it.n0 + c < p.n);
+                    }
+                } else {
                 const int row = it.m0 + sub * 128 + q * 32 + lane;
                 const size_t orow = (p.row_map && row < it.m_end) ? (size_t)p.row_map[row] : (size_t)row;
                 const size_t doff = orow * p.ldd + it.n0;
-                const float gscale = it.gscale;
 #pragma unroll 1
                 for (int c = 0; c < KQ_BN; c += 32) {
                     uint32_t v[32];
@@ -428,11 +453,13 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                                 for (int pr = 0; pr < p.nout; ++pr) *reinterpret_cast<uint4*>(p.d[pr] + doff + c + j) = o;
                             }
                         } else {
+#pragma unroll
                             for (int j = 0; j < 32; ++j)
                                 if (it.n0 + c + j < p.n)
                                     for (int pr = 0; pr < p.nout; ++pr) p.d[pr][doff + c + j] = sat_half(__uint_as_float(v[j]) * gscale);
                         }
                     }
+                }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -492,6 +519,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
 #undef KYB_KQ_PREFETCH
         }
     }
+    if (warp >= 2 && warp < 6 && lane == 0 && p.tma_out) tma_store_wait_all();         // the staging buffer must outlive its stores
     if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
     tc_fence_before();
     __syncthreads();
@@ -505,7 +533,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
 
 namespace {
 
-int kq_launch(int fmt, const CUtensorMap& ta, kyb::KqParams p, int num_items, cudaStream_t st) {
+int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqParams p, int num_items, cudaStream_t st) {
     static std::mutex mu;
     static unsigned done[4] = {0, 0, 0, 0};
     static int sms = 0;
@@ -516,8 +544,8 @@ int kq_launch(int fmt, const CUtensorMap& ta, kyb::KqParams p, int num_items, cu
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
                                              : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
     const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
-    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 1024 + 256;
-    const size_t cap = 226 * 1024;
+    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * kyb::KQ_STG + 1024 + 256;
+    const size_t cap = 227 * 1024;
     p.stages = (int)std::min<size_t>(8, (cap - fixed) / stage_bytes);
     const size_t smem = (size_t)p.stages * stage_bytes + fixed;
     {
@@ -528,15 +556,15 @@ int kq_launch(int fmt, const CUtensorMap& ta, kyb::KqParams p, int num_items, cu
         }
         if (!sms) KYB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     }
-    void* args[] = {(void*)&ta, (void*)&p, (void*)&num_items};
+    void* args[] = {(void*)&ta, (void*)&outs, (void*)&p, (void*)&num_items};
     KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)std::min(num_items, sms)), dim3(kyb::KQ_THREADS), args, smem, st));
     return kyb_launch_check("gemm_kq");
 }
 
 }  // namespace
 
-static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd, int msub,
-                    void* stream) {
+static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
+                    int64_t col0, int msub, void* stream) {
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
@@ -551,11 +579,21 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     kyb::KqParams p;
     p.t16 = (const uint8_t*)t16, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.nb = (int)(k / 256), p.rt_total = (int)((n + 15) / 16);
     p.nout = nout;
-    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] : nullptr;
+    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] + col0 : nullptr;
     p.gscale = gscale, p.status = status, p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
     p.msub = msub ? msub : (m > 128 ? 2 : 1);
     p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN), p.tiles_m = (int)((m + 128 * p.msub - 1) / (128 * p.msub));
-    return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+    // tiled bulk stores need 16-byte aligned bases and row pitches; otherwise the epilogue stores from registers
+    KybOutMaps outs;
+    memset(&outs, 0, sizeof(outs));
+    p.col0 = (int)col0;
+    p.tma_out = (ldd % 8 == 0 && col0 % 8 == 0) ? 1 : 0;
+    for (int i = 0; i < nout && p.tma_out; ++i)
+        if ((uintptr_t)d[i] & 15) p.tma_out = 0;
+    for (int i = 0; i < nout && p.tma_out; ++i)
+        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+    return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }
 
 // D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub: 1 or 2 blocks of 128
@@ -564,7 +602,7 @@ extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const
                            void* stream) {
     KYB_REQUIRE(d && ((uintptr_t)d & 1) == 0, "null or odd output pointer");
     void* outs[1] = {d};
-    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, 1, ldd, msub, stream);
+    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, 1, ldd, 0, msub, stream);
 }
 
 // The same product with the all-gather of an N-sharded linear folded into the epilogue: every tile goes to the output matrix of every rank, at column col0.
@@ -575,9 +613,9 @@ extern "C" int kyb_gemm_kq_ag(int fmt, const void* t16, int64_t n, int64_t k, co
     void* outs[8];
     for (int i = 0; i < out->count; ++i) {
         KYB_REQUIRE(out->ptr[i] && ((uintptr_t)out->ptr[i] & 15) == 0, "peer output %d is null or not 16-byte aligned", i);
-        outs[i] = (__half*)out->ptr[i] + col0;
+        outs[i] = out->ptr[i];
     }
-    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, out->count, ldd, msub, stream);
+    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, out->count, ldd, col0, msub, stream);
 }
 
 // Grouped form for routed experts: a fp16 [s, k] rows sorted by expert (segment e = rows [off[e], off[e + 1])), T16 of the expert stack (experts * n rows),
@@ -607,5 +645,8 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     p.msub = mt / 128;
     p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
-    return kq_launch(fmt, ta, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+    p.tma_out = 0, p.col0 = 0;                                                     // rows are scattered (row_map) or end inside a tile: stores from registers
+    KybOutMaps outs;
+    memset(&outs, 0, sizeof(outs));
+    return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }

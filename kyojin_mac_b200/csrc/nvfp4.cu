@@ -7,6 +7,8 @@
 // Scale-factor chunk layout ("SF512"): rows are cut in blocks of 128, k in blocks of 64 (= 4 scales); chunk (rb, kb) holds 512 bytes at ((rb * k/64) + kb) * 512,
 // byte (r % 32) * 16 + (r / 32) * 4 + c = scale c of row r of the block. One chunk is what `tcgen05.cp 32x128b.warpx4` moves into 4 tensor-memory columns.
 #include <cuda_bf16.h>
+
+#include <cstring>
 #include <cuda_fp8.h>
 
 #include <mutex>
@@ -100,6 +102,7 @@ struct NvGemmParams {
     const uint8_t* sfb;      // SF512 of B
     __half* d[8];            // output matrix on every receiving rank (one entry without sharding), already offset to this rank's first column
     int nout;
+    int tma_out, col0;       // the epilogue stores through the tensor maps (tiled bulk stores) at column col0 + n0
     int64_t ldd;
     int m, n, k;
     float gscale;
@@ -127,11 +130,12 @@ __device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint6
 
 // Persistent: CTA c works on tiles c, c + gridDim.x, ... (n tile fastest). Tensor memory: accumulator 256 columns + scale columns; the producer runs ahead
 // into the next tile while the epilogue drains the accumulator.
-__global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const NvGemmParams p,
-                                                                   const int tiles_n, const int num_tiles) {
+__global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                                                                   const __grid_constant__ KybOutMaps outs, const NvGemmParams p, const int tiles_n, const int num_tiles) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem0 + NV_STAGES * NV_STAGE_BYTES;
+    const uint32_t stg0 = smem0 + NV_STAGES * NV_STAGE_BYTES;                      // epilogue staging, 4 warps
+    const uint32_t bars = stg0 + 4 * KYB_STG_BYTES;
     const uint32_t full0 = bars, empty0 = bars + 8 * NV_STAGES, accf = bars + 16 * NV_STAGES, acce = accf + 8, tmem_slot = acce + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = p.k / NV_BK, k64 = p.k / 64;
@@ -214,6 +218,29 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
             const int n0 = (t % tiles_n) * NV_BN, m0 = (t / tiles_n) * NV_BM;
             if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
             tc_fence_after();
+            if (p.tma_out) {
+                const uint32_t stg = stg0 + (uint32_t)q * KYB_STG_BYTES;
+                const int row0 = m0 + q * 32;
+#pragma unroll 1
+                for (int c = 0; c < NV_BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
+                    tmem_ld_wait();
+                    uint32_t w[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float f0 = __uint_as_float(v[2 * j]) * p.gscale, f1 = __uint_as_float(v[2 * j + 1]) * p.gscale;
+                        if (p.out_bf16) {
+                            __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                            w[j] = *reinterpret_cast<uint32_t*>(&h);
+                        } else {
+                            __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                            w[j] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                    }
+                    epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + n0 + c, row0, !failed && row0 < p.m && n0 + c < p.n);
+                }
+            } else {
             const int row = m0 + q * 32 + lane;
             const size_t doff = (size_t)row * p.ldd + n0;
             const bool vec = (p.ldd & 7) == 0;
@@ -241,7 +268,9 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                             for (int pr = 0; pr < p.nout; ++pr) *reinterpret_cast<uint4*>(p.d[pr] + doff + c + j) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     } else {
-                        for (int j = 0; j < 32 && n0 + c + j < p.n; ++j) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (n0 + c + j >= p.n) break;
                             const float f = __uint_as_float(v[j]) * p.gscale;
                             for (int pr = 0; pr < p.nout; ++pr) {
                                 if (p.out_bf16) reinterpret_cast<__nv_bfloat16*>(p.d[pr])[doff + c + j] = __float2bfloat16_rn(f);
@@ -251,11 +280,13 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                     }
                 }
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_a(acce);
         }
     }
+    if (warp >= 2 && lane == 0 && p.tma_out) tma_store_wait_all();                 // the staging buffer must outlive its stores
     if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
     tc_fence_before();
     __syncthreads();
@@ -311,7 +342,7 @@ extern "C" int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* 
 
 // D [m, n] = sat(gscale * A B^T): a_codes [m, k/2], b_codes [n, k/2] packed e2m1 (two per byte, low nibble first), sfa / sfb in the SF512 layout.
 static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
-                           void* const* d, int nout, int64_t ldd, void* stream) {
+                           void* const* d, int nout, int64_t ldd, int64_t col0, void* stream) {
     KYB_REQUIRE(a_codes && sfa && b_codes && sfb, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(n % 256 == 0, "n=%lld must be a multiple of 256 (one CTA covers two 128-row scale chunks of B)", (long long)n);
@@ -325,8 +356,17 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
     kyb::NvGemmParams p;
     p.sfa = (const uint8_t*)sfa, p.sfb = (const uint8_t*)sfb, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale;
     p.out_bf16 = out_dtype == 2, p.status = status, p.nout = nout;
-    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] : nullptr;
-    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
+    for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] + col0 : nullptr;
+    KybOutMaps outs;
+    memset(&outs, 0, sizeof(outs));
+    p.col0 = (int)col0;
+    p.tma_out = (ldd % 8 == 0 && col0 % 8 == 0) ? 1 : 0;                            // tiled bulk stores need 16-byte aligned bases and row pitches
+    for (int i = 0; i < nout && p.tma_out; ++i)
+        if ((uintptr_t)d[i] & 15) p.tma_out = 0;
+    for (int i = 0; i < nout && p.tma_out; ++i)
+        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
     static std::mutex mu;
     static unsigned done = 0;
     int dev = 0;
@@ -341,7 +381,7 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
     int sms = 148;
     KYB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int tiles_n = (int)((n + kyb::NV_BN - 1) / kyb::NV_BN), num_tiles = tiles_n * (int)((m + kyb::NV_BM - 1) / kyb::NV_BM);
-    kyb::gemm_nvfp4_kernel<<<(unsigned)(num_tiles < sms ? num_tiles : sms), kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, p, tiles_n, num_tiles);
+    kyb::gemm_nvfp4_kernel<<<(unsigned)(num_tiles < sms ? num_tiles : sms), kyb::NV_THREADS, smem, (cudaStream_t)stream>>>(ta, tb, outs, p, tiles_n, num_tiles);
     return kyb_launch_check("gemm_nvfp4");
 }
 
@@ -349,7 +389,7 @@ extern "C" int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* 
                               void* d, int64_t ldd, void* stream) {
     KYB_REQUIRE(d, "null pointer");
     void* outs[1] = {d};
-    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, 1, ldd, stream);
+    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, 1, ldd, 0, stream);
 }
 
 // The same product with the all-gather of an N-sharded linear folded into the epilogue: every tile goes to the output matrix of every rank, at column col0.
@@ -360,7 +400,7 @@ extern "C" int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const voi
     void* outs[8];
     for (int i = 0; i < out->count; ++i) {
         KYB_REQUIRE(out->ptr[i] && ((uintptr_t)out->ptr[i] & 15) == 0, "peer output %d is null or not 16-byte aligned", i);
-        outs[i] = (__half*)out->ptr[i] + col0;
+        outs[i] = out->ptr[i];
     }
-    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, out->count, ldd, stream);
+    return nvfp4_gemm_impl(a_codes, sfa, b_codes, sfb, m, n, k, gscale, out_dtype, outs, out->count, ldd, col0, stream);
 }

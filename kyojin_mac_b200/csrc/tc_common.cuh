@@ -21,10 +21,10 @@ static inline kyb_encode_tiled_fn kyb_get_encode_tiled() {
     return fn;
 }
 
-// 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, row stride `ld_bytes`; box [box_rows, box_cols]; 128-byte swizzle
-// (box_cols * elem_bytes must be 128). Out-of-range parts of a box are filled with zeros.
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-wide elements, row stride `ld_bytes`; box [box_rows, box_cols]; 128-byte swizzle by default
+// (box_cols * elem_bytes must equal the swizzle width). Out-of-range parts of a box are filled with zeros on loads and dropped on stores.
 static inline int kyb_make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_bytes,
-                                   uint32_t box_rows, uint32_t box_cols) {
+                                   uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     kyb_encode_tiled_fn enc = kyb_get_encode_tiled();
     if (!enc) {
         kyb_set_error("cuTensorMapEncodeTiled is not available from this driver");
@@ -35,7 +35,7 @@ static inline int kyb_make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dt, int 
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     (void)elem_bytes;
-    const CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    const CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         kyb_set_error("cuTensorMapEncodeTiled failed with CUresult %d (base %p rows %llu cols %llu ld %llu box %u x %u)", (int)r, base, (unsigned long long)rows,
@@ -44,6 +44,12 @@ static inline int kyb_make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dt, int 
     }
     return KYB_OK;
 }
+
+// Tensor maps of the output matrix on every receiving rank (one entry without sharding): 16-bit elements, box 32 rows x 32 columns, 64-byte swizzle.
+struct KybOutMaps {
+    CUtensorMap m[8];
+};
+constexpr uint32_t KYB_STG_BYTES = 2048;    // epilogue staging per warp: 32 rows x 32 16-bit columns
 
 #ifdef __CUDACC__
 namespace kyb {
@@ -54,6 +60,31 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm), "r"(x), "r"(y),
                  "r"(bar)
                  : "memory");
+}
+// shared -> global tiled store (bulk async group of the issuing thread); x * elem_bytes must be a multiple of 16, coordinates must not be negative
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tm), "r"(x), "r"(y), "r"(src) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }   // the sources of this thread's stores have been read
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }          // this thread's stores are complete
+// Epilogue step of one warp: 32 rows (one per lane) x 32 columns given as 16 packed pairs w[16] go to the warp's staging buffer (64-byte swizzle, conflict-free
+// 16-byte stores) and leave as one tiled bulk store per receiving rank at (x, y); rows / columns outside the matrix are dropped by the tensor map.
+__device__ __forceinline__ void epilogue_stage_store(const KybOutMaps& outs, int nout, uint32_t stg, int lane, const uint32_t (&w)[16], int x, int y, bool issue) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the previous step's stores have read the staging buffer
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4)), "r"(w[4 * j]), "r"(w[4 * j + 1]),
+                     "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                     : "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0 && issue) {
+        for (int pr = 0; pr < nout; ++pr)
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&outs.m[pr]), "r"(x), "r"(y), "r"(stg) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
 }
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) { asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory"); }
 
