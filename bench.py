@@ -274,7 +274,7 @@ def run_ours(args):
     h2d = sum(2 * m * k for m in BATCHES for k in ks)
     d2h = sum(2 * m * n for m in BATCHES for _, _, n, _ in mats)
 
-    def e2e_step(s):
+    def e2e_eager(s):
         layer = mods[s % copies]
         for m in BATCHES:
             dx = {k: hx[(m, k)].to(dev, non_blocking=True) for k in ks}
@@ -284,6 +284,33 @@ def run_ours(args):
                     dist.all_gather_into_tensor(yg[(m, i)], y)
                 hy[(m, i)].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
+
+    # single GPU: the step goes through the package's HostGraph (pinned inputs -> h2d -> the layer's modules -> d2h into pinned outputs, one CUDA graph per
+    # layer copy): the same copies and launches as the eager loop, without the per-call Python dispatch
+    hgraphs = None
+    if world == 1 and not args.e2e_eager:
+        from kyojin_mac_b200.host_graph import HostGraph
+        try:
+            hgraphs = []
+            for c in range(copies):
+                layer = mods[c]
+                stages = []
+                for m in BATCHES:                                                # one stage per batch size: its upload / download overlap the neighbours' products
+                    def stage_fn(*dx, layer=layer):
+                        d = dict(zip(ks, dx))
+                        return [layer[i](d[k_]) for i, (nm_, f_, n_, k_) in enumerate(mats)]
+                    stages.append((stage_fn, [hx[(m, k)] for k in ks]))
+                hgraphs.append(HostGraph.staged(stages, dev))
+            h2d, d2h = hgraphs[0].h2d_bytes, hgraphs[0].d2h_bytes                 # what the copies of a step move (inputs / results, 256-byte aligned slots)
+        except Exception as e:
+            hgraphs = None
+            print(f"[bench] HostGraph capture unavailable ({type(e).__name__}: {e}); e2e through eager module calls", file=sys.stderr)
+
+    def e2e_step(s):
+        if hgraphs is not None:
+            hgraphs[s % copies]()
+        else:
+            e2e_eager(s)
 
     for s in range(args.warmup):
         e2e_step(s)
@@ -317,7 +344,9 @@ def run_ours(args):
                            "parallelism": f"n-sharded x{world} + NCCL all-gather of output slices" if world > 1 else "single GPU",
                            "bytes_per_step": step_bytes},
                 "roofline": roofline, "cpu_baseline": cpu,
-                "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps},
+                "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
+                        "api": "kyojin_mac_b200.host_graph.HostGraph.staged over ForeignLinear modules, one stage per batch size (pinned host activations in, pinned host results out)" if hgraphs is not None
+                        else "ForeignLinear modules called eagerly (pinned host activations in, pinned host results out)"},
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
         print(json.dumps(line))
     if world > 1:
@@ -338,6 +367,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-group", action="store_true", help="launch q, k, v and gate, up separately instead of as same-input groups")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-eager", action="store_true", help="end-to-end leg through eager module calls instead of the HostGraph step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -177,6 +177,10 @@ int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int64_t n, flo
 int kyb_q4mma(const void* w, const void* scales, const void* biases, int group, const void* x, int64_t ldx, int64_t rows, int64_t n, int64_t k,
               void* y, int64_t ldy, void* stream);
 
+/* up to 64 device arrays copied into (slots of) one buffer by a single launch; addresses and sizes are multiples of 16 bytes. Used by the host-side step
+ * (kyojin_mac_b200/host_graph.py) so that the results of a decode step leave the device with one copy; the reference needs no counterpart (unified memory). */
+int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* bytes, int count, void* stream);
+
 /* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).
  * Meant for hosts that cannot call cudaMalloc when they need a GEMV: a server that gave all free HBM to its KV-cache pool at start-up, a decode loop that
  * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a runtime whose plug-in rules forbid the callee to allocate.

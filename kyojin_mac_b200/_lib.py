@@ -105,6 +105,7 @@ SIGNATURES = {
     "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
     "kyb_dequant_rows_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_router_logits": (_int, [_vp, _int, _i64, _vp, _vp, _i64, _int, _i64, _vp, _i64, _vp]),
+    "kyb_gather_flat": (_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _int, _vp]),
     "kyb_q4mma": (_int, [_vp, _vp, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp, _i64, _vp]),
     "kyb_gemv_t16_static": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
     "kyb_gemm_f16_tn": (_int, [_vp, _i64, _vp, _i64, _i64, _i64, _i64, _f32, _vp, _i64, _vp]),

@@ -77,3 +77,38 @@ size_t kyb_raw_row_bytes(int fmt, int64_t k) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ results of a step gathered into one buffer
+// Up to 64 device arrays copied into one contiguous buffer by a single launch (16-byte units; sizes and addresses multiples of 16): the results of a decode step
+// leave the device with one copy instead of one per product.
+namespace kyb {
+struct GatherList {
+    const uint4* src[64];
+    uint4* dst[64];
+    uint32_t units[64];
+    int count;
+};
+__global__ void gather_flat_kernel(const GatherList g) {
+    const int j = blockIdx.y;
+    if (j >= g.count) return;
+    const uint4* s = g.src[j];
+    uint4* d = g.dst[j];
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < g.units[j]; i += gridDim.x * blockDim.x) d[i] = s[i];
+}
+}  // namespace kyb
+
+extern "C" int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* bytes, int count, void* stream) {
+    KYB_REQUIRE(srcs && dsts && bytes && count >= 1 && count <= 64, "1..64 arrays");
+    kyb::GatherList g;
+    uint32_t most = 0;
+    for (int i = 0; i < count; ++i) {
+        KYB_REQUIRE(srcs[i] && dsts[i] && bytes[i] > 0 && bytes[i] % 16 == 0 && bytes[i] < (1ll << 35), "array %d: null, empty or not a multiple of 16 bytes", i);
+        KYB_REQUIRE(((uintptr_t)srcs[i] & 15) == 0 && ((uintptr_t)dsts[i] & 15) == 0, "array %d is not 16-byte aligned", i);
+        g.src[i] = (const uint4*)srcs[i], g.dst[i] = (uint4*)dsts[i], g.units[i] = (uint32_t)(bytes[i] / 16);
+        most = g.units[i] > most ? g.units[i] : most;
+    }
+    g.count = count;
+    const unsigned bx = (unsigned)((most + 255) / 256 < 64 ? (most + 255) / 256 : 64);
+    kyb::gather_flat_kernel<<<dim3(bx ? bx : 1, (unsigned)count), 256, 0, (cudaStream_t)stream>>>(g);
+    return kyb_launch_check("gather_flat");
+}

@@ -28,10 +28,72 @@ __device__ __forceinline__ size_t sf512_offset(int64_t row, int64_t s, int64_t k
     return (size_t)((rb * kblocks64 + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4 + c);
 }
 
-// One thread per block of 16 inputs. amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6); v = clip(x / scale, -6, 6);
+// One thread per 64 inputs (four blocks of 16, one 4-byte group of the scale layouts). Per block: amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6) (true
+// fp32 divide); v = clip(x / scale, -6, 6); code = #(|v| > .25, 1.25, 2.5, 5) + #(|v| >= .75, 1.75, 3.5) (round to nearest even onto e2m1), sign bit 3 for v < 0;
+// two codes per byte, low first (kyojin_mlx/fp4pack.py:30-48).
+// The quotient itself is never formed: for 16-bit inputs fl(|x| / s) > t holds exactly when |x| > t s (t s is exact in fp32, and a 16-bit |x| above t s exceeds it
+// by at least 2^-11 relative, far more than half an fp32 ulp, so the correctly rounded quotient cannot land on t), likewise for >=; the clip at 6 only touches
+// values that already passed the last threshold. The sign of the code is the sign of x with +-0 and underflowed quotients mapped as the division would: x / s is
+// negative exactly when x < 0 (s > 0, and a non-zero 16-bit x over s <= 448 does not underflow to zero in fp32).
+template <typename T>
+__device__ __forceinline__ float2 pair_to_float2(uint32_t w);
+template <>
+__device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
+template <>
+__device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
+
+template <typename T>
+__global__ void __launch_bounds__(128) nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes,
+                                                               uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_swz) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t ngrp = k >> 6;
+    if (i >= rows * ngrp) return;
+    const int64_t row = i / ngrp, gq = i % ngrp;
+    const uint4* xp = reinterpret_cast<const uint4*>(x + row * ldx + gq * 64);
+    uint4 raw[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) raw[j] = __ldg(xp + j);
+    uint32_t sbytes = 0;
+    uint32_t packed[8];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        float v[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint4 r = raw[2 * b + h];
+            const float2 p0 = pair_to_float2<T>(r.x), p1 = pair_to_float2<T>(r.y), p2 = pair_to_float2<T>(r.z), p3 = pair_to_float2<T>(r.w);
+            v[8 * h + 0] = p0.x, v[8 * h + 1] = p0.y, v[8 * h + 2] = p1.x, v[8 * h + 3] = p1.y, v[8 * h + 4] = p2.x, v[8 * h + 5] = p2.y, v[8 * h + 6] = p3.x, v[8 * h + 7] = p3.y;
+        }
+        float amax = 6.0f * 0.001953125f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        const uint32_t s8 = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3) & 255u;
+        const float scale = e4m3_to_float(s8);
+        sbytes |= s8 << (8 * b);
+        const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale, t5 = 3.5f * scale, t6 = 5.0f * scale;   // exact products
+        uint32_t pk[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float mag = fabsf(v[j]);
+            // thresholds are ordered: a three-level search instead of seven comparisons
+            uint32_t code;
+            if (mag >= t3) code = mag >= t5 ? (mag > t6 ? 7u : 6u) : (mag > t4 ? 5u : 4u);
+            else code = mag >= t1 ? (mag > t2 ? 3u : 2u) : (mag > t0 ? 1u : 0u);
+            pk[j >> 3] |= (code | (v[j] < 0.0f ? 8u : 0u)) << (4 * (j & 7));
+        }
+        packed[2 * b] = pk[0], packed[2 * b + 1] = pk[1];
+    }
+    uint4* cp = reinterpret_cast<uint4*>(codes + row * (k >> 1) + gq * 32);
+    cp[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    cp[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    if (sf_plain) *reinterpret_cast<uint32_t*>(sf_plain + row * (k >> 4) + gq * 4) = sbytes;
+    if (sf_swz) *reinterpret_cast<uint32_t*>(sf_swz + sf512_offset(row, gq * 4, ngrp)) = sbytes;
+}
+
+// General form (any k % 16 == 0, any alignment): one thread per block of 16 inputs, the quotient formed with a true divide. amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6); v = clip(x / scale, -6, 6);
 // code = #(|v| > .25, 1.25, 2.5, 5) + #(|v| >= .75, 1.75, 3.5) (round to nearest even onto e2m1), sign bit 3 for v < 0; two codes per byte, low first.
 template <typename T>
-__global__ void nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain,
+__global__ void nvfp4_quant_rows16_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_plain,
                                         uint8_t* __restrict__ sf_swz) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nblk = k >> 4;
@@ -310,12 +372,19 @@ extern "C" int kyb_nvfp4_quant_rows(const void* x, int x_dtype, int64_t ldx, int
     KYB_REQUIRE(!sf_swz || k % 64 == 0, "the tensor-core scale layout needs k %% 64 == 0");
     KYB_REQUIRE(x_dtype == 1 || x_dtype == 2, "x_dtype: 1 = fp16, 2 = bf16");
     KYB_REQUIRE(((uintptr_t)codes & 7) == 0, "codes must be 8-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (sf_swz && rows % 128) KYB_CUDA(cudaMemsetAsync(sf_swz, 0, kyb_nvfp4_sf_bytes(rows, k), st));   // padding rows of the last 128-row block read as zero scales
+    if (k % 64 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 && (!sf_plain || ((uintptr_t)sf_plain & 3) == 0)) {
+        const int64_t groups = rows * (k / 64);
+        const unsigned gb = (unsigned)((groups + 127) / 128);
+        if (x_dtype == 1) kyb::nvfp4_quant_rows_kernel<__half><<<gb, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+        else kyb::nvfp4_quant_rows_kernel<__nv_bfloat16><<<gb, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+        return kyb_launch_check("nvfp4_quant_rows");
+    }
     const int64_t total = rows * (k / 16);
     const unsigned blocks = (unsigned)((total + 127) / 128);
-    cudaStream_t st = (cudaStream_t)stream;
-    if (sf_swz) KYB_CUDA(cudaMemsetAsync(sf_swz, 0, kyb_nvfp4_sf_bytes(rows, k), st));            // padding rows of the last 128-row block read as zero scales
-    if (x_dtype == 1) kyb::nvfp4_quant_rows_kernel<__half><<<blocks, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
-    else kyb::nvfp4_quant_rows_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+    if (x_dtype == 1) kyb::nvfp4_quant_rows16_kernel<__half><<<blocks, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+    else kyb::nvfp4_quant_rows16_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
     return kyb_launch_check("nvfp4_quant_rows");
 }
 

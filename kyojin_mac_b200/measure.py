@@ -3,6 +3,7 @@
     python -m kyojin_mac_b200.measure cfg0            # Q4_K GEMV 4096 x 4096, M = 1 (weights rotate through copies larger than L2)
     python -m kyojin_mac_b200.measure cfg2            # Q3_K prefill GEMM, M = 2048, 3072 -> 12288 and 12288 -> 3072
     python -m kyojin_mac_b200.measure cfg3            # NVFP4 prefill GEMM, 4096 x 7168 -> 18432, activations quantised on the fly
+    python -m kyojin_mac_b200.measure fp4peak         # the vendor library's block-scaled NVFP4 GEMM (torch._scaled_mm), a measured fp4 denominator
     python -m kyojin_mac_b200.measure cfg4 [E]        # routed-expert layer, E (default 256) experts, top-8, hidden 7168, T = 64 and 4096
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 -m kyojin_mac_b200.measure dist
                                                       # cfg 2 / 3 N-sharded with all-gather, cfg 4 expert-parallel with all-to-all, on N GPUs
@@ -97,6 +98,23 @@ def cfg3():
     t_a = timeit(lambda: dp.apply_a4(x, torch.bfloat16))[1]
     print(json.dumps({"case": "cfg3 nvfp4 gemm 7168->18432 m=4096", "quant_us": t_q, "gemm_us": t_g, "apply_us": t_a, "gemm_TFLOPs": fl / t_g / 1e6,
                       "apply_TFLOPs": fl / t_a / 1e6, "scale_rule": "e4m3 RNE of 2^U[-8,0]"}), flush=True)
+
+
+def fp4_library_peak():
+    """Block-scaled NVFP4 GEMM of the vendor library through torch._scaled_mm (8192^3, random codes, unit scales) as a measured denominator for the fp4 roofline;
+    prints the exception text when this torch build does not expose it."""
+    n = 8192
+    try:
+        a = torch.randint(0, 256, (n, n // 2), dtype=torch.uint8, device="cuda").view(torch.float4_e2m1fn_x2)
+        b = torch.randint(0, 256, (n, n // 2), dtype=torch.uint8, device="cuda").view(torch.float4_e2m1fn_x2)
+        sa = torch.full((n * n // 16,), 1.0, device="cuda").to(torch.float8_e4m3fn)
+        sb = torch.full((n * n // 16,), 1.0, device="cuda").to(torch.float8_e4m3fn)
+        f = lambda: torch._scaled_mm(a, b.t(), sa, sb, out_dtype=torch.bfloat16)
+        lo, med = timeit(f)
+        print(json.dumps({"case": "library nvfp4 gemm 8192^3 (torch._scaled_mm)", "us_min": lo, "us_median": med, "TFLOPs_best": 2.0 * n ** 3 / lo / 1e6,
+                          "TFLOPs_median": 2.0 * n ** 3 / med / 1e6}), flush=True)
+    except Exception as e:                                                   # noqa: BLE001 - the probe reports whatever the library says
+        print(json.dumps({"case": "library nvfp4 gemm (torch._scaled_mm)", "unavailable": str(e)[:300]}), flush=True)
 
 
 def cfg4(E=256):
@@ -218,6 +236,8 @@ def main(argv):
         cfg2()
     elif what == "cfg3":
         cfg3()
+    elif what == "fp4peak":
+        fp4_library_peak()
     elif what == "cfg4":
         cfg4(int(argv[1]) if len(argv) > 1 else 256)
     elif what == "dist":

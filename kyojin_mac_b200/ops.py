@@ -180,6 +180,22 @@ def dequant_rows(fmt, t16: torch.Tensor, n: int, k: int, rows: torch.Tensor, dty
     return out
 
 
+def gather_flat(srcs, dsts) -> None:
+    """Copies each contiguous device tensor srcs[i] into dsts[i] (same byte count, multiples of 16 bytes, 16-byte aligned) with one launch; up to 64 pairs."""
+    import ctypes as C
+    n = len(srcs)
+    if n == 0:
+        return
+    _need_cuda(*srcs, *dsts)
+    for a, b in zip(srcs, dsts):
+        if not (a.is_contiguous() and b.is_contiguous()) or a.numel() * a.element_size() != b.numel() * b.element_size():
+            raise ValueError("gather_flat copies contiguous tensors of equal byte counts")
+    S = (C.c_void_p * n)(*[t.data_ptr() for t in srcs])
+    D = (C.c_void_p * n)(*[t.data_ptr() for t in dsts])
+    B = (C.c_int64 * n)(*[t.numel() * t.element_size() for t in srcs])
+    _lib.check(_lib.lib().kyb_gather_flat(S, D, B, n, _stream()))
+
+
 def moe_plan(ids: torch.Tensor, E: int, topk: int, mt: int = 128, wts: torch.Tensor | None = None, rank: torch.Tensor | None = None):
     """Counting sort of the slots by expert. Returns dict(order, inv, tok, ids_s, wts_s, off, tb)."""
     _need_cuda(ids)

@@ -17,12 +17,24 @@ def test_quantiser_equals_restatement(dtype):
     x = (torch.randn((96, 512), device="cuda", generator=g) * torch.exp(torch.rand((96, 1), device="cuda", generator=g) * 6 - 3)).to(dtype)
     x[3] = 0
     x[4, :16] = 1e4 if dtype == torch.float16 else 3e4                    # large block: scale near the top of e4m3
+    # a block whose scale is exactly 1 (amax 6) with values ON the rounding thresholds, one step above / below them, and a negative zero
+    ties = torch.tensor([6.0, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -0.0], device="cuda").to(dtype)
+    x[5, :16] = ties
+    up = (ties.view(torch.int16) + 1).view(dtype)                          # next representable value away from zero
+    x[5, 16:32] = up
+    x[5, 16] = 6.0
+    x[5, 32:48] = (ties.view(torch.int16) - 1).view(dtype)
+    x[5, 32], x[5, 47] = 6.0, 0.0
     codes, sc = fp4pack.pack(x, 16, True)
     wc, ws = F4.pack(x.float().cpu().numpy())
     np.testing.assert_array_equal(sc.cpu().numpy(), ws)
     np.testing.assert_array_equal(codes.cpu().numpy(), wc)
     y = fp4pack.unpack(codes, sc, 16, True, torch.float32)
     np.testing.assert_array_equal(y.cpu().numpy(), F4.unpack(wc, ws))
+    xs = x[:, :48].contiguous()                                            # a width that is not a multiple of 64 takes the general kernel
+    c2, s2 = fp4pack.pack(xs, 16, True)
+    np.testing.assert_array_equal(c2.cpu().numpy(), wc[:, :24])
+    np.testing.assert_array_equal(s2.cpu().numpy(), ws[:, :3])
 
 
 def test_sf_layout_round_trip():
