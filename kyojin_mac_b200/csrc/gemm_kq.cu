@@ -21,13 +21,6 @@
 #include "t16_decode.cuh"
 #include "tc_common.cuh"
 
-#ifndef KYB_KQ_ABL
-#define KYB_KQ_ABL 0          // experiment switches (what limits the decoders); 0 in every shipped build
-#endif
-#ifndef KYB_KQ_PF
-#define KYB_KQ_PF 2           // the next tile's loads are issued before quarter KYB_KQ_PF of the current one
-#endif
-
 namespace kyb {
 
 constexpr int KQ_BN = 256, KQ_BK = 64, KQ_DW = 16, KQ_THREADS = (6 + KQ_DW) * 32;
@@ -110,17 +103,7 @@ __device__ __forceinline__ uint32_t ldg16s(const uint8_t* p) {
     asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
 }
-#if KYB_KQ_ABL & 4
-// experiment: the values are computed and folded into one predicate-guarded store instead of being written
-__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
-    if ((x ^ y) == 0x12345678u) asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
-}
-#elif KYB_KQ_ABL & 16
-// experiment: stores without the arithmetic (the address still depends on the lane)
-__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) { asm volatile("st.shared.v2.b32 [%0], {%1, %1};" ::"r"(a), "r"(a) : "memory"); }
-#else
 __device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) { asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory"); }
-#endif
 __device__ __forceinline__ void sts128(uint32_t a, uint4 v) { asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory"); }
 
 __device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b) {
@@ -236,10 +219,10 @@ __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t s
     }
 }
 
-// Quarter P (inputs [64 P, 64 P + 64)) of the tile: fp16 weights of rows g and g + 8 into the B stage. dst_g / dst_h: this lane's row addresses (8 (t & 1) already
-// added); cx[i]: swizzled byte offset of 16-input slice i for this lane, ((2 i + (t >> 1)) ^ g) * 16.
+// Quarter P (inputs [64 P, 64 P + 64)) of the tile: this lane's fp16 weights of rows g (h = 0) and g + 8 (h = 1), four consecutive inputs of every 16-input slice i
+// as the two registers r[4 i + 2 h], r[4 i + 2 h + 1].
 template <int FMT, int P>
-__device__ __forceinline__ void kq_decode_quarter(const KqTile<FMT>& tr, uint32_t scr, uint32_t dst_g, uint32_t dst_h, const uint32_t (&cx)[4], int lane) {
+__device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32_t scr, int lane, uint32_t (&r)[16]) {
     const int g = lane >> 2;
     if constexpr (FMT == KYB_FMT_Q4_K) {
         const uint4 u = tr.q[P];
@@ -256,9 +239,8 @@ __device__ __forceinline__ void kq_decode_quarter(const KqTile<FMT>& tr, uint32_
                 const uint32_t l01 = h2_sub(and_or(p01, 0x000F000Fu, 0x64006400u), 0x64006400u), l23 = h2_sub(and_or(p23, 0x000F000Fu, 0x64006400u), 0x64006400u);
                 const uint32_t h01 = h2_fma(and_or(p01, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
                 const uint32_t h23 = h2_fma(and_or(p23, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
-                const uint32_t dst = h ? dst_h : dst_g;
-                sts64(dst + cx[c], h2_fma(l01, s_lo, z_lo), h2_fma(l23, s_lo, z_lo));
-                sts64(dst + cx[2 + c], h2_fma(h01, s_hi, z_hi), h2_fma(h23, s_hi, z_hi));
+                r[4 * c + 2 * h] = h2_fma(l01, s_lo, z_lo), r[4 * c + 2 * h + 1] = h2_fma(l23, s_lo, z_lo);
+                r[4 * (2 + c) + 2 * h] = h2_fma(h01, s_hi, z_hi), r[4 * (2 + c) + 2 * h + 1] = h2_fma(h23, s_hi, z_hi);
             }
         }
     } else {
@@ -316,9 +298,66 @@ __device__ __forceinline__ void kq_decode_quarter(const KqTile<FMT>& tr, uint32_
                 g01 = prmt(eg, og, 0x5410u), g23 = prmt(eg, og, 0x7632u);
                 h01 = prmt(eh, oh, 0x5410u), h23 = prmt(eh, oh, 0x7632u);
             }
-            sts64(dst_g + cx[i], h2_mul(g01, sg[i]), h2_mul(g23, sg[i]));
-            sts64(dst_h + cx[i], h2_mul(h01, sh[i]), h2_mul(h23, sh[i]));
+            r[4 * i] = h2_mul(g01, sg[i]), r[4 * i + 1] = h2_mul(g23, sg[i]);
+            r[4 * i + 2] = h2_mul(h01, sh[i]), r[4 * i + 3] = h2_mul(h23, sh[i]);
         }
+    }
+}
+
+// The quarter's registers into the B stage. dst_g / dst_h: this lane's row addresses (8 (t & 1) already added). Under the 128-byte swizzle the 16-byte chunk of
+// slice i sits at ((2 i + (t >> 1)) ^ g) * 16, and the 16 lanes an 8-byte store serves together have only four values of g: if all of them stored the same slice they
+// would cover 4 distinct chunks (two-way bank conflict). So in step k the lanes with odd g store slice k ^ 2 instead of slice k: the 16 lanes then cover all 8
+// chunks of their rows and every store is conflict-free. cxs[k] is the swizzled offset of the slice this lane stores in step k.
+__device__ __forceinline__ void kq_store_quarter(uint32_t dst_g, uint32_t dst_h, const uint32_t (&cxs)[4], bool odd, const uint32_t (&r)[16]) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int a = 4 * k, b = 4 * (k ^ 2);
+        sts64(dst_g + cxs[k], odd ? r[b] : r[a], odd ? r[b + 1] : r[a + 1]);
+        sts64(dst_h + cxs[k], odd ? r[b + 2] : r[a + 2], odd ? r[b + 3] : r[a + 3]);
+    }
+}
+
+// After quarter P of a tile has been computed, the registers it alone used are refilled from the next tile (in place: one register set, every unit is requested a
+// whole tile ahead of its next use). Units shared by two quarters are refilled after the second one.
+template <int FMT, int P>
+__device__ __forceinline__ void kq_refill(const uint8_t* next, int lane, KqTile<FMT>& tr) {
+    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+        if constexpr (P == 1) tr.q[4] = ldg128s(next + 2048 + lane * 16);                    // 2-bit planes of quarters 0, 1
+        if constexpr (P == 3) tr.q[5] = ldg128s(next + 2048 + (32 + lane) * 16);             // ... of quarters 2, 3
+    } else {
+        if constexpr (P == 1) {
+            tr.q[0] = ldg128s(next + lane * 16);                                             // 2-bit codes of quarters 0, 1 and their high bits
+            const uint2 hb = ldg64s(next + 1024 + lane * 16);
+            tr.q[2].x = hb.x, tr.q[2].y = hb.y;
+        }
+        if constexpr (P == 3) {
+            tr.q[1] = ldg128s(next + (32 + lane) * 16);
+            const uint2 hb = ldg64s(next + 1024 + lane * 16 + 8);
+            tr.q[2].z = hb.x, tr.q[2].w = hb.y;
+        }
+    }
+}
+
+// The scale bytes of the next tile, requested once the scales of the current one have been prepared.
+template <int FMT>
+__device__ __forceinline__ void kq_refill_scales(const uint8_t* tile, int lane, KqTile<FMT>& tr) {
+    const int r = lane >> 1, hf = lane & 1;
+    if constexpr (FMT == KYB_FMT_Q4_K) {
+        tr.sc = ldg128s(tile + 2048 + r * 16);
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+        const uint2 s = ldg64s(tile + 3072 + r * 16 + 8 * hf);
+        tr.sc.x = s.x, tr.sc.y = s.y;
+        tr.d16 = ldg16s(tile + 3328 + r * 2);
+    } else if constexpr (FMT == KYB_FMT_Q3_K) {
+        const uint8_t* sp = tile + 1536 + r * 12;
+        tr.sc.x = ldg32s(sp), tr.sc.y = ldg32s(sp + 4), tr.sc.z = ldg32s(sp + 8);
+        tr.d16 = ldg16s(tile + 1728 + r * 2);
+    } else {
+        const uint2 s = ldg64s(tile + 2048 + r * 16 + 8 * hf);
+        tr.sc.x = s.x, tr.sc.y = s.y;
     }
 }
 
@@ -472,9 +511,10 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         const uint32_t scr = scr0 + dw * KQ_SCR;
         // rows 16 dw + g and 16 dw + g + 8 of the B tile: 128-byte rows in 8-row groups of 1024 bytes, 16-byte chunks XOR-swizzled with the row number (row & 7 = g)
         const uint32_t row_off = (uint32_t)(2 * dw) * 1024u + (uint32_t)g * 128u + 8u * (uint32_t)(tq & 1);
-        uint32_t cx[4];
+        const bool odd = (g & 1) != 0;
+        uint32_t cx[4];                                                              // offset of the slice this lane stores in step k (see kq_store_quarter)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) cx[i] = (uint32_t)(((2 * i + (tq >> 1)) ^ g) * 16);
+        for (int i = 0; i < 4; ++i) cx[i] = (uint32_t)(((2 * (i ^ (odd ? 2 : 0)) + (tq >> 1)) ^ g) * 16);
         uint32_t parity = 1;
         int s = 0;
         for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
@@ -482,41 +522,58 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             if (!it.valid) continue;
             const int rt = min(it.b_rt0 + dw, p.rt_total - 1);
             const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
-            KqTile<FMT> ta, tb_;
-            kq_load<FMT>(tp, lane, ta);
-#define KYB_KQ_QUARTER(P)                                                                                         \
+            // Software pipeline over the 64-input quarters: while the stores of quarter q drain into the stage (and before the proxy fence that publishes them), the
+            // registers of quarter q + 1 are computed, so the wait for a free stage, the scale loads and the arithmetic overlap the shared-memory traffic.
+            KqTile<FMT> tr;
+            uint32_t r[16];
+            kq_load<FMT>(tp, lane, tr);
+            kq_prep_scales<FMT>(tr, scr, lane);
+            __syncwarp();
+            if (p.nb > 1) kq_refill_scales<FMT>(tp + TB, lane, tr);
+            kq_compute_quarter<FMT, 0>(tr, scr, lane, r);
+            if (p.nb > 1) kq_refill<FMT, 0>(tp + TB, lane, tr);
+#define KYB_KQ_PUBLISH()                                                                                          \
     {                                                                                                             \
-        if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
-        const uint32_t b_dst = smem0 + s * stage_bytes + a_bytes + row_off;                                       \
-        if (!(KYB_KQ_ABL & 2)) kq_decode_quarter<FMT, P>(cur, scr, b_dst, b_dst + 1024u, cx, lane);               \
-        if (!(KYB_KQ_ABL & 8)) fence_proxy_async_smem();                                                          \
+        fence_proxy_async_smem();                                                                                 \
         __syncwarp();                                                                                             \
         if (lane == 0) mbar_arrive_a(full0 + 8 * s);                                                              \
         if (++s == STAGES) s = 0, parity ^= 1u;                                                                   \
     }
-#define KYB_KQ_PREFETCH(AT)                                                                                       \
-    if (KYB_KQ_PF == AT && !(KYB_KQ_ABL & 1) && kb + 1 < p.nb) kq_load<FMT>(tp + (size_t)(kb + 1) * TB, lane, nxt);
-            // one T16 tile from registers; the next tile's loads are issued part-way through so that they are in flight for two quarters, not four
-            // (a wait on a shared-memory result can share a scoreboard with loads still in flight)
-            auto tile = [&](const KqTile<FMT>& cur, KqTile<FMT>& nxt, const int kb) {
-                KYB_KQ_PREFETCH(0)
-                kq_prep_scales<FMT>(cur, scr, lane);
-                __syncwarp();
-                KYB_KQ_QUARTER(0)
-                KYB_KQ_PREFETCH(1)
-                KYB_KQ_QUARTER(1)
-                KYB_KQ_PREFETCH(2)
-                KYB_KQ_QUARTER(2)
-                KYB_KQ_PREFETCH(3)
-                KYB_KQ_QUARTER(3)
-                __syncwarp();                                                        // the scratch is rewritten for the next tile
-            };
-            for (int kb = 0; kb < p.nb && !failed; kb += 2) {                        // two register sets alternate: no copies between them
-                tile(ta, tb_, kb);
-                if (kb + 1 < p.nb && !failed) tile(tb_, ta, kb + 1);
+#define KYB_KQ_STORE()                                                                                            \
+    {                                                                                                             \
+        if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
+        const uint32_t b_dst = smem0 + s * stage_bytes + a_bytes + row_off;                                       \
+        kq_store_quarter(b_dst, b_dst + 1024u, cx, odd, r);                                                       \
+    }
+            for (int kb = 0; kb < p.nb && !failed; ++kb) {
+                const bool more = kb + 1 < p.nb, more2 = kb + 2 < p.nb;
+                const uint8_t* nx = tp + (size_t)(kb + 1) * TB;                      // the next tile, two tiles ahead for the units already consumed
+                KYB_KQ_STORE()
+                kq_compute_quarter<FMT, 1>(tr, scr, lane, r);
+                if (more) kq_refill<FMT, 1>(nx, lane, tr);
+                KYB_KQ_PUBLISH()
+                KYB_KQ_STORE()
+                kq_compute_quarter<FMT, 2>(tr, scr, lane, r);
+                if (more) kq_refill<FMT, 2>(nx, lane, tr);
+                KYB_KQ_PUBLISH()
+                KYB_KQ_STORE()
+                kq_compute_quarter<FMT, 3>(tr, scr, lane, r);
+                if (more) kq_refill<FMT, 3>(nx, lane, tr);
+                KYB_KQ_PUBLISH()                                                     // its warp barrier also ends every lane's reads of this tile's scales
+                if (more) {
+                    kq_prep_scales<FMT>(tr, scr, lane);                              // tr.sc holds the next tile's scale bytes
+                    __syncwarp();
+                    if (more2) kq_refill_scales<FMT>(nx + TB, lane, tr);
+                }
+                KYB_KQ_STORE()
+                if (more) {
+                    kq_compute_quarter<FMT, 0>(tr, scr, lane, r);                    // quarter 0 of the next tile
+                    if (more2) kq_refill<FMT, 0>(nx + TB, lane, tr);
+                }
+                KYB_KQ_PUBLISH()
             }
-#undef KYB_KQ_QUARTER
-#undef KYB_KQ_PREFETCH
+#undef KYB_KQ_PUBLISH
+#undef KYB_KQ_STORE
         }
     }
     if (warp >= 2 && warp < 6 && lane == 0 && p.tma_out) tma_store_wait_all();         // the staging buffer must outlive its stores
