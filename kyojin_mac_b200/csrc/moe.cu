@@ -135,6 +135,25 @@ __global__ void silu_mul_kernel(const __half* __restrict__ a, const __half* __re
     h[r * ldh + c] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
 }
 
+// the same on 8 consecutive columns per thread (16-byte loads and stores): n, ld, ldh multiples of 8, 16-byte aligned bases, no permutation
+__global__ void silu_mul8_kernel(const __half* __restrict__ a, const __half* __restrict__ b, int64_t ld, int64_t total8, int n8, float limit, __half* __restrict__ h, int64_t ldh) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const int64_t r = i / n8;
+    const int c = (int)(i % n8) * 8;
+    const uint4 av4 = __ldg(reinterpret_cast<const uint4*>(a + r * ld + c)), bv4 = __ldg(reinterpret_cast<const uint4*>(b + r * ld + c));
+    const __half* ah = reinterpret_cast<const __half*>(&av4);
+    const __half* bh = reinterpret_cast<const __half*>(&bv4);
+    __half o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float av = __half2float(ah[j]), bv = __half2float(bh[j]);
+        if (limit > 0.f) av = fminf(av, limit), bv = fminf(fmaxf(bv, -limit), limit);
+        o[j] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
+    }
+    *reinterpret_cast<uint4*>(h + r * ldh + c) = *reinterpret_cast<const uint4*>(o);
+}
+
 // o[t, c] = sum_k f32(y[t K + k, c]) * scs[t K + k] (+ sgs[t] * shared[t, c]); fp16 saturated or fp32 output (foreign_moe.py:112-119)
 template <typename OUT>
 __global__ void moe_combine_kernel(const __half* __restrict__ y, int64_t ldy, const float* __restrict__ scs, const float* __restrict__ sgs, const __half* __restrict__ shared,
@@ -168,6 +187,42 @@ template <> struct XVec4<__nv_bfloat16> {
         return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
     }
 };
+
+// the combine on 8 consecutive columns per thread: the same sum in the same order (k ascending, then the shared expert), 16-byte loads
+template <typename OUT>
+__global__ void moe_combine8_kernel(const __half* __restrict__ y, int64_t ldy, const float* __restrict__ scs, const float* __restrict__ sgs, const __half* __restrict__ shared,
+                                    int64_t lds, int T, int K, int H8, OUT* __restrict__ o, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)T * H8) return;
+    const int t = (int)(i / H8), c = (int)(i % H8) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < K; ++k) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + ((size_t)t * K + k) * ldy + c));
+        const __half* vh = reinterpret_cast<const __half*>(&v);
+        const float w = scs[(size_t)t * K + k];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += __half2float(vh[j]) * w;
+    }
+    if (shared) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(shared + (size_t)t * lds + c));
+        const __half* vh = reinterpret_cast<const __half*>(&v);
+        const float w = sgs[t];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += w * __half2float(vh[j]);
+    }
+    if constexpr (sizeof(OUT) == 2) {
+        __half oh[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) oh[j] = sat_half(acc[j]);
+        *reinterpret_cast<uint4*>(o + (size_t)t * ldo + c) = *reinterpret_cast<const uint4*>(oh);
+    } else {
+        float4* op = reinterpret_cast<float4*>(o + (size_t)t * ldo + c);
+        op[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        op[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
 
 template <typename XT, int TT>
 __global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E, int H,
@@ -258,6 +313,11 @@ extern "C" int kyb_silu_mul(const void* a, const void* b, int64_t ld, int64_t ro
     KYB_REQUIRE(a && b && h, "null pointer");
     KYB_REQUIRE(rows > 0 && n > 0 && ld >= n && ldh >= n, "rows=%lld n=%lld ld=%lld ldh=%lld", (long long)rows, (long long)n, (long long)ld, (long long)ldh);
     const int64_t total = rows * n;
+    if (!perm && n % 8 == 0 && ld % 8 == 0 && ldh % 8 == 0 && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)h) & 15) == 0) {
+        const int64_t total8 = total / 8;
+        kyb::silu_mul8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)a, (const __half*)b, ld, total8, (int)(n / 8), limit, (__half*)h, ldh);
+        return kyb_launch_check("silu_mul");
+    }
     kyb::silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)a, (const __half*)b, ld, total, (int)n, limit, (const uint32_t*)perm,
                                                                                            (__half*)h, ldh);
     return kyb_launch_check("silu_mul");
@@ -270,6 +330,16 @@ extern "C" int kyb_moe_combine(const void* y, int64_t ldy, const void* scs, cons
     KYB_REQUIRE(!shared || sgs, "a shared-expert output needs its gate values (sgs)");
     KYB_REQUIRE(out_dtype == KYB_DT_F32 || out_dtype == KYB_DT_F16, "out_dtype %d", out_dtype);
     const int64_t total = T * H;
+    if (H % 8 == 0 && ldy % 8 == 0 && ldo % 8 == 0 && (!shared || lds % 8 == 0) && (((uintptr_t)y | (uintptr_t)o | (uintptr_t)shared) & 15) == 0) {
+        const unsigned b8 = (unsigned)((total / 8 + 255) / 256);
+        if (out_dtype == KYB_DT_F16)
+            kyb::moe_combine8_kernel<__half><<<b8, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
+                                                                                   (int)(H / 8), (__half*)o, ldo);
+        else
+            kyb::moe_combine8_kernel<float><<<b8, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
+                                                                                  (int)(H / 8), (float*)o, ldo);
+        return kyb_launch_check("moe_combine");
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == KYB_DT_F16)
         kyb::moe_combine_kernel<__half><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __half*)y, ldy, (const float*)scs, (const float*)sgs, (const __half*)shared, lds, (int)T, K,
