@@ -180,6 +180,19 @@ def run_ours(args):
     two = ops.TWO_LAUNCH                                              # split-k shapes: gemv_t16_kernel + gemv_finalize_kernel
     launches_per_step = sum(1 + (two and ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
 
+    # N > 1: the output slices of a whole step are exchanged by ONE copy launch into every rank's symmetric buffer plus ONE device-side barrier
+    # (kyojin_mac_b200.dist.PeerGather); --nccl-gather uses one NCCL all-gather per product instead
+    pg = None
+    if world > 1 and not args.nccl_gather:
+        from kyojin_mac_b200.dist import PeerGather
+        order = [(m, i) for m in BATCHES for i in range(len(mats))]
+        try:
+            pg = PeerGather([tuple(ys[key].shape) for key in order], dev)
+        except Exception as e:
+            pg = None
+            if rank == 0:
+                print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); NCCL all-gathers", file=sys.stderr)
+
     def one_step(layer, timed=None):
         works = []
         for m in BATCHES:
@@ -191,10 +204,12 @@ def run_ours(args):
                 if timed is not None and i == timed[0]:
                     e1.record()
                     timed[1].append((m, e0, e1))
-                if world > 1:                                    # gathers run on NCCL's stream and overlap the following products; joined at the end of the step
+                if world > 1 and pg is None:                     # gathers run on NCCL's stream and overlap the following products; joined at the end of the step
                     works.append(dist.all_gather_into_tensor(yg[(m, i)], ys[(m, i)], async_op=True))
         for w in works:
             w.wait()
+        if pg is not None:
+            pg([ys[key] for key in order])
 
     def barrier():
         if world > 1:
@@ -341,7 +356,8 @@ def run_ours(args):
                 "config": {"workload": "cfg1: decode GEMV sweep over a 32B-class layer (q,k,v,o,gate,up Q4_K; down Q6_K), M=1,2,4,8 per step",
                            "launch_list": [f"{nm}:{f}:{n}x{k}" for nm, f, n, k in mats], "same_input_groups": not args.no_group,
                            "l2": "two layer copies alternate; one layer (328 MB) exceeds the 126 MB L2", "timing": "CUDA graph per step, CUDA events, max over ranks" if graphs is not None else "eager launches, CUDA events, max over ranks",
-                           "parallelism": f"n-sharded x{world} + NCCL all-gather of output slices" if world > 1 else "single GPU",
+                           "parallelism": (f"n-sharded x{world} + peer-store gather of the step's output slices (one launch + one barrier per step)" if pg is not None
+                                           else f"n-sharded x{world} + NCCL all-gather of output slices") if world > 1 else "single GPU",
                            "bytes_per_step": step_bytes},
                 "roofline": roofline, "cpu_baseline": cpu,
                 "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
@@ -367,6 +383,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-group", action="store_true", help="launch q, k, v and gate, up separately instead of as same-input groups")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--nccl-gather", action="store_true", help="N > 1: one NCCL all-gather per product instead of the one-launch peer gather of the step")
     ap.add_argument("--e2e-eager", action="store_true", help="end-to-end leg through eager module calls instead of the HostGraph step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

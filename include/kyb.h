@@ -177,8 +177,10 @@ int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int64_t n, flo
 int kyb_q4mma(const void* w, const void* scales, const void* biases, int group, const void* x, int64_t ldx, int64_t rows, int64_t n, int64_t k,
               void* y, int64_t ldy, void* stream);
 
-/* up to 64 device arrays copied into (slots of) one buffer by a single launch; addresses and sizes are multiples of 16 bytes. Used by the host-side step
- * (kyojin_mac_b200/host_graph.py) so that the results of a decode step leave the device with one copy; the reference needs no counterpart (unified memory). */
+/* up to 128 device arrays copied by a single launch; addresses and sizes are multiples of 16 bytes; destinations may be peer-mapped addresses of other GPUs. Used by
+ * the host-side step (kyojin_mac_b200/host_graph.py: the results of a decode step leave the device with one copy) and by the decode all-gather of N-sharded
+ * linears (kyojin_mac_b200/dist.py PeerGather: every rank stores its output slices into all ranks' buffers with one launch per step). No counterpart in the
+ * reference (unified memory, one device). */
 int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* bytes, int count, void* stream);
 
 /* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).

@@ -79,13 +79,13 @@ size_t kyb_raw_row_bytes(int fmt, int64_t k) {
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------------------ results of a step gathered into one buffer
-// Up to 64 device arrays copied into one contiguous buffer by a single launch (16-byte units; sizes and addresses multiples of 16): the results of a decode step
+// Up to 128 device arrays copied into one contiguous buffer by a single launch (16-byte units; sizes and addresses multiples of 16): the results of a decode step
 // leave the device with one copy instead of one per product.
 namespace kyb {
 struct GatherList {
-    const uint4* src[64];
-    uint4* dst[64];
-    uint32_t units[64];
+    const uint4* src[128];
+    uint4* dst[128];
+    uint32_t units[128];
     int count;
 };
 __global__ void gather_flat_kernel(const GatherList g) {
@@ -98,7 +98,7 @@ __global__ void gather_flat_kernel(const GatherList g) {
 }  // namespace kyb
 
 extern "C" int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* bytes, int count, void* stream) {
-    KYB_REQUIRE(srcs && dsts && bytes && count >= 1 && count <= 64, "1..64 arrays");
+    KYB_REQUIRE(srcs && dsts && bytes && count >= 1 && count <= 128, "1..128 arrays");
     kyb::GatherList g;
     uint32_t most = 0;
     for (int i = 0; i < count; ++i) {

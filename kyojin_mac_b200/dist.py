@@ -56,6 +56,51 @@ class ShardedLinear:
         return torch.cat([out[r, :, :s] for r, s in enumerate(self.splits)], dim=1)
 
 
+class PeerGather:
+    """All-gather of the output slices of a whole decode step: every rank stores its (small) local outputs into ALL ranks' gathered buffers with ONE copy launch
+    (plain 16-byte stores to peer-mapped symmetric memory over NVLink) followed by ONE device-side barrier, instead of one NCCL all-gather per product.
+    shapes[i] = (m, n_local) of product i (the same on every rank; pad uneven shards); dtype float16. gathered(i) is this rank's [world, m, n_local] view, valid
+    until the call after next (two buffer sets alternate)."""
+
+    def __init__(self, shapes, device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        self.group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.shapes = [tuple(s) for s in shapes]
+        self.bytes = [m * n * 2 for m, n in self.shapes]
+        if any(b % 16 for b in self.bytes):
+            raise ValueError("every local output must be a multiple of 16 bytes")
+        self.offs, tot = [], 0
+        for b in self.bytes:
+            self.offs.append(tot)
+            tot += (self.world * b + 255) // 256 * 256
+        self.bufs = [symm.empty(tot, dtype=torch.uint8, device=device) for _ in range(2)]
+        self.hdls = [symm.rendezvous(b, self.group) for b in self.bufs]
+        self.turn, self.last = 0, 0
+
+    def __call__(self, outs) -> None:
+        """outs[i]: this rank's contiguous fp16 [m, n_local] result of product i (on the current stream)."""
+        from . import ops
+        i, self.turn = self.turn, self.turn ^ 1
+        hdl = self.hdls[i]
+        srcs, dsts, sizes = [], [], []
+        for o, off, b in zip(outs, self.offs, self.bytes):
+            if o.numel() * o.element_size() != b or not o.is_contiguous():
+                raise ValueError("output does not match its registered shape")
+            for base in hdl.buffer_ptrs:
+                srcs.append(o)
+                dsts.append(int(base) + off + self.rank * b)
+                sizes.append(b)
+        ops.gather_flat(srcs, dsts, sizes)
+        hdl.barrier()
+        self.last = i
+
+    def gathered(self, i: int) -> torch.Tensor:
+        m, n = self.shapes[i]
+        b = self.bytes[i]
+        return self.bufs[self.last][self.offs[i]:self.offs[i] + self.world * b].view(torch.float16).reshape(self.world, m, n)
+
+
 class FusedShardedLinear:
     """N-sharded prefill linear whose GEMM writes every output tile into the output matrix of EVERY rank (peer stores over NVLink from the epilogue), so the
     all-gather overlaps the tensor-core work tile by tile; one device-side barrier per call tells the ranks that all tiles have landed. `dev` is this rank's DevPack

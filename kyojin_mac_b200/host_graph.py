@@ -65,8 +65,7 @@ class _Stage:
             self.outputs = [_view(self.hout, p, tuple(o.shape), o.dtype) for p, o in zip(oo, outs)]
         pairs = list(zip(outs, self.oviews))
         fast = [(o, d) for o, d in pairs if o.is_contiguous() and (o.numel() * o.element_size()) % 16 == 0 and o.data_ptr() % 16 == 0]
-        for i in range(0, len(fast), 64):                                    # one launch per 64 results
-            ops.gather_flat([o for o, _ in fast[i:i + 64]], [d for _, d in fast[i:i + 64]])
+        ops.gather_flat([o for o, _ in fast], [d for _, d in fast])          # one launch per 128 results
         for o, d in pairs:
             if not any(o is f for f, _ in fast):
                 d.copy_(o)

@@ -180,20 +180,34 @@ def dequant_rows(fmt, t16: torch.Tensor, n: int, k: int, rows: torch.Tensor, dty
     return out
 
 
-def gather_flat(srcs, dsts) -> None:
-    """Copies each contiguous device tensor srcs[i] into dsts[i] (same byte count, multiples of 16 bytes, 16-byte aligned) with one launch; up to 64 pairs."""
+def gather_flat(srcs, dsts, nbytes=None) -> None:
+    """Copies srcs[i] into dsts[i] (equal byte counts, multiples of 16 bytes, 16-byte aligned) with one launch per 128 pairs. Entries are contiguous device tensors
+    or raw device addresses (ints, e.g. peer-mapped pointers; then nbytes[i] gives the size)."""
     import ctypes as C
     n = len(srcs)
     if n == 0:
         return
-    _need_cuda(*srcs, *dsts)
-    for a, b in zip(srcs, dsts):
-        if not (a.is_contiguous() and b.is_contiguous()) or a.numel() * a.element_size() != b.numel() * b.element_size():
-            raise ValueError("gather_flat copies contiguous tensors of equal byte counts")
-    S = (C.c_void_p * n)(*[t.data_ptr() for t in srcs])
-    D = (C.c_void_p * n)(*[t.data_ptr() for t in dsts])
-    B = (C.c_int64 * n)(*[t.numel() * t.element_size() for t in srcs])
-    _lib.check(_lib.lib().kyb_gather_flat(S, D, B, n, _stream()))
+    ptr = lambda t: t if isinstance(t, int) else t.data_ptr()
+    sizes = []
+    for i, (a, b) in enumerate(zip(srcs, dsts)):
+        sz = None
+        for t in (a, b):
+            if isinstance(t, torch.Tensor):
+                if not t.is_cuda or not t.is_contiguous():
+                    raise ValueError("gather_flat copies contiguous CUDA tensors")
+                tsz = t.numel() * t.element_size()
+                if sz is not None and tsz != sz:
+                    raise ValueError("gather_flat: source and destination differ in size")
+                sz = tsz
+        if sz is None:
+            sz = int(nbytes[i])
+        sizes.append(sz)
+    for i in range(0, n, 128):
+        m = min(128, n - i)
+        S = (C.c_void_p * m)(*[ptr(t) for t in srcs[i:i + m]])
+        D = (C.c_void_p * m)(*[ptr(t) for t in dsts[i:i + m]])
+        B = (C.c_int64 * m)(*sizes[i:i + m])
+        _lib.check(_lib.lib().kyb_gather_flat(S, D, B, m, _stream()))
 
 
 def moe_plan(ids: torch.Tensor, E: int, topk: int, mt: int = 128, wts: torch.Tensor | None = None, rank: torch.Tensor | None = None):

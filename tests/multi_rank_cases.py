@@ -27,6 +27,16 @@ def main():
         got = fused(x)
         assert torch.equal(got, want), "fused all-gather differs from the unsharded product"
     assert torch.equal(nccl, want), "NCCL all-gather differs from the unsharded product"
+    # ---- decode: the slices of several products gathered with one copy launch + one barrier
+    shapes = [(1, 512), (4, 512), (8, 256)]
+    pgather = D.PeerGather(shapes, x.device)
+    for it in range(3):
+        outs = [torch.full(sh, float(rank * 10 + i + it), dtype=torch.float16, device="cuda") for i, sh in enumerate(shapes)]
+        pgather(outs)
+        for i, sh in enumerate(shapes):
+            got_i = pgather.gathered(i)
+            for r in range(world):
+                assert torch.all(got_i[r] == float(r * 10 + i + it)), "peer gather: wrong slice"
     # ---- NVFP4 W4A4 shard
     n4 = 512 * world
     full4 = synth.t16_random_device("nvfp4", n4, k, seed=4)
