@@ -108,9 +108,10 @@ class FusedShardedLinear:
     the fly). Outputs live in two alternating symmetric-memory buffers of max_rows rows: the tensor returned by call c is valid until call c + 2, and the
     consumer must read it on the stream of the call. Rows <= 32 (decode) are served by ShardedLinear (GEMV + NCCL all-gather): they are latency-bound either way."""
 
-    def __init__(self, dev, n_total: int, max_rows: int, group=None, a4: bool = False, out_dtype=torch.float16):
+    def __init__(self, dev, n_total: int, max_rows: int, group=None, a4: bool = False, out_dtype=torch.float16, msub: int = 0):
         import torch.distributed._symmetric_memory as symm
         self.dev, self.n, self.group, self.a4, self.out_dtype = dev, n_total, group or dist.group.WORLD, a4, out_dtype
+        self.msub = msub                                                     # K-quant GEMM: activation blocks per work item (1: the peer stores of a tile overlap the next tile's MMAs)
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         align = 256 if a4 else 16
         self.col0, rows = shard_rows(n_total, self.world, self.rank, align)
@@ -140,7 +141,7 @@ class FusedShardedLinear:
         else:
             if self.out_dtype != torch.float16:
                 raise ValueError("the K-quant GEMM writes float16")
-            ops.gemm_kq_ag(d.fmt, d.t16, d.n, d.k, x.to(torch.float16), ptrs, self.n, self.col0, d.gscale)
+            ops.gemm_kq_ag(d.fmt, d.t16, d.n, d.k, x.to(torch.float16), ptrs, self.n, self.col0, d.gscale, self.msub)
         hdl.barrier()                                                        # every rank's tiles have landed in every buffer
         return buf[:m]
 

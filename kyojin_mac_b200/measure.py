@@ -190,10 +190,11 @@ def dist_cases(E=256):
         lin = D.ShardedLinear(dp.apply, n)
         x = torch.randn((m, k), device="cuda", generator=gen).to(torch.float16)
         fused = D.FusedShardedLinear(dp, n, m)
-        t_local, t_all, t_fused = tmax(lambda: dp.apply(x)), tmax(lambda: lin(x)), tmax(lambda: fused(x))
+        fused1 = D.FusedShardedLinear(dp, n, m, msub=1)
+        t_local, t_all, t_fused, t_fused1 = tmax(lambda: dp.apply(x)), tmax(lambda: lin(x)), tmax(lambda: fused(x)), tmax(lambda: fused1(x))
         same = bool(torch.equal(fused(x), lin(x)))
         fl = 2.0 * m * n * k
-        say(case=f"cfg2 q3_k {k}->{n} m={m} N-sharded", local_us=t_local, nccl_allgather_us=t_all, fused_allgather_us=t_fused, local_TFLOPs=fl / t_local / 1e6,
+        say(case=f"cfg2 q3_k {k}->{n} m={m} N-sharded", local_us=t_local, nccl_allgather_us=t_all, fused_allgather_us=t_fused, fused_msub1_us=t_fused1, local_TFLOPs=fl / t_local / 1e6,
             nccl_allgather_TFLOPs=fl / t_all / 1e6, fused_allgather_TFLOPs=fl / t_fused / 1e6, fused_equals_nccl=same)
     n, k, m = 18432, 7168, 4096
     row0, rows = D.shard_rows(n, world, rank, align=256)
