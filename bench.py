@@ -303,17 +303,24 @@ def run_ours(args):
     # single GPU: the step goes through the package's HostGraph (pinned inputs -> h2d -> the layer's modules -> d2h into pinned outputs, one CUDA graph per
     # layer copy): the same copies and launches as the eager loop, without the per-call Python dispatch
     hgraphs = None
-    if world == 1 and not args.e2e_eager:
+    if (world == 1 or pg is not None) and not args.e2e_eager:
         from kyojin_mac_b200.host_graph import HostGraph
         try:
             hgraphs = []
+            pgs = None
+            if world > 1:                                                        # N > 1: every stage ends with the peer gather of its four products
+                from kyojin_mac_b200.dist import PeerGather
+                pgs = {m: PeerGather([(m, n_) for _, _, n_, _ in mats], dev) for m in BATCHES}
             for c in range(copies):
                 layer = mods[c]
                 stages = []
                 for m in BATCHES:                                                # one stage per batch size: its upload / download overlap the neighbours' products
-                    def stage_fn(*dx, layer=layer):
+                    def stage_fn(*dx, layer=layer, m=m):
                         d = dict(zip(ks, dx))
-                        return [layer[i](d[k_]) for i, (nm_, f_, n_, k_) in enumerate(mats)]
+                        outs = [layer[i](d[k_]) for i, (nm_, f_, n_, k_) in enumerate(mats)]
+                        if pgs is not None:
+                            pgs[m](outs)
+                        return outs
                     stages.append((stage_fn, [hx[(m, k)] for k in ks]))
                 hgraphs.append(HostGraph.staged(stages, dev))
             h2d, d2h = hgraphs[0].h2d_bytes, hgraphs[0].d2h_bytes                 # what the copies of a step move (inputs / results, 256-byte aligned slots)

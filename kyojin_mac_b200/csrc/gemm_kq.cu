@@ -225,27 +225,22 @@ template <int FMT, int P>
 __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32_t scr, int lane, uint32_t (&r)[16]) {
     const int g = lane >> 2;
     if constexpr (FMT == KYB_FMT_Q4_K) {
-        // Slices c (low nibbles) and 2 + c (high nibbles) come from the same words, so lanes with odd g produce them directly in the swapped order the
-        // conflict-free store wants (kq_store_quarter): mask, de-bias constants and scale pair are per-lane values, the instruction sequence is the same.
-        const bool odd = (g & 1) != 0;
-        const uint32_t m_a = odd ? 0x00F000F0u : 0x000F000Fu, m_b = odd ? 0x000F000Fu : 0x00F000F0u;
-        // low nibble: (1024 + q) * 1 - 1024; high nibble: (1024 + 16 q) / 16 - 64; both exact
-        const uint32_t mul_a = odd ? 0x2C002C00u : 0x3C003C00u, add_a = odd ? 0xD400D400u : 0xE400E400u;
-        const uint32_t mul_b = odd ? 0x3C003C00u : 0x2C002C00u, add_b = odd ? 0xE400E400u : 0xD400D400u;
-        const uint32_t off_a = odd ? 4u : 0u, off_b = 4u - off_a;                            // scale of sub-block 2 P (low nibbles) or 2 P + 1 (high nibbles)
-        const uint32_t u4[4] = {tr.q[P].x, tr.q[P].y, tr.q[P].z, tr.q[P].w};
+        const uint4 u = tr.q[P];
+        const uint2 sg = lds64(scr + g * 32 + 8 * P), zg = lds64(scr + 512 + g * 32 + 8 * P);
+        const uint2 sh = lds64(scr + (g + 8) * 32 + 8 * P), zh = lds64(scr + 512 + (g + 8) * 32 + 8 * P);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint32_t sp = scr + (g + 8 * h) * 32 + 8 * P;
-            const uint32_t s_a = lds32(sp + off_a), s_b = lds32(sp + off_b), z_a = lds32(sp + 512 + off_a), z_b = lds32(sp + 512 + off_b);
+        for (int c = 0; c < 2; ++c) {
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const uint32_t w = u4[2 * c + h];
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t w = h ? (c ? u.w : u.y) : (c ? u.z : u.x);
+                const uint32_t s_lo = h ? sh.x : sg.x, s_hi = h ? sh.y : sg.y, z_lo = h ? zh.x : zg.x, z_hi = h ? zh.y : zg.y;
                 const uint32_t p01 = prmt(w, 0u, 0x4140u), p23 = prmt(w, 0u, 0x4342u);       // bytes (b0, 0, b1, 0), (b2, 0, b3, 0)
-                const uint32_t a01 = h2_fma(and_or(p01, m_a, 0x64006400u), mul_a, add_a), a23 = h2_fma(and_or(p23, m_a, 0x64006400u), mul_a, add_a);
-                const uint32_t b01 = h2_fma(and_or(p01, m_b, 0x64006400u), mul_b, add_b), b23 = h2_fma(and_or(p23, m_b, 0x64006400u), mul_b, add_b);
-                r[4 * c + 2 * h] = h2_fma(a01, s_a, z_a), r[4 * c + 2 * h + 1] = h2_fma(a23, s_a, z_a);
-                r[4 * (2 + c) + 2 * h] = h2_fma(b01, s_b, z_b), r[4 * (2 + c) + 2 * h + 1] = h2_fma(b23, s_b, z_b);
+                // low nibbles: 1024 + q, minus 1024; high nibbles: (1024 + 16 q) / 16 - 64; both exact
+                const uint32_t l01 = h2_sub(and_or(p01, 0x000F000Fu, 0x64006400u), 0x64006400u), l23 = h2_sub(and_or(p23, 0x000F000Fu, 0x64006400u), 0x64006400u);
+                const uint32_t h01 = h2_fma(and_or(p01, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
+                const uint32_t h23 = h2_fma(and_or(p23, 0x00F000F0u, 0x64006400u), 0x2C002C00u, 0xD400D400u);
+                r[4 * c + 2 * h] = h2_fma(l01, s_lo, z_lo), r[4 * c + 2 * h + 1] = h2_fma(l23, s_lo, z_lo);
+                r[4 * (2 + c) + 2 * h] = h2_fma(h01, s_hi, z_hi), r[4 * (2 + c) + 2 * h + 1] = h2_fma(h23, s_hi, z_hi);
             }
         }
     } else {
@@ -313,19 +308,12 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
 // slice i sits at ((2 i + (t >> 1)) ^ g) * 16, and the 16 lanes an 8-byte store serves together have only four values of g: if all of them stored the same slice they
 // would cover 4 distinct chunks (two-way bank conflict). So in step k the lanes with odd g store slice k ^ 2 instead of slice k: the 16 lanes then cover all 8
 // chunks of their rows and every store is conflict-free. cxs[k] is the swizzled offset of the slice this lane stores in step k.
-// PRESWAPPED: the registers of odd-g lanes already hold the slices in that order (Q4_K computes them so); otherwise they are selected here.
-template <bool PRESWAPPED>
 __device__ __forceinline__ void kq_store_quarter(uint32_t dst_g, uint32_t dst_h, const uint32_t (&cxs)[4], bool odd, const uint32_t (&r)[16]) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int a = 4 * k, b = 4 * (k ^ 2);
-        if constexpr (PRESWAPPED) {
-            sts64(dst_g + cxs[k], r[a], r[a + 1]);
-            sts64(dst_h + cxs[k], r[a + 2], r[a + 3]);
-        } else {
-            sts64(dst_g + cxs[k], odd ? r[b] : r[a], odd ? r[b + 1] : r[a + 1]);
-            sts64(dst_h + cxs[k], odd ? r[b + 2] : r[a + 2], odd ? r[b + 3] : r[a + 3]);
-        }
+        sts64(dst_g + cxs[k], odd ? r[b] : r[a], odd ? r[b + 1] : r[a + 1]);
+        sts64(dst_h + cxs[k], odd ? r[b + 2] : r[a + 2], odd ? r[b + 3] : r[a + 3]);
     }
 }
 
@@ -555,7 +543,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
     {                                                                                                             \
         if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
         const uint32_t b_dst = smem0 + s * stage_bytes + a_bytes + row_off;                                       \
-        kq_store_quarter<FMT == KYB_FMT_Q4_K>(b_dst, b_dst + 1024u, cx, odd, r);                                  \
+        kq_store_quarter(b_dst, b_dst + 1024u, cx, odd, r);                                                       \
     }
             for (int kb = 0; kb < p.nb && !failed; ++kb) {
                 const bool more = kb + 1 < p.nb, more2 = kb + 2 < p.nb;
