@@ -638,8 +638,18 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     p.nout = nout;
     for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] + col0 : nullptr;
     p.gscale = gscale, p.status = status, p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
-    p.msub = msub ? msub : (m > 128 ? 2 : 1);
-    p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN), p.tiles_m = (int)((m + 128 * p.msub - 1) / (128 * p.msub));
+    p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN);
+    if (!msub) {
+        // two activation blocks per item halve the decode work per flop, but they halve the number of items and keep both accumulators busy (no overlap of
+        // the epilogue with the next item): one block when the rows fit one block, when two-block items would leave more than half of the SMs idle, or when the
+        // epilogue also feeds other GPUs (its peer stores then overlap the next item's MMAs)
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int64_t items2 = (int64_t)p.tiles_n * ((m + 255) / 256);
+        msub = (m <= 128 || items2 * 2 < sms || nout > 1) ? 1 : 2;
+    }
+    p.msub = msub;
+    p.tiles_m = (int)((m + 128 * p.msub - 1) / (128 * p.msub));
     // tiled bulk stores need 16-byte aligned bases and row pitches; otherwise the epilogue stores from registers
     KybOutMaps outs;
     memset(&outs, 0, sizeof(outs));

@@ -225,7 +225,7 @@ __global__ void moe_combine8_kernel(const __half* __restrict__ y, int64_t ldy, c
 }
 
 template <typename XT, int TT>
-__global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E, int H,
+__global__ void __launch_bounds__(512) router_logits_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E, int H,
                                                             float* __restrict__ lg, int64_t ldl) {
     extern __shared__ __align__(16) unsigned char router_smem[];
     XT* xs = reinterpret_cast<XT*>(router_smem);
@@ -238,9 +238,9 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const XT* __restrict
         *reinterpret_cast<uint4*>(xs + (size_t)j * H + (size_t)c * PER) = *reinterpret_cast<const uint4*>(x + (size_t)t * ldx + (size_t)c * PER);
     }
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, R = E + (sgw ? 1 : 0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, R = E + (sgw ? 1 : 0), nw = blockDim.x >> 5;
     // weight rows are dealt to (blockIdx.y, warp) in groups of RE
-    for (int r0 = (blockIdx.y * 8 + warp) * RE; r0 < R; r0 += gridDim.y * 8 * RE) {
+    for (int r0 = (blockIdx.y * nw + warp) * RE; r0 < R; r0 += gridDim.y * nw * RE) {
         const float4* wp[RE];
 #pragma unroll
         for (int e = 0; e < RE; ++e) {
@@ -359,9 +359,10 @@ static int launch_router(const void* x, int64_t ldx, const float* gw, const floa
         configured = true;
     }
     const int64_t gx = (T + TT - 1) / TT;
-    const int R = E + (sgw ? 1 : 0), ymax = (R + 31) / 32;                   // 8 warps x 4 rows per pass
+    const int threads = T >= 1024 ? 512 : 256;                               // many tokens: 16 warps per CTA hide the L2 latency of the weight rows
+    const int R = E + (sgw ? 1 : 0), ymax = (R + threads / 8 - 1) / (threads / 8);   // warps x 4 rows per pass
     const int gy = (int)std::min<int64_t>(ymax, std::max<int64_t>(1, (2 * 148 + gx - 1) / gx));   // few tokens: spread the weight rows over more CTAs
-    kyb::router_logits_kernel<XT, TT><<<dim3((unsigned)gx, (unsigned)gy), 256, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
+    kyb::router_logits_kernel<XT, TT><<<dim3((unsigned)gx, (unsigned)gy), threads, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
     return kyb_launch_check("router_logits");
 }
 
