@@ -37,6 +37,12 @@ BPW = {"q4_k": 144 / 256, "q6_k": 210 / 256, "q3_k": 110 / 256, "nvfp4": 144 / 2
 METRIC = "quant GEMV GB/s (% HBM peak)"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes in the ncu capture of this kernel on the 27648 x 5120 Q4_K matrix, M = 1 (half of the
+# benchmark's gate|up launch; traffic grows with the rows): 79.73 MB over 79.64 MB
+NCU_TRAFFIC_RATIO = 1.0011
+NCU_TRAFFIC_NOTE = "ncu capture of gemv_t16_kernel on 27648 x 5120 (profiles/gemv_q4k_27648x5120_m1_ncu.md), scaled to this launch by its rows"
+
+
 def alg_bytes(fmt, n, k, m):
     """Algorithmic bytes of one GEMV: stored weight bytes + fp16 activations in + fp16 results out."""
     return n * k * BPW[fmt] + 2 * m * k + 2 * m * n
@@ -277,7 +283,7 @@ def run_ours(args):
     peak, peak_src = peaks()
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": f"gemv_t16_kernel<{f}> on {nm} [{n} x {k}]", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": peak_src, "traffic": None, "alg_bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3,
+                "peak_source": peak_src, "traffic": dom_bytes * NCU_TRAFFIC_RATIO, "traffic_source": NCU_TRAFFIC_NOTE, "alg_bytes_per_launch": dom_bytes, "us_per_launch": dom_ms * 1e3,
                 "us_per_launch_by_m": {str(m): float(np.mean(v)) * 1e3 for m, v in per_m.items()},
                 "whole_step_frac_of_peak": value / world / peak}
 
