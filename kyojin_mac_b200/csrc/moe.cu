@@ -224,6 +224,23 @@ __global__ void moe_combine8_kernel(const __half* __restrict__ y, int64_t ldy, c
     }
 }
 
+// two fp32 multiply-adds in one instruction (sm_100: fma.rn.f32x2 on register pairs)
+__device__ __forceinline__ unsigned long long ffma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long p;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(lo), "f"(hi));
+    return p;
+}
+__device__ __forceinline__ float sum2(unsigned long long p) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+    return lo + hi;
+}
+
 template <typename XT, int TT>
 __global__ void __launch_bounds__(512) router_logits_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E, int H,
                                                             float* __restrict__ lg, int64_t ldl) {
@@ -247,27 +264,32 @@ __global__ void __launch_bounds__(512) router_logits_kernel(const XT* __restrict
             const int r = min(r0 + e, R - 1);                               // a short last group repeats its last row; the repeats are not stored
             wp[e] = reinterpret_cast<const float4*>(r < E ? gw + (size_t)r * H : sgw);
         }
-        float acc[RE][TT];
+        // every accumulator is a pair (sum over even inputs, sum over odd inputs) so that one packed instruction does two multiply-adds
+        unsigned long long acc[RE][TT];
 #pragma unroll
         for (int e = 0; e < RE; ++e)
 #pragma unroll
-            for (int j = 0; j < TT; ++j) acc[e][j] = 0.f;
+            for (int j = 0; j < TT; ++j) acc[e][j] = 0ull;
         for (int i = lane; i < H / 4; i += 32) {
-            float4 w[RE];
+            unsigned long long wlo[RE], whi[RE];
 #pragma unroll
-            for (int e = 0; e < RE; ++e) w[e] = __ldg(wp[e] + i);
+            for (int e = 0; e < RE; ++e) {
+                const float4 w = __ldg(wp[e] + i);
+                wlo[e] = pack2(w.x, w.y), whi[e] = pack2(w.z, w.w);
+            }
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
                 const float4 v = XVec4<XT>::ld(xs + (size_t)j * H + 4 * i);
+                const unsigned long long vlo = pack2(v.x, v.y), vhi = pack2(v.z, v.w);
 #pragma unroll
-                for (int e = 0; e < RE; ++e) acc[e][j] = fmaf(w[e].x, v.x, fmaf(w[e].y, v.y, fmaf(w[e].z, v.z, fmaf(w[e].w, v.w, acc[e][j]))));
+                for (int e = 0; e < RE; ++e) acc[e][j] = ffma2(whi[e], vhi, ffma2(wlo[e], vlo, acc[e][j]));
             }
         }
 #pragma unroll
         for (int e = 0; e < RE; ++e)
 #pragma unroll
             for (int j = 0; j < TT; ++j) {
-                float v = acc[e][j];
+                float v = sum2(acc[e][j]);
 #pragma unroll
                 for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
                 if (lane == 0 && t0 + j < T && r0 + e < R) lg[(size_t)(t0 + j) * ldl + r0 + e] = v;
