@@ -46,6 +46,7 @@ struct KqParams {
     int tiles_m, tiles_n;
     int msub, stages;
     int tma_out, col0;          // dense form: the epilogue stores through the tensor maps (bulk tiled stores), at column col0 + n0
+    int wide;                   // ... in 32 x 64 boxes (4 KB of staging per epilogue warp) instead of 32 x 32: used when the tiles also go to other GPUs
 };
 
 struct KqItem {
@@ -373,7 +374,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t scr0 = smem0 + (uint32_t)STAGES * stage_bytes;
     const uint32_t stg0 = scr0 + KQ_DW * KQ_SCR;                                    // epilogue staging, 4 warps
-    const uint32_t bars = stg0 + 4 * KQ_STG;                                        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+    const uint32_t stg_bytes = p.wide ? 2 * KQ_STG : KQ_STG;
+    const uint32_t bars = stg0 + 4 * stg_bytes;                                     // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16, tmem_slot = acce0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = p.k / KQ_BK;
@@ -455,7 +457,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                 if (p.tma_out) {
                     // ---- staged tiled stores: 32 rows x 32 columns per step go to shared memory (64-byte swizzle, conflict-free 16-byte stores) and leave as one bulk
                     // tensor store per receiving rank: full 64-byte row segments on the wire, rows / columns past the matrix are dropped by the tensor map
-                    const uint32_t stg = stg0 + (uint32_t)q * KQ_STG;
+                    const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
                     const int row0 = it.m0 + sub * 128 + q * 32;
 #pragma unroll 1
                     for (int c = 0; c < KQ_BN; c += 32) {
@@ -468,7 +470,11 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                             __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * j]) * gscale), sat_half(__uint_as_float(v[2 * j + 1]) * gscale));
                             w[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
-                        epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + it.n0 + c, row0, !failed && row0 < it.m_end && it.n0 + c < p.n);
+                        if (p.wide)
+                            epilogue_stage_store_wide(outs, p.nout, stg, lane, w, (c >> 5) & 1, p.col0 + it.n0 + (c & ~63), row0,
+                                                      !failed && row0 < it.m_end && it.n0 + (c & ~63) < p.n);
+                        else
+                            epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + it.n0 + c, row0, !failed && row0 < it.m_end && it.n0 + c < p.n);
                     }
                 } else {
                 const int row = it.m0 + sub * 128 + q * 32 + lane;
@@ -601,7 +607,7 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
                                              : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
     const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
-    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * kyb::KQ_STG + 1024 + 256;
+    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * (p.wide ? 2 : 1) * kyb::KQ_STG + 1024 + 256;
     const size_t cap = 227 * 1024;
     p.stages = (int)std::min<size_t>(8, (cap - fixed) / stage_bytes);
     const size_t smem = (size_t)p.stages * stage_bytes + fixed;
@@ -657,8 +663,10 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     p.tma_out = (ldd % 8 == 0 && col0 % 8 == 0) ? 1 : 0;
     for (int i = 0; i < nout && p.tma_out; ++i)
         if ((uintptr_t)d[i] & 15) p.tma_out = 0;
+    p.wide = (p.tma_out && nout > 1) ? 1 : 0;
     for (int i = 0; i < nout && p.tma_out; ++i)
-        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
+                                      p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
     return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }
@@ -712,7 +720,7 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     p.msub = mt / 128;
     p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
-    p.tma_out = 0, p.col0 = 0;                                                     // rows are scattered (row_map) or end inside a tile: stores from registers
+    p.tma_out = 0, p.col0 = 0, p.wide = 0;                                         // rows are scattered (row_map) or end inside a tile: stores from registers
     KybOutMaps outs;
     memset(&outs, 0, sizeof(outs));
     return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);

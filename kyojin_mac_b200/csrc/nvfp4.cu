@@ -165,6 +165,7 @@ struct NvGemmParams {
     __half* d[8];            // output matrix on every receiving rank (one entry without sharding), already offset to this rank's first column
     int nout;
     int tma_out, col0;       // the epilogue stores through the tensor maps (tiled bulk stores) at column col0 + n0
+    int wide, stages;        // 32 x 64 boxes (outputs that also go to other GPUs; one pipeline stage fewer to make room for the staging), ring depth
     int64_t ldd;
     int m, n, k;
     float gscale;
@@ -196,15 +197,17 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                                                                    const __grid_constant__ KybOutMaps outs, const NvGemmParams p, const int tiles_n, const int num_tiles) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t stg0 = smem0 + NV_STAGES * NV_STAGE_BYTES;                      // epilogue staging, 4 warps
-    const uint32_t bars = stg0 + 4 * KYB_STG_BYTES;
-    const uint32_t full0 = bars, empty0 = bars + 8 * NV_STAGES, accf = bars + 16 * NV_STAGES, acce = accf + 8, tmem_slot = acce + 8;
+    const int STAGES = p.stages;
+    const uint32_t stg0 = smem0 + STAGES * NV_STAGE_BYTES;                         // epilogue staging, 4 warps
+    const uint32_t stg_bytes = p.wide ? 2 * KYB_STG_BYTES : KYB_STG_BYTES;
+    const uint32_t bars = stg0 + 4 * stg_bytes;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf = bars + 16 * STAGES, acce = accf + 8, tmem_slot = acce + 8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = p.k / NV_BK, k64 = p.k / 64;
     constexpr uint32_t TMEM_COLS = 512, COL_SFA = 256, COL_SFB = 272;       // accumulator [0, 256), scales of A [256, 272), of B [272, 304)
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NV_STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
         mbar_init_a(accf, 1);
         mbar_init_a(acce, 4);
         mbar_fence_init();
@@ -239,7 +242,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sfb_dst + h * 2048), "l"(sb), "r"(2048u), "r"(bar)
                                      : "memory");
                     }
-                    if (++s == NV_STAGES) s = 0, parity ^= 1u;
+                    if (++s == STAGES) s = 0, parity ^= 1u;
                 }
             }
         }
@@ -268,7 +271,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                     for (int j = 0; j < 4; ++j)                                              // 64 e2m1 = 32 bytes along k inside the swizzle atom
                         umma_nvf4(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + COL_SFA + 4 * j, tmem_base + COL_SFB + 8 * j, (kb | j) != 0);
                     umma_commit(empty0 + 8 * s);
-                    if (++s == NV_STAGES) s = 0, parity ^= 1u;
+                    if (++s == STAGES) s = 0, parity ^= 1u;
                 }
                 umma_commit(accf);
             }
@@ -281,7 +284,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
             if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
             tc_fence_after();
             if (p.tma_out) {
-                const uint32_t stg = stg0 + (uint32_t)q * KYB_STG_BYTES;
+                const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
                 const int row0 = m0 + q * 32;
 #pragma unroll 1
                 for (int c = 0; c < NV_BN; c += 32) {
@@ -300,7 +303,10 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                             w[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
                     }
-                    epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + n0 + c, row0, !failed && row0 < p.m && n0 + c < p.n);
+                    if (p.wide)
+                        epilogue_stage_store_wide(outs, p.nout, stg, lane, w, (c >> 5) & 1, p.col0 + n0 + (c & ~63), row0, !failed && row0 < p.m && n0 + (c & ~63) < p.n);
+                    else
+                        epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + n0 + c, row0, !failed && row0 < p.m && n0 + c < p.n);
                 }
             } else {
             const int row = m0 + q * 32 + lane;
@@ -432,10 +438,14 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
     p.tma_out = (ldd % 8 == 0 && col0 % 8 == 0) ? 1 : 0;                            // tiled bulk stores need 16-byte aligned bases and row pitches
     for (int i = 0; i < nout && p.tma_out; ++i)
         if ((uintptr_t)d[i] & 15) p.tma_out = 0;
+    p.wide = (p.tma_out && nout > 1) ? 1 : 0;
+    p.stages = p.wide ? kyb::NV_STAGES - 1 : kyb::NV_STAGES;
     for (int i = 0; i < nout && p.tma_out; ++i)
-        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B))
+        if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
+                                      p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
-    constexpr size_t smem = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
+    const size_t smem = (size_t)p.stages * kyb::NV_STAGE_BYTES + 4 * (p.wide ? 2 : 1) * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
+    constexpr size_t smem_max = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
     static std::mutex mu;
     static unsigned done = 0;
     int dev = 0;
@@ -443,7 +453,7 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!(done & (1u << (dev & 31)))) {
-            KYB_CUDA(cudaFuncSetAttribute(kyb::gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            KYB_CUDA(cudaFuncSetAttribute(kyb::gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max));
             done |= 1u << (dev & 31);
         }
     }

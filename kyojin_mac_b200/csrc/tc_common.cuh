@@ -86,6 +86,28 @@ __device__ __forceinline__ void epilogue_stage_store(const KybOutMaps& outs, int
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
 }
+// Wide form for outputs that also go to other GPUs: two 32-column steps (half = 0, then 1) fill a [32 rows][128 bytes] buffer (128-byte swizzle; 4 KB, 1024-byte
+// aligned) and leave as one tiled bulk store of 32 x 64 columns per receiving rank: full 128-byte row segments on NVLink instead of 64-byte ones.
+__device__ __forceinline__ void epilogue_stage_store_wide(const KybOutMaps& outs, int nout, uint32_t stg, int lane, const uint32_t (&w)[16], int half, int x, int y, bool issue) {
+    if (half == 0) {
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + (uint32_t)lane * 128u + (uint32_t)(((j + 4 * half) ^ (lane & 7)) << 4)), "r"(w[4 * j]), "r"(w[4 * j + 1]),
+                     "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                     : "memory");
+    if (half == 1) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0 && issue) {
+            for (int pr = 0; pr < nout; ++pr)
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(&outs.m[pr]), "r"(x), "r"(y), "r"(stg) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) { asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory"); }
 
 __device__ __forceinline__ void mbar_init_a(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
