@@ -191,7 +191,7 @@ __device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint6
         : "memory");
 }
 
-// Persistent: CTA c works on tiles c, c + gridDim.x, ... (n tile fastest). Tensor memory: accumulator 256 columns + scale columns; the producer runs ahead
+// Persistent: CTA c works on tiles c, c + gridDim.x, ... (m tile fastest: the CTAs running together share a few weight tiles, the activation codes stay in L2). Tensor memory: accumulator 256 columns + scale columns; the producer runs ahead
 // into the next tile while the epilogue drains the accumulator.
 __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                                                                    const __grid_constant__ KybOutMaps outs, const NvGemmParams p, const int tiles_n, const int num_tiles) {
@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
             uint32_t parity = 1;
             int s = 0;
             for (int t = blockIdx.x; t < num_tiles && !failed; t += gridDim.x) {
-                const int n0 = (t % tiles_n) * NV_BN, m0 = (t / tiles_n) * NV_BM;
+                const int tiles_m = num_tiles / tiles_n, n0 = (t / tiles_m) * NV_BN, m0 = (t % tiles_m) * NV_BM;   // m fastest: CTAs running together share the weight rows
                 for (int kb = 0; kb < kblocks && !failed; ++kb) {
                     if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
                     const uint32_t a_dst = smem0 + s * NV_STAGE_BYTES, b_dst = a_dst + NV_A_BYTES, sfa_dst = b_dst + NV_B_BYTES, sfb_dst = sfa_dst + NV_SFA_BYTES;
@@ -280,7 +280,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
         const int q = warp & 3;
         int it = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
-            const int n0 = (t % tiles_n) * NV_BN, m0 = (t / tiles_n) * NV_BM;
+            const int tiles_m = num_tiles / tiles_n, n0 = (t / tiles_m) * NV_BN, m0 = (t % tiles_m) * NV_BM;   // m fastest: CTAs running together share the weight rows
             if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
             tc_fence_after();
             if (p.tma_out) {
