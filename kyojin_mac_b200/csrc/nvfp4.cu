@@ -28,7 +28,7 @@ __device__ __forceinline__ size_t sf512_offset(int64_t row, int64_t s, int64_t k
     return (size_t)((rb * kblocks64 + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4 + c);
 }
 
-// One thread per 64 inputs (four blocks of 16, one 4-byte group of the scale layouts). Per block: amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6) (true
+// One thread per block of 16 inputs, four lanes per 4-byte group of the scale layouts. Per block: amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6) (true
 // fp32 divide); v = clip(x / scale, -6, 6); code = #(|v| > .25, 1.25, 2.5, 5) + #(|v| >= .75, 1.75, 3.5) (round to nearest even onto e2m1), sign bit 3 for v < 0;
 // two codes per byte, low first (kyojin_mlx/fp4pack.py:30-48).
 // The quotient itself is never formed: for 16-bit inputs fl(|x| / s) > t holds exactly when |x| > t s (t s is exact in fp32, and a 16-bit |x| above t s exceeds it
@@ -43,51 +43,50 @@ template <>
 __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
 
 template <typename T>
-__global__ void __launch_bounds__(128) nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes,
+__global__ void __launch_bounds__(256) nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes,
                                                                uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_swz) {
+    // one thread per block of 16 inputs (two 16-byte loads; a warp reads 1 KB of a row contiguously); the four lanes of a 64-input group combine their scale bytes
+    // with shuffles and one of them writes the 4-byte group of both scale layouts
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t ngrp = k >> 6;
-    if (i >= rows * ngrp) return;
-    const int64_t row = i / ngrp, gq = i % ngrp;
-    const uint4* xp = reinterpret_cast<const uint4*>(x + row * ldx + gq * 64);
-    uint4 raw[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) raw[j] = __ldg(xp + j);
-    uint32_t sbytes = 0;
-    uint32_t packed[8];
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-        float v[16];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const uint4 r = raw[2 * b + h];
-            const float2 p0 = pair_to_float2<T>(r.x), p1 = pair_to_float2<T>(r.y), p2 = pair_to_float2<T>(r.z), p3 = pair_to_float2<T>(r.w);
-            v[8 * h + 0] = p0.x, v[8 * h + 1] = p0.y, v[8 * h + 2] = p1.x, v[8 * h + 3] = p1.y, v[8 * h + 4] = p2.x, v[8 * h + 5] = p2.y, v[8 * h + 6] = p3.x, v[8 * h + 7] = p3.y;
-        }
-        float amax = 6.0f * 0.001953125f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
-        const uint32_t s8 = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3) & 255u;
-        const float scale = e4m3_to_float(s8);
-        sbytes |= s8 << (8 * b);
-        const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale, t5 = 3.5f * scale, t6 = 5.0f * scale;   // exact products
-        uint32_t pk[2] = {0u, 0u};
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float mag = fabsf(v[j]);
-            // thresholds are ordered: a three-level search instead of seven comparisons
-            uint32_t code;
-            if (mag >= t3) code = mag >= t5 ? (mag > t6 ? 7u : 6u) : (mag > t4 ? 5u : 4u);
-            else code = mag >= t1 ? (mag > t2 ? 3u : 2u) : (mag > t0 ? 1u : 0u);
-            pk[j >> 3] |= (code | (v[j] < 0.0f ? 8u : 0u)) << (4 * (j & 7));
-        }
-        packed[2 * b] = pk[0], packed[2 * b + 1] = pk[1];
+    const int64_t nblk = k >> 4, total = rows * nblk;
+    const bool live = i < total;
+    const int64_t ii = live ? i : total - 1;                               // lanes past the end repeat the last block (no stores) so that the shuffles stay full-warp
+    const int64_t row = ii / nblk, b = ii % nblk;
+    const uint4* xp = reinterpret_cast<const uint4*>(x + row * ldx + b * 16);
+    const uint4 r0 = __ldg(xp), r1 = __ldg(xp + 1);
+    float v[16];
+    {
+        const float2 p0 = pair_to_float2<T>(r0.x), p1 = pair_to_float2<T>(r0.y), p2 = pair_to_float2<T>(r0.z), p3 = pair_to_float2<T>(r0.w);
+        const float2 p4 = pair_to_float2<T>(r1.x), p5 = pair_to_float2<T>(r1.y), p6 = pair_to_float2<T>(r1.z), p7 = pair_to_float2<T>(r1.w);
+        v[0] = p0.x, v[1] = p0.y, v[2] = p1.x, v[3] = p1.y, v[4] = p2.x, v[5] = p2.y, v[6] = p3.x, v[7] = p3.y;
+        v[8] = p4.x, v[9] = p4.y, v[10] = p5.x, v[11] = p5.y, v[12] = p6.x, v[13] = p6.y, v[14] = p7.x, v[15] = p7.y;
     }
-    uint4* cp = reinterpret_cast<uint4*>(codes + row * (k >> 1) + gq * 32);
-    cp[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    cp[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-    if (sf_plain) *reinterpret_cast<uint32_t*>(sf_plain + row * (k >> 4) + gq * 4) = sbytes;
-    if (sf_swz) *reinterpret_cast<uint32_t*>(sf_swz + sf512_offset(row, gq * 4, ngrp)) = sbytes;
+    float amax = 6.0f * 0.001953125f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    const uint32_t s8 = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3) & 255u;
+    const float scale = e4m3_to_float(s8);
+    const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale, t5 = 3.5f * scale, t6 = 5.0f * scale;   // exact products
+    uint32_t pk[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float mag = fabsf(v[j]);
+        // thresholds are ordered: a three-level search instead of seven comparisons
+        uint32_t code;
+        if (mag >= t3) code = mag >= t5 ? (mag > t6 ? 7u : 6u) : (mag > t4 ? 5u : 4u);
+        else code = mag >= t1 ? (mag > t2 ? 3u : 2u) : (mag > t0 ? 1u : 0u);
+        pk[j >> 3] |= (code | (v[j] < 0.0f ? 8u : 0u)) << (4 * (j & 7));
+    }
+    if (live) *reinterpret_cast<uint2*>(codes + row * (k >> 1) + b * 8) = make_uint2(pk[0], pk[1]);
+    // scale bytes of the 64-input group (k % 64 == 0, so a group never straddles two rows and its four lanes sit in one warp)
+    const int lane = threadIdx.x & 31;
+    uint32_t word = s8 << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if (live && (lane & 3) == 0) {
+        if (sf_plain) *reinterpret_cast<uint32_t*>(sf_plain + row * nblk + b) = word;
+        if (sf_swz) *reinterpret_cast<uint32_t*>(sf_swz + sf512_offset(row, b, k >> 6)) = word;
+    }
 }
 
 // General form (any k % 16 == 0, any alignment): one thread per block of 16 inputs, the quotient formed with a true divide. amax = max(|x|, 6 * 2^-9); scale byte = e4m3_rn(amax / 6); v = clip(x / scale, -6, 6);
@@ -381,10 +380,10 @@ extern "C" int kyb_nvfp4_quant_rows(const void* x, int x_dtype, int64_t ldx, int
     cudaStream_t st = (cudaStream_t)stream;
     if (sf_swz && rows % 128) KYB_CUDA(cudaMemsetAsync(sf_swz, 0, kyb_nvfp4_sf_bytes(rows, k), st));   // padding rows of the last 128-row block read as zero scales
     if (k % 64 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)codes & 15) == 0 && (!sf_plain || ((uintptr_t)sf_plain & 3) == 0)) {
-        const int64_t groups = rows * (k / 64);
-        const unsigned gb = (unsigned)((groups + 127) / 128);
-        if (x_dtype == 1) kyb::nvfp4_quant_rows_kernel<__half><<<gb, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
-        else kyb::nvfp4_quant_rows_kernel<__nv_bfloat16><<<gb, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+        const int64_t blocks16 = rows * (k / 16);
+        const unsigned gb = (unsigned)((blocks16 + 255) / 256);
+        if (x_dtype == 1) kyb::nvfp4_quant_rows_kernel<__half><<<gb, 256, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
+        else kyb::nvfp4_quant_rows_kernel<__nv_bfloat16><<<gb, 256, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sf_plain, (uint8_t*)sf_swz);
         return kyb_launch_check("nvfp4_quant_rows");
     }
     const int64_t total = rows * (k / 16);
