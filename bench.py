@@ -259,7 +259,14 @@ def run_ours(args):
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
-        time.sleep(0.25)
+        # the timed region lasts a few milliseconds, less than one sampling period: the same steps keep running (untimed, the same count on every rank: a step
+        # holds a cross-rank barrier) for about another second so that the clock record holds samples taken under this load
+        n_load = 2000
+        for s in range(n_load):
+            run_step(s)
+            if s % 100 == 99:
+                torch.cuda.synchronize()
+        barrier()
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -376,7 +383,8 @@ def run_ours(args):
                 "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / args.steps,
                         "api": "kyojin_mac_b200.host_graph.HostGraph.staged over ForeignLinear modules, one stage per batch size (pinned host activations in, pinned host results out)" if hgraphs is not None
                         else "ForeignLinear modules called eagerly (pinned host activations in, pinned host results out)"},
-                "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
+                "gpu_launches": launches_per_step * args.steps,
+                "clocks": dict(clk.summary(), note=f"sampled every 200 ms from 0.25 s before the timed steps to the end of {n_load} further untimed steps of the same kind")}
         print(json.dumps(line))
     if world > 1:
         # leave without tearing NCCL down: captured collectives keep communicator resources alive and a destroy can block at exit
