@@ -68,7 +68,7 @@ def host_plan(ids, E: int, mt: int):
 def routed_layer(x, inds, Wg, Wu, Wd, K: int, ref_path: bool, limit=None):
     """Unweighted per-slot outputs [T*K, H] of a routed SwiGLU layer from dequantised expert weights W* [E, n, k].
     ref_path False: fp64 throughout, no intermediate rounding (the accuracy reference). True: the reference's rounding points (fp16 a, b, h, y with
-    fp32 accumulation; SURVEY numerics contract steps 2-4)."""
+    fp32 accumulation: gate / up products rounded to fp16, the gated activation rounded to fp16, the down product rounded to fp16; kyojin_mlx/foreign_linear.py:1353-1361, :1448)."""
     x = np.asarray(x)
     T = x.shape[0]
     e = np.asarray(inds).reshape(T, K)
