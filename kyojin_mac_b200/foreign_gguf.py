@@ -3,11 +3,14 @@ kyojin_mlx/foreign_linear.py `_read_gguf` (:2240-2328), for the formats this pac
 as arrays). The container format is the public GGUF layout (little endian, versions 2 and 3): magic, version, tensor count, key count, typed key / value pairs,
 tensor infos (name, dimensions with the fastest first, ggml type id, offset), then the data section aligned to `general.alignment` (default 32).
 Tensor bytes are memory-mapped (zero copy); `load_linear` / `load_experts` hand them to foreign_pack.to_pack and the T16 repack on the device.
-Not built: split shard sets (gguf-split) and the two layouts of type id 43; such files are refused with a clear message."""
+A split shard set (gguf-split: <name>-00001-of-0000N.gguf ...) opened through its FIRST shard reads as one logical file: key / value pairs of shard 1, the tensors
+of every shard, bytes mapped from the shard that holds the tensor; any gap in the set is an error, never a partial load (kyojin_mlx/foreign_gguf.py:247-285).
+Not built: the two layouts of type id 43 (that id is not in the type table here, so such tensors are refused by name)."""
 from __future__ import annotations
 
 import mmap
 import os
+import re
 import struct
 
 import numpy as np
@@ -24,6 +27,9 @@ TYPES = {
     29: ("IQ1_M", 256, 56), 30: ("BF16", 1, 2), 34: ("TQ1_0", 256, 54), 35: ("TQ2_0", 256, 66), 39: ("MXFP4", 32, 17), 40: ("NVFP4", 64, 36),
 }
 KERNEL_TYPES = ("Q4_K", "Q3_K", "Q6_K", "NVFP4")          # stored formats the CUDA kernels read (after the lossless T16 repack)
+
+
+_SHARD_NAME = re.compile(r"^(.*)-(\d{5})-of-(\d{5})\.gguf$")
 
 
 class GgufError(ValueError):
@@ -95,8 +101,9 @@ class _Cursor:
 class GgufFile:
     """One GGUF file: `kv` (dict), `tensors` (name -> TensorInfo), `raw(name)` (uint8 view [rows.., row bytes]), `array(name)` for F32 / F16 / BF16 tensors."""
 
-    def __init__(self, path):
+    def __init__(self, path, _member=False):
         self.path = str(path)
+        self._owner, self._members = {}, []                  # tensor name -> shard that holds it (split sets); the other shards
         self._f = open(self.path, "rb")
         size = os.fstat(self._f.fileno()).st_size
         self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size else None
@@ -129,13 +136,51 @@ class GgufFile:
         if al <= 0 or al & (al - 1):
             raise GgufError(f"general.alignment {al}")
         self.data_start = (c.p + al - 1) // al * al
-        if int(self.kv.get("split.count", 1) or 1) > 1:
-            raise GgufError(f"{path}: split shard sets are not read by this loader (merge the shards first)")
         for ti in self.tensors.values():
             if self.data_start + ti.offset + ti.nbytes > size:
                 raise GgufError(f"tensor {ti.name}: data past the end of the file")
+        if not _member and int(self.kv.get("split.count", 1) or 1) > 1:
+            self._attach_shards()
+
+    def _attach_shards(self):
+        """This file is shard 1 of a split set: open and check the others (count, numbering, no duplicate tensor, tensor total)."""
+        n, no = int(self.kv["split.count"]), int(self.kv.get("split.no", 0))
+        m = _SHARD_NAME.match(os.path.basename(self.path))
+        if no != 0:
+            raise GgufError(f"{self.path}: shard split.no={no} of {n}: open the FIRST shard (-00001-of-{n:05d}.gguf)")
+        if not m or int(m.group(2)) != 1 or int(m.group(3)) != n:
+            raise GgufError(f"{self.path}: split.count={n} but the file name is not <name>-00001-of-{n:05d}.gguf")
+        folder, base = os.path.dirname(os.path.realpath(self.path)), m.group(1)
+        members = [self]
+        try:
+            for i in range(2, n + 1):
+                f = os.path.join(folder, f"{base}-{i:05d}-of-{n:05d}.gguf")
+                if not os.path.isfile(f):
+                    raise GgufError(f"{self.path}: shard {i} of {n} is missing ({os.path.basename(f)})")
+                s = GgufFile(f, _member=True)
+                members.append(s)
+                if int(s.kv.get("split.count", 0) or 0) != n or int(s.kv.get("split.no", -1)) != i - 1:
+                    raise GgufError(f"{f}: split.no={s.kv.get('split.no')} split.count={s.kv.get('split.count')}, expected {i - 1} / {n}")
+            for s in members:
+                for name, ti in s.tensors.items():
+                    if s is not self:
+                        if name in self.tensors:
+                            raise GgufError(f"duplicate tensor {name} across shards ({os.path.basename(s.path)})")
+                        self.tensors[name] = ti
+                    self._owner[name] = s
+            want = self.kv.get("split.tensors.count")
+            if want is not None and int(want) != len(self.tensors):
+                raise GgufError(f"{self.path}: shard set holds {len(self.tensors)} tensors, split.tensors.count says {want}")
+        except BaseException:
+            for s in members[1:]:
+                s.close()
+            raise
+        self._members = members[1:]
 
     def close(self):
+        for s in self._members:
+            s.close()
+        self._members = []
         mm, self._mm = self._mm, None
         try:
             if mm is not None:
@@ -156,7 +201,8 @@ class GgufFile:
         if not ti.known:
             raise GgufTypeError(f"tensor {name}: ggml type id {ti.type} is not in the type table of this reader")
         _, be, bb = TYPES[ti.type]
-        a = np.frombuffer(self._mm, dtype=np.uint8, count=ti.nbytes, offset=self.data_start + ti.offset)
+        src = self._owner.get(name, self)
+        a = np.frombuffer(src._mm, dtype=np.uint8, count=ti.nbytes, offset=src.data_start + ti.offset)
         return a.reshape(ti.shape[:-1] + (ti.ne[0] // be * bb,)) if ti.ne else a
 
     def array(self, name) -> np.ndarray:

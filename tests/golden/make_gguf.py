@@ -51,6 +51,15 @@ def main():
     out["data_start"] = np.array(g.data_start)
     np.savez_compressed(os.path.join(HERE, "tiny_gguf.npz"), **out)
     print("wrote", path, os.path.getsize(path), "bytes;", len(g.tensors), "tensors; kv", list(g.kv))
+    # a two-shard split set (gguf-split conventions: split.no / split.count / split.tensors.count, -0000i-of-0000N names)
+    base = os.path.join(HERE, "tinysplit")
+    FS.write_gguf(f"{base}-00001-of-00002.gguf", dict(kv, **{"split.no": 0, "split.count": 2, "split.tensors.count": len(tensors)}), tensors[:3])
+    FS.write_gguf(f"{base}-00002-of-00002.gguf", {"split.no": 1, "split.count": 2, "split.tensors.count": len(tensors)}, tensors[3:])
+    gs = GF.GgufFile(f"{base}-00001-of-00002.gguf")
+    assert list(gs.tensors) == [t[0] for t in tensors]
+    for i, name in enumerate(gs.tensors):
+        assert np.array_equal(np.array(gs.raw(name)).reshape(-1), out[f"raw_{i}"]), name      # the reference reader sees the same bytes through the set
+    print("wrote the split set", base, "-0000[12]-of-00002.gguf")
 
 
 if __name__ == "__main__":

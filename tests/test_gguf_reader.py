@@ -63,6 +63,26 @@ def test_packs_hold_the_stored_rows(gold):
         assert w.shape == (16, 256) and np.isfinite(w).all()
 
 
+def test_split_shard_set_reads_as_one_file(gold, tmp_path):
+    import shutil
+    first = os.path.join(HERE, "golden", "tinysplit-00001-of-00002.gguf")
+    with GG.GgufFile(first) as g:
+        assert list(g.tensors) == [str(n) for n in gold["names"]]
+        for i, name in enumerate(g.tensors):
+            np.testing.assert_array_equal(np.asarray(g.raw(name)).reshape(-1), gold[f"raw_{i}"])       # bytes come from the shard that holds the tensor
+        assert g.kv["general.architecture"] == "tiny" and g.kv["split.count"] == 2
+    with pytest.raises(GG.GgufError):                                      # the second shard is not an entry point
+        GG.GgufFile(os.path.join(HERE, "golden", "tinysplit-00002-of-00002.gguf"))._attach_shards()
+    lone = tmp_path / "tinysplit-00001-of-00002.gguf"
+    shutil.copy(first, lone)
+    with pytest.raises(GG.GgufError):                                      # a missing shard is an error, never a partial load
+        GG.GgufFile(lone)
+    renamed = tmp_path / "other.gguf"
+    shutil.copy(first, renamed)
+    with pytest.raises(GG.GgufError):
+        GG.GgufFile(renamed)
+
+
 def test_refusals(tmp_path):
     bad = tmp_path / "bad.gguf"
     bad.write_bytes(b"NOPE" + b"\0" * 40)
