@@ -42,11 +42,31 @@ __device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t w) { return __
 template <>
 __device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
 
+// Packed 16-bit arithmetic of the quantiser: two inputs per instruction in their own type. Every threshold t s has at most 7 significant bits, so it is exact in
+// fp16 and in bf16, and the comparisons |x| > t s / |x| >= t s give the same truth values as in fp32.
+template <typename T>
+struct Pk;
+template <>
+struct Pk<__half> {
+    using V = __half2;
+    static __device__ __forceinline__ V splat(float f) { return __float2half2_rn(f); }
+    static __device__ __forceinline__ float hi_lo_max(V m) { return fmaxf(__low2float(m), __high2float(m)); }
+    static constexpr uint32_t MAGIC = 0x64006400u;                        // 1024 + code is exact: the code sits in the low mantissa bits
+};
+template <>
+struct Pk<__nv_bfloat16> {
+    using V = __nv_bfloat162;
+    static __device__ __forceinline__ V splat(float f) { return __float2bfloat162_rn(f); }
+    static __device__ __forceinline__ float hi_lo_max(V m) { return fmaxf(__low2float(m), __high2float(m)); }
+    static constexpr uint32_t MAGIC = 0x43004300u;                        // 128 + code (code < 16) is exact in bf16
+};
+
 template <typename T>
 __global__ void __launch_bounds__(256) nvfp4_quant_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes,
                                                                uint8_t* __restrict__ sf_plain, uint8_t* __restrict__ sf_swz) {
     // one thread per block of 16 inputs (two 16-byte loads; a warp reads 1 KB of a row contiguously); the four lanes of a 64-input group combine their scale bytes
     // with shuffles and one of them writes the 4-byte group of both scale layouts
+    using V = typename Pk<T>::V;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t nblk = k >> 4, total = rows * nblk;
     const bool live = i < total;
@@ -54,28 +74,34 @@ __global__ void __launch_bounds__(256) nvfp4_quant_rows_kernel(const T* __restri
     const int64_t row = ii / nblk, b = ii % nblk;
     const uint4* xp = reinterpret_cast<const uint4*>(x + row * ldx + b * 16);
     const uint4 r0 = __ldg(xp), r1 = __ldg(xp + 1);
-    float v[16];
-    {
-        const float2 p0 = pair_to_float2<T>(r0.x), p1 = pair_to_float2<T>(r0.y), p2 = pair_to_float2<T>(r0.z), p3 = pair_to_float2<T>(r0.w);
-        const float2 p4 = pair_to_float2<T>(r1.x), p5 = pair_to_float2<T>(r1.y), p6 = pair_to_float2<T>(r1.z), p7 = pair_to_float2<T>(r1.w);
-        v[0] = p0.x, v[1] = p0.y, v[2] = p1.x, v[3] = p1.y, v[4] = p2.x, v[5] = p2.y, v[6] = p3.x, v[7] = p3.y;
-        v[8] = p4.x, v[9] = p4.y, v[10] = p5.x, v[11] = p5.y, v[12] = p6.x, v[13] = p6.y, v[14] = p7.x, v[15] = p7.y;
-    }
-    float amax = 6.0f * 0.001953125f;
+    const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    V a[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t m = w[j] & 0x7FFF7FFFu;
+        a[j] = *reinterpret_cast<const V*>(&m);
+    }
+    V mx = a[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = __hmax2(mx, a[j]);
+    const float amax = fmaxf(6.0f * 0.001953125f, Pk<T>::hi_lo_max(mx));
     const uint32_t s8 = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(amax, 6.0f), __NV_SATFINITE, __NV_E4M3) & 255u;
     const float scale = e4m3_to_float(s8);
-    const float t0 = 0.25f * scale, t1 = 0.75f * scale, t2 = 1.25f * scale, t3 = 1.75f * scale, t4 = 2.5f * scale, t5 = 3.5f * scale, t6 = 5.0f * scale;   // exact products
+    const V t0 = Pk<T>::splat(0.25f * scale), t1 = Pk<T>::splat(0.75f * scale), t2 = Pk<T>::splat(1.25f * scale), t3 = Pk<T>::splat(1.75f * scale),
+            t4 = Pk<T>::splat(2.5f * scale), t5 = Pk<T>::splat(3.5f * scale), t6 = Pk<T>::splat(5.0f * scale);
+    const V zero = Pk<T>::splat(0.0f), eight = Pk<T>::splat(8.0f);
+    const uint32_t magic_bits = Pk<T>::MAGIC;
+    const V magic = *reinterpret_cast<const V*>(&magic_bits);
     uint32_t pk[2] = {0u, 0u};
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const float mag = fabsf(v[j]);
-        // thresholds are ordered: a three-level search instead of seven comparisons
-        uint32_t code;
-        if (mag >= t3) code = mag >= t5 ? (mag > t6 ? 7u : 6u) : (mag > t4 ? 5u : 4u);
-        else code = mag >= t1 ? (mag > t2 ? 3u : 2u) : (mag > t0 ? 1u : 0u);
-        pk[j >> 3] |= (code | (v[j] < 0.0f ? 8u : 0u)) << (4 * (j & 7));
+    for (int j = 0; j < 8; ++j) {
+        // number of thresholds passed = the e2m1 magnitude code (each comparison yields 1.0 or 0.0 per half)
+        V c = __hadd2(__hadd2(__hadd2(__hgt2(a[j], t0), __hge2(a[j], t1)), __hadd2(__hgt2(a[j], t2), __hge2(a[j], t3))),
+                      __hadd2(__hadd2(__hgt2(a[j], t4), __hge2(a[j], t5)), __hgt2(a[j], t6)));
+        c = __hfma2(__hlt2(*reinterpret_cast<const V*>(&w[j]), zero), eight, c);          // sign bit 3 for x < 0 (not for -0)
+        c = __hadd2(c, magic);
+        const uint32_t u = *reinterpret_cast<const uint32_t*>(&c) & 0x000F000Fu;
+        pk[j >> 2] |= ((u | (u >> 12)) & 0xFFu) << (8 * (j & 3));
     }
     if (live) *reinterpret_cast<uint2*>(codes + row * (k >> 1) + b * 8) = make_uint2(pk[0], pk[1]);
     // scale bytes of the 64-input group (k % 64 == 0, so a group never straddles two rows and its four lanes sit in one warp)
