@@ -4,7 +4,7 @@
     python -m kyojin_mac_b200.measure cfg2            # Q3_K prefill GEMM, M = 2048, 3072 -> 12288 and 12288 -> 3072
     python -m kyojin_mac_b200.measure cfg3            # NVFP4 prefill GEMM, 4096 x 7168 -> 18432, activations quantised on the fly
     python -m kyojin_mac_b200.measure fp4peak         # the vendor library's block-scaled NVFP4 GEMM (torch._scaled_mm), a measured fp4 denominator
-    python -m kyojin_mac_b200.measure cfg4 [E]        # routed-expert layer, E (default 256) experts, top-8, hidden 7168, T = 64 and 4096
+    python -m kyojin_mac_b200.measure cfg4 [E [T ...]]  # routed-expert layer, E (default 256) experts, top-8, hidden 7168, T = 64 and 4096 (or the given token counts)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 -m kyojin_mac_b200.measure dist
                                                       # cfg 2 / 3 N-sharded with all-gather, cfg 4 expert-parallel with all-to-all, on N GPUs
 
@@ -117,7 +117,7 @@ def fp4_library_peak():
         print(json.dumps({"case": "library nvfp4 gemm (torch._scaled_mm)", "unavailable": str(e)[:300]}), flush=True)
 
 
-def cfg4(E=256):
+def cfg4(E=256, Ts=(64, 4096)):
     H, I, K = 7168, 2048, 8
     g = DevPack.from_t16("q4_k", synth.t16_random_device("q4_k", E * I, H, seed=40), I, H, E)
     u = DevPack.from_t16("q4_k", synth.t16_random_device("q4_k", E * I, H, seed=41), I, H, E)
@@ -126,7 +126,7 @@ def cfg4(E=256):
     gen = torch.Generator(device="cuda").manual_seed(4)
     gw = torch.randn((E, H), device="cuda", generator=gen) * 0.02
     blk = FM.RoutedBlock(gw, glu, K, True)
-    for T in (64, 4096):
+    for T in Ts:
         x = torch.randn((T, H), device="cuda", generator=gen).to(torch.float16)
         lg = torch.randn((T, E + 1), device="cuda", generator=gen)           # the benchmark's router logits are N(0, 1) draws
         inds, scs, _ = ops.moe_select(lg, E, K, True)
@@ -240,7 +240,7 @@ def main(argv):
     elif what == "fp4peak":
         fp4_library_peak()
     elif what == "cfg4":
-        cfg4(int(argv[1]) if len(argv) > 1 else 256)
+        cfg4(int(argv[1]) if len(argv) > 1 else 256, tuple(int(t) for t in argv[2:]) or (64, 4096))
     elif what == "dist":
         dist_cases(int(argv[1]) if len(argv) > 1 else 256)
     else:
