@@ -35,13 +35,6 @@ __device__ __forceinline__ size_t sf512_offset(int64_t row, int64_t s, int64_t k
 // by at least 2^-11 relative, far more than half an fp32 ulp, so the correctly rounded quotient cannot land on t), likewise for >=; the clip at 6 only touches
 // values that already passed the last threshold. The sign of the code is the sign of x with +-0 and underflowed quotients mapped as the division would: x / s is
 // negative exactly when x < 0 (s > 0, and a non-zero 16-bit x over s <= 448 does not underflow to zero in fp32).
-template <typename T>
-__device__ __forceinline__ float2 pair_to_float2(uint32_t w);
-template <>
-__device__ __forceinline__ float2 pair_to_float2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
-template <>
-__device__ __forceinline__ float2 pair_to_float2<__nv_bfloat16>(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u)); }
-
 // Packed 16-bit arithmetic of the quantiser: two inputs per instruction in their own type. Every threshold t s has at most 7 significant bits, so it is exact in
 // fp16 and in bf16, and the comparisons |x| > t s / |x| >= t s give the same truth values as in fp32.
 template <typename T>
