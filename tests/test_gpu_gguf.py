@@ -21,13 +21,13 @@ def test_linear_and_experts_from_file():
             k, n = ti.ne
             lin = g.load_linear(name)
             x = torch.from_numpy(synth.activations(3, k, rng)).cuda()
-            raw = np.ascontiguousarray(g.raw(name))
+            raw = np.array(g.raw(name))
             assert torch.equal(lin(x), ForeignLinear(FP.to_pack(tname, raw, k))(x))
             w = lin.dev.dequant(torch.float32).cpu().numpy()
             np.testing.assert_array_equal(w.view(np.uint32), O.dequant(tname, raw, k).view(np.uint32))     # bit-exact decode of the file's bytes
         st = g.load_experts("blk.0.ffn_gate_exps.weight")
         assert (st.E, st.n, st.k) == (3, 16, 256)
-        raw = np.ascontiguousarray(g.raw("blk.0.ffn_gate_exps.weight"))
+        raw = np.array(g.raw("blk.0.ffn_gate_exps.weight"))
         x = torch.from_numpy(synth.activations(2, 256, rng)).cuda()
         for e in range(3):
             one = DevPack(FP.to_pack("Q4_K", raw[e], 256))
