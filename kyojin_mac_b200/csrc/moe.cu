@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "kyb_common.cuh"
 
@@ -172,20 +173,27 @@ __global__ void moe_combine_kernel(const __half* __restrict__ y, int64_t ldy, co
 // A CTA keeps TT token rows in shared memory in their own type and every warp walks weight rows, so a weight row read from L2 serves TT tokens.
 template <typename XT> struct XVec4;
 template <> struct XVec4<float> {
+    using Raw = float4;
+    static __device__ __forceinline__ Raw ldraw(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+    static __device__ __forceinline__ float4 cvt(Raw v) { return v; }
     static __device__ __forceinline__ float4 ld(const float* p) { return *reinterpret_cast<const float4*>(p); }
 };
 template <> struct XVec4<__half> {
-    static __device__ __forceinline__ float4 ld(const __half* p) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
+    using Raw = uint2;
+    static __device__ __forceinline__ Raw ldraw(const __half* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
+    static __device__ __forceinline__ float4 cvt(Raw v) {
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
         return make_float4(a.x, a.y, b.x, b.y);
     }
+    static __device__ __forceinline__ float4 ld(const __half* p) { return cvt(*reinterpret_cast<const uint2*>(p)); }
 };
 template <> struct XVec4<__nv_bfloat16> {
-    static __device__ __forceinline__ float4 ld(const __nv_bfloat16* p) {
-        const uint2 v = *reinterpret_cast<const uint2*>(p);
+    using Raw = uint2;
+    static __device__ __forceinline__ Raw ldraw(const __nv_bfloat16* p) { return __ldg(reinterpret_cast<const uint2*>(p)); }
+    static __device__ __forceinline__ float4 cvt(Raw v) {
         return make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
     }
+    static __device__ __forceinline__ float4 ld(const __nv_bfloat16* p) { return cvt(*reinterpret_cast<const uint2*>(p)); }
 };
 
 // the combine on 8 consecutive columns per thread: the same sum in the same order (k ascending, then the shared expert), 16-byte loads
@@ -297,6 +305,66 @@ __global__ void __launch_bounds__(512) router_logits_kernel(const XT* __restrict
     }
 }
 
+// The same product with the roles exchanged, for many tokens: a CTA keeps WR weight rows (fp32) in shared memory and its warps stream token rows, RE per pass,
+// so a token row read from L2 serves WR weight rows and the L2 reads fall from (T / 8) x |weights| to (R / WR) x |tokens|. Every logit is summed in the same
+// order as in router_logits_kernel (pairs over even and odd inputs per lane, lanes combined by the same shuffles), so the two kernels agree bit for bit.
+template <typename XT, int WR, int RE, int THREADS>
+__global__ void __launch_bounds__(THREADS) router_logits_wres_kernel(const XT* __restrict__ x, int64_t ldx, const float* __restrict__ gw, const float* __restrict__ sgw, int T, int E,
+                                                                     int H, float* __restrict__ lg, int64_t ldl) {
+    extern __shared__ __align__(16) unsigned char router_smem[];
+    float* ws = reinterpret_cast<float*>(router_smem);
+    const int R = E + (sgw ? 1 : 0), r0 = blockIdx.x * WR, H4 = H / 4;
+    for (int idx = threadIdx.x; idx < WR * H4; idx += THREADS) {
+        const int e = idx / H4, c = idx - e * H4;
+        const int r = min(r0 + e, R - 1);                                   // a short last group repeats its last row; the repeats are not stored
+        const float* src = r < E ? gw + (size_t)r * H : sgw;
+        *reinterpret_cast<float4*>(ws + (size_t)e * H + 4 * c) = __ldg(reinterpret_cast<const float4*>(src) + c);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int NW = THREADS / 32;
+    for (int tg = (blockIdx.y * NW + warp) * RE; tg < T; tg += gridDim.y * NW * RE) {
+        const XT* xp[RE];
+#pragma unroll
+        for (int j = 0; j < RE; ++j) xp[j] = x + (size_t)min(tg + j, T - 1) * ldx;   // rows past T repeat the last token; their results are not stored
+        unsigned long long acc[WR][RE];
+#pragma unroll
+        for (int e = 0; e < WR; ++e)
+#pragma unroll
+            for (int j = 0; j < RE; ++j) acc[e][j] = 0ull;
+        typename XVec4<XT>::Raw nxt[RE];                                    // the token chunks of the next step are in flight while this step is summed
+#pragma unroll
+        for (int j = 0; j < RE; ++j) nxt[j] = XVec4<XT>::ldraw(xp[j] + 4 * min(lane, H4 - 1));
+        for (int i = lane; i < H4; i += 32) {
+            unsigned long long vlo[RE], vhi[RE];
+#pragma unroll
+            for (int j = 0; j < RE; ++j) {
+                const float4 v = XVec4<XT>::cvt(nxt[j]);
+                vlo[j] = pack2(v.x, v.y), vhi[j] = pack2(v.z, v.w);
+            }
+            const int in = min(i + 32, H4 - 1);                             // past the end: a repeated load whose value is not used
+#pragma unroll
+            for (int j = 0; j < RE; ++j) nxt[j] = XVec4<XT>::ldraw(xp[j] + 4 * in);
+#pragma unroll
+            for (int e = 0; e < WR; ++e) {
+                const float4 w = *reinterpret_cast<const float4*>(ws + (size_t)e * H + 4 * i);
+                const unsigned long long wlo = pack2(w.x, w.y), whi = pack2(w.z, w.w);
+#pragma unroll
+                for (int j = 0; j < RE; ++j) acc[e][j] = ffma2(whi, vhi[j], ffma2(wlo, vlo[j], acc[e][j]));
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < RE; ++j)
+#pragma unroll
+            for (int e = 0; e < WR; ++e) {
+                float v = sum2(acc[e][j]);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0 && tg + j < T && r0 + e < R) lg[(size_t)(tg + j) * ldl + r0 + e] = v;
+            }
+    }
+}
+
 }  // namespace kyb
 
 extern "C" int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream) {
@@ -388,6 +456,31 @@ static int launch_router(const void* x, int64_t ldx, const float* gw, const floa
     return kyb_launch_check("router_logits");
 }
 
+static int router_sms() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+        (void)cudaGetLastError();
+    }
+    return sms;
+}
+
+template <typename XT, int WR, int RE, int THREADS>
+static int launch_router_wres(const void* x, int64_t ldx, const float* gw, const float* sgw, int64_t T, int E, int64_t H, float* lg, int64_t ldl, cudaStream_t st) {
+    const size_t smem = (size_t)WR * (size_t)H * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        KYB_CUDA(cudaFuncSetAttribute(kyb::router_logits_wres_kernel<XT, WR, RE, THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024));
+        configured = true;
+    }
+    const int R = E + (sgw ? 1 : 0), gx = (R + WR - 1) / WR;
+    const int64_t per_pass = (int64_t)(THREADS / 32) * RE;
+    const int gy = (int)std::max<int64_t>(1, std::min<int64_t>((T + per_pass - 1) / per_pass, router_sms() / gx));   // one wave of CTAs, one CTA per SM
+    kyb::router_logits_wres_kernel<XT, WR, RE, THREADS><<<dim3((unsigned)gx, (unsigned)gy), THREADS, smem, st>>>((const XT*)x, ldx, gw, sgw, (int)T, E, (int)H, lg, ldl);
+    return kyb_launch_check("router_logits");
+}
+
 extern "C" int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const void* gw, const void* sgw, int64_t T, int E, int64_t H, void* lg, int64_t ldl, void* stream) {
     KYB_REQUIRE(x && gw && lg, "null pointer");
     KYB_REQUIRE(x_dtype == KYB_DT_F32 || x_dtype == KYB_DT_F16 || x_dtype == KYB_DT_BF16, "x dtype %d", x_dtype);
@@ -397,6 +490,12 @@ extern "C" int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const 
     const size_t per_row = (size_t)H * (x_dtype == KYB_DT_F32 ? 4 : 2);
     KYB_REQUIRE(per_row * 2 <= 226 * 1024, "H=%lld: two token rows do not fit shared memory", (long long)H);
     cudaStream_t st = (cudaStream_t)stream;
+    static const bool wres = [] { const char* e = getenv("KYB_ROUTER_WRES"); return !e || atoi(e) != 0; }();   // KYB_ROUTER_WRES=0: token-resident kernel at every T
+    if (wres && T >= 1024 && (size_t)H * 4 * 7 <= 226 * 1024) {            // many tokens: 7 weight rows resident per CTA, token rows streamed 8 (fp32: 4) per warp pass
+        if (x_dtype == KYB_DT_F32) return launch_router_wres<float, 7, 4, 256>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st);
+        if (x_dtype == KYB_DT_F16) return launch_router_wres<__half, 7, 8, 256>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st);
+        return launch_router_wres<__nv_bfloat16, 7, 8, 256>(x, ldx, (const float*)gw, (const float*)sgw, T, E, H, (float*)lg, ldl, st);
+    }
     const int fit = (int)((226 * 1024) / per_row);
     const int tt = (fit >= 8 && T >= 8) ? 8 : (fit >= 4 && T >= 4) ? 4 : 2;
 #define KYB_ROUTER(XT)                                                                                                         \

@@ -229,6 +229,16 @@ def dist_cases(E=256):
     os._exit(0)                                                               # NCCL teardown at interpreter exit hung on the boxes this was developed on
 
 
+def router(T=4096, E=256, H=7168, iters=10):
+    """The fp32 router product alone: x [T, H] fp16 on the gate [E, H] fp32 plus the shared-expert gate row."""
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((T, H), device="cuda", generator=gen).to(torch.float16)
+    gw = torch.randn((E, H), device="cuda", generator=gen) * 0.02
+    sgw = torch.randn((H,), device="cuda", generator=gen) * 0.02
+    t = timeit(lambda: ops.router_logits(x, gw, sgw), iters=iters)[1]
+    print(json.dumps({"case": f"router T={T} E={E} H={H}", "us": t, "fp32_TFLOPs": 2.0 * T * (E + 1) * H / t / 1e6}), flush=True)
+
+
 def main(argv):
     what = argv[0] if argv else "cfg0"
     if what == "cfg0":
@@ -241,6 +251,8 @@ def main(argv):
         fp4_library_peak()
     elif what == "cfg4":
         cfg4(int(argv[1]) if len(argv) > 1 else 256, tuple(int(t) for t in argv[2:]) or (64, 4096))
+    elif what == "router":
+        router(*(int(a) for a in argv[1:]))
     elif what == "dist":
         dist_cases(int(argv[1]) if len(argv) > 1 else 256)
     else:

@@ -50,7 +50,8 @@ def test_rows_and_grouped():
     assert sub.n == 5 and g.rows(32).n == 32 and len(g.arrays()) == 2
 
 
-@pytest.mark.parametrize("T,E,H,dt", [(5, 64, 512, torch.float16), (300, 256, 7168, torch.float16), (2000, 32, 1024, torch.float32), (33, 16, 256, torch.bfloat16)])
+@pytest.mark.parametrize("T,E,H,dt", [(5, 64, 512, torch.float16), (300, 256, 7168, torch.float16), (2000, 32, 1024, torch.float32), (33, 16, 256, torch.bfloat16),
+                                       (1500, 256, 7168, torch.float16), (1101, 20, 512, torch.bfloat16)])
 def test_router_logits_vs_fp64(T, E, H, dt):
     g = torch.Generator(device="cuda").manual_seed(T)
     x = torch.randn((T, H), device="cuda", generator=g).to(dt)
@@ -61,6 +62,9 @@ def test_router_logits_vs_fp64(T, E, H, dt):
     assert lg.shape == (T, E + 1) and (lg.double() - want).abs().max().item() < 1e-4 * want.abs().max().item()
     lg0 = ops.router_logits(x, gw, None)
     assert torch.equal(lg0[:, :E], lg[:, :E]) and (lg0[:, E] == 0).all()
+    if T >= 1024:                                                           # many tokens take the weight-resident kernel: same bits as the token-resident one
+        parts = torch.cat([ops.router_logits(x[i:i + 500], gw, sgw) for i in range(0, T, 500)])
+        assert torch.equal(parts, lg)
 
 
 def _stack(fmt, E, n, k, seed):
