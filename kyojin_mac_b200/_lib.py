@@ -12,7 +12,7 @@ import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SO_PATH = os.environ.get("KYB_LIB_PATH") or os.path.join(HERE, "libkyb.so")     # KYB_LIB_PATH: load another build of the library (experiments)
+SO_PATH = os.path.join(HERE, "libkyb.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC"]
 
 OK, EINVAL, ECUDA, ETIMEOUT, EUNSUPPORTED, EWORKSPACE = 0, -1, -2, -3, -4, -5
@@ -39,25 +39,51 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def _headers() -> list[str]:
+    return glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(os.path.dirname(HERE), "include", "kyb.h")]
+
+
 def _stale() -> bool:
     if not os.path.exists(SO_PATH):
         return True
     t = os.path.getmtime(SO_PATH)
-    deps = sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(os.path.dirname(HERE), "include", "kyb.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+    return any(os.path.getmtime(d) > t for d in sources() + _headers())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles every .cu under csrc/ into libkyb.so for sm_100a (cross-compiles without a GPU)."""
+    """Compiles every .cu under csrc/ for sm_100a (cross-compiles without a GPU) and links libkyb.so.
+
+    One object per source under kyojin_mac_b200/build/, compiled in parallel; an object is rebuilt when its source or any
+    header is newer."""
     if not force and not _stale():
         return SO_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", SO_PATH + ".tmp"] + sources() + ["-lcuda"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = os.path.join(HERE, "build")
+    os.makedirs(objdir, exist_ok=True)
+    hdr_t = max(os.path.getmtime(h) for h in _headers())
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    jobs = []
+    for src in sources():
+        obj = os.path.join(objdir, os.path.basename(src)[:-3] + ".o")
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
+            jobs.append((src, obj))
+
+    def compile_one(job):
+        src, obj = job
+        cmd = [_nvcc()] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, src]
+        return src, subprocess.run(cmd, capture_output=True, text=True)
+
+    with ThreadPoolExecutor(max_workers=max(1, min(len(jobs), os.cpu_count() or 4))) as pool:
+        for src, r in pool.map(compile_one, jobs):
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src}:\n" + r.stdout + r.stderr)
+            if verbose:
+                print(r.stderr)
+    objs = [os.path.join(objdir, os.path.basename(s)[:-3] + ".o") for s in sources()]
+    r = subprocess.run([_nvcc(), "-shared", "-o", SO_PATH + ".tmp"] + objs + ["-lcuda"], capture_output=True, text=True)
     if r.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+        raise RuntimeError("link failed:\n" + r.stdout + r.stderr)
     os.replace(SO_PATH + ".tmp", SO_PATH)
-    if verbose:
-        print(r.stderr)
     return SO_PATH
 
 

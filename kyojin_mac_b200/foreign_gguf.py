@@ -8,15 +8,14 @@ of every shard, bytes mapped from the shard that holds the tensor; any gap in th
 Not built: the two layouts of type id 43 (that id is not in the type table here, so such tensors are refused by name)."""
 from __future__ import annotations
 
+import glob
 import mmap
 import os
-import re
 import struct
+from dataclasses import dataclass
 
 import numpy as np
 
-MAGIC = b"GGUF"
-ALIGN_DEFAULT = 32
 
 # ggml type id -> (name, block elements, block bytes): the public ggml type table (sizes are needed to size every tensor of a file, also the ones without a kernel here)
 TYPES = {
@@ -29,9 +28,6 @@ TYPES = {
 KERNEL_TYPES = ("Q4_K", "Q3_K", "Q6_K", "NVFP4")          # stored formats the CUDA kernels read (after the lossless T16 repack)
 
 
-_SHARD_NAME = re.compile(r"^(.*)-(\d{5})-of-(\d{5})\.gguf$")
-
-
 class GgufError(ValueError):
     pass
 
@@ -40,170 +36,233 @@ class GgufTypeError(GgufError):
     pass
 
 
-class TensorInfo:
-    """name, ne (fastest dimension first, as stored), ggml type id / name, offset in the data section, byte count; shape = ne reversed (rows first)."""
-    __slots__ = ("name", "ne", "type", "offset", "nbytes", "tname", "known")
+# ---- container layout (public GGUF specification): "GGUF", u32 version, u64 tensor count, u64 pair count, the pairs, the tensor records, padding, data
+_U32, _U64 = struct.Struct("<I"), struct.Struct("<Q")
+# value kind -> numpy dtype of a scalar of that kind (kinds 8 = string and 9 = array are handled apart)
+_KIND_DTYPE = {0: "u1", 1: "i1", 2: "<u2", 3: "<i2", 4: "<u4", 5: "<i4", 6: "<f4", 7: "u1", 10: "<u8", 11: "<i8", 12: "<f8"}
+_MAX_RECORDS = 1 << 20            # tensors or pairs per file
+_MAX_RANK = 4                     # ggml tensors have at most four dimensions
 
-    def __init__(self, name, ne, type_, offset):
-        self.name, self.ne, self.type, self.offset = name, tuple(int(d) for d in ne), int(type_), int(offset)
-        self.known = self.type in TYPES
-        if not self.known:                                  # the file stays readable; reading THIS tensor fails
-            self.tname, self.nbytes = f"ID{self.type}", 0
-            return
-        self.tname, be, bb = TYPES[self.type]
-        n = int(np.prod(self.ne, dtype=np.int64)) if self.ne else 1
-        if n % be or (self.ne and self.ne[0] % be):
-            raise GgufError(f"tensor {name}: row length {self.ne[0] if self.ne else n} is not a multiple of the {self.tname} block of {be}")
-        self.nbytes = n // be * bb
+
+@dataclass
+class TensorInfo:
+    """One tensor record: `ne` as stored (fastest dimension first), ggml type id, offset inside the data section. `shape` is `ne` reversed (rows first);
+    `nbytes` is 0 and `known` False for a type id outside the table (the file stays readable, reading that tensor is refused)."""
+    name: str
+    ne: tuple
+    type: int
+    offset: int
+
+    def __post_init__(self):
+        entry = TYPES.get(self.type)
+        self.known = entry is not None
+        self.tname = entry[0] if entry else f"ID{self.type}"
+        self.nbytes = 0
+        if entry:
+            _, per_block, block_bytes = entry
+            count = 1
+            for d in self.ne:
+                count *= d
+            inner = self.ne[0] if self.ne else 1
+            if inner % per_block:
+                raise GgufError(f"{self.name}: {self.tname} stores blocks of {per_block} values, the innermost dimension is {inner}")
+            self.nbytes = count // per_block * block_bytes
 
     @property
     def shape(self):
-        return tuple(reversed(self.ne))
+        return self.ne[::-1]
+
+    @property
+    def row_bytes(self):
+        _, per_block, block_bytes = TYPES[self.type]
+        return (self.ne[0] if self.ne else 1) // per_block * block_bytes
 
 
-class _Cursor:
-    def __init__(self, buf, pos):
-        self.b, self.p = buf, pos
+class _Scan:
+    """Forward-only decoder over the header bytes."""
 
-    def take(self, fmt):
-        size = struct.calcsize(fmt)
-        if self.p + size > len(self.b):
-            raise GgufError("truncated header")
-        v = struct.unpack_from(fmt, self.b, self.p)[0]
-        self.p += size
-        return v
+    def __init__(self, view, label):
+        self.view, self.at, self.label = view, 0, label
 
-    def string(self):
-        n = self.take("<Q")
-        if n > 1 << 30 or self.p + n > len(self.b):
-            raise GgufError("implausible string length in the header")
-        s = bytes(self.b[self.p:self.p + n]).decode("utf-8", errors="replace")
-        self.p += n
-        return s
+    def _span(self, n):
+        lo, hi = self.at, self.at + n
+        if n < 0 or hi > len(self.view):
+            raise GgufError(f"{self.label}: the header ends inside a field at byte {lo}")
+        self.at = hi
+        return lo
 
-    _SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 10: "<Q", 11: "<q", 12: "<d"}
+    def u32(self):
+        return _U32.unpack_from(self.view, self._span(4))[0]
 
-    def value(self, t):
-        if t in self._SCALAR:
-            return self.take(self._SCALAR[t])
-        if t == 7:
-            return bool(self.take("<B"))
-        if t == 8:
-            return self.string()
-        if t == 9:
-            et, n = self.take("<I"), self.take("<Q")
-            if n > 1 << 28:
-                raise GgufError("implausible array length in the header")
-            return [self.value(et) for _ in range(n)]
-        raise GgufError(f"unknown key / value type {t}")
+    def u64(self):
+        return _U64.unpack_from(self.view, self._span(8))[0]
+
+    def text(self):
+        n = self.u64()
+        lo = self._span(n)
+        return str(self.view[lo:lo + n], "utf-8", "replace")
+
+    def scalars(self, kind, count):
+        """`count` values of a fixed-size kind, decoded in one piece."""
+        dt = np.dtype(_KIND_DTYPE[kind])
+        lo = self._span(dt.itemsize * count)
+        vals = np.frombuffer(self.view, dtype=dt, count=count, offset=lo)
+        return vals.astype(bool) if kind == 7 else vals
+
+    def value(self, kind, depth=0):
+        if kind in _KIND_DTYPE:
+            return self.scalars(kind, 1)[0].item()
+        if kind == 8:
+            return self.text()
+        if kind == 9 and depth < 4:
+            inner, count = self.u32(), self.u64()
+            if count > len(self.view):                       # every item takes at least one byte
+                raise GgufError(f"{self.label}: an array claims {count} items, more than the file has bytes")
+            if inner in _KIND_DTYPE:
+                return self.scalars(inner, count).tolist()
+            return [self.value(inner, depth + 1) for _ in range(count)]
+        raise GgufError(f"{self.label}: value kind {kind} is not part of the GGUF specification")
+
+
+def _parse_header(view, label):
+    """-> (version, pairs, tensor records in file order, offset of the data section)."""
+    if len(view) < 24 or bytes(view[:4]) != b"GGUF":
+        raise GgufError(f"{label}: the GGUF signature is missing")
+    sc = _Scan(view, label)
+    sc.at = 4
+    version = sc.u32()
+    if version not in (2, 3):
+        raise GgufError(f"{label}: container version {version}; versions 2 and 3 (little endian) are understood")
+    n_tensors, n_pairs = sc.u64(), sc.u64()
+    if max(n_tensors, n_pairs) > _MAX_RECORDS:
+        raise GgufError(f"{label}: {n_tensors} tensors / {n_pairs} pairs is beyond what a header can hold")
+    pairs = {}
+    for _ in range(n_pairs):
+        key = sc.text()
+        pairs[key] = sc.value(sc.u32())
+    records = {}
+    for _ in range(n_tensors):
+        name, rank = sc.text(), sc.u32()
+        if rank > _MAX_RANK:
+            raise GgufError(f"{label}: {name} has rank {rank}")
+        ne = tuple(sc.u64() for _ in range(rank))
+        type_id, offset = sc.u32(), sc.u64()
+        if name in records:
+            raise GgufError(f"{label}: {name} is listed twice")
+        records[name] = TensorInfo(name, ne, type_id, offset)
+    align = pairs.get("general.alignment", 32)
+    if not isinstance(align, int) or align < 1 or align & (align - 1):
+        raise GgufError(f"{label}: general.alignment = {align!r} is not a power of two")
+    data_start = -(-sc.at // align) * align
+    for rec in records.values():
+        if data_start + rec.offset + rec.nbytes > len(view):
+            raise GgufError(f"{label}: {rec.name} needs bytes [{rec.offset}, {rec.offset + rec.nbytes}) of a data section that ends at {len(view) - data_start}")
+    return version, pairs, records, data_start
+
+
+class _Shard:
+    """One file on disk: its memory map and parsed header."""
+
+    def __init__(self, path):
+        self.path = os.fspath(path)
+        self.map = None
+        with open(self.path, "rb") as fh:
+            if os.fstat(fh.fileno()).st_size:
+                self.map = mmap.mmap(fh.fileno(), 0, access=mmap.ACCESS_READ)       # the map outlives the descriptor
+        try:
+            self.version, self.kv, self.tensors, self.data_start = _parse_header(memoryview(self.map) if self.map is not None else memoryview(b""), self.path)
+        except BaseException:
+            self.release()
+            raise
+
+    def release(self):
+        if self.map is not None:
+            try:
+                self.map.close()
+            except BufferError:                               # arrays handed out by raw() still point into the map; it is unmapped when they go
+                pass
+            self.map = None
+
+    def bytes_of(self, rec):
+        return np.frombuffer(self.map, dtype=np.uint8, count=rec.nbytes, offset=self.data_start + rec.offset)
+
+
+def _split_position(path):
+    """(stem, index, total) of a gguf-split file name `<stem>-IIIII-of-TTTTT.gguf`, or None."""
+    base = os.path.basename(path)
+    if not base.endswith(".gguf"):
+        return None
+    parts = base[:-5].rsplit("-", 3)
+    if len(parts) != 4 or parts[2] != "of" or not (len(parts[1]) == len(parts[3]) == 5 and parts[1].isdigit() and parts[3].isdigit()):
+        return None
+    return parts[0], int(parts[1]), int(parts[3])
 
 
 class GgufFile:
-    """One GGUF file: `kv` (dict), `tensors` (name -> TensorInfo), `raw(name)` (uint8 view [rows.., row bytes]), `array(name)` for F32 / F16 / BF16 tensors."""
+    """One GGUF file or split set: `kv` (dict), `tensors` (name -> TensorInfo), `raw(name)` (uint8 view [rows.., row bytes]), `array(name)` for F32 / F16 / BF16 tensors."""
 
-    def __init__(self, path, _member=False):
-        self.path = str(path)
-        self._owner, self._members = {}, []                  # tensor name -> shard that holds it (split sets); the other shards
-        self._f = open(self.path, "rb")
-        size = os.fstat(self._f.fileno()).st_size
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ) if size else None
-        if size < 24 or self._mm[:4] != MAGIC:
-            self.close()
-            raise GgufError(f"{path}: not a GGUF file")
-        c = _Cursor(memoryview(self._mm), 4)
-        self.version = c.take("<I")
-        if self.version not in (2, 3):
-            raise GgufError(f"{path}: GGUF version {self.version} (this reader: 2 and 3, little endian)")
-        nt, nkv = c.take("<Q"), c.take("<Q")
-        if nt > 1 << 22 or nkv > 1 << 22:
-            raise GgufError("implausible tensor / key count")
-        self.kv = {}
-        for _ in range(nkv):
-            k = c.string()
-            self.kv[k] = c.value(c.take("<I"))
-        self.tensors = {}
-        for _ in range(nt):
-            name = c.string()
-            nd = c.take("<I")
-            if nd > 8:
-                raise GgufError(f"tensor {name}: {nd} dimensions")
-            ne = [c.take("<Q") for _ in range(nd)]
-            t, off = c.take("<I"), c.take("<Q")
-            if name in self.tensors:
-                raise GgufError(f"duplicate tensor {name}")
-            self.tensors[name] = TensorInfo(name, ne, t, off)
-        al = int(self.kv.get("general.alignment", ALIGN_DEFAULT))
-        if al <= 0 or al & (al - 1):
-            raise GgufError(f"general.alignment {al}")
-        self.data_start = (c.p + al - 1) // al * al
-        for ti in self.tensors.values():
-            if self.data_start + ti.offset + ti.nbytes > size:
-                raise GgufError(f"tensor {ti.name}: data past the end of the file")
-        if not _member and int(self.kv.get("split.count", 1) or 1) > 1:
-            self._attach_shards()
-
-    def _attach_shards(self):
-        """This file is shard 1 of a split set: open and check the others (count, numbering, no duplicate tensor, tensor total)."""
-        n, no = int(self.kv["split.count"]), int(self.kv.get("split.no", 0))
-        m = _SHARD_NAME.match(os.path.basename(self.path))
-        if no != 0:
-            raise GgufError(f"{self.path}: shard split.no={no} of {n}: open the FIRST shard (-00001-of-{n:05d}.gguf)")
-        if not m or int(m.group(2)) != 1 or int(m.group(3)) != n:
-            raise GgufError(f"{self.path}: split.count={n} but the file name is not <name>-00001-of-{n:05d}.gguf")
-        folder, base = os.path.dirname(os.path.realpath(self.path)), m.group(1)
-        members = [self]
+    def __init__(self, path):
+        self.path = os.fspath(path)
+        first = _Shard(self.path)
+        self._shards = [first]
+        self._home = {name: first for name in first.tensors}          # tensor name -> shard whose data section holds it
+        self.version, self.kv, self.tensors, self.data_start = first.version, first.kv, dict(first.tensors), first.data_start
         try:
-            for i in range(2, n + 1):
-                f = os.path.join(folder, f"{base}-{i:05d}-of-{n:05d}.gguf")
-                if not os.path.isfile(f):
-                    raise GgufError(f"{self.path}: shard {i} of {n} is missing ({os.path.basename(f)})")
-                s = GgufFile(f, _member=True)
-                members.append(s)
-                if int(s.kv.get("split.count", 0) or 0) != n or int(s.kv.get("split.no", -1)) != i - 1:
-                    raise GgufError(f"{f}: split.no={s.kv.get('split.no')} split.count={s.kv.get('split.count')}, expected {i - 1} / {n}")
-            for s in members:
-                for name, ti in s.tensors.items():
-                    if s is not self:
-                        if name in self.tensors:
-                            raise GgufError(f"duplicate tensor {name} across shards ({os.path.basename(s.path)})")
-                        self.tensors[name] = ti
-                    self._owner[name] = s
-            want = self.kv.get("split.tensors.count")
-            if want is not None and int(want) != len(self.tensors):
-                raise GgufError(f"{self.path}: shard set holds {len(self.tensors)} tensors, split.tensors.count says {want}")
+            total = int(self.kv.get("split.count") or 1)
+            if total > 1:
+                self._open_rest_of_set(total)
         except BaseException:
-            for s in members[1:]:
-                s.close()
+            self.close()
             raise
-        self._members = members[1:]
+
+    def _open_rest_of_set(self, total):
+        """The file announces a split set of `total` files: it has to be number 1 by key and by name; files 2..total are found beside it, checked and merged."""
+        here = int(self.kv.get("split.no", 0))
+        pos = _split_position(self.path)
+        if here != 0:
+            raise GgufError(f"{self.path} is part {here + 1} of a {total}-file set; a set is opened through its part 1")
+        if pos is None or pos[1:] != (1, total):
+            raise GgufError(f"{self.path} announces a {total}-file set, so its name has to end in -00001-of-{total:05d}.gguf")
+        folder = os.path.dirname(os.path.abspath(self.path))
+        present = {}
+        for cand in glob.glob(os.path.join(glob.escape(folder), glob.escape(pos[0]) + "-*-of-*.gguf")):
+            p = _split_position(cand)
+            if p and p[0] == pos[0] and p[2] == total:
+                present[p[1]] = cand
+        absent = [i for i in range(2, total + 1) if i not in present]
+        if absent:
+            raise GgufError(f"{self.path}: parts {absent} of {total} were not found in {folder}; nothing is loaded from an incomplete set")
+        for i in range(2, total + 1):
+            part = _Shard(present[i])
+            self._shards.append(part)
+            if (part.kv.get("split.no"), part.kv.get("split.count")) != (i - 1, total):
+                raise GgufError(f"{part.path} describes itself as part {part.kv.get('split.no')!r} of {part.kv.get('split.count')!r}, its name says {i - 1} of {total}")
+            clash = self.tensors.keys() & part.tensors.keys()
+            if clash:
+                raise GgufError(f"{part.path} repeats tensors of an earlier part: {sorted(clash)[:3]}")
+            self.tensors.update(part.tensors)
+            self._home.update({name: part for name in part.tensors})
+        declared = self.kv.get("split.tensors.count")
+        if declared is not None and declared != len(self.tensors):
+            raise GgufError(f"{self.path}: the set's parts list {len(self.tensors)} tensors, the first part promises {declared}")
 
     def close(self):
-        for s in self._members:
-            s.close()
-        self._members = []
-        mm, self._mm = self._mm, None
-        try:
-            if mm is not None:
-                mm.close()
-        except BufferError:                                  # views handed out by raw() are still alive: the map goes with them
-            pass
-        self._f.close()
+        for sh in self._shards:
+            sh.release()
 
     def __enter__(self):
         return self
 
-    def __exit__(self, *a):
+    def __exit__(self, *exc):
         self.close()
 
     def raw(self, name) -> np.ndarray:
         """uint8 view of the tensor's bytes, shape [rows.., row_bytes] (zero copy)."""
-        ti = self.tensors[name]
-        if not ti.known:
-            raise GgufTypeError(f"tensor {name}: ggml type id {ti.type} is not in the type table of this reader")
-        _, be, bb = TYPES[ti.type]
-        src = self._owner.get(name, self)
-        a = np.frombuffer(src._mm, dtype=np.uint8, count=ti.nbytes, offset=src.data_start + ti.offset)
-        return a.reshape(ti.shape[:-1] + (ti.ne[0] // be * bb,)) if ti.ne else a
+        rec = self.tensors[name]
+        if not rec.known:
+            raise GgufTypeError(f"{name}: ggml type id {rec.type} has no entry in this reader's type table, so its size is unknown")
+        flat = self._home[name].bytes_of(rec)
+        return flat.reshape(rec.shape[:-1] + (rec.row_bytes,)) if rec.ne else flat
 
     def array(self, name) -> np.ndarray:
         """F32 / F16 / BF16 (as float32) / integer tensors as numpy arrays of their shape."""

@@ -72,7 +72,7 @@ def test_split_shard_set_reads_as_one_file(gold, tmp_path):
             np.testing.assert_array_equal(np.asarray(g.raw(name)).reshape(-1), gold[f"raw_{i}"])       # bytes come from the shard that holds the tensor
         assert g.kv["general.architecture"] == "tiny" and g.kv["split.count"] == 2
     with pytest.raises(GG.GgufError):                                      # the second shard is not an entry point
-        GG.GgufFile(os.path.join(HERE, "golden", "tinysplit-00002-of-00002.gguf"))._attach_shards()
+        GG.GgufFile(os.path.join(HERE, "golden", "tinysplit-00002-of-00002.gguf"))
     lone = tmp_path / "tinysplit-00001-of-00002.gguf"
     shutil.copy(first, lone)
     with pytest.raises(GG.GgufError):                                      # a missing shard is an error, never a partial load
