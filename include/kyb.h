@@ -146,17 +146,25 @@ int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const void* gw, c
  * kyb_moe_groups + kyb_gemv_group_t16: gathered GEMV over routed slots with expert election: slot s = expert eids[s] applied to row xrows[s] (or s / xdiv)
  *   of x; slots of one expert are served 8 at a time so its bytes are read once per 8 slots. Replace kyojin_mlx/foreign_linear.py:1068-1095 `DevPack.gather`
  *   (kernels foreign_metal.py:115-202 / :1004-1099 with gather=True, :1487-1557 `gemv_g2_source`, fp4tile.py:166-256) and kyojin_mlx/moe_union.py:27-129.
- *   g_expert u32 [S], g_slots u32 [8 S], ngroups u32 [1] are scratch written by kyb_moe_groups. gs: per-expert fp32 output scale or NULL. */
+ *   g_expert u32 [S], g_slots u32 [8 S], ngroups u32 [1] are scratch written by kyb_moe_groups (one election serves every projection of a layer).
+ *   gs: per-expert fp32 output scale or NULL. The two fusions of the reference's decode path are arguments of the same launch:
+ *   t16b (with gsb) = a second stack of the same shape on the same slots, results in rows [S, 2 S) of y (gate | up in one launch,
+ *   kyojin_mlx/foreign_linear.py:1119-1154 `gather_pair`); x2 = gated input, the row fed to the product is fp16(silu(x row) * x2 row) formed while it is
+ *   staged, clamp `limit` > 0 as kyb_silu_mul (foreign_linear.py:1156-1164 `gather_glu`, kernel foreign_metal.py:1107-1113). eids (optional, u32 [S]):
+ *   rows of y whose slot id is outside [0, E) are set to zero (such slots are in no group).
+ *   Ids outside [0, E) (the router's 0xFFFFFFFF for a token with NaN logits) are tolerated everywhere: kyb_moe_plan sorts such slots behind the last
+ *   segment with weight 0, kyb_gather_rows returns zeros for a source row >= xrows, the grouped products write zeros to their rows. */
 int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream);
 int kyb_moe_plan(const void* ids, const void* wts, const void* rank, int E, int64_t P, int topk, int mt, void* order, void* inv, void* tok, void* ids_s,
                  void* wts_s, void* off, void* tb, void* stream);
-int kyb_gather_rows(const void* x, int64_t ldx, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo, void* stream);
+int kyb_gather_rows(const void* x, int64_t ldx, int64_t xrows, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo, void* stream);
 int kyb_silu_mul(const void* a, const void* b, int64_t ld, int64_t rows, int64_t n, float limit, const void* perm, void* h, int64_t ldh, void* stream);
 int kyb_moe_combine(const void* y, int64_t ldy, const void* scs, const void* sgs, const void* shared, int64_t lds, int64_t T, int K, int64_t H, int out_dtype,
                     void* o, int64_t ldo, void* stream);
 int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert, void* g_slots, void* ngroups, void* stream);
-int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
-                       const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream);
+int kyb_gemv_group_t16(int fmt, const void* t16, const void* t16b, int64_t n, int64_t k, int E, const void* x, const void* x2, float limit, int64_t ldx,
+                       const void* eids, const void* xrows, int xdiv, int64_t S, const void* gs, const void* gsb, void* y, int64_t ldy, const void* g_expert,
+                       const void* g_slots, const void* ngroups, void* stream);
 
 /* single-launch form of kyb_gemv_t16: split-k partial sums are reduced inside the kernel by the last part that finishes a row tile. The workspace holds
  * kyb_gemv_counter_bytes(n) bytes of arrival counters (must be ZERO before the first call; every call leaves them zero) followed by
@@ -205,6 +213,11 @@ int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);
 /* device status word of the calling thread's current device: nonzero after a bounded wait expired inside a kernel.
  * kyb_check_device_status synchronises `stream`, reads and clears it. */
 int kyb_check_device_status(void* stream);
+
+/* self-test of that report path (no counterpart in the reference): launches one thread that waits, with the kernels' own bounded wait and a limit of `polls`
+ * polls (1..4096), on a barrier that nothing completes. The wait gives up after well under a second, the kernel records a status code and returns by itself;
+ * the next kyb_check_device_status on the stream returns KYB_ETIMEOUT and clears the word. Nothing faults and nothing is left in flight. */
+int kyb_selftest_wait_timeout(int polls, void* stream);
 
 #ifdef __cplusplus
 }

@@ -143,13 +143,14 @@ SIGNATURES = {
     "kyb_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_moe_select": (_int, [_vp, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp]),
     "kyb_moe_plan": (_int, [_vp, _vp, _vp, _int, _i64, _int, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "kyb_gather_rows": (_int, [_vp, _i64, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
+    "kyb_gather_rows": (_int, [_vp, _i64, _i64, _vp, _int, _vp, _i64, _i64, _vp, _i64, _vp]),
     "kyb_silu_mul": (_int, [_vp, _vp, _i64, _i64, _i64, _f32, _vp, _vp, _i64, _vp]),
     "kyb_moe_combine": (_int, [_vp, _i64, _vp, _vp, _vp, _i64, _i64, _int, _i64, _int, _vp, _i64, _vp]),
     "kyb_moe_groups": (_int, [_vp, _i64, _int, _vp, _vp, _vp, _vp]),
-    "kyb_gemv_group_t16": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _vp, _int, _i64, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
+    "kyb_gemv_group_t16": (_int, [_int, _vp, _vp, _i64, _i64, _int, _vp, _vp, _f32, _i64, _vp, _vp, _int, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp]),
     "kyb_gemv_plan": (_int, [_int, _i64, _i64, _i64, C.POINTER(C.c_int)]),
     "kyb_check_device_status": (_int, [_vp]),
+    "kyb_selftest_wait_timeout": (_int, [_int, _vp]),
 }
 
 

@@ -15,6 +15,8 @@ void kyb_set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+// The status word is part of the library image (zero-initialised on every device that loads it), so no entry point allocates device memory.
+static __device__ __align__(256) unsigned int g_status_word_dev[64];
 static std::mutex g_status_mu;
 static unsigned int* g_status_words[64] = {nullptr};
 
@@ -23,10 +25,9 @@ unsigned int* kyb_device_status_word() {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     std::lock_guard<std::mutex> lk(g_status_mu);
     if (!g_status_words[dev]) {
-        unsigned int* p = nullptr;
-        if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;      // one-time, 256 bytes per device, never freed
-        if (cudaMemset(p, 0, 256) != cudaSuccess) return nullptr;
-        g_status_words[dev] = p;
+        void* p = nullptr;                                             // the symbol's address on the current device (the name itself is a host-side stand-in)
+        if (cudaGetSymbolAddress(&p, g_status_word_dev) != cudaSuccess) return nullptr;
+        g_status_words[dev] = (unsigned int*)p;
     }
     return g_status_words[dev];
 }
@@ -77,6 +78,28 @@ size_t kyb_raw_row_bytes(int fmt, int64_t k) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ self-test of the bounded-wait report path
+// One thread waits on an mbarrier that nothing ever completes, with the same bounded wait the kernels use and a small poll limit; when the wait gives up the
+// kernel records a status code and returns by itself (no trap, no fault, nothing left in flight), exactly as a kernel whose copy never arrived would.
+namespace kyb {
+__global__ void selftest_wait_kernel(unsigned int* status, uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        if (!mbar_wait_bounded(&bar, 0, polls)) atomicExch(status, KYB_DEV_TIMEOUT_SELFTEST);
+    }
+}
+}  // namespace kyb
+
+extern "C" int kyb_selftest_wait_timeout(int polls, void* stream) {
+    KYB_REQUIRE(polls >= 1 && polls <= 4096, "polls=%d: 1..4096", polls);
+    unsigned int* w = kyb_device_status_word();
+    KYB_REQUIRE(w, "could not set up the device status word");
+    kyb::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(w, (uint32_t)polls);
+    return kyb_launch_check("selftest_wait");
+}
 
 // ------------------------------------------------------------------------------------------------ results of a step gathered into one buffer
 // Up to 128 device arrays copied into one contiguous buffer by a single launch (16-byte units; sizes and addresses multiples of 16): the results of a decode step

@@ -261,5 +261,6 @@ extern "C" int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, i
     p.tb = (const uint32_t*)tb_, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     const int max_tiles = (int)((s + kyb::GM_BM - 1) / kyb::GM_BM) + experts;
     cudaStream_t st = (cudaStream_t)stream;
-    return wide ? launch_gemm<256, 4>(ta, tb, p, st, max_tiles) : launch_gemm<128, 6>(ta, tb, p, st, max_tiles);
+    if (int rc = wide ? launch_gemm<256, 4>(ta, tb, p, st, max_tiles) : launch_gemm<128, 6>(ta, tb, p, st, max_tiles)) return rc;
+    return kyb_zero_tail_rows(d, ldd, n, row_map, (const uint32_t*)off + experts, s, st);                      // slots that belong to no expert: rows of zeros
 }

@@ -723,5 +723,6 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     p.tma_out = 0, p.col0 = 0, p.wide = 0;                                         // rows are scattered (row_map) or end inside a tile: stores from registers
     KybOutMaps outs;
     memset(&outs, 0, sizeof(outs));
-    return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
+    if (int rc = kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream)) return rc;
+    return kyb_zero_tail_rows(d, ldd, n, row_map, (const uint32_t*)off + experts, s, (cudaStream_t)stream);   // slots that belong to no expert: rows of zeros
 }

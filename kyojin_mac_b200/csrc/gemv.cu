@@ -549,17 +549,38 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
 // (the reference's `moe_union` election, kyojin_mlx/moe_union.py:27-63, done for 8 rows because the MMA has 8 activation columns anyway).
 struct GroupParams {
     const uint8_t* t16;            // expert stack: E matrices of n rows
+    const uint8_t* t16b;           // pair form: a second stack of the same shape served by the same launch (its results are rows [S, 2 S) of y), or null
     const __half* x;               // [*, k] source rows
+    const __half* x2;              // gated form: the staged row is fp16(silu(x row) * x2 row) (same row index, same pitch), or null
+    const uint32_t* eids;          // [S] expert of each slot, or null; rows of slots whose id is outside [0, E) are set to zero
     const uint32_t* xrows;         // [S] source row of each slot, or null (slot s reads row s / xdiv)
     const uint32_t* g_expert;      // [G]
     const uint32_t* g_slots;       // [G * 8] slot or 0xFFFFFFFF
     const uint32_t* ngroups;       // device scalar
     const float* gs;               // per-expert output scale or null
-    __half* y;                     // [S, ldy]
+    const float* gsb;              // the same for the second stack
+    __half* y;                     // [S, ldy] ([2 S, ldy] in the pair form)
     unsigned int* status;
     int64_t ldx, ldy;
+    float limit;                   // gated form: > 0 clamps as the activation kernel does
     int n, nb, kc, xdiv, rc, warps;   // rows per expert, k-blocks, canonical chunk, slot -> row divisor, row chunks per group, warps per CTA
+    int S, E;
 };
+
+// fp16(silu(a) * b) on 8 values, the arithmetic of silu_mul_kernel (fp32, saturated)
+__device__ __forceinline__ uint4 glu8(const uint4 a, const uint4 b, const float limit) {
+    const __half* ah = reinterpret_cast<const __half*>(&a);
+    const __half* bh = reinterpret_cast<const __half*>(&b);
+    uint4 o;
+    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float av = __half2float(ah[j]), bv = __half2float(bh[j]);
+        if (limit > 0.f) av = fminf(av, limit), bv = fminf(fmaxf(bv, -limit), limit);
+        oh[j] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
+    }
+    return o;
+}
 
 // Single CTA: slots -> groups. counts per expert, groups per expert = ceil(count / 8), slot p of rank r inside its expert -> group start + r / 8.
 __global__ void moe_groups_kernel(const uint32_t* __restrict__ eids, int S, int E, uint32_t* __restrict__ g_expert, uint32_t* __restrict__ g_slots, uint32_t* __restrict__ ngroups) {
@@ -615,18 +636,27 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
     const int tpc = (ntiles + p.rc - 1) / p.rc;                    // row tiles per chunk
     const uint32_t ngroups = *p.ngroups;
     const uint32_t xb0 = smem_u32(xfrag) + g * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
+    const uint32_t npair = p.t16b ? 2u : 1u;
+    // slots that belong to no expert are in no group: their rows are written here
+    if (p.eids)
+        for (int sl = blockIdx.x; sl < p.S; sl += gridDim.x)
+            if (p.eids[sl] >= (uint32_t)p.E)
+                for (uint32_t w2 = 0; w2 < npair; ++w2)
+                    for (int c = threadIdx.x; c < p.n; c += blockDim.x) p.y[((size_t)sl + (size_t)w2 * p.S) * p.ldy + c] = __float2half(0.f);
     uint32_t parity = 0;
     int stage = 0;
     bool failed = false;
-    for (uint32_t item = blockIdx.x; item < ngroups * (uint32_t)p.rc; item += gridDim.x) {
-        const uint32_t grp = item / (uint32_t)p.rc, rc = item % (uint32_t)p.rc;
+    for (uint32_t item = blockIdx.x; item < ngroups * (uint32_t)p.rc * npair; item += gridDim.x) {
+        const uint32_t which = item % npair, it2 = item / npair;              // the two stacks of a pair take neighbouring items
+        const uint32_t grp = it2 / (uint32_t)p.rc, rc = it2 % (uint32_t)p.rc;
         const uint32_t e = p.g_expert[grp];
+        const uint8_t* stack = which ? p.t16b : p.t16;
         const int rt0 = (int)rc * tpc + warp, rt_end = min(ntiles, ((int)rc + 1) * tpc);
         const int nrt = rt0 < rt_end ? (rt_end - rt0 + p.warps - 1) / p.warps : 0;      // row tiles of this warp: rt0, rt0 + warps, ...
         const int total = nrt * p.nb;
         // ---- producer (lane 0): this item's tiles of this warp
         int p_left = total, p_blk = p.nb, p_stage = stage;
-        const uint8_t* p_src = p.t16 + (((size_t)e * ntiles + rt0) * (size_t)p.nb) * TB;
+        const uint8_t* p_src = stack + (((size_t)e * ntiles + rt0) * (size_t)p.nb) * TB;
         const size_t p_jump = ((size_t)p.warps - 1) * (size_t)p.nb * TB;
         auto issue = [&]() {
             const uint32_t bar = bar_a + 8 * p_stage, dst = ring_a + p_stage * TB;
@@ -655,6 +685,11 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
                     const uint4* xp = reinterpret_cast<const uint4*>(p.x + xr * p.ldx + (size_t)c2 * 32);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) v[q] = __ldg(xp + q);
+                    if (p.x2) {                                               // gated input: the activation is formed while the row is staged
+                        const uint4* xq = reinterpret_cast<const uint4*>(p.x2 + xr * p.ldx + (size_t)c2 * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) v[q] = glu8(v[q], __ldg(xq + q), p.limit);
+                    }
                 }
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -691,7 +726,9 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
         Acc<NT> acc, tot;
 #pragma unroll
         for (int q = 0; q < 4; ++q) acc.v[0][q] = 0.f, tot.v[0][q] = 0.f;
-        const float gsc = p.gs ? p.gs[e] : 1.0f;
+        const float* gsp = which ? p.gsb : p.gs;
+        const float gsc = gsp ? gsp[e] : 1.0f;
+        const size_t yrow0 = which ? (size_t)p.S : 0;
         uint32_t xb = xb0, xa = xa0;
         int blk = 0, rt = rt0, cleft = min(p.kc, p.nb);
         for (int i = 0; i < total; ++i) {
@@ -715,7 +752,7 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
                     if (last) {
                         const uint32_t slot = s_slots[2 * t + (q & 1)];
                         const int nrow = rt * 16 + g + 8 * (q >> 1);
-                        if (slot != 0xFFFFFFFFu) p.y[(size_t)slot * p.ldy + nrow] = sat_half(tot.v[0][q] * gsc);
+                        if (slot != 0xFFFFFFFFu) p.y[(yrow0 + slot) * p.ldy + nrow] = sat_half(tot.v[0][q] * gsc);
                         tot.v[0][q] = 0.f;
                     }
                 }
@@ -1126,13 +1163,14 @@ extern "C" int kyb_moe_groups(const void* eids, int64_t S, int E, void* g_expert
     return kyb_launch_check("moe_groups");
 }
 
-extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k, int E, const void* x, int64_t ldx, const void* xrows, int xdiv, int64_t S,
-                                  const void* gs, void* y, int64_t ldy, const void* g_expert, const void* g_slots, const void* ngroups, void* stream) {
+extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, const void* t16b, int64_t n, int64_t k, int E, const void* x, const void* x2, float limit, int64_t ldx,
+                                  const void* eids, const void* xrows, int xdiv, int64_t S, const void* gs, const void* gsb, void* y, int64_t ldy, const void* g_expert,
+                                  const void* g_slots, const void* ngroups, void* stream) {
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
     KYB_REQUIRE(n > 0 && n % 16 == 0 && k > 0 && k % 256 == 0 && E > 0, "n=%lld k=%lld: expert matrices need n %% 16 == 0 and k %% 256 == 0", (long long)n, (long long)k);
     KYB_REQUIRE(t16 && x && y && g_expert && g_slots && ngroups, "null pointer");
-    KYB_REQUIRE(S > 0 && xdiv > 0 && ldx >= k && ldx % 8 == 0 && ldy >= n, "S=%lld xdiv=%d ldx=%lld ldy=%lld", (long long)S, xdiv, (long long)ldx, (long long)ldy);
-    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    KYB_REQUIRE(S > 0 && S < (1ll << 30) && xdiv > 0 && ldx >= k && ldx % 8 == 0 && ldy >= n, "S=%lld xdiv=%d ldx=%lld ldy=%lld", (long long)S, xdiv, (long long)ldx, (long long)ldy);
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)t16b & 15) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)x2 & 15) == 0, "t16, x (and t16b, x2) must be 16-byte aligned");
     unsigned int* status = kyb_device_status_word();
     KYB_REQUIRE(status, "could not set up the device status word");
     const int nb = (int)(k / 256), ntiles = (int)(n / 16), sms = device_sms();
@@ -1147,12 +1185,13 @@ extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, int64_t n, int64_t k
     }
     KYB_REQUIRE(warps > 0, "k=%lld: the staged activations of a group do not fit in shared memory", (long long)k);
     warps = std::min(warps, std::max(4, (ntiles + 3) / 4 * 4));
-    const int64_t exp_groups = std::max<int64_t>(1, std::min<int64_t>(S, E));
+    const int64_t exp_groups = std::max<int64_t>(1, std::min<int64_t>(S, E)) * (t16b ? 2 : 1);
     int rc = (int)std::min<int64_t>(std::max<int64_t>(1, (4 * sms + exp_groups - 1) / exp_groups), std::max(1, ntiles / warps));
     kyb::GroupParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.xrows = (const uint32_t*)xrows, p.g_expert = (const uint32_t*)g_expert, p.g_slots = (const uint32_t*)g_slots;
-    p.ngroups = (const uint32_t*)ngroups, p.gs = (const float*)gs, p.y = (__half*)y, p.status = status, p.ldx = ldx, p.ldy = ldy;
-    p.n = (int)n, p.nb = nb, p.kc = canonical_chunk(ntiles, nb), p.xdiv = xdiv, p.rc = rc, p.warps = warps;
+    p.t16 = (const uint8_t*)t16, p.t16b = (const uint8_t*)t16b, p.x = (const __half*)x, p.x2 = (const __half*)x2, p.eids = (const uint32_t*)eids, p.xrows = (const uint32_t*)xrows;
+    p.g_expert = (const uint32_t*)g_expert, p.g_slots = (const uint32_t*)g_slots;
+    p.ngroups = (const uint32_t*)ngroups, p.gs = (const float*)gs, p.gsb = (const float*)gsb, p.y = (__half*)y, p.status = status, p.ldx = ldx, p.ldy = ldy, p.limit = limit;
+    p.n = (int)n, p.nb = nb, p.kc = canonical_chunk(ntiles, nb), p.xdiv = xdiv, p.rc = rc, p.warps = warps, p.S = (int)S, p.E = E;
     const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q4_K>
                        : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q6_K>
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q3_K>

@@ -11,6 +11,8 @@
 // ------------------------------------------------------------------------------------------------ host side
 void kyb_set_error(const char* fmt, ...);
 unsigned int* kyb_device_status_word();   // per-device word in global memory, zero-initialised (nullptr on failure)
+// grouped products: zero the output rows of the sorted positions [*first, s) (slots that belong to no expert segment); first = device pointer to off[E]
+int kyb_zero_tail_rows(void* d, int64_t ldd, int64_t n, const void* row_map, const void* first, int64_t s, cudaStream_t st);
 
 #define KYB_REQUIRE(cond, ...)                                        \
     do {                                                              \
@@ -46,6 +48,7 @@ __host__ __device__ constexpr int kyb_raw_block_bytes(int fmt) { return fmt == K
 // status codes written to the device status word by kernels whose bounded wait expired
 #define KYB_DEV_TIMEOUT_GEMV 0x1001u
 #define KYB_DEV_TIMEOUT_GEMM 0x1002u
+#define KYB_DEV_TIMEOUT_SELFTEST 0x10FFu
 
 #ifdef __CUDACC__
 // ------------------------------------------------------------------------------------------------ device side

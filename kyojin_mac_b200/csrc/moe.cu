@@ -65,6 +65,8 @@ __global__ void moe_select_kernel(const float* __restrict__ lg, int64_t ld, int 
 // Counting sort of P slots by expert in ONE CTA (histogram, scan, scatter with shared-memory cursors). rank (optional) maps expert -> position of
 // its segment. Outputs (any may be null): order[pos] = slot, inv[slot] = pos, tok[pos] = slot / topk, ids_s[pos] = expert, wts_s[pos] = wts[slot],
 // off[E + 1] = first row of each segment, tb[E + 1] = first tile of each segment for tiles of mt rows.
+// Slots whose id is outside [0, E) (the router writes 0xFFFFFFFF for a token with NaN logits) belong to no segment: they take the positions
+// [off[E], P) behind the last segment, with weight 0, so that order / inv stay permutations and every output entry is written.
 __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, const uint32_t* __restrict__ rank, int E, int P, int topk, int mt,
                                 uint32_t* __restrict__ order, uint32_t* __restrict__ inv, uint32_t* __restrict__ tok, int32_t* __restrict__ ids_s,
                                 float* __restrict__ wts_s, uint32_t* __restrict__ off, uint32_t* __restrict__ tb) {
@@ -95,24 +97,29 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, const float* __
     __syncthreads();
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e0 = ids[p];
-        if (e0 < 0 || e0 >= E) continue;
-        const uint32_t pos = atomicAdd(&cursor[rank ? rank[e0] : (uint32_t)e0], 1u);
+        const bool valid = e0 >= 0 && e0 < E;
+        const uint32_t pos = atomicAdd(&cursor[valid ? (rank ? rank[e0] : (uint32_t)e0) : (uint32_t)E], 1u);
         if (order) order[pos] = (uint32_t)p;
         if (inv) inv[p] = pos;
         if (tok) tok[pos] = (uint32_t)(p / topk);
         if (ids_s) ids_s[pos] = e0;
-        if (wts_s && wts) wts_s[pos] = wts[p];
+        if (wts_s && wts) wts_s[pos] = valid ? wts[p] : 0.0f;
     }
 }
 
-// out[r, :] = x[src[r] / div, perm ? perm[c] : c]   (fp16 rows of k columns; 8 columns per thread)
-__global__ void gather_rows_kernel(const __half* __restrict__ x, int64_t ldx, const uint32_t* __restrict__ src, int div, const uint32_t* __restrict__ perm, int R, int k,
-                                   __half* __restrict__ out, int64_t ldo) {
+// out[r, :] = x[src[r] / div, perm ? perm[c] : c]   (fp16 rows of k columns; 8 columns per thread). A source row outside [0, xrows) gives a row of zeros.
+__global__ void gather_rows_kernel(const __half* __restrict__ x, int64_t ldx, int64_t xrows, const uint32_t* __restrict__ src, int div, const uint32_t* __restrict__ perm, int R,
+                                   int k, __half* __restrict__ out, int64_t ldo) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int kv = k >> 3;
     if (i >= (int64_t)R * kv) return;
     const int r = (int)(i / kv), c = (int)(i % kv) * 8;
-    const __half* xr = x + (size_t)(src[r] / (uint32_t)div) * ldx;
+    const uint32_t srow = src[r] / (uint32_t)div;
+    if ((int64_t)srow >= xrows) {
+        *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const __half* xr = x + (size_t)srow * ldx;
     if (!perm) {
         *reinterpret_cast<uint4*>(out + (size_t)r * ldo + c) = *reinterpret_cast<const uint4*>(xr + c);
     } else {
@@ -365,7 +372,21 @@ __global__ void __launch_bounds__(THREADS) router_logits_wres_kernel(const XT* _
     }
 }
 
+// Rows of a grouped product that belong to no expert segment (sorted positions [*first, s): slots with an id outside the stack) are set to zero, so that
+// no output row is left unwritten. A fixed small grid: the tail is empty in all but faulty inputs.
+__global__ void zero_tail_rows_kernel(__half* __restrict__ d, int64_t ldd, int n, const uint32_t* __restrict__ row_map, const uint32_t* __restrict__ first, int s) {
+    for (int pos = (int)*first + blockIdx.x; pos < s; pos += gridDim.x) {
+        __half* row = d + (size_t)(row_map ? row_map[pos] : (uint32_t)pos) * ldd;
+        for (int c = threadIdx.x; c < n; c += blockDim.x) row[c] = __float2half(0.f);
+    }
+}
+
 }  // namespace kyb
+
+int kyb_zero_tail_rows(void* d, int64_t ldd, int64_t n, const void* row_map, const void* first, int64_t s, cudaStream_t st) {
+    kyb::zero_tail_rows_kernel<<<16, 256, 0, st>>>((__half*)d, ldd, (int)n, (const uint32_t*)row_map, (const uint32_t*)first, (int)s);
+    return kyb_launch_check("zero_tail_rows");
+}
 
 extern "C" int kyb_moe_select(const void* logits, int64_t ld, int64_t T, int E, int K, int norm, int has_shared, void* inds, void* scs, void* sgs, void* stream) {
     KYB_REQUIRE(logits && inds && scs, "null pointer");
@@ -389,13 +410,14 @@ extern "C" int kyb_moe_plan(const void* ids, const void* wts, const void* rank, 
     return kyb_launch_check("moe_plan");
 }
 
-extern "C" int kyb_gather_rows(const void* x, int64_t ldx, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo, void* stream) {
-    KYB_REQUIRE(x && src && out, "null pointer");
+extern "C" int kyb_gather_rows(const void* x, int64_t ldx, int64_t xrows, const void* src, int div, const void* perm, int64_t R, int64_t k, void* out, int64_t ldo,
+                               void* stream) {
+    KYB_REQUIRE(x && src && out && xrows > 0, "null pointer or empty source");
     KYB_REQUIRE(R > 0 && k > 0 && k % 8 == 0 && div > 0 && ldx % 8 == 0 && ldo % 8 == 0, "R=%lld k=%lld: k, ldx, ldo must be multiples of 8", (long long)R, (long long)k);
     KYB_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "x and out must be 16-byte aligned");
     const int64_t total = R * (k / 8);
-    kyb::gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, ldx, (const uint32_t*)src, div, (const uint32_t*)perm, (int)R, (int)k,
-                                                                                              (__half*)out, ldo);
+    kyb::gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __half*)x, ldx, xrows, (const uint32_t*)src, div, (const uint32_t*)perm, (int)R,
+                                                                                              (int)k, (__half*)out, ldo);
     return kyb_launch_check("gather_rows");
 }
 

@@ -160,10 +160,13 @@ def owner_of(e: torch.Tensor, E: int, world: int) -> torch.Tensor:
     return torch.where(e < cut, e // (base + 1), extra + (e - cut) // max(base, 1))
 
 
-def ep_moe(x: torch.Tensor, inds: torch.Tensor, scs: torch.Tensor, E: int, local_experts, group=None, out_dtype=torch.float32) -> torch.Tensor:
+def ep_moe(x: torch.Tensor, inds: torch.Tensor, scs: torch.Tensor, E: int, local_experts, group=None, out_dtype=torch.float32, slot_dtype=None,
+           slot_width: int | None = None) -> torch.Tensor:
     """Expert-parallel routed layer. x [T, H] (this rank's tokens), inds [T, K] global expert ids, scs [T, K] routing weights.
     local_experts(rows [S, H], local_ids [S]) -> [S, H_out]: this rank's expert stack applied slot by slot (unweighted), e.g. a ForeignSwitchGLU with K = 1.
-    Returns [T, H_out] = sum_k scs[t, k] * expert(inds[t, k])(x[t]). Split sizes are exchanged first (one small all-to-all; the sizes are read on the host)."""
+    Returns [T, H_out] = sum_k scs[t, k] * expert(inds[t, k])(x[t]). Split sizes are exchanged first (one small all-to-all; the sizes are read on the host).
+    slot_dtype / slot_width: dtype and width H_out of what local_experts returns. Every rank must exchange the same element type and width, also a rank that
+    receives no slot and so never calls local_experts; give them whenever they differ from x (default: the dtype and width of x)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     T, K = inds.shape
     e = inds.reshape(-1).to(torch.int64)
@@ -180,7 +183,10 @@ def ep_moe(x: torch.Tensor, inds: torch.Tensor, scs: torch.Tensor, E: int, local
     recv_ids = torch.empty(sum(rc), dtype=torch.int32, device=x.device)
     dist.all_to_all_single(recv_rows, send_rows, rc, sc, group=group)
     dist.all_to_all_single(recv_ids, send_ids, rc, sc, group=group)
-    y_recv = local_experts(recv_rows, recv_ids) if recv_rows.shape[0] else torch.empty((0, x.shape[1]), dtype=x.dtype, device=x.device)
+    sd, sw = slot_dtype or x.dtype, slot_width or x.shape[1]
+    y_recv = local_experts(recv_rows, recv_ids) if recv_rows.shape[0] else torch.empty((0, sw), dtype=sd, device=x.device)
+    if y_recv.dtype != sd or y_recv.shape[1] != sw:
+        raise ValueError(f"local_experts returned {y_recv.dtype} [*, {y_recv.shape[1]}], the exchange was declared as {sd} [*, {sw}] (slot_dtype / slot_width)")
     y_back = torch.empty((send_rows.shape[0], y_recv.shape[1]), dtype=y_recv.dtype, device=x.device)
     dist.all_to_all_single(y_back, y_recv.contiguous(), sc, rc, group=group)
     y_slots = torch.empty_like(y_back)

@@ -171,38 +171,40 @@ class DevPack:
         return ops.dequant(self.fmt, self.t16, self.nrows, self.k, dtype, self.gscale)
 
     # ---- routed-expert slots: slot s uses expert eids[s] and row xrows[s] of x (fp16 [T, k]) -> [S, n]   (foreign_linear.py:1068-1164)
-    def gather(self, x, xrows, eids):
+    def gather(self, x, xrows, eids, groups=None):
         if not self.E or x.dtype != torch.float16:
             raise ValueError("gather() needs an expert stack and fp16 rows")
-        gs = self.gs if self.fmt == "nvfp4" else None
-        return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, gs=gs)
+        return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, gs=self._gs(), groups=groups)
+
+    def _gs(self):
+        return self.gs if self.fmt == "nvfp4" else None
 
     def pair_ok(self, o) -> bool:
         return bool(self.E) and (self.fmt, self.n, self.k, self.E) == (o.fmt, o.n, o.k, o.E)
 
-    def gather_pair(self, o, x, xrows, eids):
-        """(self.gather(...), o.gather(...)): gate | up of one expert block on the same slots (foreign_linear.py:1119-1154)."""
-        y = self.gather_pair_raw(o, x, xrows, eids)
+    def gather_pair(self, o, x, xrows, eids, groups=None):
+        """(self.gather(...), o.gather(...)): gate | up of one expert block on the same slots in ONE launch (foreign_linear.py:1119-1154)."""
+        y = self.gather_pair_raw(o, x, xrows, eids, groups)
         S = eids.numel()
         return y[:S], y[S:]
 
-    def gather_pair_raw(self, o, x, xrows, eids):
-        S = eids.numel()
-        y = torch.empty((2 * S, self.n), dtype=torch.float16, device=x.device)
-        gs = lambda d: d.gs if d.fmt == "nvfp4" else None
-        ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, gs=gs(self), out=y[:S])
-        ops.gemv_group(o.fmt, o.t16, o.n, o.k, o.E, x, eids, xrows=xrows, gs=gs(o), out=y[S:])
-        return y
+    def gather_pair_raw(self, o, x, xrows, eids, groups=None, xdiv=1):
+        """[2 S, n]: rows [0, S) = this stack, rows [S, 2 S) = stack o, on the same slots (the input of glu_rows)."""
+        if not self.pair_ok(o):
+            raise ValueError("gather_pair: two expert stacks of one format and shape")
+        return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, x, eids, xrows=xrows, xdiv=xdiv, gs=self._gs(), groups=groups, t16b=o.t16, gsb=o._gs())
 
     def glu_ok(self) -> bool:
         return bool(self.E)
 
-    def gather_glu(self, a, b, xrows, eids, act=None, limit=None):
-        """gather() of the down projection on the gated input silu(a) * b (a, b fp16 [S, k]; slot s reads row xrows[s]) (foreign_linear.py:1156-1164).
-        Bit-identical to the activation kernel followed by gather(), which is what runs here."""
+    def gather_glu(self, a, b, xrows, eids, act=None, limit=None, groups=None):
+        """gather() of the down projection on the gated input silu(a) * b (a, b fp16 [S, k]; slot s reads row xrows[s]) (foreign_linear.py:1156-1164): the
+        activation is formed while the rows are staged, one launch. Bit-identical to the activation kernel followed by gather()."""
         if act is not None:
             raise NotImplementedError("only the silu-gated activation is built")
-        return self.gather(ops.silu_mul(a, b, limit), xrows, eids)
+        if not self.E or a.dtype != torch.float16:
+            raise ValueError("gather_glu() needs an expert stack and fp16 rows")
+        return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, a, eids, xrows=xrows, gs=self._gs(), groups=groups, x2=b, limit=limit)
 
     def apply_glu(self, a, b, limit=None):
         """One matrix on the gated input silu(a) * b (foreign_linear.py:960-977)."""
@@ -323,8 +325,13 @@ class ForeignSwitchGLU(torch.nn.Module):
         return y.reshape(*lead, K, self.d.n)
 
     def _gather_path(self, x2, e32, K):
-        gs = lambda d: d.gs if d.fmt == "nvfp4" else None
-        a = ops.gemv_group(self.g.fmt, self.g.t16, self.g.n, self.g.k, self.g.E, x2, e32, xdiv=K, gs=gs(self.g))
-        b = ops.gemv_group(self.u.fmt, self.u.t16, self.u.n, self.u.k, self.u.E, x2, e32, xdiv=K, gs=gs(self.u))
-        h = ops.silu_mul(a, b, self.limit)
-        return ops.gemv_group(self.d.fmt, self.d.t16, self.d.n, self.d.k, self.d.E, h, e32, xdiv=1, gs=gs(self.d))
+        """Three projections, two launches after one election: gate | up as a pair, then down with the gated activation formed while its rows are staged."""
+        S = e32.numel()
+        groups = ops.moe_groups(e32, self.g.E)
+        if self.g.pair_ok(self.u):
+            ab = self.g.gather_pair_raw(self.u, x2, None, e32, groups, xdiv=K)
+            a, b = ab[:S], ab[S:]
+        else:                                                                 # gate and up stored in different formats
+            a = ops.gemv_group(self.g.fmt, self.g.t16, self.g.n, self.g.k, self.g.E, x2, e32, xdiv=K, gs=self.g._gs(), groups=groups)
+            b = ops.gemv_group(self.u.fmt, self.u.t16, self.u.n, self.u.k, self.u.E, x2, e32, xdiv=K, gs=self.u._gs(), groups=groups)
+        return self.d.gather_glu(a, b, None, e32, limit=self.limit, groups=groups)

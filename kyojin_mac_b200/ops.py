@@ -232,7 +232,7 @@ def gather_rows(x: torch.Tensor, src: torch.Tensor, div: int = 1, perm: torch.Te
         raise ValueError("gather_rows takes float16 rows")
     R, k = src.numel(), x.shape[1]
     out = torch.empty((R, k), dtype=torch.float16, device=x.device)
-    _lib.check(_lib.lib().kyb_gather_rows(x.data_ptr(), x.stride(0), src.data_ptr(), div, _p(perm), R, k, out.data_ptr(), k, _stream()))
+    _lib.check(_lib.lib().kyb_gather_rows(x.data_ptr(), x.stride(0), x.shape[0], src.data_ptr(), div, _p(perm), R, k, out.data_ptr(), k, _stream()))
     return out
 
 
@@ -258,22 +258,41 @@ def moe_combine(y: torch.Tensor, scs: torch.Tensor, K: int, sgs: torch.Tensor | 
     return o
 
 
+def moe_groups(eids: torch.Tensor, E: int):
+    """Expert election for the gathered GEMV: slots of one expert are served 8 at a time. Returns the scratch triple (g_expert, g_slots, ngroups) that
+    gemv_group takes as `groups`; one election serves every projection of a layer. Slots with an id outside [0, E) are in no group."""
+    _need_cuda(eids)
+    eids = eids.reshape(-1).to(torch.int32).contiguous()
+    S = eids.numel()
+    scratch = torch.empty(S * 9 + 1, dtype=torch.int32, device=eids.device)
+    g_expert, g_slots, ngroups = scratch[:S], scratch[S:9 * S], scratch[9 * S:]
+    _lib.check(_lib.lib().kyb_moe_groups(eids.data_ptr(), S, E, g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
+    return g_expert, g_slots, ngroups
+
+
 def gemv_group(fmt, t16: torch.Tensor, n: int, k: int, E: int, x: torch.Tensor, eids: torch.Tensor, xrows: torch.Tensor | None = None, xdiv: int = 1,
-               gs: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """y fp16 [S, n]: slot s = expert eids[s] applied to row xrows[s] (or s // xdiv) of x fp16 [*, k]; one weight read per expert and 8 slots."""
-    _need_cuda(t16, x, eids)
+               gs: torch.Tensor | None = None, out: torch.Tensor | None = None, groups=None, t16b: torch.Tensor | None = None, gsb: torch.Tensor | None = None,
+               x2: torch.Tensor | None = None, limit: float | None = None) -> torch.Tensor:
+    """y fp16 [S, n]: slot s = expert eids[s] applied to row xrows[s] (or s // xdiv) of x fp16 [*, k]; one weight read per expert and 8 slots.
+    t16b (+ gsb): a second stack of the same shape in the same launch, y is [2 S, n] with its results in rows [S, 2 S). x2: gated input, the row fed to the
+    product is fp16(silu(x row) * x2 row). groups: the election of moe_groups(eids, E) when the caller already has it."""
+    _need_cuda(t16, x, eids, t16b, x2)
     if x.dtype != torch.float16 or x.stride(1) != 1 or x.shape[1] != k:
         raise ValueError(f"x must be float16 [rows, {k}]")
+    if x2 is not None and (x2.dtype != torch.float16 or x2.shape != x.shape or x2.stride() != x.stride()):
+        raise ValueError("the gated form takes two float16 tensors of one shape and layout")
+    if t16b is not None and t16b.numel() != t16.numel():
+        raise ValueError("the pair form takes two stacks of one shape and format")
     S = eids.numel()
     eids = eids.reshape(-1).to(torch.int32).contiguous()
-    y = out if out is not None else torch.empty((S, n), dtype=torch.float16, device=x.device)
-    scratch = torch.empty(S * 9 + 1, dtype=torch.int32, device=x.device)
-    g_expert, g_slots, ngroups = scratch[:S], scratch[S:9 * S], scratch[9 * S:]
-    L = _lib.lib()
-    _lib.check(L.kyb_moe_groups(eids.data_ptr(), S, E, g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
+    rows = S * (2 if t16b is not None else 1)
+    y = out if out is not None else torch.empty((rows, n), dtype=torch.float16, device=x.device)
+    if y.shape[0] != rows:
+        raise ValueError(f"out must hold {rows} rows")
+    g_expert, g_slots, ngroups = groups if groups is not None else moe_groups(eids, E)
     xr = None if xrows is None else xrows.reshape(-1).to(torch.int32).contiguous()
-    _lib.check(L.kyb_gemv_group_t16(_fmt(fmt), t16.data_ptr(), n, k, E, x.data_ptr(), x.stride(0), _p(xr), xdiv, S, _p(gs), y.data_ptr(), y.stride(0),
-                                    g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
+    _lib.check(_lib.lib().kyb_gemv_group_t16(_fmt(fmt), t16.data_ptr(), _p(t16b), n, k, E, x.data_ptr(), _p(x2), float(limit or 0.0), x.stride(0), eids.data_ptr(), _p(xr), xdiv, S,
+                                             _p(gs), _p(gsb), y.data_ptr(), y.stride(0), g_expert.data_ptr(), g_slots.data_ptr(), ngroups.data_ptr(), _stream()))
     return y
 
 

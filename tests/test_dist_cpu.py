@@ -51,6 +51,15 @@ def _worker(rank, world, port, E):
         got = KD.ep_moe(xt, inds, scs, E, lambda rws, ids: _expert_fn(rws, ids + e0))
         want = sum(scs[:, kk:kk + 1] * _expert_fn(xt, inds[:, kk]) for kk in range(K))
         torch.testing.assert_close(got, want, rtol=1e-6, atol=1e-6)
+        # ---- a rank that receives no slot (every token routed to rank 0's experts), expert outputs narrower and of another type than x
+        xt64 = xt.to(torch.float64)
+        ne0 = KD.expert_range(E, world, 0)[1]
+        inds0 = torch.stack([torch.randperm(ne0, generator=gr)[:2] for _ in range(T)])
+        scs0 = torch.rand((T, 2), generator=gr)
+        half = lambda rws, ids: _expert_fn(rws, ids + e0)[:, :H // 2].contiguous()          # float32 [S, H / 2] from float64 rows
+        got0 = KD.ep_moe(xt64, inds0, scs0, E, half, slot_dtype=torch.float32, slot_width=H // 2)
+        want0 = sum(scs0[:, kk:kk + 1] * _expert_fn(xt64, inds0[:, kk])[:, :H // 2] for kk in range(2))
+        torch.testing.assert_close(got0, want0.to(torch.float32), rtol=1e-6, atol=1e-6)
     finally:
         dist.destroy_process_group()
 

@@ -59,6 +59,12 @@ def test_plan_device(P, E, topk):
     np.testing.assert_array_equal(offd.cpu().numpy().astype(np.uint32), off)
     o = order.cpu().numpy()
     assert sorted(o.tolist()) == list(range(P)) and (np.diff(ids[o]) >= 0).all()
+    bad = ids.copy()
+    bad[5], bad[P - 1] = -1, E + 3                                            # ids outside the stack: sorted behind the last segment
+    order, tbd, offd = KQ.csort(torch.from_numpy(bad).cuda(), E)
+    o, offd = order.cpu().numpy(), offd.cpu().numpy()
+    assert sorted(o.tolist()) == list(range(P)) and offd[E] == P - 2 and set(o[P - 2:].tolist()) == {5, P - 1}
+    assert (np.diff(bad[o[:P - 2]]) >= 0).all()
 
 
 def _stack(fmt, E, n, k, seed):
@@ -89,24 +95,67 @@ def test_gather_election_equals_per_expert(fmt):
     assert O.rel_fro(y.cpu().numpy(), want) <= 1e-3
 
 
-def test_pair_and_glu_equal_their_parts():
-    E, n, k, S = 4, 64, 256, 10
+def test_pair_and_glu_launches_vs_per_expert_products():
+    """gate | up in one launch and the down product with the activation formed while its rows are staged: each slot equals the expert's own one-matrix product
+    (another kernel entry, the dense GEMV) on the same input, bit for bit, and the gated input equals the numpy restatement of the activation."""
+    E, n, k, S = 4, 64, 256, 21
     g, _ = _stack("q4_k", E, n, k, 3)
     u, _ = _stack("q4_k", E, n, k, 4)
-    d, _ = _stack("q6_k", E, k, 256 if n == 256 else 256, 5) if False else _stack("q6_k", E, 256, 256, 5)
+    d, Wd = _stack("q6_k", E, 256, 256, 5)
     rng = np.random.default_rng(6)
     x = torch.from_numpy(synth.activations(5, k, rng)).cuda()
-    eids = torch.from_numpy(rng.integers(0, E, S).astype(np.int32)).cuda()
-    xrows = torch.from_numpy(rng.integers(0, 5, S).astype(np.int32)).cuda()
+    en = rng.integers(0, E, S).astype(np.int32)
+    en[:11] = 1                                                               # more than 8 slots on one expert: two groups
+    rn = rng.integers(0, 5, S).astype(np.int32)
+    eids, xrows = torch.from_numpy(en).cuda(), torch.from_numpy(rn).cuda()
     a, b = g.gather_pair(u, x, xrows, eids)
-    assert torch.equal(a, g.gather(x, xrows, eids)) and torch.equal(b, u.gather(x, xrows, eids))
+    ops.check_device_status()
+    for s in range(S):
+        assert torch.equal(a[s], g.expert(int(en[s])).apply(x[rn[s]:rn[s] + 1])[0]), s
+        assert torch.equal(b[s], u.expert(int(en[s])).apply(x[rn[s]:rn[s] + 1])[0]), s
     aa = torch.from_numpy(synth.activations(S, 256, rng)).cuda()
     bb = torch.from_numpy(synth.activations(S, 256, rng)).cuda()
     ar = torch.arange(S, dtype=torch.int32, device="cuda")
-    assert torch.equal(d.gather_glu(aa, bb, ar, eids), d.gather(ops.silu_mul(aa, bb), ar, eids))
-    np.testing.assert_array_equal(ops.silu_mul(aa, bb).cpu().numpy(), M.glu(aa.cpu().numpy(), bb.cpu().numpy()))
-    lim = ops.silu_mul(aa, bb, limit=0.5).cpu().numpy()
-    np.testing.assert_array_equal(lim, M.glu(aa.cpu().numpy(), bb.cpu().numpy(), 0.5))
+    for limit in (None, 0.5):
+        h = M.glu(aa.cpu().numpy(), bb.cpu().numpy(), limit)                  # numpy restatement of the activation
+        np.testing.assert_array_equal(ops.silu_mul(aa, bb, limit).cpu().numpy(), h)
+        y = d.gather_glu(aa, bb, ar, eids, limit=limit)
+        ops.check_device_status()
+        hd = torch.from_numpy(h).cuda()
+        for s in range(S):
+            assert torch.equal(y[s], d.expert(int(en[s])).apply(hd[s:s + 1])[0]), (limit, s)
+        want = np.stack([O.matmul_f64(h[s:s + 1], Wd[en[s]])[0] for s in range(S)])
+        assert O.rel_fro(y.cpu().numpy(), want) <= 1e-3
+
+
+def test_slots_without_an_expert_are_tolerated():
+    """A token whose router logits hold a NaN gets the id 0xFFFFFFFF from the select kernel. Such slots must not reach an unbounded read: the sort puts them
+    behind the last segment with weight 0, their output rows are zeros on both routed paths, every other slot is unaffected."""
+    E, H, I, T, K = 4, 256, 256, 40, 2
+    g, Wg = _stack("q4_k", E, I, H, 30)
+    u, Wu = _stack("q4_k", E, I, H, 31)
+    d, Wd = _stack("q4_k", E, H, I, 32)
+    rng = np.random.default_rng(33)
+    x = (synth.activations(T, H, rng).astype(np.float32) * 0.5).astype(np.float16)
+    lg = rng.standard_normal((T, E)).astype(np.float32)
+    lg[7, 1] = np.nan
+    inds, scs, _ = ops.moe_select(torch.from_numpy(lg).cuda(), E, K, True)
+    ie = inds.cpu().numpy().reshape(T, K)
+    assert (ie[7].astype(np.uint32) >= E).all() and (np.delete(ie, 7, 0).astype(np.uint32) < E).all()
+    pl = ops.moe_plan(inds, E, K, 128, wts=scs)
+    order, off, wts_s = pl["order"].cpu().numpy(), pl["off"].cpu().numpy(), pl["wts_s"].cpu().numpy()
+    assert sorted(order.tolist()) == list(range(T * K)) and off[E] == T * K - K
+    assert set(order[off[E]:].tolist()) == {7 * K, 7 * K + 1} and (wts_s[off[E]:] == 0).all()
+    blk = ForeignSwitchGLU(g, u, d)
+    xd = torch.from_numpy(x).cuda()
+    good = np.delete(np.arange(T), 7)
+    want = M.routed_layer(x[good], ie[good], Wg, Wu, Wd, K, ref_path=False).reshape(T - 1, K, H)
+    from kyojin_mac_b200 import foreign_kqgmm as KQ2
+    for name, y in (("gathered", blk._gather_path(xd, inds, K)), ("grouped", KQ2.mlp(blk, xd, inds, K))):
+        ops.check_device_status()
+        yn = y.reshape(T, K, H).cpu().numpy()
+        assert (yn[7] == 0).all(), name
+        assert O.rel_fro(yn[good], want) <= 2e-3, name
 
 
 @pytest.mark.parametrize("T,K", [(6, 4), (200, 4)])
