@@ -183,8 +183,7 @@ def run_ours(args):
     ys = {(m, i): torch.empty((m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)}
     yg = {(m, i): torch.empty((world * m, n), dtype=torch.float16, device=dev) for m in BATCHES for i, (_, _, n, _) in enumerate(mats)} if world > 1 else None
     step_bytes = sum(alg_bytes(f, n, k, m) for m in BATCHES for _, f, n, k in mats)
-    two = ops.TWO_LAUNCH                                              # split-k shapes: gemv_t16_kernel + gemv_finalize_kernel
-    launches_per_step = sum(1 + (two and ops.gemv_plan(f, n, k, m)["ksplit"] > 1) for m in BATCHES for _, f, n, k in mats)
+    launches_per_step = len(BATCHES) * len(mats)                         # one kernel per product
 
     # N > 1: the output slices of a whole step are exchanged by ONE copy launch into every rank's symmetric buffer plus ONE device-side barrier
     # (kyojin_mac_b200.dist.PeerGather); --nccl-gather uses one NCCL all-gather per product instead
@@ -206,7 +205,7 @@ def run_ours(args):
                 if timed is not None and i == timed[0]:
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                ops.gemv(f, layer[i].t16, n, k, xs[(m, k)], 1.0, out=ys[(m, i)])
+                ops.gemv(f, layer[i].t16, n, k, xs[(m, k)], 1.0, out=ys[(m, i)], chained=True)
                 if timed is not None and i == timed[0]:
                     e1.record()
                     timed[1].append((m, e0, e1))

@@ -70,10 +70,16 @@ int kyb_dequant_rows_t16(int fmt, const void* t16, int64_t n, int64_t k, const v
 /* ---- decode GEMV, m <= 32 activation rows. Replaces kyojin_mlx/foreign_linear.py:846-857 `DevPack._gemv` /
  * `_gemvk` (kernels foreign_metal.py:115-202 `gemv_source`, :1004-1099 `_gemvk_source`) and the few-row products
  * :1025-1048 `_fmma` / `_mma` / :859-863 `_mmak`. The result of an activation row does not depend on m.
- * workspace: kyb_gemv_workspace_bytes bytes (may be 0 -> workspace may be NULL); split-k partial sums live there. */
+ * workspace: kyb_gemv_workspace_bytes bytes (may be 0 -> workspace may be NULL); split-k partial sums live there.
+ * flags: 0, or KYB_GEMV_CHAINED = launch with programmatic stream serialization: the kernel's CTAs become resident, set up and start prefetching the WEIGHTS
+ *   while the preceding kernel of the stream still drains, and wait for that kernel's completion only before they touch x, y or the workspace. Consecutive
+ *   chained GEMVs of a decode step overlap their launch and pipeline-fill time this way (2 - 3 us per product). Rule for the caller: the weights must not be
+ *   written by the kernel that directly precedes a chained call on the stream (weights loaded earlier and settled are fine; the Python modules pass the flag
+ *   only from the second call of a matrix on). */
+#define KYB_GEMV_CHAINED 1
 size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m);
 int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
-                 void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
+                 void* y, int64_t ldy, void* workspace, size_t workspace_bytes, int flags, void* stream);
 
 /* ---- prefill GEMM on tcgen05 (UMMA 128 x 256 x 16, kind::f16, fp32 accumulation in tensor memory), fp16 operands:
  * d [m, n] = sat_f16(gscale * a [m, k] b [n, k]^T), k % 64 == 0, lda / ldb / ldd in elements. Replaces the library matmul of the
@@ -166,14 +172,6 @@ int kyb_gemv_group_t16(int fmt, const void* t16, const void* t16b, int64_t n, in
                        const void* eids, const void* xrows, int xdiv, int64_t S, const void* gs, const void* gsb, void* y, int64_t ldy, const void* g_expert,
                        const void* g_slots, const void* ngroups, void* stream);
 
-/* single-launch form of kyb_gemv_t16: split-k partial sums are reduced inside the kernel by the last part that finishes a row tile. The workspace holds
- * kyb_gemv_counter_bytes(n) bytes of arrival counters (must be ZERO before the first call; every call leaves them zero) followed by
- * kyb_gemv_workspace_bytes(...) bytes of partial sums. Same results, bit for bit, as kyb_gemv_t16. flags bit 0: programmatic dependent launch (the kernel's
- * set-up and weight prefetch overlap the tail of the preceding kernel on the stream; it waits for that kernel before touching x, y or the workspace). */
-size_t kyb_gemv_counter_bytes(int64_t n);
-int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
-                       void* workspace, size_t workspace_bytes, int flags, void* stream);
-
 /* two-step form with the partial sums exposed. Replaces kyojin_mlx/mma_gemv.py:129-135 `partial_mma` (-> f32 [parts, rows, n]) and :141-149 `finalize_rows`.
  * partial: f32 [kyb_gemv_chunks(n, k)][m][n padded to 16]; finalize adds the parts in k order, scales, saturates to fp16. */
 int kyb_gemv_chunks(int64_t n, int64_t k);
@@ -194,10 +192,10 @@ int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* b
 /* ---- kyb_gemv_t16 for callers that must not allocate device memory. No counterpart in the reference (MLX owns all allocation there).
  * Meant for hosts that cannot call cudaMalloc when they need a GEMV: a server that gave all free HBM to its KV-cache pool at start-up, a decode loop that
  * cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a runtime whose plug-in rules forbid the callee to allocate.
- * Same arithmetic and results as kyb_gemv_t16; the split-k partial sums and the bounded-wait status word live in a fixed 16 MiB + 256 B array inside the
+ * Same arithmetic and results as kyb_gemv_t16; the chunk sums and the bounded-wait status word live in a fixed 16 MiB + 256 B array inside the
  * library image (held by every GPU that loads the library until the process exits) instead of a caller workspace. The call allocates nothing
  * (no cudaMalloc / cudaFree, no allocating library routine). Limits and rules:
- *   - shapes whose split-k scratch exceeds 16 MiB are refused with KYB_EWORKSPACE (use kyb_gemv_t16 with your own workspace);
+ *   - shapes whose chunk sums exceed 16 MiB (kyb_gemv_workspace_bytes) are refused with KYB_EWORKSPACE (use kyb_gemv_t16 with your own workspace);
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device current); make that first call
  *     before any stream capture;
  *   - all calls on a device share the one array: two calls that overlap on the GPU (different streams) race on it - serialise them;
@@ -206,8 +204,8 @@ int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* b
 int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
                         void* y, int64_t ldy, int check, void* stream);
 
-/* launch plan the GEMV would use (diagnostics and launch counting): out8 = {column tiles, stored x rows per tile, warps per CTA,
- * ring stages, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. ksplit > 1 means two launches. */
+/* launch plan the GEMV would use (diagnostics): out8 = {column tiles, 1 if warps take whole row tiles, warps per CTA, k-blocks per canonical chunk,
+ * k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. */
 int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);
 
 /* device status word of the calling thread's current device: nonzero after a bounded wait expired inside a kernel.

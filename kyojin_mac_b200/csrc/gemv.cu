@@ -18,36 +18,30 @@
 
 #include "t16_decode.cuh"
 
-#ifndef KYB_ABL
-#define KYB_ABL 0             // experiment switches (instruction-count ablations); 0 in every shipped build
-#endif
-#ifndef KYB_Q4K_SUBNORMAL
-#define KYB_Q4K_SUBNORMAL 1   // 1: 4-bit codes enter the MMA as fp16 subnormals (code * 2^-24), 0: as 1024 + code minus 1024
-#endif
-
 namespace kyb {
 
 struct GemvParams {
     const uint8_t* t16;
     const __half* x;
     __half* y;
-    float* partial;          // [nchunks][m][npad] when ksplit > 1: one partial sum per canonical k-chunk
+    float* partial;          // [nchunks][m][npad]: sums of the canonical k-chunks (form (b))
     unsigned int* status;
     int64_t ldx, ldy;
     int n, npad, nb;         // rows, rows padded to 16, k-blocks of 256
     int m, mst;              // activation rows, rows stored per column tile (1, 2, 4, 8)
-    int kbp, ksplit;         // k-blocks per part (a multiple of kc), parts
+    int kbp, ksplit;         // k-blocks per part (cpp chunks), parts
     int kc;                  // k-blocks per canonical chunk: sums are formed per chunk and chunks are added in k order, whatever the split
-    int nchunks;             // canonical chunks along k
+    int nchunks, cpp;        // canonical chunks along k, chunks per k-part
     int pdl;                 // launched with programmatic stream serialization
-    int direct;              // one k-part and no partial output wanted: chunk sums are added in registers and y is stored by the kernel
-    unsigned int* counters;  // split k: one arrival counter per row tile (zero before the call, zero again after it); null = a finalize kernel sums the partials
+    int partial_only;        // every chunk sum goes to `partial` and nothing else is written: form (b), and the two-step entry points with exposed partial sums
+    int aligned;             // warps take whole row tiles (no row tile is shared between warps); else runs of whole chunks
     int warps, stages;
     float gscale;
 };
 
 constexpr int SCL_BYTES = 16 * 16 * 4;   // per-warp scale scratch: 16 rows x 16 floats
 constexpr int GEMV_STAGES = 2;           // ring depth per warp: a stage is handed back as soon as its tile sits in registers, so two stages keep two copies in flight
+constexpr int GEMV_DSTAGES = 2;          // the same for the dense kernel (a four-stage ring measured 1-3 % slower on large matrices: the kernel is not limited by bytes in flight)
 
 template <int FMT>
 __host__ __device__ constexpr int xaux_bytes_per_block(int nt) { return FMT == KYB_FMT_Q4_K ? 256 * nt : 0; }
@@ -67,11 +61,7 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         // 6-bit scales of sub-blocks 4 hf .. 4 hf + 3 as four bytes (kyojin_mlx/foreign_gguf.py:340-346)
         const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const float d = half_bits_to_float(mt.x & 0xffffu);
-#if KYB_Q4K_SUBNORMAL
-        const float dlo = d * 16777216.0f, dhi = d * 1048576.0f;     // even sub-blocks: code * 2^-24, odd: code * 2^-20
-#else
-        const float dlo = d, dhi = d * 0.0625f;
-#endif
+        const float dlo = d * 16777216.0f, dhi = d * 1048576.0f;     // the 4-bit codes enter the MMA as fp16 subnormals: even sub-blocks code * 2^-24, odd code * 2^-20
         // byte b -> float without a convert: 0x4B0000bb is 2^23 + b, and fma((2^23 + b), d, -2^23 d) = b d exactly
         const float nlo = dlo * -8388608.0f, nhi = dhi * -8388608.0f;
         float4 o;
@@ -163,13 +153,8 @@ __device__ __forceinline__ void load_tile(uint32_t tile, int lane, TileRegs<FMT>
         const uint32_t mng = ((up ? mg.w >> 4 : mg.z) & mka) | ((mg.z >> 2) & mkb);
         const uint32_t mnh = ((up ? mh.w >> 4 : mh.z) & mka) | ((mh.z >> 2) & mkb);
         const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
-#if KYB_Q4K_SUBNORMAL
         tr.a0 = prmt(mng, 0u, sel), tr.a1 = prmt(mnh, 0u, sel);
         tr.dmg = half_bits_to_float(mg.x >> 16) * 16777216.0f, tr.dmh = half_bits_to_float(mh.x >> 16) * 16777216.0f;
-#else
-        tr.a0 = magic_sub(prmt(mng, 0x64646464u, sel), 0x64006400u), tr.a1 = magic_sub(prmt(mnh, 0x64646464u, sel), 0x64006400u);
-        tr.dmg = half_bits_to_float(mg.x >> 16), tr.dmh = half_bits_to_float(mh.x >> 16);
-#endif
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
 #pragma unroll
         for (int P = 0; P < 4; ++P) tr.q[P] = lds128(tile + (P * 32 + lane) * 16);
@@ -207,15 +192,8 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
             for (int c = 0; c < 2; ++c) {
                 const uint32_t wg = c ? u.z : u.x, wh = c ? u.w : u.y;
                 const uint32_t wg8 = wg >> 8, wh8 = wh >> 8;
-#if KYB_Q4K_SUBNORMAL
                 const uint32_t l0 = wg & 0x000F000Fu, l1 = wh & 0x000F000Fu, l2 = wg8 & 0x000F000Fu, l3 = wh8 & 0x000F000Fu;
                 const uint32_t h0 = wg & 0x00F000F0u, h1 = wh & 0x00F000F0u, h2 = wg8 & 0x00F000F0u, h3 = wh8 & 0x00F000F0u;
-#else
-                const uint32_t l0 = magic_sub(and_or(wg, 0x000F000Fu, 0x64006400u), 0x64006400u), l1 = magic_sub(and_or(wh, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                const uint32_t l2 = magic_sub(and_or(wg8, 0x000F000Fu, 0x64006400u), 0x64006400u), l3 = magic_sub(and_or(wh8, 0x000F000Fu, 0x64006400u), 0x64006400u);
-                const uint32_t h0 = magic_sub(and_or(wg, 0x00F000F0u, 0x64006400u), 0x64006400u), h1 = magic_sub(and_or(wh, 0x00F000F0u, 0x64006400u), 0x64006400u);
-                const uint32_t h2 = magic_sub(and_or(wg8, 0x00F000F0u, 0x64006400u), 0x64006400u), h3 = magic_sub(and_or(wh8, 0x00F000F0u, 0x64006400u), 0x64006400u);
-#endif
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
                     const uint2 bl = ldb(4 * G + c, nt);
@@ -317,36 +295,47 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
     }
 }
 
-// Persistent kernel: one CTA per SM. CTA c works on k-part c % ksplit (its activations are staged once); its warps take the row tiles
-// ws, ws + TS, ... of that part (ws = warp slot among the TS warps of the part) and stream them back to back through one ring.
+// Persistent kernel, one CTA per SM. The work of a matrix is cut into UNITS: (16-row tile, canonical k-chunk of kc k-blocks); units are ordered row tile by
+// row tile, which is also their order in memory. CTA c works on k-part c % ksplit (it stages the activations of that part once); the units of a part are dealt
+// to the warps of its CTAs as contiguous, equally long runs, so every warp streams one contiguous range of tiles and all warps finish together. A warp forms the
+// sum of every chunk in registers. Two forms: (a) matrices with many row tiles: a run is whole row tiles, the warp adds the chunk sums in k order and stores y
+// itself; (b) otherwise a run is whole chunks (+-1 over the warps whatever the shape), every chunk sum goes to the workspace and gemv_finalize_kernel adds them in
+// k order. Either way an output is the left-to-right sum of the same chunk sums, so results do not depend on the batch size, the grid or the split.
 template <int FMT, int NT, int MST>
-__global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t16_kernel(const GemvParams p) {
+// At most 16 warps per CTA: 128 registers per thread let the compiler keep the unpacked operands of several MMAs in flight (with 24 warps and 80 registers the
+// kernel spilled and its steady rate was 15 % lower).
+__global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int TB = kyb_tile_bytes(FMT);
     constexpr int CS = NT * MST * 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kp = blockIdx.x % p.ksplit, cgi = blockIdx.x / p.ksplit;
-    const int kb0 = kp * p.kbp, nblk = min(p.nb, kb0 + p.kbp) - kb0;
-    const int nparts_ctas = ((int)gridDim.x - kp + p.ksplit - 1) / p.ksplit;      // CTAs working on this k-part
-    const int TS = nparts_ctas * p.warps, ws = cgi * p.warps + warp;
+    const int c0 = kp * p.cpp, cpk = min(p.nchunks, c0 + p.cpp) - c0;             // first chunk and number of chunks of this k-part
+    const int kb0 = c0 * p.kc, nblk = min(p.nb, (c0 + cpk) * p.kc) - kb0;         // its k-blocks
+    const int part_ctas = ((int)gridDim.x - kp + p.ksplit - 1) / p.ksplit;        // CTAs working on this k-part
+    const int WP = part_ctas * p.warps, ws = cgi * p.warps + warp;
     const int ntiles = p.npad >> 4;
-    const int nitems = ws < ntiles ? (ntiles - ws + TS - 1) / TS : 0;
-    const int total = nitems * nblk;
+    const int64_t UP = (int64_t)ntiles * cpk;                                     // units of this part
+    // this warp's run: whole row tiles when the plan says so (many row tiles: no row tile is shared, nothing goes through the workspace), else whole chunks
+    const int64_t u0 = p.aligned ? (int64_t)ntiles * ws / WP * cpk : UP * ws / WP, u1 = p.aligned ? (int64_t)ntiles * (ws + 1) / WP * cpk : UP * (ws + 1) / WP;
+    auto tiles_before = [&](int64_t u) -> int64_t { return (u / cpk) * nblk + (u % cpk) * p.kc; };
+    const int total = (int)(tiles_before(u1) - tiles_before(u0));
+    const int rt0 = (int)(u0 / cpk), j0 = (int)(u0 % cpk);
 
     // ---- shared memory carve-up
     uint8_t* xfrag = smem;
     uint8_t* xaux = xfrag + (size_t)p.kbp * 16 * CS;
-    constexpr int STAGES = GEMV_STAGES;
+    constexpr int STAGES = GEMV_DSTAGES;
     constexpr size_t warp_bytes = ((size_t)STAGES * TB + SCL_BYTES + 8 * (size_t)STAGES + 8 + 15) & ~(size_t)15;
     uint8_t* wbase = xaux + (size_t)p.kbp * xaux_bytes_per_block<FMT>(NT) + (size_t)warp * warp_bytes;
     uint8_t* ring = wbase;
     float* scl = reinterpret_cast<float*>(wbase + (size_t)STAGES * TB);
     uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + (size_t)STAGES * TB + SCL_BYTES);
 
-    // producer state (lane 0): next tile to request. Tiles of one row tile are contiguous; the next row tile of this warp is TS row tiles further.
-    int p_left = total, p_blk = nblk;                       // tiles still to request, tiles left in the current row tile
-    const uint8_t* p_src = p.t16 + (((size_t)ws * (size_t)p.nb) + (size_t)kb0) * TB;
-    const size_t p_jump = ((size_t)TS * (size_t)p.nb - (size_t)nblk) * TB;       // from the end of a row tile's part to the start of the next one
+    // producer state (lane 0): next tile to request. The tiles of a row tile's part are contiguous; the next row tile follows nb - nblk tiles further.
+    int p_left = total, p_blk = nblk - j0 * p.kc;             // tiles still to request, tiles left in the current row tile's part
+    const uint8_t* p_src = p.t16 + ((size_t)rt0 * (size_t)p.nb + (size_t)(kb0 + j0 * p.kc)) * TB;
+    const size_t p_jump = (size_t)(p.nb - nblk) * TB;
     const uint32_t ring_a = smem_u32(ring), bar_a = smem_u32(bars), scl_a = smem_u32(scl);
     auto issue = [&](int stage) {
         const uint32_t bar = bar_a + 8 * stage, dst = ring_a + stage * TB;
@@ -435,56 +424,43 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
     const int g = lane >> 2, t = lane & 3;
     // lanes whose activation row is not staged read a staged row instead: their output columns are never stored
     const uint32_t xb0 = smem_u32(xfrag) + (g & (MST - 1)) * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
-    uint32_t xb = xb0, xa = xa0;                                  // this lane's fragment addresses for the current k-block
+    uint32_t xb = xb0 + (uint32_t)(j0 * p.kc) * (16 * CS), xa = xa0 + (uint32_t)(j0 * p.kc) * (256 * NT);   // this lane's fragment addresses for the current k-block
 
-    Acc<NT> acc;
+    Acc<NT> acc, tot;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) acc.v[nt][0] = acc.v[nt][1] = acc.v[nt][2] = acc.v[nt][3] = 0.f;
-
-    Acc<NT> tot;
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) tot.v[nt][0] = tot.v[nt][1] = tot.v[nt][2] = tot.v[nt][3] = 0.f;
-    const int chunk0 = kb0 / p.kc;                                // parts start on chunk boundaries
-    int blk = 0, rt = ws, chunk = chunk0, cleft = min(p.kc, nblk);
+        for (int q = 0; q < 4; ++q) acc.v[nt][q] = 0.f, tot.v[nt][q] = 0.f;
+    const bool whole = !p.partial_only;                           // every row tile of the run is complete (whole row tiles per warp, one k-part)
+    int rt = rt0, j = j0, cleft = min(p.kc, nblk - j0 * p.kc);
     uint32_t parity = 0;
     bool failed = false;
     auto step = [&](const int stage) {                            // stage is a literal at every call: all shared addresses are base + immediate
         const uint32_t tile = ring_a + stage * TB;
         // a wait that gives up is remembered; the tile is then consumed as it is (its values do not matter any more) and the kernel reports at the end
-#if !(KYB_ABL & 2)
         if (!mbar_wait_fast(bar_a + 8 * stage, parity)) failed = true;
-#endif
         // phase A: everything this warp needs from the stage goes to registers / the scale scratch, then the stage is handed back and refilled
         TileRegs<FMT> tr;
         load_tile<FMT>(tile, lane, tr);
-#if !(KYB_ABL & 1)
         prep_scales<FMT>(tile, scl_a, lane);
-#endif
         __syncwarp();
-#if !(KYB_ABL & 2)
         if (lane == 0 && p_left > 0) issue(stage);
-#endif
         // phase B: arithmetic from registers
-#if !(KYB_ABL & 4)
         consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
-#else
-        acc.v[0][0] += __uint_as_float(tr.q[0].x ^ tr.q[1].y ^ tr.q[2].z ^ tr.q[3].w ^ tr.a0 ^ tr.a1) + tr.dmg + tr.dmh;
-#endif
         __syncwarp();                                             // the scale scratch is rewritten by the next tile
         xb += 16 * CS, xa += 256 * NT;
-        ++blk;
         if (--cleft == 0) {
-            // ---- end of a canonical chunk: its sum joins the running total (one part holds the whole k range) or goes to the workspace
-            // lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
-            const bool last = blk == nblk;
+            // ---- end of a canonical chunk. lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
+            const int chunk = c0 + j;
+            const bool rt_done = ++j == cpk;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
-                    if (p.direct) {
+                    if (whole) {
                         tot.v[nt][q] += acc.v[nt][q];
-                        if (last) {
+                        if (rt_done) {
                             if (m < p.m && nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(tot.v[nt][q] * p.gscale);
                             tot.v[nt][q] = 0.f;
                         }
@@ -494,42 +470,8 @@ __global__ void __launch_bounds__(NT == 1 ? 768 : NT == 2 ? 512 : 256, 1) gemv_t
                     acc.v[nt][q] = 0.f;
                 }
             }
-            ++chunk;
-            cleft = min(p.kc, nblk - blk);
-            if (last && !p.direct && p.counters) {
-                // ---- split k without a second launch: the last part to finish a row tile adds the chunk sums in k order and stores the result
-                __threadfence();                                            // this warp's partial sums are visible before it counts itself in
-                __syncwarp();                                               // every lane has fenced its own stores before lane 0 announces the warp
-                unsigned int arrived = 0;
-                if (lane == 0) arrived = atomicAdd(&p.counters[rt], 1u);
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (arrived == (unsigned int)p.ksplit - 1u) {
-                    __threadfence();
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int nrow = rt * 16 + g + 8 * (q >> 1), m = nt * 8 + 2 * t + (q & 1);
-                            if (m < p.m && nrow < p.n) {
-                                float sum = 0.f;
-                                const float* pp = p.partial + (size_t)m * p.npad + nrow;
-                                const size_t cstride = (size_t)p.m * p.npad;
-                                for (int c0 = 0; c0 < p.nchunks; c0 += 8) {                  // loads of 8 chunks in flight, added in k order
-                                    float v[8];
-#pragma unroll
-                                    for (int c = 0; c < 8; ++c) v[c] = c0 + c < p.nchunks ? __ldcg(pp + (size_t)(c0 + c) * cstride) : 0.f;
-#pragma unroll
-                                    for (int c = 0; c < 8; ++c)
-                                        if (c0 + c < p.nchunks) sum += v[c];
-                                }
-                                p.y[(size_t)m * p.ldy + nrow] = sat_half(sum * p.gscale);
-                            }
-                        }
-                    }
-                    if (lane == 0) p.counters[rt] = 0u;                     // ready for the next call
-                }
-            }
-            if (last) blk = 0, rt += TS, xb = xb0, xa = xa0, chunk = chunk0, cleft = min(p.kc, nblk);
+            if (rt_done) j = 0, ++rt, xb = xb0, xa = xa0;
+            cleft = min(p.kc, nblk - j * p.kc);
         }
     };
     static_assert(STAGES == 2, "the tile loop is unrolled over a two-stage ring");
@@ -768,8 +710,9 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
 }
 
 __global__ void gemv_finalize_kernel(const float* __restrict__ partial, int ksplit, int m, int n, int npad, float gscale, __half* __restrict__ y, int64_t ldy) {
-    // launched as a programmatic dependent of the GEMV (its CTAs may already be resident while the GEMV's last warps finish): the partial sums are
-    // complete and visible after this wait; a no-op under a plain launch
+    // in a chained launch the CTAs of this kernel may be resident while the GEMV's last warps finish, and the next kernel of the chain may start its own
+    // weight prefetch at once: the partial sums are complete and visible after the wait; both instructions are no-ops under a plain launch
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t)m * n) return;
@@ -787,13 +730,8 @@ namespace {
 struct GemvPlan {
     int nt, mst, warps, stages, kbp, ksplit, grid;
     size_t smem;
-    int kc, nchunks;
+    int kc, nchunks, cpp, aligned;
 };
-
-int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
 
 size_t plan_smem(int fmt, int nt, int mst, int kbp, int warps, int stages) {
     const size_t tb = kyb_tile_bytes(fmt);
@@ -840,61 +778,65 @@ int device_sms() {
     return sms;
 }
 
-// Cost model of one configuration. The kernel is persistent with one CTA per SM, so the model is per warp: the busiest warp's tile count times the time a
-// warp needs per tile (latency floor, or its share of the SM's issue slots), against the bandwidth floor, plus the split-k traffic.
-double plan_cost(int fmt, int sms, int ntiles, int nb, int nt, int64_t n, int64_t m, int warps, int stages, int kbp, int ksplit, int* grid_out) {
-    const double tb = kyb_tile_bytes(fmt);
-    const double lat0 = env_int("KYB_GEMV_LAT0", 900), issue_per_tile = env_int("KYB_GEMV_ISSUE", fmt == KYB_FMT_Q4_K ? 60 : 80) * nt;   // cycles
-    const int grid = (int)std::min<int64_t>(sms, std::max<int64_t>(ksplit, ((int64_t)ntiles * ksplit + warps - 1) / warps));
-    const int64_t slots = (int64_t)(grid / ksplit) * warps;                       // warps of the part with the fewest CTAs
-    const double busiest = (double)((ntiles + slots - 1) / slots) * kbp;
-    const double active = std::min<double>(warps, (double)ntiles * ksplit / grid);   // busy warps per SM
-    const double per_tile = std::max(lat0 * (stages >= 3 ? 1.0 : 1.15), active * issue_per_tile);
-    const double t_lat = busiest * per_tile / 1.9e9 + 1.5e-6;
-    const double t_bw = (double)ntiles * nb * tb / 6.6e12 + 1.0e-6;
-    double tsec = std::max(t_lat, t_bw);
-    if (ksplit > 1) tsec += 2.0 * ((nb + kbp - 1) / kbp) * m * (double)n * 4.0 / 6.6e12 + 3.0e-6;      // partial traffic + the finalize launch
-    *grid_out = grid;
-    return tsec + 1e-9 * stages + 1e-10 * warps;
-}
-
-// Canonical k-chunk of a matrix: depends on (n, k) only - never on m or on the launch shape - so the partial sums of an activation row are always
-// formed chunk by chunk and added in k order (bit-identical rows whatever m and however the chunks are spread over CTAs). Small-n matrices get short
-// chunks so that row tiles x chunks still give every SM a full set of warps.
+// Canonical k-chunk of a matrix: depends on (n, k) only - never on m or on the launch shape - so the partial sums of an activation row are always formed chunk by
+// chunk and added in k order (bit-identical rows whatever m and however the chunks are spread over warps and CTAs). At most 8 k-blocks, so that the staged
+// activations of one chunk fit in shared memory for 32 rows. Matrices with thousands of row tiles are dealt to the warps in whole row tiles and take the
+// largest even division of k; smaller ones are dealt in runs of chunks and a chunk is about half of what one of ~1800 warps gets. Among the sizes near the
+// target the one that divides k most evenly, then the larger.
 int canonical_chunk(int ntiles, int nb) {
-    const int want_chunks = (2400 + ntiles - 1) / ntiles;               // ~16 warps on each of 148 SMs
-    return std::max(1, std::min(10, nb / std::max(1, want_chunks)));
-}
-
-// Warps per CTA, chunks per part (k split) and grid are chosen per m. Environment overrides (KYB_GEMV_WARPS / _KSPLIT) exist for sweeps.
-GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
-    const int sms = device_sms();
-    const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
-    const size_t smem_cap = 226 * 1024;
-    const int fw = env_int("KYB_GEMV_WARPS", 0), fk = env_int("KYB_GEMV_KSPLIT", 0);
-    const int kc = canonical_chunk(ntiles, nb), nchunks = (nb + kc - 1) / kc;
-    const int v = variant_of(m), nt = VAR_NT[v], mst = VAR_MST[v];
-    const int max_warps = nt == 1 ? 24 : nt == 2 ? 16 : 8;
-    GemvPlan best{};
-    double best_t = 1e30;
-    for (int cpp = 1; cpp <= nchunks; ++cpp) {                           // chunks per part
-        const int ksplit = (nchunks + cpp - 1) / cpp, kbp = cpp * kc;
-        if ((nchunks + ksplit - 1) / ksplit != cpp) continue;            // one representative per distinct split
-        if (fk && ksplit != fk) continue;
-        if (ksplit > sms) continue;
-        for (int warps = 4; warps <= max_warps; warps += 4) {
-            if (fw && warps != std::min(fw, max_warps)) continue;
-            const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, kyb::GEMV_STAGES);
-            if (smem > smem_cap) continue;
-            int grid = 0;
-            const double tsec = plan_cost(fmt, sms, ntiles, nb, nt, n, m, warps, kyb::GEMV_STAGES, kbp, ksplit, &grid);
-            if (tsec < best_t) best_t = tsec, best = GemvPlan{nt, mst, warps, kyb::GEMV_STAGES, kbp, ksplit, grid, smem, kc, nchunks};
-        }
+    const int hi = std::min(nb, 8);
+    const int target = ntiles >= 3000 ? hi : std::max(1, std::min(hi, (int)((double)ntiles * nb / 3600.0 + 0.5)));
+    const int from = ntiles >= 3000 ? std::max(1, hi / 2) : std::max(1, target - target / 4);
+    int best = target, best_waste = 1 << 30;
+    for (int kc = from; kc <= std::min(hi, target + (target + 1) / 2); ++kc) {
+        const int waste = (nb + kc - 1) / kc * kc - nb;
+        if (waste < best_waste || (waste == best_waste && kc > best)) best = kc, best_waste = waste;
     }
     return best;
 }
 
-// plans are cached per (format, n, k, m): the search costs tens of microseconds, a decode step calls this per linear
+// Warps per CTA, k-parts and the way work is dealt. k is split over CTAs only as far as the staged activations of a part must fit in shared memory next to the
+// warps' rings. For every warp count two ways are scored by how even the busiest warp's share is: whole row tiles per warp (nothing goes through the workspace)
+// or runs of chunks (chunk sums through the workspace and a finalize launch); more warps per SM are mildly preferred.
+GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
+    const int sms = device_sms();
+    const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
+    const size_t smem_cap = 226 * 1024;
+    const int kc = canonical_chunk(ntiles, nb), nchunks = (nb + kc - 1) / kc;
+    const int v = variant_of(m), nt = VAR_NT[v], mst = VAR_MST[v];
+    const int max_warps = nt <= 2 ? 12 : 8;                            // measured: 13 to 16 warps per SM are slower than 10 to 12 on every shape
+    const int fw = getenv("KYB_TMP_WARPS") ? atoi(getenv("KYB_TMP_WARPS")) : 0, fk = getenv("KYB_TMP_KSPLIT") ? atoi(getenv("KYB_TMP_KSPLIT")) : 0;   // TMPSWEEP
+    const int fa = getenv("KYB_TMP_ALIGNED") ? atoi(getenv("KYB_TMP_ALIGNED")) : -1;   // TMPSWEEP
+    GemvPlan best{};
+    double best_score = -1.0;
+    for (int ksplit = 1; ksplit <= std::min(nchunks, sms); ++ksplit) {
+        const int cpp = (nchunks + ksplit - 1) / ksplit;
+        if ((nchunks + cpp - 1) / cpp != ksplit) continue;               // one representative per distinct split
+        if (fk && ksplit != fk) continue;   // TMPSWEEP
+        const int kbp = std::min(nb, cpp * kc), grid = sms / ksplit * ksplit;
+        for (int warps = 4; warps <= max_warps; ++warps) {
+            if (fw && warps != fw) continue;   // TMPSWEEP
+            const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, kyb::GEMV_DSTAGES);
+            if (smem > smem_cap) continue;
+            const double wp = (double)(grid / ksplit) * warps;                                  // warps of a part
+            const double parts = (double)nchunks / ((double)ksplit * cpp);                      // the last part may be shorter
+            const double occupancy = warps >= 10 ? 1.0 : warps == 9 ? 0.97 : warps == 8 ? 0.9 : 0.6 + 0.04 * warps;
+            const double common = parts * ((double)grid / sms) * occupancy * (1.0 - 0.02 * (ksplit - 1));
+            for (int aligned = 0; aligned < 2; ++aligned) {
+                if (fa >= 0 && aligned != fa) continue;   // TMPSWEEP
+                const double upw = aligned ? ntiles / wp : (double)ntiles * cpp / wp;           // row tiles or units per warp
+                const double balance = upw / std::ceil(upw);
+                const double shared = aligned && ksplit == 1 ? 1.0 : 0.9;                       // cost of the workspace round trip and the finalize launch
+                const double score = balance * common * shared;
+                if (score > best_score) best_score = score, best = GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, kbp, ksplit, grid, smem, kc, nchunks, cpp, aligned};
+            }
+        }
+        if (best_score > 0 && !fk) break;                                 // the smallest split that fits
+    }
+    return best;
+}
+
+// plans are cached per (format, n, k, m): a decode step calls this per linear
 GemvPlan make_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     static std::mutex mu;
     static std::unordered_map<uint64_t, GemvPlan> cache;
@@ -922,121 +864,89 @@ int ensure_smem_attr(const void* kern) {
     return KYB_OK;
 }
 
+// launches `kern` plainly or, when chained, with programmatic stream serialization (its CTAs may become resident while the preceding kernel of the stream drains)
+int launch_maybe_chained(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, void** args, bool chained, const char* what) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = chained ? 1 : 0;
+    KYB_CUDA(cudaLaunchKernelExC(&cfg, kern, args));
+    return kyb_launch_check(what);
+}
+
+bool two_step(const GemvPlan& pl) { return !(pl.aligned && pl.ksplit == 1); }     // form (b): chunk sums through the workspace, then the finalize kernel
+size_t partial_bytes(const GemvPlan& pl, int64_t n, int64_t m) { return (size_t)pl.nchunks * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float); }
+
+int check_gemv_args(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx) {
+    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
+    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
+    KYB_REQUIRE(t16 && x, "null pointer");
+    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
+    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
+    return KYB_OK;
+}
+
+// the GEMV kernel and, in form (b), the finalize kernel behind it. partial: scratch for the chunk sums (form (b)); y == nullptr: chunk sums only
+int launch_gemv(int fmt, const GemvPlan& pl, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
+                float* partial, unsigned int* status, bool chained, cudaStream_t st) {
+    const bool sums_only = y == nullptr, staged = sums_only || two_step(pl);
+    kyb::GemvParams p;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
+    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = (int)((n + 15) / 16 * 16), p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
+    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.cpp = pl.cpp, p.aligned = pl.aligned;
+    p.partial_only = staged ? 1 : 0, p.pdl = chained ? 1 : 0;
+    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
+    if (int rc = ensure_smem_attr(kern)) return rc;
+    void* args[] = {(void*)&p};
+    if (int rc = launch_maybe_chained(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), pl.smem, st, args, chained, "gemv_t16")) return rc;
+    if (staged && !sums_only) {
+        const int64_t tot = m * n;
+        const float* part = partial;
+        int nchunks = pl.nchunks, mi = (int)m, ni = (int)n, npad_i = p.npad;
+        __half* yp = (__half*)y;
+        void* fargs[] = {(void*)&part, (void*)&nchunks, (void*)&mi, (void*)&ni, (void*)&npad_i, (void*)&gscale, (void*)&yp, (void*)&ldy};
+        return launch_maybe_chained((const void*)kyb::gemv_finalize_kernel, dim3((unsigned)((tot + 255) / 256)), dim3(256), 0, st, fargs, chained, "gemv_finalize");
+    }
+    return KYB_OK;
+}
+
 }  // namespace
 
 extern "C" int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8) {
     KYB_REQUIRE(fmt >= 0 && fmt <= 3 && n > 0 && k > 0 && k % 256 == 0 && m >= 1 && m <= 32 && out8, "bad arguments");
     const GemvPlan pl = make_plan(fmt, n, k, m);
-    out8[0] = pl.nt, out8[1] = pl.mst, out8[2] = pl.warps, out8[3] = pl.stages, out8[4] = pl.kbp, out8[5] = pl.ksplit, out8[6] = (int)pl.smem, out8[7] = pl.grid;
+    out8[0] = pl.nt, out8[1] = pl.aligned, out8[2] = pl.warps, out8[3] = pl.kc, out8[4] = pl.kbp, out8[5] = pl.ksplit, out8[6] = (int)pl.smem, out8[7] = pl.grid;
     return KYB_OK;
 }
 
 extern "C" size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m) {
     if (fmt < 0 || fmt > 3 || n <= 0 || k <= 0 || k % 256 || m <= 0 || m > 32) return 0;
     const GemvPlan pl = make_plan(fmt, n, k, m);
-    return pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float) : 0;
+    return two_step(pl) ? partial_bytes(pl, n, m) : 0;
 }
-
-// Bytes at the START of the workspace that hold the row-tile arrival counters of the single-launch split-k reduction (kyb_gemv_t16_fused).
-extern "C" size_t kyb_gemv_counter_bytes(int64_t n) { return n > 0 ? (size_t)(((n + 15) / 16 * 4 + 255) / 256 * 256) : 0; }
 
 extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
-                            void* workspace, size_t workspace_bytes, void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
-    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
-    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
-    KYB_REQUIRE(t16 && x && y, "null pointer");
-    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
-    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
-    KYB_REQUIRE(ldy >= n, "ldy=%lld must be >= n", (long long)ldy);
-    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
+                            void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    if (int rc = check_gemv_args(fmt, t16, n, k, x, m, ldx)) return rc;
+    KYB_REQUIRE(y && ldy >= n, "y is null or ldy=%lld < n", (long long)ldy);
+    KYB_REQUIRE((flags & ~KYB_GEMV_CHAINED) == 0, "unknown flags 0x%x", flags);
     const GemvPlan pl = make_plan(fmt, n, k, m);
     KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
-    const int npad = (int)((n + 15) / 16 * 16);
-    const size_t need = pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
-    if (need && (!workspace || workspace_bytes < need)) {
-        kyb_set_error("gemv needs %zu bytes of workspace, got %zu", need, workspace ? workspace_bytes : (size_t)0);
-        return KYB_EWORKSPACE;
-    }
-    unsigned int* status = kyb_device_status_word();
-    KYB_REQUIRE(status, "could not set up the device status word");
-    kyb::GemvParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = (float*)workspace, p.status = status;
-    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    // KYB_PDL_FINALIZE=1: the finalize kernel is launched as a programmatic dependent of the GEMV (measured: within noise on the decode sweep, 2 % on a lone
-    // 4096 x 4096 product), off by default
-    static const int pdl_finalize = env_int("KYB_PDL_FINALIZE", 0);
-    const bool chain = pdl_finalize && pl.ksplit > 1;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.direct = pl.ksplit == 1;
-    p.pdl = chain ? 1 : 0;                                                      // the GEMV lets its dependent launch at once (its own wait is a no-op under a plain launch)
-    cudaStream_t st = (cudaStream_t)stream;
-    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
-    if (int rc = ensure_smem_attr(kern)) return rc;
-    void* args[] = {(void*)&p};
-    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, st));
-    if (pl.ksplit > 1) {
-        const int64_t tot = m * n;
-        const float* part = (const float*)workspace;
-        int nchunks = pl.nchunks, mi = (int)m, ni = (int)n, npad_i = npad;
-        __half* yp = (__half*)y;
-        void* fargs[] = {(void*)&part, (void*)&nchunks, (void*)&mi, (void*)&ni, (void*)&npad_i, (void*)&gscale, (void*)&yp, (void*)&ldy};
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)((tot + 255) / 256)), cfg.blockDim = dim3(256), cfg.dynamicSmemBytes = 0, cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr, cfg.numAttrs = chain ? 1 : 0;
-        KYB_CUDA(cudaLaunchKernelExC(&cfg, (const void*)kyb::gemv_finalize_kernel, fargs));
-        return kyb_launch_check("gemv_finalize");
-    }
-    return KYB_OK;
-}
-
-// Single-launch form: split-k partial sums are reduced inside the kernel by the last part that finishes a row tile (arrival counters in the first
-// kyb_gemv_counter_bytes(n) bytes of the workspace, then the partial sums). The counter bytes must be zero before the first call; every call leaves them zero.
-// flags bit 0: launch with programmatic stream serialization, so that in a chain of GEMVs on one stream the next kernel's set-up and weight prefetch overlap
-// the tail of this one (the kernel itself waits for its predecessor before it touches activations or outputs).
-extern "C" int kyb_gemv_t16_fused(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
-                                  void* workspace, size_t workspace_bytes, int flags, void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
-    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
-    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
-    KYB_REQUIRE(t16 && x && y, "null pointer");
-    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
-    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
-    KYB_REQUIRE(ldy >= n, "ldy=%lld must be >= n", (long long)ldy);
-    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
-    const GemvPlan pl = make_plan(fmt, n, k, m);
-    KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
-    const int npad = (int)((n + 15) / 16 * 16);
-    const size_t cbytes = kyb_gemv_counter_bytes(n);
-    const size_t need = pl.ksplit > 1 ? cbytes + (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
+    const size_t need = two_step(pl) ? partial_bytes(pl, n, m) : 0;
     if (need && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) {
-        kyb_set_error("fused gemv needs %zu bytes of 16-byte aligned workspace (counters first, zeroed once), got %zu", need, workspace ? workspace_bytes : (size_t)0);
+        kyb_set_error("gemv needs %zu bytes of 16-byte aligned workspace, got %zu", need, workspace ? workspace_bytes : (size_t)0);
         return KYB_EWORKSPACE;
     }
     unsigned int* status = kyb_device_status_word();
     KYB_REQUIRE(status, "could not set up the device status word");
-    kyb::GemvParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.status = status;
-    p.counters = need ? (unsigned int*)workspace : nullptr;
-    p.partial = need ? (float*)((unsigned char*)workspace + cbytes) : nullptr;
-    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.pdl = flags & 1, p.direct = pl.ksplit == 1;
-    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
-    if (int rc = ensure_smem_attr(kern)) return rc;
-    void* args[] = {(void*)&p};
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)pl.grid), cfg.blockDim = dim3((unsigned)pl.warps * 32), cfg.dynamicSmemBytes = pl.smem, cfg.stream = (cudaStream_t)stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr, cfg.numAttrs = (flags & 1) ? 1 : 0;
-    KYB_CUDA(cudaLaunchKernelExC(&cfg, kern, args));
-    return KYB_OK;
+    return launch_gemv(fmt, pl, t16, n, k, x, m, ldx, gscale, y, ldy, (float*)workspace, status, (flags & KYB_GEMV_CHAINED) != 0, (cudaStream_t)stream);
 }
 
-// Two-step form with the partial sums exposed (split-k partials, then finalize): the call shape of the reference's few-row MMA GEMV,
+// Two-step form with the partial sums exposed (chunk sums, then finalize): the call shape of the reference's few-row MMA GEMV,
 // kyojin_mlx/mma_gemv.py:129-149 `partial_mma` -> f32 [parts, rows, n] and `finalize_rows` -> [rows, n]. partial: f32 [kyb_gemv_chunks(n, k)][m][npad].
 extern "C" int kyb_gemv_chunks(int64_t n, int64_t k) {
     if (n <= 0 || k <= 0 || k % 256) return 0;
@@ -1045,26 +955,13 @@ extern "C" int kyb_gemv_chunks(int64_t n, int64_t k) {
 }
 
 extern "C" int kyb_gemv_partial_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, void* partial, void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
-    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
-    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
-    KYB_REQUIRE(t16 && x && partial, "null pointer");
-    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
-    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    if (int rc = check_gemv_args(fmt, t16, n, k, x, m, ldx)) return rc;
+    KYB_REQUIRE(partial, "null pointer");
     const GemvPlan pl = make_plan(fmt, n, k, m);
     KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
     unsigned int* status = kyb_device_status_word();
     KYB_REQUIRE(status, "could not set up the device status word");
-    kyb::GemvParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = nullptr, p.partial = (float*)partial, p.status = status;
-    p.ldx = ldx, p.ldy = 0, p.n = (int)n, p.npad = (int)((n + 15) / 16 * 16), p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = 1.0f, p.kc = pl.kc, p.nchunks = pl.nchunks;
-    p.counters = nullptr, p.pdl = 0, p.direct = 0;
-    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
-    if (int rc = ensure_smem_attr(kern)) return rc;
-    void* args[] = {(void*)&p};
-    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, (cudaStream_t)stream));
-    return KYB_OK;
+    return launch_gemv(fmt, pl, t16, n, k, x, m, ldx, 1.0f, nullptr, 0, (float*)partial, status, false, (cudaStream_t)stream);
 }
 
 extern "C" int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int64_t n, float gscale, void* y, int64_t ldy, void* stream) {
@@ -1078,11 +975,12 @@ extern "C" int kyb_gemv_finalize(const void* partial, int chunks, int64_t m, int
 // ------------------------------------------------------------------------------------------------ decode GEMV without any allocation
 // Some hosts may not allocate device memory at the moment they need a GEMV: a serving process that handed every free byte of HBM to its KV-cache
 // pool at start-up (a later cudaMalloc fails or fragments the pool), a latency-critical decode loop that cannot take the implicit device
-// synchronisation of cudaMalloc / cudaFree, or an embedding runtime whose plug-in contract forbids the callee to allocate. For them the split-k
-// partial sums and the timeout word of this variant live in a fixed array that is part of the library image: every GPU that loads the library
-// holds KYB_GEMV_STATIC_SCRATCH_BYTES + 256 bytes of it until the process exits.
+// synchronisation of cudaMalloc / cudaFree, or an embedding runtime whose plug-in contract forbids the callee to allocate. For them the scratch of
+// this variant (chunk sums, timeout word) lives in a fixed array that is part of the library image: every GPU that loads the library holds
+// KYB_GEMV_STATIC_SCRATCH_BYTES + 256 bytes of it until the process exits.
 #define KYB_GEMV_STATIC_SCRATCH_BYTES (16u << 20)
-static __device__ __align__(256) unsigned char g_gemv_static_scratch[KYB_GEMV_STATIC_SCRATCH_BYTES + 256];   // [0, 256): status word, then fp32 partial sums
+// [0, 256): status word (zero when the library is loaded; a successful call never writes it); then the fp32 chunk sums
+static __device__ __align__(256) unsigned char g_gemv_static_scratch[256 + KYB_GEMV_STATIC_SCRATCH_BYTES];
 
 namespace {
 // In host code the array's name is only a stand-in; the device address is looked up once per device (with that device current) and cached.
@@ -1105,20 +1003,13 @@ int static_scratch_address(unsigned char** out) {
 
 extern "C" int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
                                    int check, void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
-    KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
-    KYB_REQUIRE(m >= 1 && m <= 32, "m=%lld: this entry point serves 1..32 activation rows", (long long)m);
-    KYB_REQUIRE(t16 && x && y, "null pointer");
-    KYB_REQUIRE(((uintptr_t)t16 & 15) == 0 && ((uintptr_t)x & 15) == 0, "t16 and x must be 16-byte aligned");
-    KYB_REQUIRE(ldx >= k && ldx % 8 == 0, "ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
-    KYB_REQUIRE(ldy >= n, "ldy=%lld must be >= n", (long long)ldy);
-    KYB_REQUIRE(n <= (int64_t)1 << 30 && k <= (int64_t)1 << 24, "matrix too large for 32-bit tile indices");
+    if (int rc = check_gemv_args(fmt, t16, n, k, x, m, ldx)) return rc;
+    KYB_REQUIRE(y && ldy >= n, "y is null or ldy=%lld < n", (long long)ldy);
     const GemvPlan pl = make_plan(fmt, n, k, m);
     KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
-    const int npad = (int)((n + 15) / 16 * 16);
-    const size_t need = pl.ksplit > 1 ? (size_t)pl.nchunks * (size_t)m * (size_t)npad * sizeof(float) : 0;
+    const size_t need = two_step(pl) ? partial_bytes(pl, n, m) : 0;
     if (need > KYB_GEMV_STATIC_SCRATCH_BYTES) {
-        kyb_set_error("kyb_gemv_t16_static: this shape needs %zu bytes of split-k scratch, the built-in array holds %u; use kyb_gemv_t16 with a caller workspace", need,
+        kyb_set_error("kyb_gemv_t16_static: this shape needs %zu bytes of chunk sums, the built-in array holds %u; use kyb_gemv_t16 with a caller workspace", need,
                       (unsigned)KYB_GEMV_STATIC_SCRATCH_BYTES);
         return KYB_EWORKSPACE;
     }
@@ -1126,21 +1017,9 @@ extern "C" int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t 
     if (int rc = static_scratch_address(&base)) return rc;
     unsigned int* status = (unsigned int*)base;
     float* partial = (float*)(base + 256);
-    kyb::GemvParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
-    p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = npad, p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
-    p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.counters = nullptr, p.pdl = 0, p.direct = pl.ksplit == 1;
     cudaStream_t st = (cudaStream_t)stream;
-    const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
-    if (int rc = ensure_smem_attr(kern)) return rc;
-    void* args[] = {(void*)&p};
-    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)pl.grid), dim3((unsigned)pl.warps * 32), args, pl.smem, st));
-    if (pl.ksplit > 1) {
-        // every partial sum the finalize pass reads was written by the launch above, so nothing in the array has to start at zero
-        const int64_t tot = m * n;
-        kyb::gemv_finalize_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(partial, pl.nchunks, (int)m, (int)n, npad, gscale, (__half*)y, ldy);
-        if (int rc = kyb_launch_check("gemv_finalize")) return rc;
-    }
+    // every chunk sum the finalize pass reads was written by the launch before it, so nothing in the array has to start at zero
+    if (int rc = launch_gemv(fmt, pl, t16, n, k, x, m, ldx, gscale, y, ldy, partial, status, false, st)) return rc;
     if (check) {
         unsigned int v = 0;
         KYB_CUDA(cudaMemcpyAsync(&v, status, sizeof(v), cudaMemcpyDeviceToHost, st));

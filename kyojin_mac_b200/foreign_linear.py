@@ -114,7 +114,9 @@ class DevPack:
         if R == 0:
             return torch.empty((0, self.n), dtype=torch.float16, device=x2.device)
         if R <= F.GEMV_ROWS:
-            return ops.gemv(self.fmt, self.t16, self.n, self.k, x2, self.gscale)
+            # chained launches only once a plain launch of this matrix has run: whatever wrote the weights then lies further back in the stream
+            chained, self._settled = F.GEMV_CHAINED and getattr(self, "_settled", False), True
+            return ops.gemv(self.fmt, self.t16, self.n, self.k, x2, self.gscale, chained=chained)
         if R < F.GEMM_MIN_ROWS:
             return self._rows_chunked(x2)
         return self._prefill(x2)

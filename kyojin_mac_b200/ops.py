@@ -65,24 +65,25 @@ def dequant(fmt, t16: torch.Tensor, n: int, k: int, dtype=torch.float16, gscale:
 _ws: dict = {}
 
 
-def workspace(device, nbytes: int, tag: int = 0) -> torch.Tensor:
-    """Grow-only ZEROED scratch buffer per (device, stream, tag): split-k partial sums of the GEMV live here; the single-launch form keeps one buffer per
-    counter-area size (tag), so that partial sums of one shape never land in the arrival counters (kept zero by the kernels) of another."""
-    key = (device.index, _stream(), tag)
+def workspace(device, nbytes: int) -> torch.Tensor:
+    """Grow-only scratch buffer per (device, stream): the chunk sums of the GEMV's two-launch form live here."""
+    key = (device.index, _stream())
     buf = _ws.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = _ws[key] = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        buf = _ws[key] = torch.empty(max(nbytes, 4 << 20), dtype=torch.uint8, device=device)
     return buf
 
 
-import os as _os
-PDL = _os.environ.get("KYB_PDL", "0") not in ("0", "")          # chain GEMVs with programmatic dependent launches (KYB_PDL=0: fully serialised launches)
-TWO_LAUNCH = _os.environ.get("KYB_GEMV_TWO_LAUNCH", "1") not in ("0", "")   # split-k sums by a separate finalize kernel (measured faster than the in-kernel reduction, whose release fence per row tile costs more than the second launch)
+def release_workspaces(stream_id: int | None = None) -> None:
+    """Drops the cached workspaces (of one stream id, or all): for callers that create and retire many streams."""
+    for key in [k for k in _ws if stream_id is None or k[1] == stream_id]:
+        del _ws[key]
 
 
-def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, two_launch: bool | None = None, pdl: bool | None = None) -> torch.Tensor:
-    """y fp16 [m, n] = x fp16 [m, k] @ W^T for m <= 32, W in T16. two_launch (default TWO_LAUNCH): split-k sums by the finalize kernel; False: reduced inside the GEMV (one launch, optionally a
-    programmatic dependent launch). All forms return the same bits."""
+def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, chained: bool = False) -> torch.Tensor:
+    """y fp16 [m, n] = x fp16 [m, k] @ W^T for m <= 32, W in T16.
+    chained: launch with programmatic stream serialization (the kernel sets up and prefetches weights while the preceding kernel of the stream drains, and waits
+    for it before touching x or y): only when the weights were not written by the kernel directly before this call on the stream. Same bits either way."""
     _need_cuda(t16, x)
     if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != k:
         raise ValueError(f"x must be float16 [m, {k}], got {x.dtype} {tuple(x.shape)}")
@@ -92,15 +93,9 @@ def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float 
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
     L = _lib.lib()
     need = L.kyb_gemv_workspace_bytes(_fmt(fmt), n, k, m)
-    if TWO_LAUNCH if two_launch is None else two_launch:
-        ws = workspace(x.device, need) if need else None
-        _lib.check(L.kyb_gemv_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
-                                  ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream()))
-        return y
-    cb = L.kyb_gemv_counter_bytes(n) if need else 0
-    ws = workspace(x.device, need + cb, cb) if need else None
-    _lib.check(L.kyb_gemv_t16_fused(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
-                                    ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 1 if (PDL if pdl is None else pdl) else 0, _stream()))
+    ws = workspace(x.device, need) if need else None
+    _lib.check(L.kyb_gemv_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
+                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 1 if chained else 0, _stream()))
     return y
 
 
@@ -124,7 +119,7 @@ def gemv_plan(fmt, n: int, k: int, m: int) -> dict:
     import ctypes
     out = (ctypes.c_int * 8)()
     _lib.check(_lib.lib().kyb_gemv_plan(_fmt(fmt), n, k, m, out))
-    return dict(zip(("nt", "mst", "warps", "stages", "kbp", "ksplit", "smem", "grid"), list(out)))
+    return dict(zip(("nt", "aligned", "warps", "kc", "kbp", "ksplit", "smem", "grid"), list(out)))
 
 
 def check_device_status() -> None:

@@ -44,10 +44,10 @@ def test_size_helpers(lib):
 
 def test_argument_errors_are_reported_without_a_device(lib):
     # shape errors are detected before any CUDA call
-    assert lib.kyb_gemv_t16(0, None, 16, 100, None, 1, 100, 1.0, None, 16, None, 0, None) == _lib.EINVAL
+    assert lib.kyb_gemv_t16(0, None, 16, 100, None, 1, 100, 1.0, None, 16, None, 0, 0, None) == _lib.EINVAL
     assert b"multiple of 256" in lib.kyb_last_error()
-    assert lib.kyb_gemv_t16(7, None, 16, 256, None, 1, 256, 1.0, None, 16, None, 0, None) == _lib.EINVAL
-    assert lib.kyb_gemv_t16(0, None, 16, 256, None, 40, 256, 1.0, None, 16, None, 0, None) == _lib.EINVAL
+    assert lib.kyb_gemv_t16(7, None, 16, 256, None, 1, 256, 1.0, None, 16, None, 0, 0, None) == _lib.EINVAL
+    assert lib.kyb_gemv_t16(0, None, 16, 256, None, 40, 256, 1.0, None, 16, None, 0, 0, None) == _lib.EINVAL
     assert lib.kyb_dequant_t16(0, None, 16, 256, 0, 16, 1.0, 0, None, 256, None) == _lib.EINVAL
     with pytest.raises(_lib.KybError):
         _lib.check(lib.kyb_repack_raw_to_t16(0, None, 16, 256, None, None))

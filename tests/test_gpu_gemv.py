@@ -136,14 +136,19 @@ def test_full_size_properties(fmt, n, k):
     assert torch.equal(y2, y * 2)
 
 
-@pytest.mark.parametrize("fmt,n,k,m", [("q4_k", 512, 5120, 8), ("q6_k", 1024, 8192, 3), ("q4_k", 10240, 5120, 1)])
-def test_single_launch_reduction_equals_two_launch(fmt, n, k, m):
-    """Split-k sums reduced inside the kernel (with and without a programmatic dependent launch) == the finalize-kernel form, bit for bit, call after call."""
+@pytest.mark.parametrize("fmt,n,k,m", [("q4_k", 512, 5120, 8), ("q6_k", 1024, 8192, 3), ("q4_k", 10240, 5120, 1), ("q6_k", 5120, 27648, 8), ("q3_k", 48, 3072, 5)])
+def test_product_equals_exposed_partial_sums(fmt, n, k, m):
+    """The product == the two-step entry points whose chunk sums are all written out (mma_gemv.partial_mma) and added in k order (finalize_rows), bit for bit,
+    call after call, plain and chained launches, whichever way the library deals the work (whole row tiles per warp or runs of chunks)."""
+    from kyojin_mac_b200 import mma_gemv
+    from kyojin_mac_b200.foreign_linear import DevPack
     t16 = synth.t16_random_device(fmt, n, k, seed=3)
     g = torch.Generator(device="cuda").manual_seed(4)
+    dev = DevPack.from_t16(fmt, t16, n, k)
     for _ in range(3):
         x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
-        want = ops.gemv(fmt, t16, n, k, x, two_launch=True)
-        assert torch.equal(ops.gemv(fmt, t16, n, k, x, two_launch=False, pdl=False), want)
-        assert torch.equal(ops.gemv(fmt, t16, n, k, x, two_launch=False, pdl=True), want)
+        want = mma_gemv.finalize_rows(dev, mma_gemv.partial_mma(dev, x, m), m)
+        assert torch.equal(ops.gemv(fmt, t16, n, k, x), want)
+        assert torch.equal(ops.gemv(fmt, t16, n, k, x, chained=True), want)
+        assert torch.equal(ops.gemv(fmt, t16, n, k, x, chained=True), want)             # ... directly behind another chained product
     ops.check_device_status()
