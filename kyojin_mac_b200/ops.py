@@ -122,6 +122,11 @@ def gemv_plan(fmt, n: int, k: int, m: int) -> dict:
     return dict(zip(("nt", "aligned", "warps", "kc", "kbp", "ksplit", "smem", "grid"), list(out)))
 
 
+def gemv_workspace_bytes(fmt, n: int, k: int, m: int) -> int:
+    """Bytes of scratch the product needs (0: one launch; else chunk sums through the workspace and a finalize launch)."""
+    return int(_lib.lib().kyb_gemv_workspace_bytes(_fmt(fmt), n, k, m))
+
+
 def check_device_status() -> None:
     _lib.check(_lib.lib().kyb_check_device_status(_stream()))
 
