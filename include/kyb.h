@@ -81,6 +81,12 @@ size_t kyb_gemv_workspace_bytes(int fmt, int64_t n, int64_t k, int64_t m);
 int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
                  void* y, int64_t ldy, void* workspace, size_t workspace_bytes, int flags, void* stream);
 
+/* the same product on a gated input: the row fed to the product is fp16(silu(a[r]) * b[r]) (a, b fp16 [m, k] with one row stride ldx; fp32 arithmetic, saturated;
+ * limit > 0 clamps as kyb_silu_mul), formed while the rows are staged. Replaces kyojin_mlx/foreign_linear.py:960-977 `DevPack.apply_glu` (the reference folds the
+ * activation into the x staging of its down product the same way). Bit-identical to kyb_silu_mul followed by kyb_gemv_t16. */
+int kyb_gemv_glu_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* a, const void* b, float limit, int64_t m, int64_t ldx, float gscale,
+                     void* y, int64_t ldy, void* workspace, size_t workspace_bytes, int flags, void* stream);
+
 /* ---- prefill GEMM on tcgen05 (UMMA 128 x 256 x 16, kind::f16, fp32 accumulation in tensor memory), fp16 operands:
  * d [m, n] = sat_f16(gscale * a [m, k] b [n, k]^T), k % 64 == 0, lda / ldb / ldd in elements. Replaces the library matmul of the
  * reference's large-row path, kyojin_mlx/foreign_linear.py:710 and :737 (`x2 @ self.dequant().T`), which the reference takes for

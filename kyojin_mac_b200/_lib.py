@@ -120,6 +120,7 @@ SIGNATURES = {
     "kyb_dequant_t16": (_int, [_int, _vp, _i64, _i64, _i64, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_gemv_workspace_bytes": (_sz, [_int, _i64, _i64, _i64]),
     "kyb_gemv_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _int, _vp]),
+    "kyb_gemv_glu_t16": (_int, [_int, _vp, _i64, _i64, _vp, _vp, _f32, _i64, _i64, _f32, _vp, _i64, _vp, _sz, _int, _vp]),
     "kyb_gemv_chunks": (_int, [_i64, _i64]),
     "kyb_gemv_partial_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "kyb_gemv_finalize": (_int, [_vp, _int, _i64, _i64, _f32, _vp, _i64, _vp]),

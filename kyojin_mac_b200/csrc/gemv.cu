@@ -23,6 +23,7 @@ namespace kyb {
 struct GemvParams {
     const uint8_t* t16;
     const __half* x;
+    const __half* x2;        // gated input: the staged row is fp16(silu(x row) * x2 row) (same pitch), or null
     __half* y;
     float* partial;          // [nchunks][m][npad]: sums of the canonical k-chunks (form (b))
     unsigned int* status;
@@ -37,9 +38,11 @@ struct GemvParams {
     int aligned;             // warps take whole row tiles (no row tile is shared between warps); else runs of whole chunks
     int warps, stages;
     float gscale;
+    float limit;             // gated input: > 0 clamps as the activation kernel does
 };
 
-constexpr int SCL_BYTES = 16 * 16 * 4;   // per-warp scale scratch: 16 rows x 16 floats
+constexpr int SCL_STRIDE = 20;                // floats per row of the scale scratch: 16 used; a pitch of 80 bytes lets the 8 row groups of a warp load their 16-byte pieces without bank conflicts
+constexpr int SCL_BYTES = 16 * SCL_STRIDE * 4;   // per-warp scale scratch: 16 rows x 16 floats
 constexpr int GEMV_STAGES = 2;           // ring depth per warp: a stage is handed back as soon as its tile sits in registers, so two stages keep two copies in flight
 constexpr int GEMV_DSTAGES = 2;          // the same for the dense kernel (a four-stage ring measured 1-3 % slower on large matrices: the kernel is not limited by bytes in flight)
 
@@ -69,7 +72,7 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         o.y = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7441u)), dhi, nhi);
         o.z = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7442u)), dlo, nlo);
         o.w = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7443u)), dhi, nhi);
-        sts128f(scl + 4 * (r * 16 + 4 * hf), o);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 4 * hf), o);
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         const uint2 sw = lds64(tile + 3072 + r * 16 + 8 * hf);
         const float d = half_bits_to_float(lds16(tile + 3328 + r * 2));
@@ -82,8 +85,8 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         b.y = d * (float)(int)(int8_t)((sw.y >> 8) & 255u);
         b.z = d * (float)(int)(int8_t)((sw.y >> 16) & 255u);
         b.w = d * (float)(int)(int8_t)(sw.y >> 24);
-        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
-        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf), a);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf + 4), b);
     } else if constexpr (FMT == KYB_FMT_Q3_K) {
         const uint32_t sp = tile + 1536 + r * 12;
         const uint32_t w0 = lds32(sp), w1 = lds32(sp + 4), w2 = lds32(sp + 8);
@@ -99,8 +102,8 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         b.y = d * (float)((int)((gb >> 8) & 255u) - 32);
         b.z = d * (float)((int)((gb >> 16) & 255u) - 32);
         b.w = d * (float)((int)(gb >> 24) - 32);
-        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
-        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf), a);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf + 4), b);
     } else {
         const uint2 sw = lds64(tile + 2048 + r * 16 + 8 * hf);
         float4 a, b;                                                   // e2m1 operands carry 2^-14: fold 2^14 here
@@ -112,8 +115,8 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         b.y = e4m3_unsigned(sw.y >> 8) * 16384.0f;
         b.z = e4m3_unsigned(sw.y >> 16) * 16384.0f;
         b.w = e4m3_unsigned(sw.y >> 24) * 16384.0f;
-        sts128f(scl + 4 * (r * 16 + 8 * hf), a);
-        sts128f(scl + 4 * (r * 16 + 8 * hf + 4), b);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf), a);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf + 4), b);
     }
 }
 
@@ -122,14 +125,15 @@ struct Acc {
     float v[NT][4];
 };
 
-template <int NT>
+// ONE: a single activation row is staged (column 0 of the MMA), so the odd accumulator columns are never stored and need no arithmetic
+template <int NT, bool ONE>
 __device__ __forceinline__ void scale_acc(Acc<NT>& acc, const float (&c)[NT][4], float s_lo, float s_hi) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         acc.v[nt][0] = fmaf(s_lo, c[nt][0], acc.v[nt][0]);
-        acc.v[nt][1] = fmaf(s_lo, c[nt][1], acc.v[nt][1]);
+        if (!ONE) acc.v[nt][1] = fmaf(s_lo, c[nt][1], acc.v[nt][1]);
         acc.v[nt][2] = fmaf(s_hi, c[nt][2], acc.v[nt][2]);
-        acc.v[nt][3] = fmaf(s_hi, c[nt][3], acc.v[nt][3]);
+        if (!ONE) acc.v[nt][3] = fmaf(s_hi, c[nt][3], acc.v[nt][3]);
     }
 }
 
@@ -180,8 +184,8 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
     auto ldb = [&](int chunk, int nt) -> uint2 { return lds64(xb + chunk * CS + nt * MST * 32); };
     if constexpr (FMT == KYB_FMT_Q4_K) {
         // scales of rows g and g + 8 for the 8 sub-blocks
-        const float4 s0a = lds128f(scl + 4 * (g * 16)), s0b = lds128f(scl + 4 * (g * 16 + 4));
-        const float4 s1a = lds128f(scl + 4 * ((g + 8) * 16)), s1b = lds128f(scl + 4 * ((g + 8) * 16 + 4));
+        const float4 s0a = lds128f(scl + 4 * (g * SCL_STRIDE)), s0b = lds128f(scl + 4 * (g * SCL_STRIDE + 4));
+        const float4 s1a = lds128f(scl + 4 * ((g + 8) * SCL_STRIDE)), s1b = lds128f(scl + 4 * ((g + 8) * SCL_STRIDE + 4));
         const float sg[8] = {s0a.x, s0a.y, s0a.z, s0a.w, s0b.x, s0b.y, s0b.z, s0b.w};
         const float sh[8] = {s1a.x, s1a.y, s1a.z, s1a.w, s1b.x, s1b.y, s1b.z, s1b.w};
 #pragma unroll
@@ -207,8 +211,8 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
                     }
                 }
             }
-            scale_acc<NT>(acc, clo, sg[2 * G], sh[2 * G]);
-            scale_acc<NT>(acc, chi, sg[2 * G + 1], sh[2 * G + 1]);
+            scale_acc<NT, MST == 1>(acc, clo, sg[2 * G], sh[2 * G]);
+            scale_acc<NT, MST == 1>(acc, chi, sg[2 * G + 1], sh[2 * G + 1]);
         }
         // minus dmin * sum_j mn_j * (sum of x over sub-block j): an m16n8k8 product of the 6-bit mins with the staged sums (fp16 hi + lo)
         const uint32_t a0 = tr.a0, a1 = tr.a1;
@@ -219,9 +223,9 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
             mma1688_z(tt, a0, a1, lds32(xa + (0 * NT + nt) * 128));
             mma1688(tt, a0, a1, lds32(xa + (1 * NT + nt) * 128));
             acc.v[nt][0] = fmaf(-dmg, tt[0], acc.v[nt][0]);
-            acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
+            if (MST != 1) acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
             acc.v[nt][2] = fmaf(-dmh, tt[2], acc.v[nt][2]);
-            acc.v[nt][3] = fmaf(-dmh, tt[3], acc.v[nt][3]);
+            if (MST != 1) acc.v[nt][3] = fmaf(-dmh, tt[3], acc.v[nt][3]);
         }
     } else {
         uint4 hi = make_uint4(0, 0, 0, 0), hb = make_uint4(0, 0, 0, 0);
@@ -229,7 +233,7 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
 #pragma unroll
         for (int P = 0; P < 4; ++P) {
             // one scale per MMA slice s = 4 P + i
-            const float4 sg4 = lds128f(scl + 4 * (g * 16 + 4 * P)), sh4 = lds128f(scl + 4 * ((g + 8) * 16 + 4 * P));
+            const float4 sg4 = lds128f(scl + 4 * (g * SCL_STRIDE + 4 * P)), sh4 = lds128f(scl + 4 * ((g + 8) * SCL_STRIDE + 4 * P));
             const float sg[4] = {sg4.x, sg4.y, sg4.z, sg4.w}, sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
             uint4 u;
             if constexpr (FMT == KYB_FMT_Q6_K) {
@@ -289,9 +293,58 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
                     const uint2 b = ldb(s, nt);
                     mma16816_z(c[nt], a0, a1, a2, a3, b.x, b.y);
                 }
-                scale_acc<NT>(acc, c, sg[i], sh[i]);
+                scale_acc<NT, MST == 1>(acc, c, sg[i], sh[i]);
             }
         }
+    }
+}
+
+// fp16(silu(a) * b) on 8 values, the arithmetic of silu_mul_kernel (fp32, saturated)
+__device__ __forceinline__ uint4 glu8(const uint4 a, const uint4 b, const float limit) {
+    const __half* ah = reinterpret_cast<const __half*>(&a);
+    const __half* bh = reinterpret_cast<const __half*>(&b);
+    uint4 o;
+    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float av = __half2float(ah[j]), bv = __half2float(bh[j]);
+        if (limit > 0.f) av = fminf(av, limit), bv = fminf(fmaxf(bv, -limit), limit);
+        oh[j] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
+    }
+    return o;
+}
+
+// Single CTA: slots -> groups. counts per expert, groups per expert = ceil(count / 8), slot p of rank r inside its expert -> group start + r / 8.
+__global__ void moe_groups_kernel(const uint32_t* __restrict__ eids, int S, int E, uint32_t* __restrict__ g_expert, uint32_t* __restrict__ g_slots, uint32_t* __restrict__ ngroups) {
+    extern __shared__ uint32_t gsm[];
+    uint32_t* counts = gsm;          // [E]
+    uint32_t* gstart = gsm + E;      // [E + 1]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0u;
+    for (int i = threadIdx.x; i < S * 8; i += blockDim.x) g_slots[i] = 0xFFFFFFFFu;
+    __syncthreads();
+    for (int p = threadIdx.x; p < S; p += blockDim.x)
+        if (eids[p] < (uint32_t)E) atomicAdd(&counts[eids[p]], 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t g = 0;
+        for (int e = 0; e < E; ++e) {
+            gstart[e] = g;
+            g += (counts[e] + 7u) >> 3;
+        }
+        gstart[E] = g;
+        *ngroups = g;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        for (uint32_t g = gstart[e]; g < gstart[e + 1]; ++g) g_expert[g] = (uint32_t)e;
+        counts[e] = 0u;                                   // reused as the rank cursor
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < S; p += blockDim.x) {
+        const uint32_t e = eids[p];
+        if (e >= (uint32_t)E) continue;
+        const uint32_t r = atomicAdd(&counts[e], 1u);
+        g_slots[(size_t)(gstart[e] + (r >> 3)) * 8 + (r & 7u)] = (uint32_t)p;
     }
 }
 
@@ -363,7 +416,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
     // fp16 hi + lo and laid out as m16n8k8 B fragments (lane 4 g + t: sub-blocks 2t, 2t + 1 of row g).
     {
         const int items = nblk * 8 * NT * MST;
-        constexpr int U = 2;                                   // loads of U items are in flight together (x comes from L2)
+        constexpr int U = 4;                                   // loads of U items are in flight together (x comes from L2)
         for (int it0 = threadIdx.x; it0 < items; it0 += U * blockDim.x) {
             uint4 v[U][4];
 #pragma unroll
@@ -378,6 +431,11 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
                         const uint4* xp = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c2 * 32);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) v[u][q] = __ldg(xp + q);
+                        if (p.x2) {                                          // gated input: the activation is formed while the row is staged
+                            const uint4* xq = reinterpret_cast<const uint4*>(p.x2 + (size_t)m * p.ldx + (size_t)kb0 * 256 + (size_t)c2 * 32);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) v[u][q] = glu8(v[u][q], __ldg(xq + q), p.limit);
+                        }
                     }
                 }
             }
@@ -474,7 +532,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
             cleft = min(p.kc, nblk - j * p.kc);
         }
     };
-    static_assert(STAGES == 2, "the tile loop is unrolled over a two-stage ring");
+    static_assert(STAGES == 2, "the tile loop alternates the stages of a two-stage ring");
     int i = 0;
     for (; i + 1 < total; i += 2) {
         step(0);
@@ -508,55 +566,6 @@ struct GroupParams {
     int n, nb, kc, xdiv, rc, warps;   // rows per expert, k-blocks, canonical chunk, slot -> row divisor, row chunks per group, warps per CTA
     int S, E;
 };
-
-// fp16(silu(a) * b) on 8 values, the arithmetic of silu_mul_kernel (fp32, saturated)
-__device__ __forceinline__ uint4 glu8(const uint4 a, const uint4 b, const float limit) {
-    const __half* ah = reinterpret_cast<const __half*>(&a);
-    const __half* bh = reinterpret_cast<const __half*>(&b);
-    uint4 o;
-    __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        float av = __half2float(ah[j]), bv = __half2float(bh[j]);
-        if (limit > 0.f) av = fminf(av, limit), bv = fminf(fmaxf(bv, -limit), limit);
-        oh[j] = sat_half(av * (1.0f / (1.0f + expf(-av))) * bv);
-    }
-    return o;
-}
-
-// Single CTA: slots -> groups. counts per expert, groups per expert = ceil(count / 8), slot p of rank r inside its expert -> group start + r / 8.
-__global__ void moe_groups_kernel(const uint32_t* __restrict__ eids, int S, int E, uint32_t* __restrict__ g_expert, uint32_t* __restrict__ g_slots, uint32_t* __restrict__ ngroups) {
-    extern __shared__ uint32_t gsm[];
-    uint32_t* counts = gsm;          // [E]
-    uint32_t* gstart = gsm + E;      // [E + 1]
-    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0u;
-    for (int i = threadIdx.x; i < S * 8; i += blockDim.x) g_slots[i] = 0xFFFFFFFFu;
-    __syncthreads();
-    for (int p = threadIdx.x; p < S; p += blockDim.x)
-        if (eids[p] < (uint32_t)E) atomicAdd(&counts[eids[p]], 1u);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t g = 0;
-        for (int e = 0; e < E; ++e) {
-            gstart[e] = g;
-            g += (counts[e] + 7u) >> 3;
-        }
-        gstart[E] = g;
-        *ngroups = g;
-    }
-    __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        for (uint32_t g = gstart[e]; g < gstart[e + 1]; ++g) g_expert[g] = (uint32_t)e;
-        counts[e] = 0u;                                   // reused as the rank cursor
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < S; p += blockDim.x) {
-        const uint32_t e = eids[p];
-        if (e >= (uint32_t)E) continue;
-        const uint32_t r = atomicAdd(&counts[e], 1u);
-        g_slots[(size_t)(gstart[e] + (r >> 3)) * 8 + (r & 7u)] = (uint32_t)p;
-    }
-}
 
 template <int FMT>
 __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p) {
@@ -805,17 +814,13 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     const int kc = canonical_chunk(ntiles, nb), nchunks = (nb + kc - 1) / kc;
     const int v = variant_of(m), nt = VAR_NT[v], mst = VAR_MST[v];
     const int max_warps = nt <= 2 ? 12 : 8;                            // measured: 13 to 16 warps per SM are slower than 10 to 12 on every shape
-    const int fw = getenv("KYB_TMP_WARPS") ? atoi(getenv("KYB_TMP_WARPS")) : 0, fk = getenv("KYB_TMP_KSPLIT") ? atoi(getenv("KYB_TMP_KSPLIT")) : 0;   // TMPSWEEP
-    const int fa = getenv("KYB_TMP_ALIGNED") ? atoi(getenv("KYB_TMP_ALIGNED")) : -1;   // TMPSWEEP
     GemvPlan best{};
     double best_score = -1.0;
     for (int ksplit = 1; ksplit <= std::min(nchunks, sms); ++ksplit) {
         const int cpp = (nchunks + ksplit - 1) / ksplit;
         if ((nchunks + cpp - 1) / cpp != ksplit) continue;               // one representative per distinct split
-        if (fk && ksplit != fk) continue;   // TMPSWEEP
         const int kbp = std::min(nb, cpp * kc), grid = sms / ksplit * ksplit;
         for (int warps = 4; warps <= max_warps; ++warps) {
-            if (fw && warps != fw) continue;   // TMPSWEEP
             const size_t smem = plan_smem(fmt, nt, mst, kbp, warps, kyb::GEMV_DSTAGES);
             if (smem > smem_cap) continue;
             const double wp = (double)(grid / ksplit) * warps;                                  // warps of a part
@@ -823,7 +828,6 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
             const double occupancy = warps >= 10 ? 1.0 : warps == 9 ? 0.97 : warps == 8 ? 0.9 : 0.6 + 0.04 * warps;
             const double common = parts * ((double)grid / sms) * occupancy * (1.0 - 0.02 * (ksplit - 1));
             for (int aligned = 0; aligned < 2; ++aligned) {
-                if (fa >= 0 && aligned != fa) continue;   // TMPSWEEP
                 const double upw = aligned ? ntiles / wp : (double)ntiles * cpp / wp;           // row tiles or units per warp
                 const double balance = upw / std::ceil(upw);
                 const double shared = aligned && ksplit == 1 ? 1.0 : 0.9;                       // cost of the workspace round trip and the finalize launch
@@ -831,7 +835,7 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
                 if (score > best_score) best_score = score, best = GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, kbp, ksplit, grid, smem, kc, nchunks, cpp, aligned};
             }
         }
-        if (best_score > 0 && !fk) break;                                 // the smallest split that fits
+        if (best_score > 0) break;                                        // the smallest split that fits
     }
     return best;
 }
@@ -892,10 +896,10 @@ int check_gemv_args(int fmt, const void* t16, int64_t n, int64_t k, const void* 
 
 // the GEMV kernel and, in form (b), the finalize kernel behind it. partial: scratch for the chunk sums (form (b)); y == nullptr: chunk sums only
 int launch_gemv(int fmt, const GemvPlan& pl, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale, void* y, int64_t ldy,
-                float* partial, unsigned int* status, bool chained, cudaStream_t st) {
+                float* partial, unsigned int* status, bool chained, cudaStream_t st, const void* x2 = nullptr, float limit = 0.f) {
     const bool sums_only = y == nullptr, staged = sums_only || two_step(pl);
     kyb::GemvParams p;
-    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.y = (__half*)y, p.partial = partial, p.status = status;
+    p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.x2 = (const __half*)x2, p.limit = limit, p.y = (__half*)y, p.partial = partial, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = (int)((n + 15) / 16 * 16), p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
     p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.cpp = pl.cpp, p.aligned = pl.aligned;
     p.partial_only = staged ? 1 : 0, p.pdl = chained ? 1 : 0;
@@ -944,6 +948,26 @@ extern "C" int kyb_gemv_t16(int fmt, const void* t16, int64_t n, int64_t k, cons
     unsigned int* status = kyb_device_status_word();
     KYB_REQUIRE(status, "could not set up the device status word");
     return launch_gemv(fmt, pl, t16, n, k, x, m, ldx, gscale, y, ldy, (float*)workspace, status, (flags & KYB_GEMV_CHAINED) != 0, (cudaStream_t)stream);
+}
+
+// The same product on a gated input: row r fed to the product is fp16(silu(a[r]) * b[r]) (fp32 arithmetic, saturated, optional clamp), formed while the rows are
+// staged, so the activation kernel and its round trip through HBM disappear. Replaces kyojin_mlx/foreign_linear.py:960-977 `DevPack.apply_glu`.
+extern "C" int kyb_gemv_glu_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* a, const void* b, float limit, int64_t m, int64_t ldx, float gscale, void* y,
+                                int64_t ldy, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+    if (int rc = check_gemv_args(fmt, t16, n, k, a, m, ldx)) return rc;
+    KYB_REQUIRE(b && ((uintptr_t)b & 15) == 0, "b is null or not 16-byte aligned");
+    KYB_REQUIRE(y && ldy >= n, "y is null or ldy=%lld < n", (long long)ldy);
+    KYB_REQUIRE((flags & ~KYB_GEMV_CHAINED) == 0, "unknown flags 0x%x", flags);
+    const GemvPlan pl = make_plan(fmt, n, k, m);
+    KYB_REQUIRE(pl.warps > 0, "no launch configuration fits shared memory for k=%lld m=%lld", (long long)k, (long long)m);
+    const size_t need = two_step(pl) ? partial_bytes(pl, n, m) : 0;
+    if (need && (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15))) {
+        kyb_set_error("gemv needs %zu bytes of 16-byte aligned workspace, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+        return KYB_EWORKSPACE;
+    }
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    return launch_gemv(fmt, pl, t16, n, k, a, m, ldx, gscale, y, ldy, (float*)workspace, status, (flags & KYB_GEMV_CHAINED) != 0, (cudaStream_t)stream, b, limit);
 }
 
 // Two-step form with the partial sums exposed (chunk sums, then finalize): the call shape of the reference's few-row MMA GEMV,

@@ -209,7 +209,13 @@ class DevPack:
         return ops.gemv_group(self.fmt, self.t16, self.n, self.k, self.E, a, eids, xrows=xrows, gs=self._gs(), groups=groups, x2=b, limit=limit)
 
     def apply_glu(self, a, b, limit=None):
-        """One matrix on the gated input silu(a) * b (foreign_linear.py:960-977)."""
+        """One matrix on the gated input silu(a) * b (foreign_linear.py:960-977). Up to the decode row limit the activation is formed while the down product
+        stages its rows (one launch, no round trip of the gated rows through HBM); more rows run the activation kernel and then the prefill product."""
+        if self.E:
+            raise ValueError("apply_glu() is for one matrix")
+        if 0 < a.shape[0] <= F.GEMV_ROWS and a.dtype == torch.float16 and b.dtype == torch.float16:
+            chained, self._settled = F.GEMV_CHAINED and getattr(self, "_settled", False), True
+            return ops.gemv(self.fmt, self.t16, self.n, self.k, a, self.gscale, chained=chained, x2=b, limit=limit)
         return self.apply(ops.silu_mul(a, b, limit))
 
     def expert(self, e: int) -> "DevPack":

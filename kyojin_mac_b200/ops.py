@@ -80,22 +80,33 @@ def release_workspaces(stream_id: int | None = None) -> None:
         del _ws[key]
 
 
-def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, chained: bool = False) -> torch.Tensor:
+def gemv(fmt, t16: torch.Tensor, n: int, k: int, x: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, chained: bool = False,
+         x2: torch.Tensor | None = None, limit: float | None = None) -> torch.Tensor:
     """y fp16 [m, n] = x fp16 [m, k] @ W^T for m <= 32, W in T16.
     chained: launch with programmatic stream serialization (the kernel sets up and prefetches weights while the preceding kernel of the stream drains, and waits
-    for it before touching x or y): only when the weights were not written by the kernel directly before this call on the stream. Same bits either way."""
-    _need_cuda(t16, x)
+    for it before touching x or y): only when the weights were not written by the kernel directly before this call on the stream. Same bits either way.
+    x2: gated input, the row fed to the product is fp16(silu(x row) * x2 row), formed while the rows are staged (optional clamp `limit`)."""
+    _need_cuda(t16, x, x2)
     if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != k:
         raise ValueError(f"x must be float16 [m, {k}], got {x.dtype} {tuple(x.shape)}")
     if x.stride(1) != 1:
         x = x.contiguous()
+    if x2 is not None:
+        if x2.dtype != torch.float16 or x2.shape != x.shape:
+            raise ValueError("the gated form takes two float16 tensors of one shape")
+        if x2.stride() != x.stride():
+            x, x2 = x.contiguous(), x2.contiguous()
     m = x.shape[0]
     y = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=x.device)
     L = _lib.lib()
     need = L.kyb_gemv_workspace_bytes(_fmt(fmt), n, k, m)
     ws = workspace(x.device, need) if need else None
-    _lib.check(L.kyb_gemv_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
-                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, 1 if chained else 0, _stream()))
+    wp, wn = (ws.data_ptr(), ws.numel()) if ws is not None else (None, 0)
+    if x2 is not None:
+        _lib.check(L.kyb_gemv_glu_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), x2.data_ptr(), float(limit or 0.0), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0),
+                                      wp, wn, 1 if chained else 0, _stream()))
+        return y
+    _lib.check(L.kyb_gemv_t16(_fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), m, x.stride(0), float(gscale), y.data_ptr(), y.stride(0), wp, wn, 1 if chained else 0, _stream()))
     return y
 
 

@@ -152,3 +152,21 @@ def test_product_equals_exposed_partial_sums(fmt, n, k, m):
         assert torch.equal(ops.gemv(fmt, t16, n, k, x, chained=True), want)
         assert torch.equal(ops.gemv(fmt, t16, n, k, x, chained=True), want)             # ... directly behind another chained product
     ops.check_device_status()
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [("q6_k", 512, 2048, 1), ("q4_k", 4096, 1024, 7), ("q4_k", 640, 5120, 20)])
+def test_gated_input_formed_while_staging(fmt, n, k, m):
+    """DevPack.apply_glu on decode rows: the activation fp16(silu(a) * b) is formed inside the product's staging. Equal, bit for bit, to the plain product on the
+    output of the activation kernel (another kernel; that one agrees with the numpy restatement of the activation to one fp16 step: the device and the host
+    exponential may differ in the last place), with and without the clamp."""
+    from kyojin_mac_b200.foreign_linear import DevPack
+    from oracle import moe_numpy as M
+    dev = DevPack.from_t16(fmt, synth.t16_random_device(fmt, n, k, seed=8), n, k)
+    rng = np.random.default_rng(m)
+    a, b = synth.activations(m, k, rng), synth.activations(m, k, rng)
+    ad, bd = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    for limit in (None, 0.75):
+        h = ops.silu_mul(ad, bd, limit)
+        np.testing.assert_allclose(h.float().cpu().numpy(), M.glu(a, b, limit).astype(np.float32), rtol=1.1e-3, atol=1e-7)
+        assert torch.equal(dev.apply_glu(ad, bd, limit), dev.apply(h)), limit
+    ops.check_device_status()
