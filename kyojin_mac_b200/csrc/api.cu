@@ -68,12 +68,12 @@ int kyb_check_device_status(void* stream) {
 }
 
 size_t kyb_t16_nbytes(int fmt, int64_t n, int64_t k) {
-    if (fmt < 0 || fmt > 3 || n <= 0 || k <= 0 || k % 256) return 0;
+    if (fmt < 0 || fmt >= KYB_FMT_COUNT || n <= 0 || k <= 0 || k % 256) return 0;
     return (size_t)((n + 15) / 16) * (size_t)(k / 256) * (size_t)kyb_tile_bytes(fmt);
 }
 
 size_t kyb_raw_row_bytes(int fmt, int64_t k) {
-    if (fmt < 0 || fmt > 3 || k <= 0 || k % kyb_raw_block_elems(fmt)) return 0;
+    if (fmt < 0 || fmt >= KYB_FMT_COUNT || k <= 0 || k % kyb_raw_block_elems(fmt)) return 0;
     return (size_t)(k / kyb_raw_block_elems(fmt)) * (size_t)kyb_raw_block_bytes(fmt);
 }
 

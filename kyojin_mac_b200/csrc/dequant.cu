@@ -79,7 +79,7 @@ static void launch_dequant(const uint8_t* t16, int64_t n, int64_t nb, int64_t rt
 
 extern "C" int kyb_dequant_t16(int fmt, const void* t16, int64_t n, int64_t k, int64_t row0, int64_t nrows, float gscale, int out_dtype, void* out,
                                int64_t ld, void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
     KYB_REQUIRE(t16 && out, "null pointer");
     KYB_REQUIRE(out_dtype == KYB_DT_F32 || out_dtype == KYB_DT_F16, "out_dtype %d is neither KYB_DT_F32 nor KYB_DT_F16", out_dtype);
@@ -95,6 +95,8 @@ extern "C" int kyb_dequant_t16(int fmt, const void* t16, int64_t n, int64_t k, i
         case KYB_FMT_Q4_K: launch_dequant<KYB_FMT_Q4_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q6_K: launch_dequant<KYB_FMT_Q6_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q3_K: launch_dequant<KYB_FMT_Q3_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_Q5_K: launch_dequant<KYB_FMT_Q5_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_Q8_0: launch_dequant<KYB_FMT_Q8_0>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         default: launch_dequant<KYB_FMT_NVFP4>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
     }
     return kyb_launch_check("dequant_t16");
@@ -110,7 +112,7 @@ static void launch_dequant_rows(const uint8_t* t16, int64_t n, int64_t nb, const
 
 extern "C" int kyb_dequant_rows_t16(int fmt, const void* t16, int64_t n, int64_t k, const void* rows, int64_t nrows, float gscale, int out_dtype, void* out, int64_t ld,
                                     void* stream) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: k must be a positive multiple of 256", (long long)n, (long long)k);
     KYB_REQUIRE(t16 && rows && out, "null pointer");
     KYB_REQUIRE(out_dtype == KYB_DT_F32 || out_dtype == KYB_DT_F16, "out_dtype %d is neither KYB_DT_F32 nor KYB_DT_F16", out_dtype);
@@ -125,6 +127,8 @@ extern "C" int kyb_dequant_rows_t16(int fmt, const void* t16, int64_t n, int64_t
         case KYB_FMT_Q4_K: launch_dequant_rows<KYB_FMT_Q4_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q6_K: launch_dequant_rows<KYB_FMT_Q6_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q3_K: launch_dequant_rows<KYB_FMT_Q3_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_Q5_K: launch_dequant_rows<KYB_FMT_Q5_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_Q8_0: launch_dequant_rows<KYB_FMT_Q8_0>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         default: launch_dequant_rows<KYB_FMT_NVFP4>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
     }
     return kyb_launch_check("dequant_rows_t16");

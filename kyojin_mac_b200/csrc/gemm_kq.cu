@@ -628,6 +628,10 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
                     int64_t col0, int msub, void* stream) {
+    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0) {
+        kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
+        return KYB_EUNSUPPORTED;
+    }
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
@@ -700,6 +704,10 @@ extern "C" int kyb_gemm_kq_ag(int fmt, const void* t16, int64_t n, int64_t k, co
 extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
                                    const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream) {
     KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
+    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0) {
+        kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
+        return KYB_EUNSUPPORTED;
+    }
     KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
     KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,

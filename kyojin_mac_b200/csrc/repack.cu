@@ -17,6 +17,11 @@ __device__ __forceinline__ uint32_t raw_code(const uint8_t* blk, int e) {
     } else if (FMT == KYB_FMT_Q3_K) {                // input 128H + 32j + l: qs[32H + l] bits 2j, hmask[l] bit 4H + j
         const int H = e >> 7, j = (e >> 5) & 3, l = e & 31;
         return ((blk[32 + 32 * H + l] >> (2 * j)) & 3u) | (((blk[l] >> (4 * H + j)) & 1u) << 2);
+    } else if (FMT == KYB_FMT_Q5_K) {                // as Q4_K behind the 32 bytes of high bits: bit e / 32 of qh[e % 32]
+        const uint32_t byte = blk[48 + (e >> 6) * 32 + (e & 31)];
+        return ((e & 32) ? (byte >> 4) : (byte & 15u)) | (((blk[16 + (e & 31)] >> (e >> 5)) & 1u) << 4);
+    } else if (FMT == KYB_FMT_Q8_0) {                // eight 34-byte blocks: fp16 d, 32 int8
+        return blk[34 * (e >> 5) + 2 + (e & 31)];
     } else {                                         // 64-block B, 16-sub-block u, l: byte 4 + 8u + (l & 7), nibble l >> 3
         const int B = e >> 6, u = (e >> 4) & 3, l = e & 15;
         const uint32_t byte = blk[36 * B + 4 + 8 * u + (l & 7)];
@@ -27,7 +32,7 @@ __device__ __forceinline__ uint32_t raw_code(const uint8_t* blk, int e) {
 template <int FMT>
 __global__ void raw_to_t16_kernel(const uint8_t* __restrict__ raw, int64_t n, int64_t nb, uint8_t* __restrict__ t16, int64_t total_words) {
     constexpr int TB = kyb_tile_bytes(FMT), TW = TB / 4;
-    constexpr int RB = (FMT == KYB_FMT_NVFP4) ? 144 : kyb_raw_block_bytes(FMT);      // stored bytes of one 256-input block
+    constexpr int RB = kyb_raw_kblock_bytes(FMT);                                     // stored bytes of one 256-input block
     const int64_t gw = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gw >= total_words) return;
     const int64_t tile = gw / TW;
@@ -108,6 +113,39 @@ __global__ void raw_to_t16_kernel(const uint8_t* __restrict__ raw, int64_t n, in
                 if (b) out |= ((uint32_t)b[108] | ((uint32_t)b[109] << 8)) << (16 * q);
             }
         }
+    } else if (FMT == KYB_FMT_Q5_K) {
+        if (wi < 512) {                              // nibble plane (low 4 bits of the code): s0 = 4P + 2a, s1 = s0 + 1
+            unit(wi, P, g, t, a, h);
+            const uint8_t* b = blk_of(g + 8 * h);
+            if (b)
+                for (int i = 0; i < 4; ++i) {
+                    const int e0 = 16 * (4 * P + 2 * a) + 4 * t + i;
+                    out |= ((raw_code<FMT>(b, e0) & 15u) | ((raw_code<FMT>(b, e0 + 16) & 15u) << 4)) << (8 * i);
+                }
+        } else if (wi < 640) {                       // 1-bit plane (the fifth bit): s = 8a + i8
+            unit(wi - 512, P, g, t, a, h);
+            const uint8_t* b = blk_of(g + 8 * h);
+            if (b)
+                for (int i = 0; i < 4; ++i)
+                    for (int i8 = 0; i8 < 8; ++i8) out |= (raw_code<FMT>(b, 16 * (8 * a + i8) + 4 * t + i) >> 4) << (8 * i + i8);
+        } else {                                     // d, dmin, 12 scale bytes of every row
+            const int r = (wi - 640) >> 2, w = (wi - 640) & 3;
+            const uint8_t* b = blk_of(r);
+            if (b)
+                for (int i = 0; i < 4; ++i) out |= (uint32_t)b[4 * w + i] << (8 * i);
+        }
+    } else if (FMT == KYB_FMT_Q8_0) {
+        if (wi < 1024) {                             // byte plane: unit P holds slices 2P (a = 0) and 2P + 1 (a = 1)
+            unit(wi, P, g, t, a, h);
+            const uint8_t* b = blk_of(g + 8 * h);
+            if (b)
+                for (int i = 0; i < 4; ++i) out |= raw_code<FMT>(b, 16 * (2 * P + a) + 4 * t + i) << (8 * i);
+        } else {                                     // eight fp16 d per row, two per word
+            const int r = (wi - 1024) >> 2, w = (wi - 1024) & 3;
+            const uint8_t* b = blk_of(r);
+            if (b)
+                for (int q = 0; q < 2; ++q) out |= ((uint32_t)b[34 * (2 * w + q)] | ((uint32_t)b[34 * (2 * w + q) + 1] << 8)) << (16 * q);
+        }
     } else {
         if (wi < 512) {                              // bit-sliced e2m1 codes
             unit(wi, P, g, t, a, h);
@@ -133,7 +171,7 @@ __global__ void raw_to_t16_kernel(const uint8_t* __restrict__ raw, int64_t n, in
 template <int FMT>
 __global__ void t16_to_raw_kernel(const uint8_t* __restrict__ t16, int64_t n, int64_t nb, uint8_t* __restrict__ raw, int64_t total_bytes) {
     constexpr int TB = kyb_tile_bytes(FMT);
-    constexpr int RB = (FMT == KYB_FMT_NVFP4) ? 144 : kyb_raw_block_bytes(FMT);
+    constexpr int RB = kyb_raw_kblock_bytes(FMT);
     const int64_t gb = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (gb >= total_bytes) return;
     const int64_t blk = gb / RB;
@@ -165,6 +203,17 @@ __global__ void t16_to_raw_kernel(const uint8_t* __restrict__ t16, int64_t n, in
             for (int j = 0; j < 4; ++j) out |= (tile_code<FMT>(tile, r, 128 * H + 32 * j + l) & 3u) << (2 * j);
         } else if (o < 108) out = tile[1536 + r * 12 + (o - 96)];
         else out = tile[1728 + r * 2 + (o - 108)];
+    } else if (FMT == KYB_FMT_Q5_K) {
+        if (o < 16) out = tile[2560 + r * 16 + o];
+        else if (o < 48) {
+            for (int i = 0; i < 8; ++i) out |= (tile_code<FMT>(tile, r, 32 * i + (o - 16)) >> 4) << i;
+        } else {
+            const int G = (o - 48) >> 5, l = (o - 48) & 31;
+            out = (tile_code<FMT>(tile, r, 64 * G + l) & 15u) | ((tile_code<FMT>(tile, r, 64 * G + 32 + l) & 15u) << 4);
+        }
+    } else if (FMT == KYB_FMT_Q8_0) {
+        const int B = o / 34, p = o % 34;
+        out = p < 2 ? tile[4096 + r * 16 + 2 * B + p] : tile_code<FMT>(tile, r, 32 * B + p - 2);
     } else {
         const int B = o / 36, p = o % 36;
         if (p < 4) out = tile[2048 + r * 16 + 4 * B + p];
@@ -180,7 +229,7 @@ __global__ void t16_to_raw_kernel(const uint8_t* __restrict__ t16, int64_t n, in
 }  // namespace kyb
 
 static int check_fmt_shape(int fmt, int64_t n, int64_t k) {
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(n > 0 && k > 0 && k % 256 == 0, "n=%lld k=%lld: n must be positive and k a positive multiple of 256", (long long)n, (long long)k);
     return KYB_OK;
 }
@@ -199,6 +248,8 @@ extern "C" int kyb_repack_raw_to_t16(int fmt, const void* raw, int64_t n, int64_
         case KYB_FMT_Q4_K: kyb::raw_to_t16_kernel<KYB_FMT_Q4_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q6_K: kyb::raw_to_t16_kernel<KYB_FMT_Q6_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q3_K: kyb::raw_to_t16_kernel<KYB_FMT_Q3_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
+        case KYB_FMT_Q5_K: kyb::raw_to_t16_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
+        case KYB_FMT_Q8_0: kyb::raw_to_t16_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         default: kyb::raw_to_t16_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
     }
     return kyb_launch_check("raw_to_t16");
@@ -218,6 +269,8 @@ extern "C" int kyb_repack_t16_to_raw(int fmt, const void* t16, int64_t n, int64_
         case KYB_FMT_Q4_K: kyb::t16_to_raw_kernel<KYB_FMT_Q4_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q6_K: kyb::t16_to_raw_kernel<KYB_FMT_Q6_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q3_K: kyb::t16_to_raw_kernel<KYB_FMT_Q3_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
+        case KYB_FMT_Q5_K: kyb::t16_to_raw_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
+        case KYB_FMT_Q8_0: kyb::t16_to_raw_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         default: kyb::t16_to_raw_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
     }
     return kyb_launch_check("t16_to_raw");

@@ -61,6 +61,12 @@ __device__ __forceinline__ uint32_t tile_code(const uint8_t* tile, int r, int e)
         const uint32_t lb = tile[((s >> 3) * 32 + L) * 16 + (2 * ((s >> 2) & 1) + h) * 4 + b];
         const uint32_t hb = tile[1024 + L * 16 + (2 * (s >> 3) + h) * 4 + b];
         return ((lb >> (2 * (s & 3))) & 3u) | (((hb >> (s & 7)) & 1u) << 2);
+    } else if (FMT == KYB_FMT_Q5_K) {
+        const uint32_t nb = tile[((s >> 2) * 32 + L) * 16 + (2 * ((s >> 1) & 1) + h) * 4 + b];
+        const uint32_t hb = tile[2048 + L * 16 + (2 * (s >> 3) + h) * 4 + b];
+        return ((s & 1) ? (nb >> 4) : (nb & 15u)) | (((hb >> (s & 7)) & 1u) << 4);
+    } else if (FMT == KYB_FMT_Q8_0) {
+        return tile[((s >> 1) * 32 + L) * 16 + (2 * (s & 1) + h) * 4 + b];
     } else {
         const uint32_t word = ldw(tile + ((s >> 2) * 32 + L) * 16 + (2 * ((s >> 1) & 1) + h) * 4);
         const int v = 2 * (s & 1) + (b & 1), j = b >> 1;
@@ -124,6 +130,31 @@ struct TileDecode<KYB_FMT_Q3_K> {
             const int q = (int)((lb >> (2 * (s & 3))) & 3u) - (((hb >> (s & 7)) & 1u) ? 0 : 4);
             w[b] = __fmul_rn(dl, (float)q);
         }
+    }
+};
+
+template <>
+struct TileDecode<KYB_FMT_Q5_K> {
+    // w[b] = (d * sc) * q - dmin * mn, q = 4-bit code | high bit << 4 (kyojin_mlx/foreign_gguf.py:470-480)
+    static __device__ __forceinline__ void row4(const uint8_t* tile, int g, int t, int h, int s, float gscale, float (&w)[4]) {
+        const uint8_t* meta = tile + 2560 + (g + 8 * h) * 16;
+        const float d = ldh(meta), dmin = ldh(meta + 2);
+        int sc, mn;
+        q4k_scale_min(meta + 4, s >> 1, sc, mn);
+        const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) w[b] = __fsub_rn(__fmul_rn(ds, (float)tile_code<KYB_FMT_Q5_K>(tile, g + 8 * h, 16 * s + 4 * t + b)), dm);
+    }
+};
+
+template <>
+struct TileDecode<KYB_FMT_Q8_0> {
+    // w[b] = q * d with one fp16 d per 32 inputs (kyojin_mlx/foreign_gguf.py:447-448)
+    static __device__ __forceinline__ void row4(const uint8_t* tile, int g, int t, int h, int s, float gscale, float (&w)[4]) {
+        const int r = g + 8 * h;
+        const float d = ldh(tile + 4096 + r * 16 + (s >> 1) * 2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) w[b] = __fmul_rn((float)(int)(int8_t)tile_code<KYB_FMT_Q8_0>(tile, r, 16 * s + 4 * t + b), d);
     }
 };
 

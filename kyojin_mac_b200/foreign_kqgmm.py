@@ -1,8 +1,8 @@
 """Expert-grouped GEMM on routed slots (prefill), torch mirror of kyojin_mlx/foreign_kqgmm.py: `csort` :191-196, `plan` :210-216, `gmm` :225-239,
 `gather_perm` :264-268, `silu_perm` :283-290, `mlp` :293-314, `dense` :343-354. Slots are sorted by expert on the device (no host readback), tiles of MT
 rows of ONE expert run on tcgen05 (kyb_gemm_f16_grouped), the down projection scatters its rows back to slot order.
-The weights reach the tensor cores as fp16 tiles of the dequantised stack (the reference decodes inside its NAX kernel; here the decode is a separate
-pass over the stack, fused decode is the planned next step)."""
+The weights are decoded from their T16 tiles inside the grouped GEMM (kyb_gemm_kq_grouped; no fp16 copy of the stack in HBM), as the reference decodes
+inside its own grouped kernel; formats without a fused decoder and stacks with n % 256 != 0 take the staged form (fp16 copy of the stack, kyb_gemm_f16_grouped)."""
 from __future__ import annotations
 
 import torch
@@ -16,7 +16,8 @@ MT_FUSED = 256               # rows of one expert per work item when the weights
 
 def fused_ok(dev) -> bool:
     """The expert stack can go through the grouped GEMM that decodes its T16 tiles in the kernel."""
-    return dev.n % 256 == 0 and not F.PREFILL_TWO_STEP
+    from .layout import PREFILL_FUSED
+    return dev.n % 256 == 0 and not F.PREFILL_TWO_STEP and dev.fmt in PREFILL_FUSED
 
 
 def csort(e32: torch.Tensor, E: int, mt: int = MT):

@@ -132,7 +132,8 @@ class DevPack:
         """Prefill: one tcgen05 GEMM whose weight operand is decoded from the T16 tiles inside the kernel (fp16 weights in shared memory only, fp32
         accumulation); role of the reference's large-row path (foreign_linear.py:710 `x2 @ self.dequant().T`). The NVFP4 per-tensor scale is applied to the
         fp32 accumulator, not folded into the fp16 weights. KYB_PREFILL_TWO_STEP=1 runs the staged form instead (fp16 matrix in HBM, then the fp16 GEMM)."""
-        if F.PREFILL_TWO_STEP:
+        from .layout import PREFILL_FUSED
+        if F.PREFILL_TWO_STEP or self.fmt not in PREFILL_FUSED:
             return self._prefill_two_step(x2)
         return ops.gemm_kq(self.fmt, self.t16, self.n, self.k, x2, self.gscale)
 

@@ -26,16 +26,20 @@ Tile contents (offsets in bytes; "word(P, L, i)" = 32-bit word i of the 16-byte 
                     carry the first/second input of the pairs (4t, 4t+2) [v0], (4t+1, 4t+3) [v1] of MMA s0 = 4P+2p and the same of s1 [v2, v3];
                     magnitude bits of v0..v3 at [11:9], [8:6], [5:3], [2:0], sign bits at 15, 12, 13, 14
         [2048,2304) row r: 16 e4m3 scale bytes (one per 16 inputs)
+  q5_k  [0,2048)    the low 4 bits of the 5-bit codes as the q6_k nibble plane   [2048,2560) the fifth bits as the q3_k 1-bit plane
+        [2560,2816) row r: the first 16 stored bytes of its block (d, dmin, 12 bytes of 6-bit scales/mins)
+  q8_0  [0,4096)    word(P, L, 2p+h): byte b = the int8 of input 16 (2P + p) + 4t + b       [4096,4352) row r: the eight fp16 d of its 32-input blocks
 """
 from __future__ import annotations
 
 import numpy as np
 
-FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4")
-FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3}
-TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304}
-RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36)}     # GGUF block elements / bytes
-GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4"}
+FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0")
+FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5}
+TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352}
+RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34)}     # GGUF block elements / bytes
+GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0"}
+PREFILL_FUSED = ("q4_k", "q6_k", "q3_k", "nvfp4")       # formats the prefill GEMM decodes inside the kernel; the others are decoded to fp16 first
 ROWS = 16
 KBLOCK = 256
 
@@ -186,6 +190,44 @@ def _q6k_from_codes(q, B):
     B[..., 128:192] = qh.reshape(q.shape[:-3] + (64,))
 
 
+def _byte_plane(c):
+    """c uint8 [nrt, nb, h, g, 256] (8-bit fields, natural input order) -> bytes [nrt, nb, 4096]."""
+    a = c.reshape(c.shape[:4] + (8, 2, 4, 4))                              # P, p, t, b   (s = 2P + p)
+    out = a.transpose(0, 1, 4, 3, 6, 5, 2, 7)                               # P, g, t, p, h, b
+    return np.ascontiguousarray(out).reshape(out.shape[:2] + (4096,))
+
+
+def _byte_plane_inv(plane):
+    a = plane.reshape(plane.shape[:2] + (8, 8, 4, 2, 2, 4))                # P, g, t, p, h, b
+    a = a.transpose(0, 1, 6, 3, 2, 5, 4, 7)                                 # h, g, P, p, t, b
+    return np.ascontiguousarray(a).reshape(a.shape[:4] + (256,))
+
+
+def _q5k_codes(B):
+    """[.., 176] -> 5-bit codes [.., 256] in natural input order: element 64G + 32u + l = nibble u of qs[32G + l] | bit 2G + u of qh[l] << 4
+    (kyojin_mlx/foreign_gguf.py:470-478)."""
+    qh = B[..., 16:48]
+    qs = B[..., 48:176].reshape(B.shape[:-1] + (4, 32))
+    q = np.empty(B.shape[:-1] + (4, 2, 32), np.uint8)
+    for G in range(4):
+        for u in range(2):
+            nib = (qs[..., G, :] >> 4) if u else (qs[..., G, :] & 15)
+            q[..., G, u, :] = nib | (((qh >> (2 * G + u)) & 1) << 4)
+    return q.reshape(B.shape[:-1] + (256,))
+
+
+def _q5k_from_codes(q, B):
+    q = q.reshape(q.shape[:-1] + (4, 2, 32))
+    qs = np.zeros(q.shape[:-3] + (4, 32), np.uint8)
+    qh = np.zeros(q.shape[:-3] + (32,), np.uint8)
+    for G in range(4):
+        for u in range(2):
+            qs[..., G, :] |= (q[..., G, u, :] & 15) << (4 * u)
+            qh |= (q[..., G, u, :] >> 4) << (2 * G + u)
+    B[..., 16:48] = qh
+    B[..., 48:176] = qs.reshape(q.shape[:-3] + (128,))
+
+
 def _q3k_codes(B):
     """[.., 110] -> (2-bit codes, high bits) [.., 256] each, natural input order (foreign_gguf.py:551-555)."""
     hm = B[..., 0:32]
@@ -256,9 +298,15 @@ def raw_to_t16(fmt: str, raw, n: int, k: int) -> np.ndarray:
     if fmt == "nvfp4":
         codes, sc = nvfp4_raw_to_codes(raw, k)
         return nvfp4_codes_to_t16(codes, sc)
-    B = _by_tile(_pad_rows(raw, n).reshape(padded_rows(n), nb, RAW_BLOCK[fmt][1]))           # [nrt, nb, h, g, bb]
+    B = _by_tile(_pad_rows(raw, n).reshape(padded_rows(n), nb, KBLOCK // RAW_BLOCK[fmt][0] * RAW_BLOCK[fmt][1]))           # [nrt, nb, h, g, stored bytes of 256 inputs]
     nrt = B.shape[0]
-    if fmt == "q4_k":
+    if fmt == "q5_k":
+        q = _q5k_codes(B)
+        parts = [_nibble_plane(q & 15), _onebit_plane(q >> 4), np.ascontiguousarray(B[..., 0:16]).reshape(nrt, nb, 256)]
+    elif fmt == "q8_0":
+        blk = B.reshape(B.shape[:4] + (8, 34))
+        parts = [_byte_plane(np.ascontiguousarray(blk[..., 2:34]).reshape(B.shape[:4] + (256,))), np.ascontiguousarray(blk[..., 0:2]).reshape(nrt, nb, 256)]
+    elif fmt == "q4_k":
         w = np.ascontiguousarray(B[..., 16:144]).view("<u4").reshape(nrt, nb, 2, 8, 4, 2, 4)      # h, g, G, c, t
         quant = np.ascontiguousarray(w.transpose(0, 1, 4, 3, 6, 5, 2)).view(np.uint8).reshape(nrt, nb, 2048)    # G, g, t, c, h
         parts = [quant, np.ascontiguousarray(B[..., 0:16]).reshape(nrt, nb, 256)]
@@ -299,8 +347,15 @@ def t16_to_raw(fmt: str, t16, n: int, k: int) -> np.ndarray:
         return nvfp4_codes_to_raw(*t16_to_nvfp4_codes(t16, n, k))
     T = np.asarray(t16, np.uint8).reshape(padded_rows(n) // ROWS, nb, TILE_BYTES[fmt])
     nrt = T.shape[0]
-    B = np.zeros((nrt, nb, 2, 8, RAW_BLOCK[fmt][1]), np.uint8)
-    if fmt == "q4_k":
+    B = np.zeros((nrt, nb, 2, 8, KBLOCK // RAW_BLOCK[fmt][0] * RAW_BLOCK[fmt][1]), np.uint8)
+    if fmt == "q5_k":
+        _q5k_from_codes(_nibble_plane_inv(T[..., 0:2048]) | (_onebit_plane_inv(T[..., 2048:2560]) << 4), B)
+        B[..., 0:16] = T[..., 2560:2816].reshape(nrt, nb, 2, 8, 16)
+    elif fmt == "q8_0":
+        blk = B.reshape(nrt, nb, 2, 8, 8, 34)
+        blk[..., 2:34] = _byte_plane_inv(T[..., 0:4096]).reshape(nrt, nb, 2, 8, 8, 32)
+        blk[..., 0:2] = T[..., 4096:4352].reshape(nrt, nb, 2, 8, 8, 2)
+    elif fmt == "q4_k":
         w = np.ascontiguousarray(T[..., 0:2048]).view("<u4").reshape(nrt, nb, 4, 8, 4, 2, 2)       # G, g, t, c, h
         B[..., 16:144] = np.ascontiguousarray(w.transpose(0, 1, 6, 3, 2, 5, 4)).view(np.uint8).reshape(nrt, nb, 2, 8, 128)
         B[..., 0:16] = T[..., 2048:2304].reshape(nrt, nb, 2, 8, 16)

@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 import numpy as np
 
 # block elements / block bytes (kyojin_mlx/foreign_gguf.py:27-35 TYPES)
-BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36)}
+BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36), "Q5_K": (256, 176), "Q8_0": (32, 34)}
 
 # doubled e2m1 magnitudes used with the halved scale of GGUF NVFP4 (foreign_gguf.py:69)
 _FP4_X2 = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
@@ -135,7 +135,29 @@ def _decode_nvfp4(B):
     return (v * sc[..., None]).reshape(B.shape[:-1] + (64,))
 
 
-_DECODERS = {"Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4}
+def _decode_q5k(B):
+    """[nr, nb, 176] -> [nr, nb, 256]: w = (d*sc)*q - dmin*mn, q = nibble | (bit 2G+u of qh[l]) << 4 for element 64G + 32u + l.
+    (foreign_gguf.py:470-480)"""
+    d = _half_field(B, 0)[..., None]
+    dmin = _half_field(B, 2)[..., None]
+    sc, mn = k4_scales_mins(B[..., 4:16])
+    qh = B[..., 16:48]
+    q = B[..., 48:176].reshape(B.shape[:-1] + (4, 32))
+    out = np.empty(B.shape[:-1] + (8, 32), np.float32)
+    for j in range(8):
+        nib = (q[..., j // 2, :] >> 4) if (j & 1) else (q[..., j // 2, :] & 15)
+        code = nib.astype(np.float32) + ((qh >> j) & 1).astype(np.float32) * np.float32(16.0)
+        out[..., j, :] = (d * sc[..., j:j + 1].astype(np.float32)) * code - dmin * mn[..., j:j + 1].astype(np.float32)
+    return out.reshape(B.shape[:-1] + (256,))
+
+
+def _decode_q80(B):
+    """[nr, nb, 34] -> [nr, nb, 32]: w = int8 * d. (foreign_gguf.py:447-448)"""
+    d = _half_field(B, 0)[..., None]
+    return np.ascontiguousarray(B[..., 2:34]).view(np.int8).astype(np.float32) * d
+
+
+_DECODERS = {"Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4, "Q5_K": _decode_q5k, "Q8_0": _decode_q80}
 
 
 def _dequant_chunk(tname, raw2, k):

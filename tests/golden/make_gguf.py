@@ -19,8 +19,10 @@ def main():
         raw = rng.integers(0, 256, (n, k // be * bb), dtype=np.uint8)
         b = raw.reshape(n, k // be, bb)
         f16 = lambda: (np.abs(rng.standard_normal((n, k // be))) * 1e-2).astype("<f2").view(np.uint8).reshape(n, k // be, 2)
-        if tname == "Q4_K":
+        if tname in ("Q4_K", "Q5_K"):
             b[..., 0:2], b[..., 2:4] = f16(), f16()
+        elif tname == "Q8_0":
+            b[..., 0:2] = f16()
         elif tname == "Q6_K":
             b[..., 208:210] = f16()
         elif tname == "Q3_K":
@@ -37,6 +39,8 @@ def main():
         ("blk.0.attn_norm.weight", (64,), "F32", rng.standard_normal(64).astype("<f4").view(np.uint8)),
         ("token_embd.weight", (32, 4), "F16", rng.standard_normal((4, 32)).astype("<f2").view(np.uint8)),
         ("blk.0.ffn_gate_exps.weight", (256, 16, 3), "Q4_K", blocks("Q4_K", 48, 256)),
+        ("blk.0.attn_v.weight", (256, 16), "Q5_K", blocks("Q5_K", 16, 256)),
+        ("blk.0.attn_output.weight", (256, 16), "Q8_0", blocks("Q8_0", 16, 256)),
     ]
     kv = {"general.architecture": "tiny", "general.name": "golden fixture", "tiny.block_count": 1, "tiny.rope.freq_base": 10000.0,
           "tokenizer.ggml.tokens": ["a", "b", "c"], "tiny.flag": True, "tiny.scores": [0.5, -1.0]}

@@ -16,7 +16,8 @@ PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny.
 def test_linear_and_experts_from_file():
     rng = np.random.default_rng(1)
     with GG.GgufFile(PATH) as g:
-        for name, tname in (("blk.0.attn_q.weight", "Q4_K"), ("blk.0.ffn_down.weight", "Q6_K"), ("blk.0.attn_k.weight", "Q3_K")):
+        for name, tname in (("blk.0.attn_q.weight", "Q4_K"), ("blk.0.ffn_down.weight", "Q6_K"), ("blk.0.attn_k.weight", "Q3_K"), ("blk.0.attn_v.weight", "Q5_K"),
+                            ("blk.0.attn_output.weight", "Q8_0")):
             ti = g.tensors[name]
             k, n = ti.ne
             lin = g.load_linear(name)
