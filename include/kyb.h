@@ -135,8 +135,12 @@ int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int expe
  *   code 0x7F becomes 0, which is how the reference decodes them (kyojin_mlx/foreign_pack.py:113-117). Role of kyojin_mlx/fp4tile.py:72-134 `to_tile` / `from_tile`.
  * kyb_gemm_nvfp4: d [m, n] (out_dtype 1 = fp16 saturated, 2 = bf16) = gscale * A B^T with A, B packed e2m1 + block scales, tcgen05.mma kind::mxf4nvf4
  *   (block 16, fp32 accumulation in tensor memory). k % 256 == 0, n % 256 == 0. The reference has no W4A4 product (its NVFP4 linear is W4A16,
- *   kyojin_mlx/foreign_metal.py:1487-1557); this is the benchmark's "activations quantised on the fly with the same block rule" configuration. */
+ *   kyojin_mlx/foreign_metal.py:1487-1557); this is the benchmark's "activations quantised on the fly with the same block rule" configuration.
+ * kyb_fp4_quant_block32 / kyb_fp4_unpack_block32: the other form of the same codec, kyojin_mlx/fp4pack.py:30-63 with block = 32 and e4m3_scale = False: one
+ *   exponent byte per 32 values (scale 2^(byte - 127), byte = ceil(log2(amax / 6)) + 127 with the amax floor 6 * 2^-126), same e2m1 codes. */
 size_t kyb_nvfp4_sf_bytes(int64_t rows, int64_t k);
+int kyb_fp4_quant_block32(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t k, void* codes, void* scale_bytes, void* stream);
+int kyb_fp4_unpack_block32(const void* codes, const void* scale_bytes, int64_t rows, int64_t k, int out_dtype, void* out, int64_t ldo, void* stream);
 int kyb_nvfp4_quant_rows(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t k, void* codes, void* sf_plain, void* sf_swz, void* stream);
 int kyb_nvfp4_unpack_rows(const void* codes, const void* sf_plain, int64_t rows, int64_t k, int out_dtype, void* out, int64_t ldo, void* stream);
 int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* swz, int to_swizzled, void* stream);

@@ -138,6 +138,8 @@ SIGNATURES = {
     "kyb_nvfp4_sf_bytes": (_sz, [_i64, _i64]),
     "kyb_nvfp4_quant_rows": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "kyb_nvfp4_unpack_rows": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _i64, _vp]),
+    "kyb_fp4_quant_block32": (_int, [_vp, _int, _i64, _i64, _i64, _vp, _vp, _vp]),
+    "kyb_fp4_unpack_block32": (_int, [_vp, _vp, _i64, _i64, _int, _vp, _i64, _vp]),
     "kyb_nvfp4_sf_swizzle": (_int, [_vp, _i64, _i64, _vp, _int, _vp]),
     "kyb_gemm_nvfp4": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_moe_select": (_int, [_vp, _i64, _i64, _int, _int, _int, _int, _vp, _vp, _vp, _vp]),

@@ -2,6 +2,7 @@
 // activation, weighted combine. These are launch-bound elementwise / index kernels; the arithmetic follows the reference's Metal kernels
 // (kyojin_mlx/foreign_moe.py:77-119 _SELECT / _SILU / _COMBINE, foreign_kqgmm.py:169-188 _CSORT, :242-261 _GATHER_ORD / _SILU_PERM,
 // moe_sort.py:18-45) in float32.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
 #include <algorithm>
@@ -62,43 +63,95 @@ __global__ void moe_select_kernel(const float* __restrict__ lg, int64_t ld, int 
     if (lane == 0 && sgs) sgs[t] = has_shared ? 1.0f / (1.0f + expf(-L[E])) : 0.0f;
 }
 
-// Counting sort of P slots by expert in ONE CTA (histogram, scan, scatter with shared-memory cursors). rank (optional) maps expert -> position of
-// its segment. Outputs (any may be null): order[pos] = slot, inv[slot] = pos, tok[pos] = slot / topk, ids_s[pos] = expert, wts_s[pos] = wts[slot],
+// Counting sort of P slots by expert by ONE thread-block cluster (1 CTA for a few thousand slots, 8 CTAs beyond): every CTA takes a contiguous share of
+// the slots and counts them per expert in its shared memory; after a cluster barrier every CTA reads all the CTAs' counts through distributed shared memory,
+// forms the segment starts with a parallel scan over the experts (no serial pass, no scratch in global memory) and the start of its own share inside every
+// segment; then it scatters its slots with shared-memory cursors. rank (optional) maps expert -> position of its segment.
+// Outputs (any may be null): order[pos] = slot, inv[slot] = pos, tok[pos] = slot / topk, ids_s[pos] = expert, wts_s[pos] = wts[slot],
 // off[E + 1] = first row of each segment, tb[E + 1] = first tile of each segment for tiles of mt rows.
 // Slots whose id is outside [0, E) (the router writes 0xFFFFFFFF for a token with NaN logits) belong to no segment: they take the positions
 // [off[E], P) behind the last segment, with weight 0, so that order / inv stay permutations and every output entry is written.
-__global__ void moe_plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, const uint32_t* __restrict__ rank, int E, int P, int topk, int mt,
-                                uint32_t* __restrict__ order, uint32_t* __restrict__ inv, uint32_t* __restrict__ tok, int32_t* __restrict__ ids_s,
-                                float* __restrict__ wts_s, uint32_t* __restrict__ off, uint32_t* __restrict__ tb) {
-    extern __shared__ uint32_t sm[];
-    uint32_t* counts = sm;             // [E]
-    uint32_t* cursor = sm + E;         // [E + 1]
-    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0u;
-    __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x) {
-        const int e = ids[p];
-        if (e >= 0 && e < E) atomicAdd(&counts[rank ? rank[e] : (uint32_t)e], 1u);
+constexpr int PLAN_THREADS = 1024, PLAN_PER = 9;                     // experts per thread in the scan: E + 1 <= 1024 * 9
+
+// exclusive scan of one value per thread over the CTA (1024 threads); `carry` = a shared array of 33 words
+__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t* carry, uint32_t& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += n;
     }
+    if (lane == 31) carry[warp] = inc;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t s = 0, t = 0;
-        for (int e = 0; e < E; ++e) {
-            const uint32_t c = counts[e];
-            cursor[e] = s;
-            if (off) off[e] = s;
-            if (tb) tb[e] = t;
-            s += c;
-            t += (c + (uint32_t)mt - 1u) / (uint32_t)mt;
+    if (warp == 0) {
+        uint32_t w = carry[lane], wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += n;
         }
-        cursor[E] = s;
-        if (off) off[E] = s;
-        if (tb) tb[E] = t;
+        carry[lane] = wi - w;
+        if (lane == 31) carry[32] = wi;
     }
     __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    total = carry[32];
+    const uint32_t out = carry[warp] + inc - v;
+    __syncthreads();                                                  // carry is reused by the next scan
+    return out;
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int32_t* __restrict__ ids, const float* __restrict__ wts, const uint32_t* __restrict__ rank, int E, int P,
+                                                                int topk, int mt, uint32_t* __restrict__ order, uint32_t* __restrict__ inv, uint32_t* __restrict__ tok,
+                                                                int32_t* __restrict__ ids_s, float* __restrict__ wts_s, uint32_t* __restrict__ off, uint32_t* __restrict__ tb) {
+    namespace cg = cooperative_groups;
+    extern __shared__ uint32_t sm[];
+    uint32_t* counts = sm;             // [E + 1]: this CTA's slots per segment; entry E = slots that belong to no expert
+    uint32_t* cursor = sm + E + 1;     // [E + 1]: where this CTA's next slot of a segment goes
+    uint32_t* carry = cursor + E + 1;  // [33]
+    cg::cluster_group cl = cg::this_cluster();
+    const int R = (int)cl.num_blocks(), r = (int)cl.block_rank();
+    const int share = (P + R - 1) / R, p0 = min(P, r * share), p1 = min(P, p0 + share);
+    auto key_of = [&](int e) -> uint32_t { return (e >= 0 && e < E) ? (rank ? rank[e] : (uint32_t)e) : (uint32_t)E; };
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) counts[e] = 0u;
+    __syncthreads();
+    for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) atomicAdd(&counts[key_of(ids[p])], 1u);
+    cl.sync();                                                        // every CTA's counts are complete and visible to the cluster
+    // thread t owns segments [t * PLAN_PER, (t + 1) * PLAN_PER): their sizes over all CTAs and what the CTAs before this one put into them
+    uint32_t tot[PLAN_PER], bef[PLAN_PER], rows = 0, tiles = 0;
+#pragma unroll
+    for (int j = 0; j < PLAN_PER; ++j) {
+        const int e = threadIdx.x * PLAN_PER + j;
+        tot[j] = bef[j] = 0u;
+        if (e <= E)
+            for (int c = 0; c < R; ++c) {
+                const uint32_t v = cl.map_shared_rank(counts, c)[e];
+                tot[j] += v;
+                if (c < r) bef[j] += v;
+            }
+        rows += tot[j];
+        if (e < E) tiles += (tot[j] + (uint32_t)mt - 1u) / (uint32_t)mt;
+    }
+    uint32_t all_rows, all_tiles;
+    uint32_t row0 = block_excl_scan(rows, carry, all_rows), tile0 = block_excl_scan(tiles, carry, all_tiles);
+#pragma unroll
+    for (int j = 0; j < PLAN_PER; ++j) {
+        const int e = threadIdx.x * PLAN_PER + j;
+        if (e <= E) {
+            cursor[e] = row0 + bef[j];
+            if (r == 0) {
+                if (off) off[e] = row0;
+                if (tb) tb[e] = tile0;
+            }
+            row0 += tot[j];
+            if (e < E) tile0 += (tot[j] + (uint32_t)mt - 1u) / (uint32_t)mt;
+        }
+    }
+    cl.sync();                                                        // nobody reads a peer's counts after this point (a CTA may leave while others scatter)
+    for (int p = p0 + threadIdx.x; p < p1; p += blockDim.x) {
         const int e0 = ids[p];
         const bool valid = e0 >= 0 && e0 < E;
-        const uint32_t pos = atomicAdd(&cursor[valid ? (rank ? rank[e0] : (uint32_t)e0) : (uint32_t)E], 1u);
+        const uint32_t pos = atomicAdd(&cursor[key_of(e0)], 1u);
         if (order) order[pos] = (uint32_t)p;
         if (inv) inv[p] = pos;
         if (tok) tok[pos] = (uint32_t)(p / topk);
@@ -404,9 +457,28 @@ extern "C" int kyb_moe_plan(const void* ids, const void* wts, const void* rank, 
                             void* wts_s, void* off, void* tb, void* stream) {
     KYB_REQUIRE(ids, "null pointer");
     KYB_REQUIRE(E > 0 && E <= 8192 && P > 0 && P < (1ll << 31) && topk > 0 && mt > 0, "E=%d P=%lld topk=%d mt=%d out of range", E, (long long)P, topk, mt);
-    const size_t smem = (size_t)(2 * E + 1) * sizeof(uint32_t);
-    kyb::moe_plan_kernel<<<1, 1024, smem, (cudaStream_t)stream>>>((const int32_t*)ids, (const float*)wts, (const uint32_t*)rank, E, (int)P, topk, mt, (uint32_t*)order,
-                                                                 (uint32_t*)inv, (uint32_t*)tok, (int32_t*)ids_s, (float*)wts_s, (uint32_t*)off, (uint32_t*)tb);
+    const size_t smem = (size_t)(2 * (E + 1) + 33) * sizeof(uint32_t);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        KYB_CUDA(cudaFuncSetAttribute(kyb::moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((2 * 8193 + 33) * sizeof(uint32_t))));
+        configured = true;
+    }
+    const unsigned ctas = P >= 4096 ? 8u : 1u;                                  // one cluster; 8 is the portable cluster size
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas), cfg.blockDim = dim3(kyb::PLAN_THREADS), cfg.dynamicSmemBytes = smem, cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ctas, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    const int32_t* a_ids = (const int32_t*)ids;
+    const float* a_wts = (const float*)wts;
+    const uint32_t* a_rank = (const uint32_t*)rank;
+    int a_P = (int)P;
+    uint32_t *a_order = (uint32_t*)order, *a_inv = (uint32_t*)inv, *a_tok = (uint32_t*)tok, *a_off = (uint32_t*)off, *a_tb = (uint32_t*)tb;
+    int32_t* a_ids_s = (int32_t*)ids_s;
+    float* a_wts_s = (float*)wts_s;
+    void* args[] = {&a_ids, &a_wts, &a_rank, &E, &a_P, &topk, &mt, &a_order, &a_inv, &a_tok, &a_ids_s, &a_wts_s, &a_off, &a_tb};
+    KYB_CUDA(cudaLaunchKernelExC(&cfg, (const void*)kyb::moe_plan_kernel, args));
     return kyb_launch_check("moe_plan");
 }
 

@@ -157,6 +157,56 @@ __global__ void nvfp4_unpack_rows_kernel(const uint8_t* __restrict__ codes, cons
     }
 }
 
+// ---- the block-32 form with a power-of-two scale (one exponent byte per 32 values; the reference's second branch of kyojin_mlx/fp4pack.py:30-63).
+// One thread per block: scale = 2^e with e = ceil(log2(max(amax, 6 * 2^-126) / 6)), stored as e + 127; values are divided by the scale exactly (a power of two),
+// clipped to +-6 and take the e2m1 code by the same thresholds as the block-16 form. e is the mathematical ceiling of the logarithm of the float32 quotient,
+// read from its exponent and mantissa bits (no library logarithm in the way).
+template <typename T>
+__global__ void fp4_quant_block32_kernel(const T* __restrict__ x, int64_t ldx, int64_t rows, int64_t k, uint8_t* __restrict__ codes, uint8_t* __restrict__ sbytes) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nblk = k >> 5;
+    if (i >= rows * nblk) return;
+    const int64_t row = i / nblk, b = i % nblk;
+    const T* xp = x + row * ldx + b * 32;
+    float v[32], amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (float)xp[j], amax = fmaxf(amax, fabsf(v[j]));
+    const float q = fmaxf(amax, 6.0f * 1.1754943508222875e-38f) / 6.0f;                 // >= 2^-126: a normal float32
+    const uint32_t qb = __float_as_uint(q);
+    const int e = (int)(qb >> 23) - 127 + ((qb & 0x7FFFFFu) ? 1 : 0);                    // ceil(log2 q)
+    const float inv = __uint_as_float((uint32_t)(127 - e) << 23);                          // 2^-e (e in [-126, 13] for 16-bit inputs)
+    sbytes[row * nblk + b] = (uint8_t)(e + 127);
+    uint8_t* cp = codes + row * (k >> 1) + b * 16;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+        uint32_t pair = 0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float w = fminf(fmaxf(v[j + h] * inv, -6.0f), 6.0f), mag = fabsf(w);
+            const uint32_t c = (mag > 0.25f) + (mag > 1.25f) + (mag > 2.5f) + (mag > 5.0f) + (mag >= 0.75f) + (mag >= 1.75f) + (mag >= 3.5f);
+            pair |= (c | (w < 0.f ? 8u : 0u)) << (4 * h);
+        }
+        cp[j >> 1] = (uint8_t)pair;
+    }
+}
+
+template <typename T>
+__global__ void fp4_unpack_block32_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sbytes, int64_t rows, int64_t k, T* __restrict__ out, int64_t ldo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t nblk = k >> 5;
+    if (i >= rows * nblk) return;
+    const int64_t row = i / nblk, b = i % nblk;
+    const uint4 pk = *reinterpret_cast<const uint4*>(codes + row * (k >> 1) + b * 16);
+    const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+    const float scale = exp2f((float)sbytes[row * nblk + b] - 127.0f);                  // exact for integer arguments
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t c = (words[j >> 3] >> (4 * (j & 7))) & 15u;
+        const uint32_t hb = ((c & 8u) << 12) | ((c & 7u) << 9);                       // e2m1 as fp16 bits = value * 2^-14
+        out[row * ldo + b * 32 + j] = (T)(half_bits_to_float(hb) * 16384.0f * scale);
+    }
+}
+
 // plain [rows, k/16] <-> SF512 (rows padded to 128 with zero scales); sanitize: sign bit dropped, NaN code 0x7F -> 0 (the reference's decode rule)
 __global__ void sf_swizzle_kernel(const uint8_t* __restrict__ plain, int64_t rows, int64_t k, uint8_t* __restrict__ swz, int to_swizzled) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -423,6 +473,31 @@ extern "C" int kyb_nvfp4_unpack_rows(const void* codes, const void* sf_plain, in
     else if (out_dtype == 1) kyb::nvfp4_unpack_rows_kernel<__half><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf_plain, rows, k, (__half*)out, ldo);
     else kyb::nvfp4_unpack_rows_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sf_plain, rows, k, (__nv_bfloat16*)out, ldo);
     return kyb_launch_check("nvfp4_unpack_rows");
+}
+
+extern "C" int kyb_fp4_quant_block32(const void* x, int x_dtype, int64_t ldx, int64_t rows, int64_t k, void* codes, void* sbytes, void* stream) {
+    KYB_REQUIRE(x && codes && sbytes, "null pointer");
+    KYB_REQUIRE(x_dtype == KYB_DT_F16 || x_dtype == KYB_DT_BF16, "x dtype %d: fp16 or bf16", x_dtype);
+    KYB_REQUIRE(rows > 0 && k > 0 && k % 32 == 0 && ldx >= k, "rows=%lld k=%lld: k must be a positive multiple of 32", (long long)rows, (long long)k);
+    const int64_t total = rows * (k / 32);
+    const unsigned blocks = (unsigned)((total + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (x_dtype == KYB_DT_F16) kyb::fp4_quant_block32_kernel<__half><<<blocks, 128, 0, st>>>((const __half*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sbytes);
+    else kyb::fp4_quant_block32_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)x, ldx, rows, k, (uint8_t*)codes, (uint8_t*)sbytes);
+    return kyb_launch_check("fp4_quant_block32");
+}
+
+extern "C" int kyb_fp4_unpack_block32(const void* codes, const void* sbytes, int64_t rows, int64_t k, int out_dtype, void* out, int64_t ldo, void* stream) {
+    KYB_REQUIRE(codes && sbytes && out, "null pointer");
+    KYB_REQUIRE(rows > 0 && k > 0 && k % 32 == 0 && ldo >= k && out_dtype >= 0 && out_dtype <= 2, "rows=%lld k=%lld out_dtype=%d", (long long)rows, (long long)k, out_dtype);
+    KYB_REQUIRE(((uintptr_t)codes & 15) == 0, "codes must be 16-byte aligned");
+    const int64_t total = rows * (k / 32);
+    const unsigned blocks = (unsigned)((total + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == 0) kyb::fp4_unpack_block32_kernel<float><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sbytes, rows, k, (float*)out, ldo);
+    else if (out_dtype == 1) kyb::fp4_unpack_block32_kernel<__half><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sbytes, rows, k, (__half*)out, ldo);
+    else kyb::fp4_unpack_block32_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const uint8_t*)codes, (const uint8_t*)sbytes, rows, k, (__nv_bfloat16*)out, ldo);
+    return kyb_launch_check("fp4_unpack_block32");
 }
 
 extern "C" int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* swz, int to_swizzled, void* stream) {

@@ -29,3 +29,25 @@ def test_e4m3_rounding_table():
     r = F4.e4m3_rn(mid)
     assert ((r % 2) == 0).all()
     assert F4.e4m3_rn(np.array([1e9]))[0] == 126                          # saturates at 448
+
+
+def test_power_of_two_form():
+    """Block 32 with an exponent byte: the scale is the smallest power of two with amax / scale <= 6, an all-zero block stores exponent byte 1, pack / unpack
+    round-trips are idempotent."""
+    rng = np.random.default_rng(1)
+    x = (rng.standard_normal((32, 256)) * np.exp(rng.uniform(-4, 4, (32, 1)))).astype(np.float16)
+    x[0] = 0
+    x[1, :32] = 0
+    x[1, 0] = 6.0                                                         # amax / 6 exactly 1: exponent 0
+    x[2, :32] = 0
+    x[2, 0] = 6.0078125                                                   # one fp16 step above 6: exponent 1
+    codes, sc = F4.pack(x, 32, False)
+    assert sc[0].tolist() == [1] * 8 and not codes[0].any()
+    assert sc[1, 0] == 127 and sc[2, 0] == 128
+    scale = np.ldexp(1.0, sc.astype(np.int32) - 127)
+    amax = np.abs(x.astype(np.float64)).reshape(32, -1, 32).max(-1)
+    nz = amax > 0
+    assert (amax[nz] / scale[nz] <= 6.0).all() and (amax[nz] / scale[nz] > 3.0).all()
+    y = F4.unpack(codes, sc, 32, False)
+    c2, s2 = F4.pack(y, 32, False)
+    np.testing.assert_array_equal(F4.unpack(c2, s2, 32, False), y)

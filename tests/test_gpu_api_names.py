@@ -48,6 +48,24 @@ def test_q4mma_rows_invariant_and_accurate(group):
         assert torch.equal(yr, y16[:r])                                      # bits do not depend on the row count
 
 
+def test_q4mma_ragged_shapes_and_all_row_counts():
+    """Weight rows not a multiple of the warp's 16, k a multiple of 64 only (a partial last 256-input chunk), 17 to 32 activation rows (four column tiles)."""
+    rng = np.random.default_rng(9)
+    n, k = 100, 1088
+    w = rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32)
+    s = (rng.random((n, k // 32)) * 0.02).astype(np.float16)
+    b = (rng.standard_normal((n, k // 32)) * 0.05).astype(np.float16)
+    q = ((w[..., None] >> (4 * np.arange(8, dtype=np.uint32))) & 15).reshape(n, k).astype(np.float32)
+    ref = q * np.repeat(s.astype(np.float32), 32, 1) + np.repeat(b.astype(np.float32), 32, 1)
+    x = synth.activations(32, k, rng)
+    wd, sd, bd = (torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).cuda() for a in (w, s, b))
+    xd = q4mma.prep_x(torch.from_numpy(x).cuda())
+    y32 = q4mma.q4mma4(xd, wd, sd, bd, 32)
+    assert O.rel_fro(y32.cpu().numpy(), O.matmul_f64(x, ref)) < 1e-3
+    for r in (1, 9, 16, 17, 24):
+        assert torch.equal(q4mma.q4mma(xd, wd, sd, bd, r), y32[:r]), r
+
+
 def test_fp4tile_round_trip_and_gather():
     rng = np.random.default_rng(3)
     E, n, k, S = 3, 64, 512, 20

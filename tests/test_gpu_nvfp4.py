@@ -70,3 +70,24 @@ def test_gemm_nvfp4_vs_fp64(m, n, k):
     assert err < 1e-3, err
     d2 = ops.gemm_nvfp4(acodes, asw, torch.from_numpy(qs).cuda(), sfb, m, n, k, 0.25, torch.bfloat16)
     assert O.rel_fro(d2.float().cpu().numpy(), want * 0.25) < 5e-3       # bf16 output rounding
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_power_of_two_form_equals_restatement(dtype):
+    """fp4pack with block = 32 and power-of-two scales: codes and exponent bytes equal to the numpy restatement, incl. an all-zero block, amax / 6 exactly a power
+    of two and one step above it; unpack equal in fp32."""
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = (torch.randn((64, 512), device="cuda", generator=g) * torch.exp(torch.rand((64, 1), device="cuda", generator=g) * 8 - 4)).to(dtype)
+    x[3] = 0
+    x[4, :32] = 0
+    x[4, 0] = 6.0
+    x[5, :32] = 0
+    x[5, 0] = (torch.tensor([6.0], device="cuda").to(dtype).view(torch.int16) + 1).view(dtype)[0]
+    x[6, :32] = torch.tensor([3.0, -1.5, 0.75, -0.25, 0.25001, 5.0, -5.5, 1.75] * 4, device="cuda").to(dtype)
+    codes, sc = fp4pack.pack(x, 32, False)
+    wc, ws = F4.pack(x.float().cpu().numpy(), 32, False)
+    np.testing.assert_array_equal(sc.cpu().numpy(), ws)
+    np.testing.assert_array_equal(codes.cpu().numpy(), wc)
+    np.testing.assert_array_equal(fp4pack.unpack(codes, sc, 32, False, torch.float32).cpu().numpy(), F4.unpack(wc, ws, 32, False))
+    with pytest.raises(ValueError):
+        fp4pack.pack(x, 32, True)
