@@ -344,3 +344,199 @@ class ForeignSwitchGLU(torch.nn.Module):
             a = ops.gemv_group(self.g.fmt, self.g.t16, self.g.n, self.g.k, self.g.E, x2, e32, xdiv=K, gs=self.g._gs(), groups=groups)
             b = ops.gemv_group(self.u.fmt, self.u.t16, self.u.n, self.u.k, self.u.E, x2, e32, xdiv=K, gs=self.u._gs(), groups=groups)
         return self.d.gather_glu(a, b, None, e32, limit=self.limit, groups=groups)
+
+
+# ------------------------------------------------------------------------------------------------ same-input groups and the fused dense gated MLP (installers)
+class _Group:
+    """One concatenated matrix serving several same-input linears: the first member called with an input runs the product, the others take their slice of it
+    (role of kyojin_mlx/foreign_linear.py `_Group`)."""
+
+    def __init__(self, dev: DevPack, cuts):
+        self.dev, self.cuts = dev, list(cuts)
+        self.x = self.ys = None
+
+
+class GroupMember(torch.nn.Module):
+    """Stand-in for one ForeignLinear of a same-input group: same call, same output (its own rows of the grouped product, bias, output type); mirrors
+    kyojin_mlx/foreign_linear.py:1527-1577. The grouped product runs once per distinct input object; the group keeps only a weak reference to that input."""
+
+    def __init__(self, grp: _Group, i: int, src: ForeignLinear):
+        super().__init__()
+        self._g, self._i = grp, i
+        self.in_features, self.out_features, self.fmt = src.in_features, src.out_features, src.fmt
+        self.out_dtype, self._bias = src.out_dtype, src._bias
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        import weakref
+        g, shape = self._g, x.shape
+        if g.x is None or g.x() is not x or g.ys[self._i] is None:
+            x2 = x.reshape(-1, shape[-1])
+            if x2.dtype != torch.float16:
+                x2 = x2.to(torch.float16)
+            y = g.dev.apply(x2)
+            g.ys = [y[:, a:b] for a, b in zip(g.cuts[:-1], g.cuts[1:])]
+            g.x = weakref.ref(x)
+        y, g.ys[self._i] = g.ys[self._i], None                   # every member takes its slice once
+        if y.dtype != self.out_dtype:
+            y = y.to(self.out_dtype)
+        if self._bias is not None:
+            y = y + self._bias
+        return y.reshape(*shape[:-1], self.out_features)
+
+
+def trace_calls(model: torch.nn.Module, example_inputs=None):
+    """One forward in which every ForeignLinear / GroupMember / ForeignSwitchGLU only records (id of its input object, id of the module) and returns zeros of its
+    output shape -> the list of records (role of kyojin_mlx/foreign_linear.py:1596-1613). example_inputs: the arguments of the forward (default: one token id)."""
+    calls, keep = [], []
+    orig_l, orig_s = ForeignLinear.forward, ForeignSwitchGLU.forward
+
+    def rec_l(self, x, permuted=False):
+        calls.append((id(x), id(self)))
+        keep.append(x)                                           # ids stay unique while the trace holds the tensors
+        return torch.zeros((*x.shape[:-1], self.out_features), dtype=self.out_dtype, device=x.device)
+
+    def rec_s(self, x, inds):
+        return torch.zeros((*x.shape[:-1], inds.shape[-1], self.d.n), dtype=torch.float16, device=x.device)
+
+    ForeignLinear.forward, ForeignSwitchGLU.forward = rec_l, rec_s
+    try:
+        with torch.no_grad():
+            if example_inputs is None:
+                dev = next((m.dev.t16.device for m in model.modules() if isinstance(m, ForeignLinear)), torch.device("cuda"))
+                example_inputs = (torch.zeros((1, 1), dtype=torch.int64, device=dev),)
+            model(*example_inputs)
+    finally:
+        ForeignLinear.forward, ForeignSwitchGLU.forward = orig_l, orig_s
+    return calls
+
+
+def find_groups(calls, names):
+    """calls: [(input object id, module id)] of one forward; names: module id -> name. Lists of >= 2 distinct named modules that received the same input object,
+    each called exactly once in the forward, in first-call order."""
+    times = {}
+    for _, mid in calls:
+        times[mid] = times.get(mid, 0) + 1
+    buckets = {}
+    for xid, mid in calls:
+        if times[mid] == 1 and mid in names:
+            buckets.setdefault(xid, []).append(names[mid])
+    return [members for members in buckets.values() if len(members) >= 2]
+
+
+def group_ok(lins) -> bool:
+    """The grouped rows must be what every member computes alone: plain ForeignLinears of one format, input width, output type and per-tensor scale, no input
+    permutation, no expert stacks."""
+    l0 = lins[0]
+    if any(type(l) is not ForeignLinear or l.dev is None or l.dev.E is not None or l._in_perm is not None for l in lins):
+        return False
+    return all((l.fmt, l.in_features, l.out_dtype, l.dev.gscale) == (l0.fmt, l0.in_features, l0.out_dtype, l0.dev.gscale) for l in lins)
+
+
+def _set_module(model, name, new):
+    parent = model
+    *path, leaf = name.split(".")
+    for p in path:
+        parent = getattr(parent, p)
+    setattr(parent, leaf, new)
+
+
+def group_same_input(model: torch.nn.Module, example_inputs=None, log=print) -> dict:
+    """Replaces the ForeignLinears that read the same input (q | k | v, gate | up) by GroupMembers over one concatenated matrix, so that a decode step launches
+    one product per group (kyojin_mlx/foreign_linear.py:1617-1655). Groups are built one at a time and the members' own arrays dropped before the next. A model
+    whose trace fails is left as it is. Returns {"groups", "members", "launches_saved"}."""
+    named = {n: m for n, m in model.named_modules() if type(m) is ForeignLinear}
+    try:
+        groups = find_groups(trace_calls(model, example_inputs), {id(m): n for n, m in named.items()})
+    except Exception as e:                                                # noqa: BLE001 - a forward that needs other arguments: stay as served
+        log(f"[foreign] same-input grouping skipped ({type(e).__name__}: {e})")
+        return {"groups": 0, "members": 0, "launches_saved": 0}
+    parts = []
+    for g in groups:                                                      # a same-input set of mixed formats splits into one group per (format, k, out dtype)
+        by = {}
+        for n in g:
+            by.setdefault((named[n].fmt, named[n].in_features, named[n].out_dtype), []).append(n)
+        parts += [p for p in by.values() if len(p) >= 2]
+    ngroups = members = saved = 0
+    for g in parts:
+        lins = [named[n] for n in g]
+        if not group_ok(lins):
+            continue
+        grp = _Group(DevPack.grouped([l.dev for l in lins]), [0] + list(np.cumsum([l.out_features for l in lins])))
+        for i, (n, l) in enumerate(zip(g, lins)):
+            _set_module(model, n, GroupMember(grp, i, l))
+            l.dev = None
+        ngroups, members, saved = ngroups + 1, members + len(g), saved + len(g) - 1
+    log(f"[foreign] {members} linears in {ngroups} same-input groups, {saved} fewer launches per decode step")
+    return {"groups": ngroups, "members": members, "launches_saved": saved}
+
+
+PROJ = ("gate_proj", "up_proj", "down_proj")
+
+
+class _Probe(torch.nn.Module):
+    def __init__(self, fn):
+        super().__init__()
+        self._fn = fn
+
+    def forward(self, x):
+        return self._fn(x)
+
+
+def silu_gated(mod) -> bool:
+    """True when the module's own forward is down(silu(gate(x)) * up(x)): probed on stand-in projections (gate = identity, up = ones, down = identity) against
+    silu. A gated MLP with another activation keeps its call (the fused launch computes silu). Any failure of the probe = False."""
+    import copy
+    try:
+        m = copy.copy(mod)
+        m._modules = dict(mod._modules)
+        m.gate_proj, m.up_proj, m.down_proj = _Probe(lambda x: x), _Probe(lambda x: torch.ones_like(x)), _Probe(lambda x: x)
+        x = torch.linspace(-4.0, 4.0, 33).reshape(1, 1, 33)
+        return bool(torch.allclose(type(mod).forward(m, x), torch.nn.functional.silu(x), atol=1e-5))
+    except Exception:                                                     # noqa: BLE001
+        return False
+
+
+def _glu_call(self, x):
+    """down(silu(gate(x)) * up(x)) for decode rows: the activation is formed while the down projection stages its rows, so the MLP is gate | up plus ONE launch
+    (kyojin_mlx/foreign_linear.py:1882-1907). Any other case runs the module's own forward."""
+    dn, g, u = self.down_proj, self.gate_proj, self.up_proj
+    lead, H = x.shape[:-1], x.shape[-1]
+    R = int(np.prod(lead)) if len(lead) else 1
+    K = dn.in_features
+    if dn.dev is None or R == 0 or R > F.GEMV_ROWS:
+        return self._stock_call(x)
+    x2 = x.reshape(-1, H)
+    if x2.dtype != torch.float16:
+        x2 = x2.to(torch.float16)
+    if isinstance(g, GroupMember) and isinstance(u, GroupMember):
+        grp = g._g
+        if u._g is not grp or (g._i, u._i) != (0, 1) or grp.cuts != [0, K, 2 * K]:
+            return self._stock_call(x)
+        y = grp.dev.apply(x2)                                             # [R, 2 K]: gate | up in one launch
+        out = dn.dev.apply_glu(y[:, :K], y[:, K:])
+    else:
+        if type(g) is not ForeignLinear or type(u) is not ForeignLinear or g.dev is None or u.dev is None:
+            return self._stock_call(x)
+        out = dn.dev.apply_glu(g(x).reshape(R, K), u(x).reshape(R, K))
+    return out.reshape(*lead, dn.out_features)
+
+
+def install_dense_glu(model: torch.nn.Module, log=print) -> int:
+    """Swaps the forward of every gated MLP (gate_proj / up_proj / down_proj, silu-gated by probe) whose down projection is a plain fp16 ForeignLinear for the fused
+    call above (kyojin_mlx/foreign_linear.py:1934-1953). Returns the number of modules changed."""
+    n = 0
+    for _, mod in list(model.named_modules()):
+        g, u, dn = (getattr(mod, k, None) for k in PROJ)
+        if type(dn) is not ForeignLinear or getattr(mod.__class__, "_dense_glu", False) or not silu_gated(mod):
+            continue
+        ok = lambda l: (type(l) is ForeignLinear and l.dev is not None) or type(l) is GroupMember
+        if not (ok(g) and ok(u)) or dn._bias is not None or dn._in_perm is not None or dn.out_dtype != torch.float16:
+            continue
+        if any(l.out_dtype != torch.float16 or l._bias is not None or l.out_features != dn.in_features for l in (g, u)):
+            continue
+        cls = mod.__class__
+        mod.__class__ = type("Glu" + cls.__name__, (cls,), {"forward": _glu_call, "_stock_call": cls.forward, "_dense_glu": True})
+        n += 1
+    if n:
+        log(f"[foreign] {n} gated MLPs form silu * mul inside the down projection's launch")
+    return n
