@@ -25,6 +25,7 @@ namespace kyb {
 
 constexpr int KQ_BN = 256, KQ_BK = 64, KQ_DW = 16, KQ_THREADS = (6 + KQ_DW) * 32;
 constexpr uint32_t KQ_A_SUB = 128 * KQ_BK * 2, KQ_B_BYTES = KQ_BN * KQ_BK * 2;
+constexpr int KQ_TORD = 2048;                          // grouped form: tile order table in shared memory (u16 entries)
 constexpr uint32_t KQ_SCR = 1280;                       // per decoder warp: block scales of one T16 tile as half2 pairs
 constexpr uint32_t KQ_STG = KYB_STG_BYTES;              // per epilogue warp: 32 rows x 32 fp16 columns staged for a tiled bulk store
 using KqOutMaps = KybOutMaps;                           // dense form: the [m, col0 + n] fp16 output matrix of every receiving rank
@@ -55,7 +56,7 @@ struct KqItem {
     bool valid;
 };
 
-__device__ __forceinline__ KqItem kq_item(const KqParams& p, int t) {
+__device__ __forceinline__ KqItem kq_item(const KqParams& p, int t, const uint16_t* tord = nullptr) {
     KqItem it;
     it.valid = true, it.gscale = p.gscale, it.m_end = p.m;
     if (!p.tb) {
@@ -64,12 +65,14 @@ __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t) {
         it.nsub = min(p.msub, (p.m - it.m0 + 127) >> 7);
         return it;
     }
-    const int tm = t / p.tiles_n, tn = t - tm * p.tiles_n;                              // n fastest: CTAs running together share the activation rows
+    int tm = t / p.tiles_n;
+    const int tn = t - tm * p.tiles_n;                                                   // n fastest: CTAs running together share the activation rows
     it.n0 = tn * KQ_BN;
     if ((uint32_t)tm >= p.tb[p.experts]) {
         it.valid = false;
         return it;
     }
+    if (tord) tm = (int)tord[tm];                                                        // two-block tiles first (see the kernel's prologue)
     int lo = 0, hi = p.experts;                                                          // largest e with tb[e] <= tm (empty experts repeat a value)
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -388,6 +391,40 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         prefetch_tmap(&tma_a);
     }
     if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    // Grouped form with two-block items: a tile with more than 128 rows costs about 1.5 times a tile with fewer (eight MMAs per stage instead of four), and items go
+    // to the CTAs round-robin, so the tiles are renumbered with the two-block ones first: every CTA then gets the same number of them (+-1) instead of a random
+    // share. Warp 2 builds the table (two-block tiles from the front, the others from the back) from the segment offsets; more tiles than the table holds keep
+    // their order.
+    const uint16_t* tord = nullptr;
+    if (p.tb && p.msub == 2) {
+        const uint32_t total = p.tb[p.experts];
+        if (total <= (uint32_t)KQ_TORD) {
+            uint16_t* tw = reinterpret_cast<uint16_t*>(smem_raw + (tmem_slot + 16 - smem_u32(smem_raw)));
+            tord = tw;
+            if (warp == 2) {
+                uint32_t front = 0, back = total;
+                for (int e0 = 0; e0 < p.experts; e0 += 32) {
+                    const int e = e0 + lane;
+                    uint32_t two = 0, one = 0, first = 0;
+                    if (e < p.experts) {
+                        const uint32_t rows = p.off[e + 1] - p.off[e], nt = (rows + 255u) >> 8;
+                        first = p.tb[e];
+                        one = (nt && rows - 256u * (nt - 1u) <= 128u) ? 1u : 0u;
+                        two = nt - one;
+                    }
+                    uint32_t a = two, b = one;                                          // inclusive warp scans
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const uint32_t ua = __shfl_up_sync(0xffffffffu, a, d), ub = __shfl_up_sync(0xffffffffu, b, d);
+                        if (lane >= d) a += ua, b += ub;
+                    }
+                    for (uint32_t i = 0; i < two; ++i) tw[front + a - two + i] = (uint16_t)(first + i);
+                    if (one) tw[back - b] = (uint16_t)(first + two);
+                    front += __shfl_sync(0xffffffffu, a, 31), back -= __shfl_sync(0xffffffffu, b, 31);
+                }
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -400,7 +437,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             uint32_t parity = 1;                                                    // a fresh barrier passes a wait on the previous phase
             int s = 0;
             for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
-                const KqItem it = kq_item(p, t);
+                const KqItem it = kq_item(p, t, tord);
                 if (!it.valid) continue;
                 for (int kb = 0; kb < kblocks && !failed; ++kb) {
                     if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
@@ -419,10 +456,11 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             int s = 0;
             uint32_t cnt = 0;                                                       // accumulators used so far: number cnt lives in slot cnt & 1
             for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
-                const KqItem it = kq_item(p, t);
+                const KqItem it = kq_item(p, t, tord);
                 if (!it.valid) continue;
-                for (int sub = 0; sub < it.nsub; ++sub)
-                    if (!mbar_wait_fast(acce0 + 8 * ((cnt + sub) & 1u), (((cnt + sub) >> 1) & 1u) ^ 1u)) failed = true;     // the epilogue has drained the slot
+                // the epilogue must have drained an accumulator before the first MMA into it; the second block's accumulator is waited for only when its first MMA
+                // is due, so the first stage of this item overlaps the tail of the previous item's epilogue
+                if (!mbar_wait_fast(acce0 + 8 * (cnt & 1u), ((cnt >> 1) & 1u) ^ 1u)) failed = true;
                 tc_fence_after();
                 for (int kb = 0; kb < kblocks && !failed; ++kb) {
                     if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
@@ -432,6 +470,10 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                     for (int sub = 0; sub < it.nsub; ++sub) {
                         const uint64_t adesc = umma_desc_sw128(a_src + sub * KQ_A_SUB);
                         const uint32_t tmem_d = tmem_base + (uint32_t)(((cnt + sub) & 1u) * KQ_BN);
+                        if (kb == 0 && sub) {
+                            if (!mbar_wait_fast(acce0 + 8 * ((cnt + 1u) & 1u), (((cnt + 1u) >> 1) & 1u) ^ 1u)) failed = true;
+                            tc_fence_after();
+                        }
 #pragma unroll
                         for (int kk = 0; kk < KQ_BK / 16; ++kk) umma_f16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb | kk) != 0);
                     }
@@ -447,7 +489,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         const int q = warp & 3;
         uint32_t cnt = 0;
         for (int t = blockIdx.x; t < num_items; t += gridDim.x) {
-            const KqItem it = kq_item(p, t);
+            const KqItem it = kq_item(p, t, tord);
             if (!it.valid) continue;
             for (int sub = 0; sub < it.nsub; ++sub, ++cnt) {
                 const uint32_t slot = cnt & 1u;
@@ -475,6 +517,45 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                                                       !failed && row0 < it.m_end && it.n0 + (c & ~63) < p.n);
                         else
                             epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + it.n0 + c, row0, !failed && row0 < it.m_end && it.n0 + c < p.n);
+                    }
+                } else if (p.tb && (p.ldd & 7) == 0 && ((uintptr_t)p.d[0] & 15) == 0) {
+                    // ---- grouped form: rows end inside a tile or are scattered, so no tensor map fits. A step of 32 rows x 32 columns is transposed through the warp's
+                    // staging buffer: every store instruction then writes 64-byte row segments (8 rows x 4 lanes) instead of 16 bytes of each of 32 rows
+                    const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
+                    const int row0 = it.m0 + sub * 128 + q * 32, row = row0 + lane;
+                    const uint32_t orow = (p.row_map && row < it.m_end) ? p.row_map[row] : (uint32_t)row;
+                    __half* dst[4];
+                    bool live[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int rr = 8 * i + (lane >> 2);
+                        const uint32_t o = __shfl_sync(0xffffffffu, orow, rr);
+                        live[i] = row0 + rr < it.m_end && !failed;
+                        dst[i] = p.d[0] + (size_t)o * p.ldd + it.n0 + 8 * (lane & 3);
+                    }
+#pragma unroll 1
+                    for (int c = 0; c < KQ_BN; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
+                        tmem_ld_wait();
+                        __syncwarp();                                                  // the previous step's reads of the staging buffer are done
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                __half2 h = __halves2half2(sat_half(__uint_as_float(v[8 * j + 2 * i]) * gscale), sat_half(__uint_as_float(v[8 * j + 2 * i + 1]) * gscale));
+                                w[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            sts128(stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4), make_uint4(w[0], w[1], w[2], w[3]));
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = 8 * i + (lane >> 2);
+                            const uint4 o = lds128(stg + (uint32_t)rr * 64u + (uint32_t)(((lane & 3) ^ ((rr >> 1) & 3)) << 4));
+                            if (live[i]) *reinterpret_cast<uint4*>(dst[i] + c) = o;
+                        }
                     }
                 } else {
                 const int row = it.m0 + sub * 128 + q * 32 + lane;
@@ -524,7 +605,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         uint32_t parity = 1;
         int s = 0;
         for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
-            const KqItem it = kq_item(p, t);
+            const KqItem it = kq_item(p, t, tord);
             if (!it.valid) continue;
             const int rt = min(it.b_rt0 + dw, p.rt_total - 1);
             const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
@@ -607,7 +688,7 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
                                              : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
     const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
-    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * (p.wide ? 2 : 1) * kyb::KQ_STG + 1024 + 256;
+    const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * (p.wide ? 2 : 1) * kyb::KQ_STG + 1024 + 256 + (p.tb ? 2 * kyb::KQ_TORD : 0);
     const size_t cap = 227 * 1024;
     p.stages = (int)std::min<size_t>(8, (cap - fixed) / stage_bytes);
     const size_t smem = (size_t)p.stages * stage_bytes + fixed;
