@@ -352,30 +352,51 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
             if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
             tc_fence_after();
             if (p.tma_out) {
+                // The accumulator is the only one, so the MMAs of the next tile wait for this read-out: all 8 steps of 32 columns are therefore first pulled into
+                // registers as packed 16-bit pairs (the load of step c + 1 in flight while step c is converted), the accumulator is handed back, and only then
+                // do the staged bulk stores run, under the next tile's MMAs.
                 const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
                 const int row0 = m0 + q * 32;
-#pragma unroll 1
-                for (int c = 0; c < NV_BN; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, v);
-                    tmem_ld_wait();
-                    uint32_t w[16];
+                const uint32_t tq = tmem_base + ((uint32_t)(q * 32) << 16);
+                uint32_t w[NV_BN / 32][16];
+                auto pack = [&](const uint32_t (&v)[32], uint32_t (&o)[16]) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const float f0 = __uint_as_float(v[2 * j]) * p.gscale, f1 = __uint_as_float(v[2 * j + 1]) * p.gscale;
                         if (p.out_bf16) {
                             __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                            w[j] = *reinterpret_cast<uint32_t*>(&h);
+                            o[j] = *reinterpret_cast<uint32_t*>(&h);
                         } else {
                             __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
-                            w[j] = *reinterpret_cast<uint32_t*>(&h);
+                            o[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
                     }
-                    if (p.wide)
-                        epilogue_stage_store_wide(outs, p.nout, stg, lane, w, (c >> 5) & 1, p.col0 + n0 + (c & ~63), row0, !failed && row0 < p.m && n0 + (c & ~63) < p.n);
-                    else
-                        epilogue_stage_store(outs, p.nout, stg, lane, w, p.col0 + n0 + c, row0, !failed && row0 < p.m && n0 + c < p.n);
+                };
+                {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld_32x32(tq, v0);
+#pragma unroll
+                    for (int ch = 0; ch < NV_BN / 32; ch += 2) {
+                        tmem_ld_wait();
+                        tmem_ld_32x32(tq + (uint32_t)(32 * (ch + 1)), v1);
+                        pack(v0, w[ch]);
+                        tmem_ld_wait();
+                        if (ch + 2 < NV_BN / 32) tmem_ld_32x32(tq + (uint32_t)(32 * (ch + 2)), v0);
+                        pack(v1, w[ch + 1]);
+                    }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_a(acce);                                        // this warp has read its quarter of the accumulator
+#pragma unroll
+                for (int ch = 0; ch < NV_BN / 32; ++ch) {
+                    const int c = 32 * ch;
+                    if (p.wide)
+                        epilogue_stage_store_wide(outs, p.nout, stg, lane, w[ch], ch & 1, p.col0 + n0 + (c & ~63), row0, !failed && row0 < p.m && n0 + (c & ~63) < p.n);
+                    else
+                        epilogue_stage_store(outs, p.nout, stg, lane, w[ch], p.col0 + n0 + c, row0, !failed && row0 < p.m && n0 + c < p.n);
+                }
+                continue;
             } else {
             const int row = m0 + q * 32 + lane;
             const size_t doff = (size_t)row * p.ldd + n0;
