@@ -96,6 +96,8 @@ int kyb_gemv_glu_t16(int fmt, const void* t16, int64_t n, int64_t k, const void*
  * more rows than its stored kernels serve (thresholds at foreign_linear.py:38-81); b is the fp16 output of kyb_dequant_t16. */
 int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale,
                     void* d, int64_t ldd, void* stream);
+/* the same product with the fp32 accumulators written out unrounded: d float [m, n] (ldd in floats, 16-byte aligned) */
+int kyb_gemm_f16_tn_f32(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale, void* d, int64_t ldd, void* stream);
 
 /* grouped form: rows of a sorted by expert, b = expert stack [experts * n, k] in fp16, tile list on the device (tb, off from kyb_moe_plan with mt = 128),
  * optional scatter of the output rows (row_map) and per-expert output scale (gs). Replaces kyojin_mlx/foreign_kqgmm.py:225-239 `gmm` (tile lookup
@@ -150,6 +152,16 @@ int kyb_gemm_nvfp4(const void* a_codes, const void* sfa, const void* b_codes, co
 /* router logits in fp32: lg[t, r] = sum_h gw[r, h] * x[t, h] (x fp32 / fp16 / bf16 [T, H], gw fp32 [E, H]); column E = the shared-expert gate row sgw (fp32 [H]) when
  * sgw is not null. Replaces kyojin_mlx/foreign_moe.py:122-130 `_logits` (kernels :36-75). lg: fp32 [T, ldl], ldl >= E + (sgw ? 1 : 0). */
 int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const void* gw, const void* sgw, int64_t T, int E, int64_t H, void* lg, int64_t ldl, void* stream);
+/* Router logits on the tensor cores, for many tokens (prefill): the fp32 gate is cut ONCE into three fp16 pieces per row (kyb_router_split: s w = hi + 2^-11 mid +
+ * 2^-22 lo with a power-of-two s per row, all 24 bits of w kept), each call then runs one tcgen05 GEMM of the fp16 activations on the stacked pieces with fp32
+ * accumulation (every product is exact) and one launch that recombines the three partial sums. Same contraction as kyb_router_logits
+ * (kyojin_mlx/foreign_moe.py:122-130) with a different summation order: equal to the fp64 logits within 1e-5 relative. rpad = kyb_router_rpad(E, has_shared);
+ * pieces fp16 [3 rpad, H]; inv_scale float [rpad]; work float [T, 3 rpad], 16-byte aligned; x fp16, H % 64 == 0. */
+int64_t kyb_router_rpad(int E, int has_shared);
+int kyb_router_split(const void* gw, const void* sgw, int E, int64_t H, void* pieces, void* inv_scale, void* stream);
+int kyb_router_logits_tc(const void* x, int64_t ldx, const void* pieces, const void* inv_scale, int64_t T, int E, int has_shared, int64_t H, void* work, void* lg,
+                         int64_t ldl, void* stream);
+
 
 /* ---- routed experts (MoE). Expert stacks are E matrices of n rows concatenated along rows (kyojin_mlx/foreign_linear.py:504-527).
  *

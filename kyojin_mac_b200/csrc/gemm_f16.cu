@@ -18,6 +18,7 @@ constexpr int GM_BM = 128, GM_BK = 64, GM_THREADS = 192;
 
 struct GemmParams {
     __half* d;
+    float* d32;                // when set, the epilogue stores gscale * accumulator as fp32 here (unsaturated) instead of fp16 at d
     int64_t ldd;
     int m, n, k;
     float gscale;
@@ -147,13 +148,26 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
             const int row = ti.m0 + q * 32 + lane;
             const size_t orow = (p.row_map && row < ti.m_end) ? (size_t)p.row_map[row] : (size_t)row;
             __half* drow = p.d + orow * p.ldd + ti.n0;
+            float* frow = p.d32 + orow * p.ldd + ti.n0;
             const float gscale = ti.gscale;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c), v);
                 tmem_ld_wait();
-                if (row < ti.m_end && !failed) {
+                if (p.d32) {
+                    if (row < ti.m_end && !failed) {
+                        if (ti.n0 + c + 32 <= p.n && (p.ldd & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(frow + c + j) = make_float4(__uint_as_float(v[j]) * gscale, __uint_as_float(v[j + 1]) * gscale,
+                                                                                       __uint_as_float(v[j + 2]) * gscale, __uint_as_float(v[j + 3]) * gscale);
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (ti.n0 + c + j < p.n) frow[c + j] = __uint_as_float(v[j]) * gscale;
+                        }
+                    }
+                } else if (row < ti.m_end && !failed) {
                     if (ti.n0 + c + 32 <= p.n && (p.ldd & 7) == 0) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -233,7 +247,29 @@ extern "C" int kyb_gemm_f16_tn(const void* a, int64_t lda, const void* b, int64_
     if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda * 2, kyb::GM_BM, kyb::GM_BK)) return rc;
     if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
     kyb::GemmParams p;
-    p.d = (__half*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale, p.status = status;
+    p.d = (__half*)d, p.d32 = nullptr, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale, p.status = status;
+    p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    return wide ? launch_gemm<256, 4>(ta, tb, p, st, 0) : launch_gemm<128, 6>(ta, tb, p, st, 0);
+}
+
+// The same product with the fp32 accumulators written out unrounded: d fp32 [m, n] (row stride ldd floats) = gscale * A x B^T. Used where the fp16 operands are
+// exact pieces of wider numbers and the caller recombines the partial products (the tensor-core router, csrc/moe.cu).
+extern "C" int kyb_gemm_f16_tn_f32(const void* a, int64_t lda, const void* b, int64_t ldb, int64_t m, int64_t n, int64_t k, float gscale, void* d, int64_t ldd,
+                                   void* stream) {
+    KYB_REQUIRE(a && b && d, "null pointer");
+    KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 64 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 64", (long long)m, (long long)n, (long long)k);
+    KYB_REQUIRE(lda >= k && ldb >= k && lda % 8 == 0 && ldb % 8 == 0 && ldd >= n, "leading dimensions: lda, ldb >= k and multiples of 8, ldd >= n");
+    KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)b & 15) == 0 && ((uintptr_t)d & 15) == 0, "a, b and d must be 16-byte aligned");
+    KYB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "dimension too large");
+    unsigned int* status = kyb_device_status_word();
+    KYB_REQUIRE(status, "could not set up the device status word");
+    const bool wide = n >= 256;
+    CUtensorMap ta, tb;
+    if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)m, (uint64_t)k, (uint64_t)lda * 2, kyb::GM_BM, kyb::GM_BK)) return rc;
+    if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
+    kyb::GemmParams p;
+    p.d = nullptr, p.d32 = (float*)d, p.ldd = ldd, p.m = (int)m, p.n = (int)n, p.k = (int)k, p.gscale = gscale, p.status = status;
     p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
     cudaStream_t st = (cudaStream_t)stream;
     return wide ? launch_gemm<256, 4>(ta, tb, p, st, 0) : launch_gemm<128, 6>(ta, tb, p, st, 0);
@@ -257,7 +293,7 @@ extern "C" int kyb_gemm_f16_grouped(const void* a, int64_t lda, const void* b, i
     if (int rc = kyb_make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a, (uint64_t)s, (uint64_t)k, (uint64_t)lda * 2, kyb::GM_BM, kyb::GM_BK)) return rc;
     if (int rc = kyb_make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, b, (uint64_t)experts * (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, wide ? 256 : 128, kyb::GM_BK)) return rc;
     kyb::GemmParams p;
-    p.d = (__half*)d, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.gscale = 1.0f, p.status = status;
+    p.d = (__half*)d, p.d32 = nullptr, p.ldd = ldd, p.m = (int)s, p.n = (int)n, p.k = (int)k, p.gscale = 1.0f, p.status = status;
     p.tb = (const uint32_t*)tb_, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     const int max_tiles = (int)((s + kyb::GM_BM - 1) / kyb::GM_BM) + experts;
     cudaStream_t st = (cudaStream_t)stream;

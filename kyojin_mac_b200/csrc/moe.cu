@@ -160,6 +160,51 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int32_t* _
     }
 }
 
+// ---- router logits on the tensor cores. An fp32 gate row w is cut into three fp16 pieces of s w (s = a power of two per row that puts the row's largest
+// magnitude in [2^13, 2^14)): s w = hi + 2^-11 mid + 2^-22 lo with hi = fp16(s w), mid = fp16(2^11 (s w - hi)), lo = fp16(2^11 (2^11 (s w - hi) - mid)); every
+// difference is exact in fp32, so the three pieces carry the 24 bits of w (entries more than 2^27 below the row's maximum lose low bits; they do not matter to
+// a logit). With fp16 activations every product piece * x is exact in the fp32 accumulator of the MMA, and
+//     logit = (x . hi + 2^-11 x . mid + 2^-22 x . lo) / s.
+// pieces: fp16 [3 * rpad, H], piece p of row r at row p * rpad + r; rows [R, rpad) are zero. inv_scale[r] = 1 / s.
+__global__ void router_split_kernel(const float* __restrict__ gw, const float* __restrict__ sgw, int E, int R, int rpad, int H, __half* __restrict__ pieces,
+                                    float* __restrict__ inv_scale) {
+    const int r = blockIdx.x;
+    __shared__ float red[32];
+    const float* w = r < E ? gw + (size_t)r * H : (r < R ? sgw : nullptr);
+    float mx = 0.f;
+    if (w)
+        for (int c = threadIdx.x; c < H; c += blockDim.x) mx = fmaxf(mx, fabsf(w[c]));
+    for (int d = 16; d; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) mx = fmaxf(mx, red[i]);
+    int e = 0;
+    if (mx > 0.f && mx < 3.0e38f) (void)frexpf(mx, &e);                       // mx = f 2^e, 0.5 <= f < 1: s = 2^(14 - e) puts s mx in [2^13, 2^14)
+    const float sc = ldexpf(1.0f, 14 - e);
+    if (threadIdx.x == 0) inv_scale[r] = ldexpf(1.0f, e - 14);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = w ? w[c] * sc : 0.f;
+        const __half hi = __float2half_rn(v);
+        const float r1 = (v - __half2float(hi)) * 2048.0f;
+        const __half mid = __float2half_rn(r1);
+        const __half lo = __float2half_rn((r1 - __half2float(mid)) * 2048.0f);
+        pieces[(size_t)r * H + c] = hi;
+        pieces[((size_t)rpad + r) * H + c] = mid;
+        pieces[((size_t)2 * rpad + r) * H + c] = lo;
+    }
+}
+
+// lg[t, c] = (d[t, c] + 2^-11 d[t, rpad + c] + 2^-22 d[t, 2 rpad + c]) * inv_scale[c]: the three partial products of the pieces, smallest first
+__global__ void router_combine_kernel(const float* __restrict__ d, int64_t ldd, const float* __restrict__ inv_scale, int T, int R, int rpad, float* __restrict__ lg,
+                                      int64_t ldl) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)T * R) return;
+    const int t = (int)(i / R), c = (int)(i % R);
+    const float* row = d + (size_t)t * ldd;
+    lg[(size_t)t * ldl + c] = ((row[2 * rpad + c] * (1.0f / 2048.0f) + row[rpad + c]) * (1.0f / 2048.0f) + row[c]) * inv_scale[c];
+}
+
 // out[r, :] = x[src[r] / div, perm ? perm[c] : c]   (fp16 rows of k columns; 8 columns per thread). A source row outside [0, xrows) gives a row of zeros.
 __global__ void gather_rows_kernel(const __half* __restrict__ x, int64_t ldx, int64_t xrows, const uint32_t* __restrict__ src, int div, const uint32_t* __restrict__ perm, int R,
                                    int k, __half* __restrict__ out, int64_t ldo) {
@@ -600,4 +645,32 @@ extern "C" int kyb_router_logits(const void* x, int x_dtype, int64_t ldx, const 
     if (x_dtype == KYB_DT_F16) { KYB_ROUTER(__half); }
     KYB_ROUTER(__nv_bfloat16);
 #undef KYB_ROUTER
+}
+
+// ---- tensor-core router (prefill): kyb_router_split once per gate, kyb_router_logits_tc per call.
+// pieces: fp16 [3 * rpad, H] with rpad = kyb_router_rpad(E, shared) (rows rounded up to 8); inv_scale: float [rpad].
+extern "C" int64_t kyb_router_rpad(int E, int has_shared) { return ((int64_t)E + (has_shared ? 1 : 0) + 7) / 8 * 8; }
+
+extern "C" int kyb_router_split(const void* gw, const void* sgw, int E, int64_t H, void* pieces, void* inv_scale, void* stream) {
+    KYB_REQUIRE(gw && pieces && inv_scale, "null pointer");
+    KYB_REQUIRE(E > 0 && H > 0 && H < (1ll << 31), "E=%d H=%lld", E, (long long)H);
+    const int R = E + (sgw ? 1 : 0), rpad = (int)kyb_router_rpad(E, sgw != nullptr);
+    kyb::router_split_kernel<<<(unsigned)rpad, 256, 0, (cudaStream_t)stream>>>((const float*)gw, (const float*)sgw, E, R, rpad, (int)H, (__half*)pieces, (float*)inv_scale);
+    return kyb_launch_check("router_split");
+}
+
+// lg fp32 [T, >= R] = x fp16 [T, H] on the gate whose pieces were made by kyb_router_split (R = E + has_shared columns are written). work: float [T, 3 rpad]
+// (16-byte aligned), the partial products of the three pieces. Replaces the fp32 contraction of kyojin_mlx/foreign_moe.py:122-130 for many tokens: the products
+// run on tcgen05 (fp16 x fp16 -> fp32, exact products), one more launch recombines them.
+extern "C" int kyb_router_logits_tc(const void* x, int64_t ldx, const void* pieces, const void* inv_scale, int64_t T, int E, int has_shared, int64_t H, void* work,
+                                    void* lg, int64_t ldl, void* stream) {
+    KYB_REQUIRE(x && pieces && inv_scale && work && lg, "null pointer");
+    const int R = E + (has_shared ? 1 : 0), rpad = (int)kyb_router_rpad(E, has_shared);
+    KYB_REQUIRE(T > 0 && T < (1ll << 31) && E > 0 && H > 0 && H % 64 == 0 && ldx >= H && ldx % 8 == 0 && ldl >= R, "T=%lld E=%d H=%lld: H must be a multiple of 64", (long long)T, E,
+                (long long)H);
+    if (int rc = kyb_gemm_f16_tn_f32(x, ldx, pieces, H, T, 3 * (int64_t)rpad, H, 1.0f, work, 3 * (int64_t)rpad, stream)) return rc;
+    const int64_t total = T * R;
+    kyb::router_combine_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const float*)work, 3 * (int64_t)rpad, (const float*)inv_scale, (int)T, R, rpad,
+                                                                                                  (float*)lg, ldl);
+    return kyb_launch_check("router_combine");
 }

@@ -309,13 +309,18 @@ def dist_cases(E=256):
 
 
 def router(T=4096, E=256, H=7168, iters=10):
-    """The fp32 router product alone: x [T, H] fp16 on the gate [E, H] fp32 plus the shared-expert gate row."""
+    """The router product alone, x [T, H] fp16 on the gate [E, H] fp32 plus the shared-expert gate row: the fp32 kernels and the tensor-core form."""
     gen = torch.Generator(device="cuda").manual_seed(5)
     x = torch.randn((T, H), device="cuda", generator=gen).to(torch.float16)
     gw = torch.randn((E, H), device="cuda", generator=gen) * 0.02
     sgw = torch.randn((H,), device="cuda", generator=gen) * 0.02
-    t = timeit(lambda: ops.router_logits(x, gw, sgw), iters=iters)[1]
-    print(json.dumps({"case": f"router T={T} E={E} H={H}", "us": t, "fp32_TFLOPs": 2.0 * T * (E + 1) * H / t / 1e6}), flush=True)
+    t32 = timeit(lambda: ops.router_logits(x, gw, sgw, tensor_cores=False), iters=iters)[1]
+    ttc = timeit(lambda: ops.router_logits(x, gw, sgw, tensor_cores=True), iters=iters)[1]
+    want = x.double() @ torch.cat([gw, sgw[None]]).double().T
+    err = lambda lg: float((lg.double() - want).norm() / want.norm())
+    print(json.dumps({"case": f"router T={T} E={E} H={H}", "fp32_kernel_us": t32, "tensor_core_us": ttc, "fp32_kernel_TFLOPs": 2.0 * T * (E + 1) * H / t32 / 1e6,
+                      "rel_fro_fp32_kernel": err(ops.router_logits(x, gw, sgw, tensor_cores=False)),
+                      "rel_fro_tensor_core": err(ops.router_logits(x, gw, sgw, tensor_cores=True))}), flush=True)
 
 
 def main(argv):

@@ -4,7 +4,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, flags as F
 from .layout import FMT_ID, padded_rows
 
 
@@ -166,8 +166,29 @@ def moe_select(logits: torch.Tensor, E: int, K: int, norm: bool = True, has_shar
     return inds, scs, sgs
 
 
-def router_logits(x: torch.Tensor, gw: torch.Tensor, sgw: torch.Tensor | None = None) -> torch.Tensor:
-    """fp32 [T, E + 1] router logits of x [T, H] (fp32 / fp16 / bf16) on the fp32 gate gw [E, H]; column E = shared-expert gate logit (sgw [H]) or unwritten."""
+_ROUTER_PIECES: dict = {}
+
+
+def _router_pieces(gw: torch.Tensor, sg: torch.Tensor | None):
+    """The gate cut into three fp16 pieces per row for the tensor-core router, made once per (gate tensor, version) and kept (a few MB per gate)."""
+    key = (gw.data_ptr(), gw._version, tuple(gw.shape), None if sg is None else (sg.data_ptr(), sg._version))
+    hit = _ROUTER_PIECES.get(key)
+    if hit is None:
+        E, H = gw.shape
+        rpad = int(_lib.lib().kyb_router_rpad(E, 0 if sg is None else 1))
+        pieces = torch.empty((3 * rpad, H), dtype=torch.float16, device=gw.device)
+        inv = torch.empty((rpad,), dtype=torch.float32, device=gw.device)
+        _lib.check(_lib.lib().kyb_router_split(gw.data_ptr(), _p(sg), E, H, pieces.data_ptr(), inv.data_ptr(), _stream()))
+        if len(_ROUTER_PIECES) >= 64:
+            _ROUTER_PIECES.clear()
+        hit = _ROUTER_PIECES[key] = (pieces, inv, rpad, gw, sg)              # the gate tensors are kept alive so that their addresses stay theirs
+    return hit[0], hit[1], hit[2]
+
+
+def router_logits(x: torch.Tensor, gw: torch.Tensor, sgw: torch.Tensor | None = None, tensor_cores: bool | None = None) -> torch.Tensor:
+    """fp32 [T, E + 1] router logits of x [T, H] (fp32 / fp16 / bf16) on the fp32 gate gw [E, H]; column E = shared-expert gate logit (sgw [H]) or unwritten.
+    tensor_cores: None = by size (fp16 activations, at least flags.ROUTER_TC_MIN_ROWS tokens: one tcgen05 GEMM on the gate cut into three fp16 pieces + a
+    recombining launch; below that the fp32 kernels, whose two forms agree bit for bit); True / False force one path."""
     _need_cuda(x, gw)
     if gw.dtype != torch.float32 or x.dtype not in _DT or x.dim() != 2 or x.shape[1] != gw.shape[1]:
         raise ValueError("router_logits takes x [T, H] (fp32 / fp16 / bf16) and an fp32 gate [E, H]")
@@ -177,6 +198,16 @@ def router_logits(x: torch.Tensor, gw: torch.Tensor, sgw: torch.Tensor | None = 
     lg = torch.empty((T, E + 1), dtype=torch.float32, device=x.device)
     if sg is None:
         lg[:, E].zero_()                                                    # no shared expert: the column exists (fixed row pitch) and reads as 0
+    if tensor_cores is None:
+        tensor_cores = x.dtype == torch.float16 and T >= F.ROUTER_TC_MIN_ROWS and H % 64 == 0
+    if tensor_cores:
+        if x.dtype != torch.float16 or H % 64:
+            raise ValueError("the tensor-core router takes float16 activations with H a multiple of 64")
+        pieces, inv, rpad = _router_pieces(gw, sg)
+        work = workspace(x.device, T * 3 * rpad * 4)
+        _lib.check(_lib.lib().kyb_router_logits_tc(x.data_ptr(), x.stride(0), pieces.data_ptr(), inv.data_ptr(), T, E, 0 if sg is None else 1, H, work.data_ptr(), lg.data_ptr(),
+                                                   lg.stride(0), _stream()))
+        return lg
     _lib.check(_lib.lib().kyb_router_logits(x.data_ptr(), _DT[x.dtype], x.stride(0), gw.data_ptr(), _p(sg), T, E, H, lg.data_ptr(), lg.stride(0), _stream()))
     return lg
 

@@ -57,14 +57,45 @@ def test_router_logits_vs_fp64(T, E, H, dt):
     x = torch.randn((T, H), device="cuda", generator=g).to(dt)
     gw = torch.randn((E, H), device="cuda", generator=g) * 0.05
     sgw = torch.randn((H,), device="cuda", generator=g) * 0.05
-    lg = ops.router_logits(x, gw, sgw)
+    lg = ops.router_logits(x, gw, sgw, tensor_cores=False)
     want = x.double() @ torch.cat([gw, sgw[None]]).double().T
     assert lg.shape == (T, E + 1) and (lg.double() - want).abs().max().item() < 1e-4 * want.abs().max().item()
-    lg0 = ops.router_logits(x, gw, None)
+    lg0 = ops.router_logits(x, gw, None, tensor_cores=False)
     assert torch.equal(lg0[:, :E], lg[:, :E]) and (lg0[:, E] == 0).all()
     if T >= 1024:                                                           # many tokens take the weight-resident kernel: same bits as the token-resident one
-        parts = torch.cat([ops.router_logits(x[i:i + 500], gw, sgw) for i in range(0, T, 500)])
+        parts = torch.cat([ops.router_logits(x[i:i + 500], gw, sgw, tensor_cores=False) for i in range(0, T, 500)])
         assert torch.equal(parts, lg)
+
+
+@pytest.mark.parametrize("T,E,H", [(256, 256, 7168), (300, 64, 512), (1500, 256, 7168), (4096, 20, 1024), (70, 8, 256)])
+def test_router_logits_on_tensor_cores(T, E, H):
+    """The gate cut into three fp16 pieces, one tcgen05 product with fp32 accumulation, recombined: against the fp64 logits (same bound as the fp32 kernels, and
+    a tighter one on the relative Frobenius error), with and without the shared-expert row, rows with very different magnitudes (per-row scales), a zero row,
+    and the default dispatch (fp16 batches of 512 tokens or more take this path)."""
+    g = torch.Generator(device="cuda").manual_seed(T + 1)
+    x = torch.randn((T, H), device="cuda", generator=g).to(torch.float16)
+    gw = torch.randn((E, H), device="cuda", generator=g) * 0.05
+    gw[1] *= 1e-4
+    gw[2] *= 3e3
+    gw[3] = 0
+    gw[4, ::2] *= 1e-6                                                      # entries far below the row's maximum
+    sgw = torch.randn((H,), device="cuda", generator=g) * 0.05
+    want = x.double() @ torch.cat([gw, sgw[None]]).double().T
+    lg = ops.router_logits(x, gw, sgw, tensor_cores=True)
+    ops.check_device_status()
+    err = (lg.double() - want).abs()
+    scale = want.abs().amax(0, keepdim=True).clamp_min(1e-30)
+    assert lg.shape == (T, E + 1) and (err / scale).max().item() < 1e-4       # per gate row: every row is held to its own magnitude
+    assert (err.norm() / want.norm()).item() < 1e-5
+    assert (lg[:, 3] == 0).all()
+    f32 = ops.router_logits(x, gw, sgw, tensor_cores=False)
+    assert ((lg - f32).abs() / scale.float()).max().item() < 1e-4
+    lg0 = ops.router_logits(x, gw, None, tensor_cores=True)
+    assert torch.equal(lg0[:, :E], lg[:, :E]) and (lg0[:, E] == 0).all()
+    if T >= 512:
+        assert torch.equal(ops.router_logits(x, gw, sgw), lg)
+    with pytest.raises(ValueError):
+        ops.router_logits(x.float(), gw, sgw, tensor_cores=True)
 
 
 def _stack(fmt, E, n, k, seed):
