@@ -371,7 +371,7 @@ def run_ours(args):
             for c in range(copies):
                 layer = mods[c]
                 stages = []
-                for m in BATCHES:                                                # one stage per batch size: its upload / download overlap the neighbours' products
+                for m in sorted(BATCHES, reverse=True):                           # one stage per batch size: its upload / download overlap the neighbours' products; the largest batch first, so the download left exposed at the end of the step is the smallest
                     def stage_fn(*dx, layer=layer, m=m):
                         d = dict(zip(ks, dx))
                         outs = [layer[i](d[k_]) for i, (nm_, f_, n_, k_) in enumerate(mats)]

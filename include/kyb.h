@@ -128,6 +128,11 @@ int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const void* b_codes,
 int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub, void* stream);
 int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
                         const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream);
+/* gate and up of a routed SwiGLU layer as ONE grouped product with the gated activation in its epilogue: an item's 256 weight rows are 128 rows of the gate stack
+ * and the same 128 rows of the up stack; h fp16 [s, n] (sorted order) = silu(a) * b of the two products rounded to fp16 (what two kyb_gemm_kq_grouped calls would
+ * store), optional clamp `limit` as kyb_silu_mul. Replaces gmm, gmm, silu_perm of kyojin_mlx/foreign_kqgmm.py:293-314 `mlp`. n % 128 == 0, ldh % 8 == 0. */
+int kyb_gemm_kq_grouped_glu(int fmt, const void* t16_gate, const void* t16_up, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb,
+                            const void* off, const void* gs_gate, const void* gs_up, float limit, void* h, int64_t ldh, int mt, void* stream);
 
 /* ---- NVFP4 on the block-scaled tensor-core path.
  * kyb_nvfp4_quant_rows: activations (x_dtype 1 = fp16, 2 = bf16) [rows, k] -> packed e2m1 codes [rows, k/2] (two per byte, low nibble first) + one e4m3 scale per

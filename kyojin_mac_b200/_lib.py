@@ -128,6 +128,7 @@ SIGNATURES = {
     "kyb_gemm_kq_ag": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _pp, _i64, _i64, _int, _vp]),
     "kyb_gemm_nvfp4_ag": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _pp, _i64, _i64, _vp]),
     "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),
+    "kyb_gemm_kq_grouped_glu": (_int, [_int, _vp, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _f32, _vp, _i64, _int, _vp]),
     "kyb_dequant_rows_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _f32, _int, _vp, _i64, _vp]),
     "kyb_router_rpad": (_i64, [_int, _int]),
     "kyb_router_split": (_int, [_vp, _vp, _int, _i64, _vp, _vp, _vp]),

@@ -48,17 +48,23 @@ struct KqParams {
     int msub, stages;
     int tma_out, col0;          // dense form: the epilogue stores through the tensor maps (bulk tiled stores), at column col0 + n0
     int wide;                   // ... in 32 x 64 boxes (4 KB of staging per epilogue warp) instead of 32 x 32: used when the tiles also go to other GPUs
+    // gated pair (grouped form): an item's 256 weight rows are 128 rows of the gate stack (t16) and the same 128 rows of the up stack (t16b); the epilogue writes
+    // fp16(silu(a) * b) of the two fp16-rounded products, 128 output columns per item (kyojin_mlx/foreign_kqgmm.py:293-314 `mlp`: gmm, gmm, silu_perm in one launch)
+    const uint8_t* t16b;
+    const float* gsb;           // per-expert output scale of the up stack (or null)
+    int glu;
+    float limit;                // > 0: a = min(a, limit), b = clamp(b, -limit, limit) as the activation kernel does
 };
 
 struct KqItem {
     int m0, m_end, n0, b_rt0, nsub;
-    float gscale;
+    float gscale, gscale_b;
     bool valid;
 };
 
 __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t, const uint16_t* tord = nullptr) {
     KqItem it;
-    it.valid = true, it.gscale = p.gscale, it.m_end = p.m;
+    it.valid = true, it.gscale = p.gscale, it.gscale_b = p.gscale, it.m_end = p.m;
     if (!p.tb) {
         const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;                         // m fastest: CTAs running together share the weight rows
         it.n0 = tn * KQ_BN, it.m0 = tm * 128 * p.msub, it.b_rt0 = it.n0 >> 4;
@@ -67,7 +73,7 @@ __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t, const uint16
     }
     int tm = t / p.tiles_n;
     const int tn = t - tm * p.tiles_n;                                                   // n fastest: CTAs running together share the activation rows
-    it.n0 = tn * KQ_BN;
+    it.n0 = tn * (p.glu ? KQ_BN / 2 : KQ_BN);
     if ((uint32_t)tm >= p.tb[p.experts]) {
         it.valid = false;
         return it;
@@ -83,6 +89,7 @@ __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t, const uint16
     it.nsub = min(p.msub, (it.m_end - it.m0 + 127) >> 7);                                // a segment tail of up to 128 rows runs one block
     it.b_rt0 = (lo * p.n + it.n0) >> 4;
     if (p.gs) it.gscale = p.gs[lo];
+    if (p.gsb) it.gscale_b = p.gsb[lo];
     return it;
 }
 
@@ -534,21 +541,35 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                         dst[i] = p.d[0] + (size_t)o * p.ldd + it.n0 + 8 * (lane & 3);
                     }
 #pragma unroll 1
-                    for (int c = 0; c < KQ_BN; c += 32) {
-                        uint32_t v[32];
+                    for (int c = 0; c < (p.glu ? KQ_BN / 2 : KQ_BN); c += 32) {
+                        uint32_t v[32], w[16];
                         tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
                         tmem_ld_wait();
-                        __syncwarp();                                                  // the previous step's reads of the staging buffer are done
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            uint32_t w[4];
+                        for (int i = 0; i < 16; ++i) {
+                            __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * i]) * gscale), sat_half(__uint_as_float(v[2 * i + 1]) * gscale));
+                            w[i] = *reinterpret_cast<uint32_t*>(&h);
+                        }
+                        if (p.glu) {
+                            // w holds the gate products rounded to fp16 (what the reference's two-launch form would have stored); the up products of the same
+                            // output columns sit 128 accumulator columns further
+                            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)(KQ_BN / 2 + c), v);
+                            tmem_ld_wait();
+                            const float gsb = it.gscale_b, lim = p.limit;
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                __half2 h = __halves2half2(sat_half(__uint_as_float(v[8 * j + 2 * i]) * gscale), sat_half(__uint_as_float(v[8 * j + 2 * i + 1]) * gscale));
+                            for (int i = 0; i < 16; ++i) {
+                                const __half2 a2 = *reinterpret_cast<__half2*>(&w[i]);
+                                float a0 = __low2float(a2), a1 = __high2float(a2);
+                                float b0 = __half2float(sat_half(__uint_as_float(v[2 * i]) * gsb)), b1 = __half2float(sat_half(__uint_as_float(v[2 * i + 1]) * gsb));
+                                if (lim > 0.f) a0 = fminf(a0, lim), a1 = fminf(a1, lim), b0 = fminf(fmaxf(b0, -lim), lim), b1 = fminf(fmaxf(b1, -lim), lim);
+                                __half2 h = __halves2half2(sat_half(a0 * (1.0f / (1.0f + expf(-a0))) * b0), sat_half(a1 * (1.0f / (1.0f + expf(-a1))) * b1));
                                 w[i] = *reinterpret_cast<uint32_t*>(&h);
                             }
-                            sts128(stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4), make_uint4(w[0], w[1], w[2], w[3]));
                         }
+                        __syncwarp();                                                  // the previous step's reads of the staging buffer are done
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            sts128(stg + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) << 4), make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]));
                         __syncwarp();
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -607,8 +628,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
             const KqItem it = kq_item(p, t, tord);
             if (!it.valid) continue;
-            const int rt = min(it.b_rt0 + dw, p.rt_total - 1);
-            const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
+            const int rt = min(it.b_rt0 + (p.glu ? (dw & 7) : dw), p.rt_total - 1);      // gated pair: warps 0-7 decode the gate rows, 8-15 the same rows of the up stack
+            const uint8_t* tp = ((p.glu && dw >= 8) ? p.t16b : p.t16) + (size_t)rt * (size_t)p.nb * TB;
             // Software pipeline over the 64-input quarters: while the stores of quarter q drain into the stage (and before the proxy fence that publishes them), the
             // registers of quarter q + 1 are computed, so the wait for a free stage, the scale loads and the arithmetic overlap the shared-memory traffic.
             KqTile<FMT> tr;
@@ -749,6 +770,7 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     for (int i = 0; i < nout && p.tma_out; ++i)
         if ((uintptr_t)d[i] & 15) p.tma_out = 0;
     p.wide = (p.tma_out && nout > 1) ? 1 : 0;
+    p.t16b = nullptr, p.gsb = nullptr, p.glu = 0, p.limit = 0.f;
     for (int i = 0; i < nout && p.tma_out; ++i)
         if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
                                       p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
@@ -782,8 +804,10 @@ extern "C" int kyb_gemm_kq_ag(int fmt, const void* t16, int64_t n, int64_t k, co
 // tb / off from kyb_moe_plan with the same mt (128 or 256 rows of one expert per work item: with 256 a decoded weight tile serves up to two 128-row blocks, so an
 // expert with 129..256 rows is decoded once, not twice), row_map (optional, u32 [s]) = output row of each sorted row, gs (optional) per-expert output scale.
 // d [*, n]. The item list is sized for the worst case (s / mt + experts tiles per 256 output columns); items past tb[experts] are skipped.
-extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
-                                   const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream) {
+// t16b != null: the gated pair. t16 / t16b are the gate and up stacks of one shape, d [s, n] = fp16(silu(a) * b) of their fp16-rounded products.
+static int kq_grouped(int fmt, const void* t16, const void* t16b, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
+                      const void* row_map, const void* gs, const void* gsb, float limit, void* d, int64_t ldd, int mt, void* stream) {
+    const bool glu = t16b != nullptr;
     KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
     if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0) {
         kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
@@ -793,7 +817,12 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
     KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,
                 (long long)k, experts);
-    KYB_REQUIRE(n % 256 == 0, "the grouped product needs n %% 256 == 0 (an output tile must not straddle two experts), got n=%lld", (long long)n);
+    if (glu) {
+        KYB_REQUIRE(n % 128 == 0, "the gated pair needs n %% 128 == 0, got n=%lld", (long long)n);
+        KYB_REQUIRE(ldd % 8 == 0 && ((uintptr_t)d & 15) == 0 && ((uintptr_t)t16b & 15) == 0 && !row_map, "the gated pair stores 16-byte pieces in sorted order: ldd %% 8 == 0, aligned d, no row_map");
+    } else {
+        KYB_REQUIRE(n % 256 == 0, "the grouped product needs n %% 256 == 0 (an output tile must not straddle two experts), got n=%lld", (long long)n);
+    }
     KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
     KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0, "a and t16 must be 16-byte aligned");
     KYB_REQUIRE(s < (1ll << 31) && (int64_t)experts * n < (1ll << 31) && k < (1ll << 24), "dimension too large");
@@ -808,10 +837,25 @@ extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t 
     p.rt_total = (int)((int64_t)experts * n / 16);
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     p.msub = mt / 128;
-    p.tiles_n = (int)(n / kyb::KQ_BN), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
-    p.tma_out = 0, p.col0 = 0, p.wide = 0;                                         // rows are scattered (row_map) or end inside a tile: stores from registers
+    p.t16b = (const uint8_t*)t16b, p.gsb = (const float*)gsb, p.glu = glu ? 1 : 0, p.limit = limit;
+    p.tiles_n = (int)(n / (glu ? kyb::KQ_BN / 2 : kyb::KQ_BN)), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
+    p.tma_out = 0, p.col0 = 0, p.wide = 0;                                         // rows are scattered (row_map) or end inside a tile: no tensor map fits
     KybOutMaps outs;
     memset(&outs, 0, sizeof(outs));
     if (int rc = kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream)) return rc;
     return kyb_zero_tail_rows(d, ldd, n, row_map, (const uint32_t*)off + experts, s, (cudaStream_t)stream);   // slots that belong to no expert: rows of zeros
+}
+
+extern "C" int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
+                                   const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream) {
+    return kq_grouped(fmt, t16, nullptr, n, k, experts, a, lda, s, tb, off, row_map, gs, nullptr, 0.f, d, ldd, mt, stream);
+}
+
+// Gate and up of a routed SwiGLU layer as ONE grouped product with the gated activation in its epilogue: h fp16 [s, n] (sorted order) = silu(a) * b with
+// a = fp16(x W_gate^T), b = fp16(x W_up^T) (the values the two-launch form would have written) and the optional clamp of kyb_silu_mul. Replaces two
+// kyb_gemm_kq_grouped calls and kyb_silu_mul (kyojin_mlx/foreign_kqgmm.py:293-314 `mlp`: gmm, gmm, silu_perm).
+extern "C" int kyb_gemm_kq_grouped_glu(int fmt, const void* t16_gate, const void* t16_up, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s,
+                                       const void* tb, const void* off, const void* gs_gate, const void* gs_up, float limit, void* h, int64_t ldh, int mt, void* stream) {
+    KYB_REQUIRE(t16_up, "null pointer");
+    return kq_grouped(fmt, t16_gate, t16_up, n, k, experts, a, lda, s, tb, off, nullptr, gs_gate, gs_up, limit, h, ldh, mt, stream);
 }

@@ -453,6 +453,198 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ the same product by CTA pairs (tcgen05 cta_group::2)
+// A cluster of two CTAs on neighbouring SMs computes a 256 x 256 tile: each CTA holds 128 rows of A and ONE HALF (128 rows) of the B tile in its shared memory,
+// and a single MMA instruction issued by the pair's leader (cluster rank 0) runs on both tensor cores, each reading its own A rows and both halves of B. Per SM
+// the B operand bytes written by TMA and read by the MMA are halved, which is what bounds the one-CTA kernel above (shared-memory bandwidth). Protocol:
+//   full[s]   lives in the leader: one arrival (the leader's producer, with the byte count of BOTH CTAs' loads); every load of either CTA completes on it
+//             (cp.async.bulk.tensor ... cta_group::2 with the leader's barrier address; no multicast anywhere)
+//   empty[s]  lives in each CTA: the leader's tcgen05.commit arrives on both (commit multicast to the pair)
+//   accf      in each CTA (commit multicast): the accumulator of the tile is complete; acce in the leader: 8 arrivals, the 4 epilogue warps of each CTA
+// Scale factors: every CTA loads the chunks of its own 128 A rows and of ALL 256 B rows (4 KB per stage; both tensor cores need every column's scales), as tiled
+// loads through two more tensor maps over the SF512 arrays, and tcgen05.cp cta_group::2 moves them into the tensor memory of both CTAs.
+// Every wait is bounded; the pair meets at a cluster barrier before tensor memory is freed, so neither CTA leaves while the other can still signal it.
+constexpr int NP_STAGES = 5;
+constexpr uint32_t NP_A_BYTES = 128 * NV_BK / 2, NP_B_BYTES = 128 * NV_BK / 2, NP_STAGE_BYTES = NP_A_BYTES + NP_B_BYTES + NV_SFA_BYTES + NV_SFB_BYTES;   // 16 K + 16 K + 2 K + 4 K
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// tiled load into this CTA's shared memory whose bytes complete on a barrier of the pair's leader (bar: shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm), "r"(x),
+                 "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) { asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) { asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory"); }
+__device__ __forceinline__ void tmem_cp_32x128b_x4_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_nvf4_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa, uint32_t tsfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once every tcgen05 operation issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NV_THREADS, 1)
+    gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_sfa,
+                           const __grid_constant__ CUtensorMap tma_sfb, const __grid_constant__ KybOutMaps outs, const NvGemmParams p, const int tiles_n, const int num_tiles) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    constexpr int STAGES = NP_STAGES;
+    const uint32_t stg0 = smem0 + STAGES * NP_STAGE_BYTES;                         // epilogue staging, 4 warps
+    const uint32_t bars = stg0 + 4 * KYB_STG_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf = bars + 16 * STAGES, acce = accf + 8, tmem_slot = acce + 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
+    const int kblocks = p.k / NV_BK, k64 = p.k / 64;
+    const int tiles_m = num_tiles / tiles_n;                                       // 256-row tiles
+    constexpr uint32_t TMEM_COLS = 512, COL_SFA = 256, COL_SFB = 272;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init_a(full0 + 8 * s, 1), mbar_init_a(empty0 + 8 * s, 1);
+        mbar_init_a(accf, 1);
+        mbar_init_a(acce, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tma_a);
+        prefetch_tmap(&tma_b);
+        prefetch_tmap(&tma_sfa);
+        prefetch_tmap(&tma_sfb);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    cluster_sync_all();                                                            // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    bool failed = false;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            uint32_t parity = 1;
+            int s = 0;
+            for (int t = pair; t < num_tiles && !failed; t += pairs) {
+                const int n0 = (t / tiles_m) * NV_BN, m0 = (t % tiles_m) * 256 + (int)rank * 128;      // m fastest; this CTA's 128 rows of the tile
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                    const uint32_t a_dst = smem0 + s * NP_STAGE_BYTES, b_dst = a_dst + NP_A_BYTES, sfa_dst = b_dst + NP_B_BYTES, sfb_dst = sfa_dst + NV_SFA_BYTES;
+                    if (rank == 0) mbar_expect_tx_a(full0 + 8 * s, 2 * NP_STAGE_BYTES);
+                    const uint32_t bar = map_to_rank(full0 + 8 * s, 0);
+                    tma_load_2d_pair(a_dst, &tma_a, kb * (NV_BK / 2), m0, bar);
+                    tma_load_2d_pair(b_dst, &tma_b, kb * (NV_BK / 2), n0 + (int)rank * 128, bar);   // this CTA's half of the B tile
+                    tma_load_2d_pair(sfa_dst, &tma_sfa, 0, (m0 >> 7) * k64 + kb * 4, bar);
+                    tma_load_2d_pair(sfb_dst, &tma_sfb, 0, (n0 >> 7) * k64 + kb * 4, bar);
+                    tma_load_2d_pair(sfb_dst + 2048, &tma_sfb, 0, ((n0 >> 7) + 1) * k64 + kb * 4, bar);
+                    if (++s == STAGES) s = 0, parity ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_nvf4(256, NV_BN);
+            uint32_t parity = 0;
+            int s = 0, it = 0;
+            for (int t = pair; t < num_tiles && !failed; t += pairs, ++it) {
+                if (!mbar_wait_fast(acce, ((uint32_t)it & 1u) ^ 1u)) failed = true;         // both CTAs' epilogues have read the accumulator
+                tc_fence_after();
+                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                    if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                    tc_fence_after();
+                    const uint32_t a_src = smem0 + s * NP_STAGE_BYTES, b_src = a_src + NP_A_BYTES, sfa_src = b_src + NP_B_BYTES, sfb_src = sfa_src + NV_SFA_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        tmem_cp_32x128b_x4_pair(tmem_base + COL_SFA + 4 * j, sf_desc(sfa_src + 512 * j));
+                        tmem_cp_32x128b_x4_pair(tmem_base + COL_SFB + 8 * j, sf_desc(sfb_src + 512 * j));
+                        tmem_cp_32x128b_x4_pair(tmem_base + COL_SFB + 8 * j + 4, sf_desc(sfb_src + 2048 + 512 * j));
+                    }
+                    const uint64_t adesc = umma_desc_sw128(a_src), bdesc = umma_desc_sw128(b_src);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        umma_nvf4_pair(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, tmem_base + COL_SFA + 4 * j, tmem_base + COL_SFB + 8 * j, (kb | j) != 0);
+                    umma_commit_pair(empty0 + 8 * s);
+                    if (++s == STAGES) s = 0, parity ^= 1u;
+                }
+                umma_commit_pair(accf);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const uint32_t acce_leader = map_to_rank(acce, 0);
+        int it = 0;
+        for (int t = pair; t < num_tiles; t += pairs, ++it) {
+            const int n0 = (t / tiles_m) * NV_BN, m0 = (t % tiles_m) * 256 + (int)rank * 128;
+            if (!mbar_wait_fast(accf, (uint32_t)it & 1u)) failed = true;
+            tc_fence_after();
+            const uint32_t stg = stg0 + (uint32_t)q * KYB_STG_BYTES;
+            const int row0 = m0 + q * 32;
+            const uint32_t tq = tmem_base + ((uint32_t)(q * 32) << 16);
+            uint32_t w[NV_BN / 32][16];
+            auto pack = [&](const uint32_t (&v)[32], uint32_t (&o)[16]) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float f0 = __uint_as_float(v[2 * j]) * p.gscale, f1 = __uint_as_float(v[2 * j + 1]) * p.gscale;
+                    if (p.out_bf16) {
+                        __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                        o[j] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                        __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                        o[j] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                }
+            };
+            {
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32(tq, v0);
+#pragma unroll
+                for (int ch = 0; ch < NV_BN / 32; ch += 2) {
+                    tmem_ld_wait();
+                    tmem_ld_32x32(tq + (uint32_t)(32 * (ch + 1)), v1);
+                    pack(v0, w[ch]);
+                    tmem_ld_wait();
+                    if (ch + 2 < NV_BN / 32) tmem_ld_32x32(tq + (uint32_t)(32 * (ch + 2)), v0);
+                    pack(v1, w[ch + 1]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acce_leader);                               // this warp has read its quarter of this CTA's accumulator
+#pragma unroll
+            for (int ch = 0; ch < NV_BN / 32; ++ch)
+                epilogue_stage_store(outs, 1, stg, lane, w[ch], n0 + 32 * ch, row0, !failed && row0 < p.m);
+        }
+    }
+    if (warp >= 2 && lane == 0) tma_store_wait_all();                              // the staging buffer must outlive its stores
+    if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
+    tc_fence_before();
+    cluster_sync_all();                                                            // neither CTA frees tensor memory or leaves while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace kyb
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -531,7 +723,7 @@ extern "C" int kyb_nvfp4_sf_swizzle(void* plain, int64_t rows, int64_t k, void* 
 
 // D [m, n] = sat(gscale * A B^T): a_codes [m, k/2], b_codes [n, k/2] packed e2m1 (two per byte, low nibble first), sfa / sfb in the SF512 layout.
 static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_codes, const void* sfb, int64_t m, int64_t n, int64_t k, float gscale, int out_dtype,
-                           void* const* d, int nout, int64_t ldd, int64_t col0, void* stream) {
+                           void* const* d, int nout, int64_t ldd, int64_t col0, void* stream, bool pair_ok = true) {
     KYB_REQUIRE(a_codes && sfa && b_codes && sfb, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(n % 256 == 0, "n=%lld must be a multiple of 256 (one CTA covers two 128-row scale chunks of B)", (long long)n);
@@ -558,12 +750,46 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
         if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
                                       p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
-    const size_t smem = (size_t)p.stages * kyb::NV_STAGE_BYTES + 4 * (p.wide ? 2 : 1) * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
-    constexpr size_t smem_max = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
-    static std::mutex mu;
-    static unsigned done = 0;
     int dev = 0;
     KYB_CUDA(cudaGetDevice(&dev));
+    static std::mutex mu;
+    if (nout == 1 && p.tma_out && m > 128 && pair_ok) {
+        // one destination and at least two row blocks: CTA pairs (cta_group::2), each CTA holding half of the B tile
+        CUtensorMap tbh, tsa, tsb;
+        const uint64_t k64 = (uint64_t)(k / 64);
+        if (int rc = kyb_make_tmap_2d(&tbh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_codes, (uint64_t)n, (uint64_t)(k / 2), (uint64_t)(k / 2), 128, 128)) return rc;
+        if (int rc = kyb_make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sfa, (uint64_t)((m + 127) / 128) * k64, 128, 512, 4, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+        if (int rc = kyb_make_tmap_2d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sfb, (uint64_t)(n / 128) * k64, 128, 512, 4, 128, CU_TENSOR_MAP_SWIZZLE_NONE)) return rc;
+        constexpr size_t psmem = (size_t)kyb::NP_STAGES * kyb::NP_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NP_STAGES + 32 + 1024;
+        static unsigned pdone = 0;
+        static int pairs_max[32] = {0};
+        {
+            std::lock_guard<std::mutex> lk(mu);
+            if (!(pdone & (1u << (dev & 31)))) {
+                KYB_CUDA(cudaFuncSetAttribute(kyb::gemm_nvfp4_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)psmem));
+                // how many pairs the device can hold at once (one CTA per SM, pairs on neighbouring SMs)
+                cudaLaunchConfig_t qc = {};
+                qc.gridDim = dim3(2), qc.blockDim = dim3(kyb::NV_THREADS), qc.dynamicSmemBytes = psmem;
+                int nc = 0;
+                if (cudaOccupancyMaxActiveClusters(&nc, kyb::gemm_nvfp4_pair_kernel, &qc) != cudaSuccess || nc <= 0) {
+                    (void)cudaGetLastError();
+                    nc = 0;
+                }
+                pairs_max[dev & 31] = nc;
+                pdone |= 1u << (dev & 31);
+            }
+        }
+        const int pm = pairs_max[dev & 31];
+        if (pm > 0) {
+            const int tiles_n = (int)(n / kyb::NV_BN), num_tiles = tiles_n * (int)((m + 255) / 256);
+            const int pairs = num_tiles < pm ? num_tiles : pm;
+            kyb::gemm_nvfp4_pair_kernel<<<(unsigned)(2 * pairs), kyb::NV_THREADS, psmem, (cudaStream_t)stream>>>(ta, tbh, tsa, tsb, outs, p, tiles_n, num_tiles);
+            return kyb_launch_check("gemm_nvfp4_pair");
+        }
+    }
+    const size_t smem = (size_t)p.stages * kyb::NV_STAGE_BYTES + 4 * (p.wide ? 2 : 1) * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
+    constexpr size_t smem_max = (size_t)kyb::NV_STAGES * kyb::NV_STAGE_BYTES + 4 * KYB_STG_BYTES + 16 * kyb::NV_STAGES + 32 + 1024;
+    static unsigned done = 0;
     {
         std::lock_guard<std::mutex> lk(mu);
         if (!(done & (1u << (dev & 31)))) {

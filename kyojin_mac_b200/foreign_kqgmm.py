@@ -20,6 +20,12 @@ def fused_ok(dev) -> bool:
     return dev.n % 256 == 0 and not F.PREFILL_TWO_STEP and dev.fmt in PREFILL_FUSED
 
 
+def glu_fused_ok(glu) -> bool:
+    """gate and up can run as one grouped product: both decoded inside the GEMM, one format and shape, 128 output columns per work item."""
+    g, u = glu.g, glu.u
+    return fused_ok(g) and fused_ok(u) and (g.fmt, g.n, g.k, g.E) == (u.fmt, u.n, u.k, u.E) and g.n % 128 == 0
+
+
 def csort(e32: torch.Tensor, E: int, mt: int = MT):
     """Slots -> (order [S] sorted position -> slot, tb [E+1] first tile of each expert, off [E+1] first row of each expert)."""
     pl = ops.moe_plan(e32, E, 1, mt)
@@ -62,9 +68,13 @@ def mlp(glu, x2: torch.Tensor, e32: torch.Tensor, K: int, mt: int | None = None)
         mt = MT_FUSED if all(fused_ok(d) for d in (glu.g, glu.u, glu.d)) else MT
     order, tb, off = csort(e32, glu.g.E, mt)
     xg = gather_perm(x2, order, K)
-    a = gmm(glu.g, xg, tb, off, S, mt)
-    b = gmm(glu.u, xg, tb, off, S, mt)
-    h = silu_perm(a, b, None, glu.limit)
+    if glu_fused_ok(glu):                                                            # gate | up as one grouped product, silu(a) * b in its epilogue
+        gsg, gsu = (glu.g.gs, glu.u.gs) if glu.g.fmt == "nvfp4" else (None, None)
+        h = ops.gemm_kq_grouped_glu(glu.g.fmt, glu.g.t16, glu.u.t16, glu.g.n, glu.g.k, glu.g.E, xg, tb, off, gsg, gsu, glu.limit, mt)
+    else:
+        a = gmm(glu.g, xg, tb, off, S, mt)
+        b = gmm(glu.u, xg, tb, off, S, mt)
+        h = silu_perm(a, b, None, glu.limit)
     return gmm(glu.d, h, tb, off, S, mt, orow=order)
 
 

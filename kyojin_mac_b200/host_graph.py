@@ -119,12 +119,23 @@ class HostGraph:
                 body()
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
+        # the capture runs on the warm-up stream: per-stream scratch (ops.workspace) set up by the warm-up is found again, so nothing is allocated inside the graph
+        from . import ops
+        self._side = side
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=side):
             body()
+        self._scratch = ops._ws.get((self.device.index, side.cuda_stream))  # the graph holds this buffer's address: it lives as long as the graph
         self.outputs = [v for st in self.stages for v in st.outputs]
         self.h2d_bytes = sum(int(st.hin.numel()) for st in self.stages)
         self.d2h_bytes = sum(int(st.hout.numel()) for st in self.stages)
+
+    def __del__(self):
+        try:
+            from . import ops
+            ops.release_workspaces(self._side.cuda_stream)                  # the scratch cached for this graph's capture stream goes with the graph
+        except Exception:
+            pass
 
     def launch(self):
         """Replays the step without waiting (results are valid after a synchronisation of the current stream)."""

@@ -386,6 +386,18 @@ def gemm_kq_grouped(fmt, t16: torch.Tensor, n: int, k: int, E: int, a: torch.Ten
     return d
 
 
+def gemm_kq_grouped_glu(fmt, t16_gate: torch.Tensor, t16_up: torch.Tensor, n: int, k: int, E: int, a: torch.Tensor, tb: torch.Tensor, off: torch.Tensor,
+                        gs_gate: torch.Tensor | None = None, gs_up: torch.Tensor | None = None, limit: float | None = None, mt: int = 256) -> torch.Tensor:
+    """h fp16 [s, n] = silu(a W_gate^T) * (a W_up^T) on sorted rows, the gate and up stacks of a routed layer in ONE grouped product with the gated activation in
+    its epilogue (both products rounded to fp16 first, as the separate launches would store them)."""
+    _need_cuda(t16_gate, t16_up, a, tb, off)
+    s = a.shape[0]
+    h = torch.empty((s, n), dtype=torch.float16, device=a.device)
+    _lib.check(_lib.lib().kyb_gemm_kq_grouped_glu(_fmt(fmt), t16_gate.data_ptr(), t16_up.data_ptr(), n, k, E, a.data_ptr(), a.stride(0), s, tb.data_ptr(), off.data_ptr(),
+                                                  _p(gs_gate), _p(gs_up), float(limit or 0.0), h.data_ptr(), h.stride(0), mt, _stream()))
+    return h
+
+
 # ------------------------------------------------------------------------------------------------ NVFP4 tensor-core path
 _DT = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
 

@@ -208,3 +208,27 @@ def test_grouped_gemm_equals_per_expert(mt):
         np.testing.assert_array_equal(yn[rows], one)                          # same tile arithmetic, row for row
         want = O.matmul_f64(x[rows], W[ex])
         assert O.rel_fro(yn[rows], want) <= 1e-3
+
+
+@pytest.mark.parametrize("fmt,mt,limit", [("q4_k", 256, None), ("q4_k", 128, 7.0), ("q6_k", 256, None), ("nvfp4", 256, 3.0)])
+def test_gated_pair_in_one_grouped_product(fmt, mt, limit):
+    """gate | up as ONE grouped product with silu(a) * b in its epilogue == two grouped products + the activation launch, bit for bit (the epilogue rounds both
+    products to fp16 first, as the separate launches store them), on ragged segments incl. an empty expert, segments of more than 128 and more than 256 rows,
+    and slots without an expert (rows of zeros)."""
+    E, n, k, S = 6, 512, 512, 1100
+    g, _ = _stack(fmt, E, n, k, 30)
+    u, _ = _stack(fmt, E, n, k, 31)
+    rng = np.random.default_rng(32)
+    e = rng.choice(E, S, p=[0.45, 0.0, 0.05, 0.2, 0.2, 0.1]).astype(np.int32)  # expert 1 empty, expert 0 ~ 500 rows
+    e[5:9] = -1
+    x = torch.from_numpy(synth.activations(S, k, rng)).cuda()
+    order, tb, off = KQ.csort(torch.from_numpy(e).cuda(), E, mt)
+    xg = KQ.gather_perm(x, order, 1)
+    a = KQ.gmm(g, xg, tb, off, S, mt)
+    b = KQ.gmm(u, xg, tb, off, S, mt)
+    want = KQ.silu_perm(a, b, None, limit)
+    gsg, gsu = (g.gs, u.gs) if fmt == "nvfp4" else (None, None)
+    got = ops.gemm_kq_grouped_glu(fmt, g.t16, u.t16, n, k, E, xg, tb, off, gsg, gsu, limit, mt)
+    ops.check_device_status()
+    assert torch.equal(got, want)
+    assert (got[S - 4:] == 0).all()                                            # the four slots without an expert sort to the tail
