@@ -49,7 +49,7 @@ constexpr int GEMV_STAGES = 2;           // ring depth per warp: a stage is hand
 constexpr int GEMV_DSTAGES = 2;          // the same for the dense kernel (a four-stage ring measured 1-3 % slower on large matrices: the kernel is not limited by bytes in flight)
 
 template <int FMT>
-__host__ __device__ constexpr int xaux_bytes_per_block(int nt) { return kyb_has_mins(FMT) ? 256 * nt : 0; }
+__host__ __device__ constexpr int xaux_bytes_per_block(int nt) { return kyb_has_mins(FMT) ? 256 * nt : kyb_has_mins16(FMT) ? 512 * nt : 0; }
 
 __device__ __forceinline__ uint32_t magic_sub(uint32_t h2_with_magic, uint32_t sub_bits) {
     __half2 a = *reinterpret_cast<__half2*>(&h2_with_magic), b = *reinterpret_cast<__half2*>(&sub_bits);
@@ -116,6 +116,14 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         o.z = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7442u)), d, nd);
         o.w = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7443u)), d, nd);
         sts128f(scl + 4 * (r * SCL_STRIDE + 4 * hf), o);
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        const uint2 sw = lds64(tile + 1024 + r * 16 + 8 * hf);             // scale | min << 4 of slices 8 hf .. 8 hf + 7
+        const float d = half_bits_to_float(lds16(tile + 1280 + r * 4)) * 16777216.0f;   // the 2-bit codes enter the MMA as fp16 subnormals (code * 2^-24)
+        float4 a, b;
+        a.x = d * (float)(sw.x & 15u), a.y = d * (float)((sw.x >> 8) & 15u), a.z = d * (float)((sw.x >> 16) & 15u), a.w = d * (float)((sw.x >> 24) & 15u);
+        b.x = d * (float)(sw.y & 15u), b.y = d * (float)((sw.y >> 8) & 15u), b.z = d * (float)((sw.y >> 16) & 15u), b.w = d * (float)((sw.y >> 24) & 15u);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf), a);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 8 * hf + 4), b);
     } else if constexpr (FMT == KYB_FMT_Q8_0) {
         const uint2 dw = lds64(tile + 4096 + r * 16 + 8 * hf);             // four of the row's eight fp16 d
         float4 o;
@@ -157,8 +165,9 @@ __device__ __forceinline__ void scale_acc(Acc<NT>& acc, const float (&c)[NT][4],
 // ---- the part of a tile one lane keeps in registers, so that the ring stage can be handed back to the copy engine before the arithmetic starts
 template <int FMT>
 struct TileRegs {
-    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : FMT == KYB_FMT_Q5_K ? 5 : FMT == KYB_FMT_Q8_0 ? 8 : 4];
-    uint32_t a0, a1;      // q4_k, q5_k: 6-bit mins of rows g, g + 8 as m16n8k8 A operands
+    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : FMT == KYB_FMT_Q5_K ? 5 : FMT == KYB_FMT_Q8_0 ? 8 : FMT == KYB_FMT_Q2_K ? 2 : 4];
+    uint32_t a0, a1;      // q4_k, q5_k: 6-bit mins of rows g, g + 8 as m16n8k8 A operands; q2_k: 4-bit mins of slices 2t, 2t + 1 (a0, a1) and 2t + 8, 2t + 9 (a2, a3) as m16n8k16 A operands
+    uint32_t a2, a3;
     float dmg, dmh;       // q4_k, q5_k: dmin of rows g, g + 8 (scaled to the operand convention)
 };
 
@@ -195,6 +204,16 @@ __device__ __forceinline__ void load_tile(uint32_t tile, int lane, TileRegs<FMT>
         for (int P = 0; P < 4; ++P) tr.q[P] = lds128(tile + (P * 32 + lane) * 16);
         tr.q[4] = lds128(tile + 2048 + lane * 16);
         tr.q[5] = lds128(tile + 2048 + (32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        tr.q[0] = lds128(tile + lane * 16);
+        tr.q[1] = lds128(tile + (32 + lane) * 16);
+        // 4-bit mins (high nibbles of the 16 scale bytes of a row) of slices 2t, 2t + 1 and 2t + 8, 2t + 9 as fp16 subnormals (mn * 2^-24)
+        const uint4 sg = lds128(tile + 1024 + g * 16), sh = lds128(tile + 1024 + (g + 8) * 16);
+        const uint32_t lo_g = (t & 2) ? sg.y : sg.x, hi_g = (t & 2) ? sg.w : sg.z, lo_h = (t & 2) ? sh.y : sh.x, hi_h = (t & 2) ? sh.w : sh.z;
+        const uint32_t sel = (t & 1) ? 0x4342u : 0x4140u;
+        tr.a0 = prmt((lo_g >> 4) & 0x0f0f0f0fu, 0u, sel), tr.a1 = prmt((lo_h >> 4) & 0x0f0f0f0fu, 0u, sel);
+        tr.a2 = prmt((hi_g >> 4) & 0x0f0f0f0fu, 0u, sel), tr.a3 = prmt((hi_h >> 4) & 0x0f0f0f0fu, 0u, sel);
+        tr.dmg = half_bits_to_float(lds16(tile + 1280 + g * 4 + 2)) * 16777216.0f, tr.dmh = half_bits_to_float(lds16(tile + 1280 + (g + 8) * 4 + 2)) * 16777216.0f;
     } else if constexpr (FMT == KYB_FMT_Q3_K) {
         tr.q[0] = lds128(tile + lane * 16);
         tr.q[1] = lds128(tile + (32 + lane) * 16);
@@ -202,6 +221,46 @@ __device__ __forceinline__ void load_tile(uint32_t tile, int lane, TileRegs<FMT>
     } else {
 #pragma unroll
         for (int P = 0; P < 4; ++P) tr.q[P] = lds128(tile + (P * 32 + lane) * 16);
+    }
+}
+
+// Sums of the staged activations the minima are multiplied with, as B operands of the correcting MMA (fp16 hi + lo of each fp32 sum). v: 32 inputs (group c2 of
+// activation row `row` of column tile nt). Q4_K / Q5_K: one sum per 32 inputs, m16n8k8 order (lane 4 row + j / 2, half j % 2 for sub-block j = c2 % 8; hi at
+// word nt * 32 + lane, lo NT * 32 words further). Q2_K: one sum per 16 inputs, m16n8k16 order (slice s: lane 4 row + (s % 8) / 2, register s / 8, half s % 2;
+// 8 bytes per lane, hi at (nt * 32 + lane), lo NT * 32 lanes further).
+template <int FMT, int NT>
+__device__ __forceinline__ void stage_sums(const uint4 (&v)[4], uint8_t* xaux, int c2, int nt, int row) {
+    if constexpr (kyb_has_mins(FMT) || kyb_has_mins16(FMT)) {
+        float sum[2] = {0.f, 0.f};                                   // one running sum per 32 inputs (element order), or one per 16 inputs
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __half2* hp = reinterpret_cast<const __half2*>(&v[q]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(hp[e]);
+                sum[kyb_has_mins16(FMT) ? (q >> 1) : 0] += f.x + f.y;
+            }
+        }
+        const int blk = c2 >> 3, j = c2 & 7;
+        __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * xaux_bytes_per_block<FMT>(NT));
+        if constexpr (kyb_has_mins(FMT)) {
+            const float tot = sum[0];
+            const __half hi = __float2half_rn(tot);
+            const __half lo = __float2half_rn(tot - __half2float(hi));
+            const int idx = (row * 4 + (j >> 1)) * 2 + (j & 1);
+            xa[((0 * NT + nt) * 32) * 2 + idx] = hi;
+            xa[((1 * NT + nt) * 32) * 2 + idx] = lo;
+        } else {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int sl = 2 * j + hf;
+                const __half hi = __float2half_rn(sum[hf]);
+                const __half lo = __float2half_rn(sum[hf] - __half2float(hi));
+                const int idx = ((row * 4 + ((sl & 7) >> 1)) * 2 + (sl >> 3)) * 2 + (sl & 1);
+                xa[((0 * NT + nt) * 32) * 4 + idx] = hi;
+                xa[((1 * NT + nt) * 32) * 4 + idx] = lo;
+            }
+        }
     }
 }
 
@@ -313,7 +372,7 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
             if constexpr (FMT == KYB_FMT_Q6_K) {
                 u = tr.q[P];
                 hi = tr.q[4 + (P >> 1)];
-            } else if constexpr (FMT == KYB_FMT_Q3_K) {
+            } else if constexpr (FMT == KYB_FMT_Q3_K || FMT == KYB_FMT_Q2_K) {
                 hi = tr.q[P >> 1];                                                       // 2-bit plane
                 u = hi;
             } else {
@@ -350,6 +409,12 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
                     a2 = magic_sub(prmt(vg, 0x64646464u, 0x4341u), 0x64046404u);
                     a1 = magic_sub(prmt(vh, 0x64646464u, 0x4240u), 0x64046404u);
                     a3 = magic_sub(prmt(vh, 0x64646464u, 0x4341u), 0x64046404u);
+                } else if constexpr (FMT == KYB_FMT_Q2_K) {
+                    uint32_t wg = (P & 1) ? u.z : u.x, wh = (P & 1) ? u.w : u.y;     // word a = (s >> 2) & 1 = P & 1
+                    wg = (wg >> (2 * i)) & 0x03030303u, wh = (wh >> (2 * i)) & 0x03030303u;
+                    // a byte in a 16-bit lane is the fp16 subnormal code * 2^-24: exact, and the 2^24 sits in the block scale
+                    a0 = prmt(wg, 0u, 0x4240u), a2 = prmt(wg, 0u, 0x4341u);
+                    a1 = prmt(wh, 0u, 0x4240u), a3 = prmt(wh, 0u, 0x4341u);
                 } else {
                     const int p = i >> 1;
                     const uint32_t wg = p ? u.z : u.x, wh = p ? u.w : u.y;
@@ -380,6 +445,21 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
             float tt[4];
             mma1688_z(tt, a0, a1, lds32(xa + (0 * NT + nt) * 128));
             mma1688(tt, a0, a1, lds32(xa + (1 * NT + nt) * 128));
+            acc.v[nt][0] = fmaf(-dmg, tt[0], acc.v[nt][0]);
+            if (MST != 1) acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
+            acc.v[nt][2] = fmaf(-dmh, tt[2], acc.v[nt][2]);
+            if (MST != 1) acc.v[nt][3] = fmaf(-dmh, tt[3], acc.v[nt][3]);
+        }
+    }
+    if constexpr (kyb_has_mins16(FMT)) {
+        // minus dmin * sum_s mn_s * (sum of x over slice s): one m16n8k16 product of the 4-bit mins with the staged per-slice sums (fp16 hi + lo)
+        const float dmg = tr.dmg, dmh = tr.dmh;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            float tt[4];
+            const uint2 bh = lds64(xa + (0 * NT + nt) * 256), bl = lds64(xa + (1 * NT + nt) * 256);
+            mma16816_z(tt, tr.a0, tr.a1, tr.a2, tr.a3, bh.x, bh.y);
+            mma16816(tt, tr.a0, tr.a1, tr.a2, tr.a3, bl.x, bl.y);
             acc.v[nt][0] = fmaf(-dmg, tt[0], acc.v[nt][0]);
             if (MST != 1) acc.v[nt][1] = fmaf(-dmg, tt[1], acc.v[nt][1]);
             acc.v[nt][2] = fmaf(-dmh, tt[2], acc.v[nt][2]);
@@ -542,25 +622,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
                         uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)(2 * c2 + c) * CS + (nt * MST + row) * 32);
                         dst[0] = oa, dst[1] = ob;
                     }
-                    if constexpr (kyb_has_mins(FMT)) {
-                        float sum = 0.f;
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const __half2* hp = reinterpret_cast<const __half2*>(&v[u][q]);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 f = __half22float2(hp[e]);
-                                sum += f.x + f.y;
-                            }
-                        }
-                        const __half hi = __float2half_rn(sum);
-                        const __half lo = __float2half_rn(sum - __half2float(hi));
-                        const int blk = c2 >> 3, j = c2 & 7;
-                        __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * 256 * NT);
-                        const int idx = (row * 4 + (j >> 1)) * 2 + (j & 1);
-                        xa[((0 * NT + nt) * 32) * 2 + idx] = hi;
-                        xa[((1 * NT + nt) * 32) * 2 + idx] = lo;
-                    }
+                    stage_sums<FMT, NT>(v[u], xaux, c2, nt, row);
                 }
             }
         }
@@ -570,8 +632,8 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
 
     const int g = lane >> 2, t = lane & 3;
     // lanes whose activation row is not staged read a staged row instead: their output columns are never stored
-    const uint32_t xb0 = smem_u32(xfrag) + (g & (MST - 1)) * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
-    uint32_t xb = xb0 + (uint32_t)(j0 * p.kc) * (16 * CS), xa = xa0 + (uint32_t)(j0 * p.kc) * (256 * NT);   // this lane's fragment addresses for the current k-block
+    const uint32_t xb0 = smem_u32(xfrag) + (g & (MST - 1)) * 32 + t * 8, xa0 = smem_u32(xaux) + lane * (kyb_has_mins16(FMT) ? 8 : 4);
+    uint32_t xb = xb0 + (uint32_t)(j0 * p.kc) * (16 * CS), xa = xa0 + (uint32_t)(j0 * p.kc) * xaux_bytes_per_block<FMT>(NT);   // this lane's fragment addresses for the current k-block
 
     Acc<NT> acc, tot;
 #pragma unroll
@@ -595,7 +657,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
         // phase B: arithmetic from registers
         consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
         __syncwarp();                                             // the scale scratch is rewritten by the next tile
-        xb += 16 * CS, xa += 256 * NT;
+        xb += 16 * CS, xa += xaux_bytes_per_block<FMT>(NT);
         if (--cleft == 0) {
             // ---- end of a canonical chunk. lane (g, t) holds rows g, g + 8 x activation rows 2t, 2t + 1 of each column tile
             const int chunk = c0 + j;
@@ -675,7 +737,7 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
     const int ntiles = p.n >> 4;                                   // row tiles per expert (n % 16 == 0)
     const int tpc = (ntiles + p.rc - 1) / p.rc;                    // row tiles per chunk
     const uint32_t ngroups = *p.ngroups;
-    const uint32_t xb0 = smem_u32(xfrag) + g * 32 + t * 8, xa0 = smem_u32(xaux) + lane * 4;
+    const uint32_t xb0 = smem_u32(xfrag) + g * 32 + t * 8, xa0 = smem_u32(xaux) + lane * (kyb_has_mins16(FMT) ? 8 : 4);
     const uint32_t npair = p.t16b ? 2u : 1u;
     // slots that belong to no expert are in no group: their rows are written here
     if (p.eids)
@@ -740,25 +802,7 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
                     uint4* dst = reinterpret_cast<uint4*>(xfrag + (size_t)(2 * c2 + c) * CS + row * 32);
                     dst[0] = oa, dst[1] = ob;
                 }
-                if constexpr (kyb_has_mins(FMT)) {
-                    float sum = 0.f;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const __half2* hp = reinterpret_cast<const __half2*>(&v[q]);
-#pragma unroll
-                        for (int e2 = 0; e2 < 4; ++e2) {
-                            const float2 f = __half22float2(hp[e2]);
-                            sum += f.x + f.y;
-                        }
-                    }
-                    const __half hi = __float2half_rn(sum);
-                    const __half lo = __float2half_rn(sum - __half2float(hi));
-                    const int blk = c2 >> 3, j = c2 & 7;
-                    __half* xa = reinterpret_cast<__half*>(xaux + (size_t)blk * 256 * NT);
-                    const int idx = (row * 4 + (j >> 1)) * 2 + (j & 1);
-                    xa[idx] = hi;
-                    xa[64 + idx] = lo;
-                }
+                stage_sums<FMT, NT>(v, xaux, c2, 0, row);
             }
         }
         __syncthreads();
@@ -781,7 +825,7 @@ __global__ void __launch_bounds__(768, 1) gemv_group_kernel(const GroupParams p)
             if (lane == 0 && p_left > 0) issue();
             consume_tile<FMT, NT, MST>(tr, scl_a, xb, xa, lane, acc);
             __syncwarp();
-            xb += 16 * CS, xa += 256 * NT;
+            xb += 16 * CS, xa += xaux_bytes_per_block<FMT>(NT);
             ++blk;
             if (--cleft == 0) {
                 const bool last = blk == p.nb;
@@ -834,7 +878,7 @@ struct GemvPlan {
 size_t plan_smem(int fmt, int nt, int mst, int kbp, int warps, int stages) {
     const size_t tb = kyb_tile_bytes(fmt);
     const size_t xfrag = (size_t)kbp * 16 * nt * mst * 32;
-    const size_t xaux = kyb_has_mins(fmt) ? (size_t)kbp * 256 * nt : 0;
+    const size_t xaux = kyb_has_mins(fmt) ? (size_t)kbp * 256 * nt : kyb_has_mins16(fmt) ? (size_t)kbp * 512 * nt : 0;
     const size_t wb = ((size_t)stages * tb + kyb::SCL_BYTES + 8 * (size_t)stages + 8 + 15) & ~(size_t)15;
     return xfrag + xaux + warps * wb;
 }
@@ -864,6 +908,7 @@ const void* gemv_kernel_ptr(int fmt, int v) {
         case KYB_FMT_Q3_K: return kernel_of_fmt<KYB_FMT_Q3_K>(v);
         case KYB_FMT_Q5_K: return kernel_of_fmt<KYB_FMT_Q5_K>(v);
         case KYB_FMT_Q8_0: return kernel_of_fmt<KYB_FMT_Q8_0>(v);
+        case KYB_FMT_Q2_K: return kernel_of_fmt<KYB_FMT_Q2_K>(v);
         default: return kernel_of_fmt<KYB_FMT_NVFP4>(v);
     }
 }
@@ -1194,6 +1239,7 @@ extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, const void* t16b, in
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q3_K>
                        : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q5_K>
                        : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q8_0>
+                       : fmt == KYB_FMT_Q2_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q2_K>
                                              : (const void*)kyb::gemv_group_kernel<KYB_FMT_NVFP4>;
     if (int r = ensure_smem_attr(kern)) return r;
     void* args[] = {(void*)&p};

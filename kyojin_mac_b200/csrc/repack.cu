@@ -22,6 +22,9 @@ __device__ __forceinline__ uint32_t raw_code(const uint8_t* blk, int e) {
         return ((e & 32) ? (byte >> 4) : (byte & 15u)) | (((blk[16 + (e & 31)] >> (e >> 5)) & 1u) << 4);
     } else if (FMT == KYB_FMT_Q8_0) {                // eight 34-byte blocks: fp16 d, 32 int8
         return blk[34 * (e >> 5) + 2 + (e & 31)];
+    } else if (FMT == KYB_FMT_Q2_K) {                // input 128H + 32j + l: qs[32H + l] bits 2j, behind the 16 scale bytes
+        const int H = e >> 7, j = (e >> 5) & 3, l = e & 31;
+        return (blk[16 + 32 * H + l] >> (2 * j)) & 3u;
     } else {                                         // 64-block B, 16-sub-block u, l: byte 4 + 8u + (l & 7), nibble l >> 3
         const int B = e >> 6, u = (e >> 4) & 3, l = e & 15;
         const uint32_t byte = blk[36 * B + 4 + 8 * u + (l & 7)];
@@ -134,6 +137,23 @@ __global__ void raw_to_t16_kernel(const uint8_t* __restrict__ raw, int64_t n, in
             if (b)
                 for (int i = 0; i < 4; ++i) out |= (uint32_t)b[4 * w + i] << (8 * i);
         }
+    } else if (FMT == KYB_FMT_Q2_K) {
+        if (wi < 256) {                              // 2-bit plane (as Q3_K)
+            unit(wi, P, g, t, a, h);
+            const uint8_t* b = blk_of(g + 8 * h);
+            if (b)
+                for (int i = 0; i < 4; ++i)
+                    for (int i2 = 0; i2 < 4; ++i2) out |= raw_code<FMT>(b, 16 * (8 * P + 4 * a + i2) + 4 * t + i) << (8 * i + 2 * i2);
+        } else if (wi < 320) {                       // 16 scale | min bytes per row = 4 words
+            const int r = (wi - 256) >> 2, w = (wi - 256) & 3;
+            const uint8_t* b = blk_of(r);
+            if (b)
+                for (int i = 0; i < 4; ++i) out |= (uint32_t)b[4 * w + i] << (8 * i);
+        } else {                                     // fp16 d, fp16 dmin of one row
+            const uint8_t* b = blk_of(wi - 320);
+            if (b)
+                for (int i = 0; i < 4; ++i) out |= (uint32_t)b[80 + i] << (8 * i);
+        }
     } else if (FMT == KYB_FMT_Q8_0) {
         if (wi < 1024) {                             // byte plane: unit P holds slices 2P (a = 0) and 2P + 1 (a = 1)
             unit(wi, P, g, t, a, h);
@@ -211,6 +231,12 @@ __global__ void t16_to_raw_kernel(const uint8_t* __restrict__ t16, int64_t n, in
             const int G = (o - 48) >> 5, l = (o - 48) & 31;
             out = (tile_code<FMT>(tile, r, 64 * G + l) & 15u) | ((tile_code<FMT>(tile, r, 64 * G + 32 + l) & 15u) << 4);
         }
+    } else if (FMT == KYB_FMT_Q2_K) {
+        if (o < 16) out = tile[1024 + r * 16 + o];
+        else if (o < 80) {
+            const int H = (o - 16) >> 5, l = (o - 16) & 31;
+            for (int j = 0; j < 4; ++j) out |= tile_code<FMT>(tile, r, 128 * H + 32 * j + l) << (2 * j);
+        } else out = tile[1280 + r * 4 + (o - 80)];
     } else if (FMT == KYB_FMT_Q8_0) {
         const int B = o / 34, p = o % 34;
         out = p < 2 ? tile[4096 + r * 16 + 2 * B + p] : tile_code<FMT>(tile, r, 32 * B + p - 2);
@@ -250,6 +276,7 @@ extern "C" int kyb_repack_raw_to_t16(int fmt, const void* raw, int64_t n, int64_
         case KYB_FMT_Q3_K: kyb::raw_to_t16_kernel<KYB_FMT_Q3_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q5_K: kyb::raw_to_t16_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q8_0: kyb::raw_to_t16_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
+        case KYB_FMT_Q2_K: kyb::raw_to_t16_kernel<KYB_FMT_Q2_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         default: kyb::raw_to_t16_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
     }
     return kyb_launch_check("raw_to_t16");
@@ -271,6 +298,7 @@ extern "C" int kyb_repack_t16_to_raw(int fmt, const void* t16, int64_t n, int64_
         case KYB_FMT_Q3_K: kyb::t16_to_raw_kernel<KYB_FMT_Q3_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q5_K: kyb::t16_to_raw_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q8_0: kyb::t16_to_raw_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
+        case KYB_FMT_Q2_K: kyb::t16_to_raw_kernel<KYB_FMT_Q2_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         default: kyb::t16_to_raw_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
     }
     return kyb_launch_check("t16_to_raw");

@@ -67,6 +67,9 @@ __device__ __forceinline__ uint32_t tile_code(const uint8_t* tile, int r, int e)
         return ((s & 1) ? (nb >> 4) : (nb & 15u)) | (((hb >> (s & 7)) & 1u) << 4);
     } else if (FMT == KYB_FMT_Q8_0) {
         return tile[((s >> 1) * 32 + L) * 16 + (2 * (s & 1) + h) * 4 + b];
+    } else if (FMT == KYB_FMT_Q2_K) {
+        const uint32_t lb = tile[((s >> 3) * 32 + L) * 16 + (2 * ((s >> 2) & 1) + h) * 4 + b];
+        return (lb >> (2 * (s & 3))) & 3u;
     } else {
         const uint32_t word = ldw(tile + ((s >> 2) * 32 + L) * 16 + (2 * ((s >> 1) & 1) + h) * 4);
         const int v = 2 * (s & 1) + (b & 1), j = b >> 1;
@@ -155,6 +158,18 @@ struct TileDecode<KYB_FMT_Q8_0> {
         const float d = ldh(tile + 4096 + r * 16 + (s >> 1) * 2);
 #pragma unroll
         for (int b = 0; b < 4; ++b) w[b] = __fmul_rn((float)(int)(int8_t)tile_code<KYB_FMT_Q8_0>(tile, r, 16 * s + 4 * t + b), d);
+    }
+};
+
+template <>
+struct TileDecode<KYB_FMT_Q2_K> {
+    // w[b] = (d * (sc & 15)) * code - dmin * (sc >> 4), one scale byte per 16 inputs (kyojin_mlx/foreign_gguf.py:538-545)
+    static __device__ __forceinline__ void row4(const uint8_t* tile, int g, int t, int h, int s, float gscale, float (&w)[4]) {
+        const int r = g + 8 * h;
+        const uint32_t sb = tile[1024 + r * 16 + s];
+        const float ds = __fmul_rn(ldh(tile + 1280 + r * 4), (float)(sb & 15u)), dm = __fmul_rn(ldh(tile + 1280 + r * 4 + 2), (float)(sb >> 4));
+#pragma unroll
+        for (int b = 0; b < 4; ++b) w[b] = __fsub_rn(__fmul_rn(ds, (float)tile_code<KYB_FMT_Q2_K>(tile, r, 16 * s + 4 * t + b)), dm);
     }
 };
 

@@ -29,16 +29,17 @@ Tile contents (offsets in bytes; "word(P, L, i)" = 32-bit word i of the 16-byte 
   q5_k  [0,2048)    the low 4 bits of the 5-bit codes as the q6_k nibble plane   [2048,2560) the fifth bits as the q3_k 1-bit plane
         [2560,2816) row r: the first 16 stored bytes of its block (d, dmin, 12 bytes of 6-bit scales/mins)
   q8_0  [0,4096)    word(P, L, 2p+h): byte b = the int8 of input 16 (2P + p) + 4t + b       [4096,4352) row r: the eight fp16 d of its 32-input blocks
+  q2_k  [0,1024)    the 2-bit codes as the q3_k 2-bit plane     [1024,1280) row r: the 16 stored scale | min << 4 bytes     [1280,1344) row r: fp16 d, fp16 dmin
 """
 from __future__ import annotations
 
 import numpy as np
 
-FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0")
-FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5}
-TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352}
-RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34)}     # GGUF block elements / bytes
-GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0"}
+FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0", "q2_k")
+FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5, "q2_k": 6}
+TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352, "q2_k": 1344}
+RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34), "q2_k": (256, 84)}     # GGUF block elements / bytes
+GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
 PREFILL_FUSED = ("q4_k", "q6_k", "q3_k", "nvfp4")       # formats the prefill GEMM decodes inside the kernel; the others are decoded to fp16 first
 ROWS = 16
 KBLOCK = 256
@@ -306,6 +307,11 @@ def raw_to_t16(fmt: str, raw, n: int, k: int) -> np.ndarray:
     elif fmt == "q8_0":
         blk = B.reshape(B.shape[:4] + (8, 34))
         parts = [_byte_plane(np.ascontiguousarray(blk[..., 2:34]).reshape(B.shape[:4] + (256,))), np.ascontiguousarray(blk[..., 0:2]).reshape(nrt, nb, 256)]
+    elif fmt == "q2_k":
+        qs = B[..., 16:80].reshape(B.shape[:-1] + (2, 32))
+        lo = np.stack([(qs >> (2 * j)) & 3 for j in range(4)], -2)                                   # [.., half128, j, l]: element 128 h + 32 j + l
+        parts = [_twobit_plane(np.ascontiguousarray(lo).reshape(B.shape[:-1] + (256,))), np.ascontiguousarray(B[..., 0:16]).reshape(nrt, nb, 256),
+                 np.ascontiguousarray(B[..., 80:84]).reshape(nrt, nb, 64)]
     elif fmt == "q4_k":
         w = np.ascontiguousarray(B[..., 16:144]).view("<u4").reshape(nrt, nb, 2, 8, 4, 2, 4)      # h, g, G, c, t
         quant = np.ascontiguousarray(w.transpose(0, 1, 4, 3, 6, 5, 2)).view(np.uint8).reshape(nrt, nb, 2048)    # G, g, t, c, h
@@ -355,6 +361,14 @@ def t16_to_raw(fmt: str, t16, n: int, k: int) -> np.ndarray:
         blk = B.reshape(nrt, nb, 2, 8, 8, 34)
         blk[..., 2:34] = _byte_plane_inv(T[..., 0:4096]).reshape(nrt, nb, 2, 8, 8, 32)
         blk[..., 0:2] = T[..., 4096:4352].reshape(nrt, nb, 2, 8, 8, 2)
+    elif fmt == "q2_k":
+        lo = _twobit_plane_inv(T[..., 0:1024]).reshape(nrt, nb, 2, 8, 2, 4, 32)                    # half128, j, l
+        qs = np.zeros((nrt, nb, 2, 8, 2, 32), np.uint8)
+        for j in range(4):
+            qs |= lo[..., j, :] << (2 * j)
+        B[..., 16:80] = qs.reshape(nrt, nb, 2, 8, 64)
+        B[..., 0:16] = T[..., 1024:1280].reshape(nrt, nb, 2, 8, 16)
+        B[..., 80:84] = T[..., 1280:1344].reshape(nrt, nb, 2, 8, 4)
     elif fmt == "q4_k":
         w = np.ascontiguousarray(T[..., 0:2048]).view("<u4").reshape(nrt, nb, 4, 8, 4, 2, 2)       # G, g, t, c, h
         B[..., 16:144] = np.ascontiguousarray(w.transpose(0, 1, 6, 3, 2, 5, 4)).view(np.uint8).reshape(nrt, nb, 2, 8, 128)

@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 import numpy as np
 
 # block elements / block bytes (kyojin_mlx/foreign_gguf.py:27-35 TYPES)
-BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36), "Q5_K": (256, 176), "Q8_0": (32, 34)}
+BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36), "Q5_K": (256, 176), "Q8_0": (32, 34), "Q2_K": (256, 84)}
 
 # doubled e2m1 magnitudes used with the halved scale of GGUF NVFP4 (foreign_gguf.py:69)
 _FP4_X2 = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
@@ -157,7 +157,24 @@ def _decode_q80(B):
     return np.ascontiguousarray(B[..., 2:34]).view(np.int8).astype(np.float32) * d
 
 
-_DECODERS = {"Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4, "Q5_K": _decode_q5k, "Q8_0": _decode_q80}
+def _decode_q2k(B):
+    """[nr, nb, 84] -> [nr, nb, 256]: w = (d * (sc & 15)) * code - dmin * (sc >> 4), one scale byte per 16 elements (index 8 * half128 + 2 * j + sub16),
+    element 128 h + 32 j + l = bits 2j of qs[32 h + l]. (foreign_gguf.py:538-545)"""
+    sc = B[..., 0:16]
+    qs = B[..., 16:80].reshape(B.shape[:-1] + (2, 32))
+    d = _half_field(B, 80)[..., None]
+    dmin = _half_field(B, 82)[..., None]
+    out = np.empty(B.shape[:-1] + (2, 4, 32), np.float32)
+    for h in range(2):
+        for j in range(4):
+            q = ((qs[..., h, :] >> (2 * j)) & 3).astype(np.float32)
+            for c in range(2):
+                s8 = sc[..., 8 * h + 2 * j + c][..., None]
+                out[..., h, j, 16 * c:16 * c + 16] = (d * (s8 & 15).astype(np.float32)) * q[..., 16 * c:16 * c + 16] - dmin * (s8 >> 4).astype(np.float32)
+    return out.reshape(B.shape[:-1] + (256,))
+
+
+_DECODERS = {"Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4, "Q5_K": _decode_q5k, "Q8_0": _decode_q80, "Q2_K": _decode_q2k}
 
 
 def _dequant_chunk(tname, raw2, k):
