@@ -98,6 +98,7 @@ extern "C" int kyb_dequant_t16(int fmt, const void* t16, int64_t n, int64_t k, i
         case KYB_FMT_Q5_K: launch_dequant<KYB_FMT_Q5_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q8_0: launch_dequant<KYB_FMT_Q8_0>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q2_K: launch_dequant<KYB_FMT_Q2_K>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_IQ4_XS: launch_dequant<KYB_FMT_IQ4_XS>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
         default: launch_dequant<KYB_FMT_NVFP4>(t, nlim, nb, rt0, ntiles, gscale, out_dtype, out, ld, st); break;
     }
     return kyb_launch_check("dequant_t16");
@@ -131,6 +132,7 @@ extern "C" int kyb_dequant_rows_t16(int fmt, const void* t16, int64_t n, int64_t
         case KYB_FMT_Q5_K: launch_dequant_rows<KYB_FMT_Q5_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q8_0: launch_dequant_rows<KYB_FMT_Q8_0>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         case KYB_FMT_Q2_K: launch_dequant_rows<KYB_FMT_Q2_K>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
+        case KYB_FMT_IQ4_XS: launch_dequant_rows<KYB_FMT_IQ4_XS>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
         default: launch_dequant_rows<KYB_FMT_NVFP4>(t, n, nb, r, nrows, gscale, out_dtype, out, ld, st); break;
     }
     return kyb_launch_check("dequant_rows_t16");

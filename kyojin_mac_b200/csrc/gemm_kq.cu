@@ -730,7 +730,7 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
                     int64_t col0, int msub, void* stream) {
-    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K) {
+    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
         kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
         return KYB_EUNSUPPORTED;
     }
@@ -809,7 +809,7 @@ static int kq_grouped(int fmt, const void* t16, const void* t16b, int64_t n, int
                       const void* row_map, const void* gs, const void* gsb, float limit, void* d, int64_t ldd, int mt, void* stream) {
     const bool glu = t16b != nullptr;
     KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
-    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K) {
+    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
         kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
         return KYB_EUNSUPPORTED;
     }

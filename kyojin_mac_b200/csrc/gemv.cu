@@ -116,6 +116,16 @@ __device__ __forceinline__ void prep_scales(uint32_t tile, uint32_t scl, int lan
         o.z = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7442u)), d, nd);
         o.w = fmaf(__uint_as_float(prmt(scw, 0x4B000000u, 0x7443u)), d, nd);
         sts128f(scl + 4 * (r * SCL_STRIDE + 4 * hf), o);
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+        const uint2 mw = lds64(tile + 2048 + r * 8);                       // d | scales_h << 16, four scales_l bytes
+        const float d = half_bits_to_float(mw.x & 0xffffu);
+        const uint32_t sh = mw.x >> (16 + 8 * hf), sl = mw.y >> (16 * hf);  // sub-blocks 4 hf .. 4 hf + 3: two scales_l bytes, one scales_h byte
+        float4 o;
+        o.x = d * (float)((int)((sl & 15u) | ((sh & 3u) << 4)) - 32);
+        o.y = d * (float)((int)(((sl >> 4) & 15u) | (((sh >> 2) & 3u) << 4)) - 32);
+        o.z = d * (float)((int)(((sl >> 8) & 15u) | (((sh >> 4) & 3u) << 4)) - 32);
+        o.w = d * (float)((int)(((sl >> 12) & 15u) | (((sh >> 6) & 3u) << 4)) - 32);
+        sts128f(scl + 4 * (r * SCL_STRIDE + 4 * hf), o);
     } else if constexpr (FMT == KYB_FMT_Q2_K) {
         const uint2 sw = lds64(tile + 1024 + r * 16 + 8 * hf);             // scale | min << 4 of slices 8 hf .. 8 hf + 7
         const float d = half_bits_to_float(lds16(tile + 1280 + r * 4)) * 16777216.0f;   // the 2-bit codes enter the MMA as fp16 subnormals (code * 2^-24)
@@ -329,6 +339,45 @@ __device__ __forceinline__ void consume_tile(const TileRegs<FMT>& tr, uint32_t s
                     const uint32_t vg = and_or(wg, 0x0F0F0F0Fu, bg & 0x10101010u), vh = and_or(wh, 0x0F0F0F0Fu, bh & 0x10101010u);
                     const uint32_t a0 = magic_sub(prmt(vg, 0x64646464u, 0x4240u), 0x64006400u), a2 = magic_sub(prmt(vg, 0x64646464u, 0x4341u), 0x64006400u);
                     const uint32_t a1 = magic_sub(prmt(vh, 0x64646464u, 0x4240u), 0x64006400u), a3 = magic_sub(prmt(vh, 0x64646464u, 0x4341u), 0x64006400u);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const uint2 b = ldb(s, nt);
+                        if (ii == 0) mma16816_z(c[nt], a0, a1, a2, a3, b.x, b.y);
+                        else mma16816(c[nt], a0, a1, a2, a3, b.x, b.y);
+                    }
+                }
+                scale_acc<NT, MST == 1>(acc, c, sg[2 * P + jj], sh[2 * P + jj]);
+            }
+        }
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+        // scales of rows g and g + 8 for the 8 sub-blocks (d * (ls - 32)); every 4-bit code is an index into the 16-entry int8 grid: two byte permutes pick
+        // the entry from the low and the high half of the table (selector = low 3 bits of four codes at once), bit 3 of each code chooses between them
+        const float4 s0a = lds128f(scl + 4 * (g * SCL_STRIDE)), s0b = lds128f(scl + 4 * (g * SCL_STRIDE + 4));
+        const float4 s1a = lds128f(scl + 4 * ((g + 8) * SCL_STRIDE)), s1b = lds128f(scl + 4 * ((g + 8) * SCL_STRIDE + 4));
+        const float sg[8] = {s0a.x, s0a.y, s0a.z, s0a.w, s0b.x, s0b.y, s0b.z, s0b.w};
+        const float sh[8] = {s1a.x, s1a.y, s1a.z, s1a.w, s1b.x, s1b.y, s1b.z, s1b.w};
+        auto grid4 = [](uint32_t idx) -> uint32_t {                                   // four codes (one per byte) -> their four grid values + 128 (unsigned bytes)
+            const uint32_t x = idx & 0x07070707u, y = x | (x >> 4);
+            const uint32_t sel = prmt(y, 0u, 0x4420u);
+            const uint32_t lo = prmt(0xBFAD9881u, 0xF6EADDCFu, sel), hi = prmt(0x26190D01u, 0x71594535u, sel);
+            const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xFFu;
+            return ((lo & ~m) | (hi & m)) ^ 0x80808080u;
+        };
+#pragma unroll
+        for (int P = 0; P < 4; ++P) {
+            const uint4 u = tr.q[P];
+#pragma unroll
+            for (int jj = 0; jj < 2; ++jj) {                                         // sub-block 2 P + jj = MMA slices 4 P + 2 jj, + 1
+                float c[NT][4];
+#pragma unroll
+                for (int ii = 0; ii < 2; ++ii) {
+                    const int s = 4 * P + 2 * jj + ii;
+                    uint32_t wg = jj ? u.z : u.x, wh = jj ? u.w : u.y;
+                    if (ii) wg >>= 4, wh >>= 4;
+                    const uint32_t vg = grid4(wg & 0x0F0F0F0Fu), vh = grid4(wh & 0x0F0F0F0Fu);
+                    // bytes -> fp16 (1024 + v + 128) - 1152 = v, exact
+                    const uint32_t a0 = magic_sub(prmt(vg, 0x64646464u, 0x4240u), 0x64806480u), a2 = magic_sub(prmt(vg, 0x64646464u, 0x4341u), 0x64806480u);
+                    const uint32_t a1 = magic_sub(prmt(vh, 0x64646464u, 0x4240u), 0x64806480u), a3 = magic_sub(prmt(vh, 0x64646464u, 0x4341u), 0x64806480u);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         const uint2 b = ldb(s, nt);
@@ -909,6 +958,7 @@ const void* gemv_kernel_ptr(int fmt, int v) {
         case KYB_FMT_Q5_K: return kernel_of_fmt<KYB_FMT_Q5_K>(v);
         case KYB_FMT_Q8_0: return kernel_of_fmt<KYB_FMT_Q8_0>(v);
         case KYB_FMT_Q2_K: return kernel_of_fmt<KYB_FMT_Q2_K>(v);
+        case KYB_FMT_IQ4_XS: return kernel_of_fmt<KYB_FMT_IQ4_XS>(v);
         default: return kernel_of_fmt<KYB_FMT_NVFP4>(v);
     }
 }
@@ -1240,6 +1290,7 @@ extern "C" int kyb_gemv_group_t16(int fmt, const void* t16, const void* t16b, in
                        : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q5_K>
                        : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q8_0>
                        : fmt == KYB_FMT_Q2_K ? (const void*)kyb::gemv_group_kernel<KYB_FMT_Q2_K>
+                       : fmt == KYB_FMT_IQ4_XS ? (const void*)kyb::gemv_group_kernel<KYB_FMT_IQ4_XS>
                                              : (const void*)kyb::gemv_group_kernel<KYB_FMT_NVFP4>;
     if (int r = ensure_smem_attr(kern)) return r;
     void* args[] = {(void*)&p};

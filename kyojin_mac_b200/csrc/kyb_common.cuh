@@ -42,11 +42,11 @@ static inline int kyb_launch_check(const char* what) {
 
 // T16 tile geometry (kyojin_mac_b200/layout.py holds the layout description)
 __host__ __device__ constexpr int kyb_tile_bytes(int fmt) {
-    return fmt == KYB_FMT_Q4_K ? 2304 : fmt == KYB_FMT_Q6_K ? 3360 : fmt == KYB_FMT_Q3_K ? 1760 : fmt == KYB_FMT_Q5_K ? 2816 : fmt == KYB_FMT_Q8_0 ? 4352 : fmt == KYB_FMT_Q2_K ? 1344 : 2304;
+    return fmt == KYB_FMT_Q4_K ? 2304 : fmt == KYB_FMT_Q6_K ? 3360 : fmt == KYB_FMT_Q3_K ? 1760 : fmt == KYB_FMT_Q5_K ? 2816 : fmt == KYB_FMT_Q8_0 ? 4352 : fmt == KYB_FMT_Q2_K ? 1344 : fmt == KYB_FMT_IQ4_XS ? 2176 : 2304;
 }
 __host__ __device__ constexpr int kyb_raw_block_elems(int fmt) { return fmt == KYB_FMT_NVFP4 ? 64 : fmt == KYB_FMT_Q8_0 ? 32 : 256; }
 __host__ __device__ constexpr int kyb_raw_block_bytes(int fmt) {
-    return fmt == KYB_FMT_Q4_K ? 144 : fmt == KYB_FMT_Q6_K ? 210 : fmt == KYB_FMT_Q3_K ? 110 : fmt == KYB_FMT_Q5_K ? 176 : fmt == KYB_FMT_Q8_0 ? 34 : fmt == KYB_FMT_Q2_K ? 84 : 36;
+    return fmt == KYB_FMT_Q4_K ? 144 : fmt == KYB_FMT_Q6_K ? 210 : fmt == KYB_FMT_Q3_K ? 110 : fmt == KYB_FMT_Q5_K ? 176 : fmt == KYB_FMT_Q8_0 ? 34 : fmt == KYB_FMT_Q2_K ? 84 : fmt == KYB_FMT_IQ4_XS ? 136 : 36;
 }
 // stored bytes of one 256-input block of a row (NVFP4: four 36-byte blocks, Q8_0: eight 34-byte blocks)
 __host__ __device__ constexpr int kyb_raw_kblock_bytes(int fmt) { return 256 / kyb_raw_block_elems(fmt) * kyb_raw_block_bytes(fmt); }

@@ -22,6 +22,9 @@ __device__ __forceinline__ uint32_t raw_code(const uint8_t* blk, int e) {
         return ((e & 32) ? (byte >> 4) : (byte & 15u)) | (((blk[16 + (e & 31)] >> (e >> 5)) & 1u) << 4);
     } else if (FMT == KYB_FMT_Q8_0) {                // eight 34-byte blocks: fp16 d, 32 int8
         return blk[34 * (e >> 5) + 2 + (e & 31)];
+    } else if (FMT == KYB_FMT_IQ4_XS) {              // sub-block ib of 32: byte j of its 16 = input 32 ib + j (low nibble), 32 ib + 16 + j (high), behind 8 bytes of d / scales
+        const uint32_t byte = blk[8 + 16 * (e >> 5) + (e & 15)];
+        return (e & 16) ? (byte >> 4) : (byte & 15u);
     } else if (FMT == KYB_FMT_Q2_K) {                // input 128H + 32j + l: qs[32H + l] bits 2j, behind the 16 scale bytes
         const int H = e >> 7, j = (e >> 5) & 3, l = e & 31;
         return (blk[16 + 32 * H + l] >> (2 * j)) & 3u;
@@ -137,6 +140,21 @@ __global__ void raw_to_t16_kernel(const uint8_t* __restrict__ raw, int64_t n, in
             if (b)
                 for (int i = 0; i < 4; ++i) out |= (uint32_t)b[4 * w + i] << (8 * i);
         }
+    } else if (FMT == KYB_FMT_IQ4_XS) {
+        if (wi < 512) {                              // nibble plane: s0 = 4P + 2a, s1 = s0 + 1
+            unit(wi, P, g, t, a, h);
+            const uint8_t* b = blk_of(g + 8 * h);
+            if (b)
+                for (int i = 0; i < 4; ++i) {
+                    const int e0 = 16 * (4 * P + 2 * a) + 4 * t + i;
+                    out |= (raw_code<FMT>(b, e0) | (raw_code<FMT>(b, e0 + 16) << 4)) << (8 * i);
+                }
+        } else {                                     // d, scales_h, scales_l of every row: 2 words
+            const int r = (wi - 512) >> 1, w = (wi - 512) & 1;
+            const uint8_t* b = blk_of(r);
+            if (b)
+                for (int i = 0; i < 4; ++i) out |= (uint32_t)b[4 * w + i] << (8 * i);
+        }
     } else if (FMT == KYB_FMT_Q2_K) {
         if (wi < 256) {                              // 2-bit plane (as Q3_K)
             unit(wi, P, g, t, a, h);
@@ -231,6 +249,12 @@ __global__ void t16_to_raw_kernel(const uint8_t* __restrict__ t16, int64_t n, in
             const int G = (o - 48) >> 5, l = (o - 48) & 31;
             out = (tile_code<FMT>(tile, r, 64 * G + l) & 15u) | ((tile_code<FMT>(tile, r, 64 * G + 32 + l) & 15u) << 4);
         }
+    } else if (FMT == KYB_FMT_IQ4_XS) {
+        if (o < 8) out = tile[2048 + r * 8 + o];
+        else {
+            const int ib = (o - 8) >> 4, j = (o - 8) & 15;
+            out = tile_code<FMT>(tile, r, 32 * ib + j) | (tile_code<FMT>(tile, r, 32 * ib + 16 + j) << 4);
+        }
     } else if (FMT == KYB_FMT_Q2_K) {
         if (o < 16) out = tile[1024 + r * 16 + o];
         else if (o < 80) {
@@ -277,6 +301,7 @@ extern "C" int kyb_repack_raw_to_t16(int fmt, const void* raw, int64_t n, int64_
         case KYB_FMT_Q5_K: kyb::raw_to_t16_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q8_0: kyb::raw_to_t16_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         case KYB_FMT_Q2_K: kyb::raw_to_t16_kernel<KYB_FMT_Q2_K><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
+        case KYB_FMT_IQ4_XS: kyb::raw_to_t16_kernel<KYB_FMT_IQ4_XS><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
         default: kyb::raw_to_t16_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(r, n, nb, o, words); break;
     }
     return kyb_launch_check("raw_to_t16");
@@ -299,6 +324,7 @@ extern "C" int kyb_repack_t16_to_raw(int fmt, const void* t16, int64_t n, int64_
         case KYB_FMT_Q5_K: kyb::t16_to_raw_kernel<KYB_FMT_Q5_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q8_0: kyb::t16_to_raw_kernel<KYB_FMT_Q8_0><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         case KYB_FMT_Q2_K: kyb::t16_to_raw_kernel<KYB_FMT_Q2_K><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
+        case KYB_FMT_IQ4_XS: kyb::t16_to_raw_kernel<KYB_FMT_IQ4_XS><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
         default: kyb::t16_to_raw_kernel<KYB_FMT_NVFP4><<<blocks, threads, 0, st>>>(t, n, nb, o, bytes); break;
     }
     return kyb_launch_check("t16_to_raw");

@@ -70,6 +70,9 @@ __device__ __forceinline__ uint32_t tile_code(const uint8_t* tile, int r, int e)
     } else if (FMT == KYB_FMT_Q2_K) {
         const uint32_t lb = tile[((s >> 3) * 32 + L) * 16 + (2 * ((s >> 2) & 1) + h) * 4 + b];
         return (lb >> (2 * (s & 3))) & 3u;
+    } else if (FMT == KYB_FMT_IQ4_XS) {
+        const uint32_t nb = tile[((s >> 2) * 32 + L) * 16 + (2 * ((s >> 1) & 1) + h) * 4 + b];
+        return (s & 1) ? (nb >> 4) : (nb & 15u);
     } else {
         const uint32_t word = ldw(tile + ((s >> 2) * 32 + L) * 16 + (2 * ((s >> 1) & 1) + h) * 4);
         const int v = 2 * (s & 1) + (b & 1), j = b >> 1;
@@ -158,6 +161,29 @@ struct TileDecode<KYB_FMT_Q8_0> {
         const float d = ldh(tile + 4096 + r * 16 + (s >> 1) * 2);
 #pragma unroll
         for (int b = 0; b < 4; ++b) w[b] = __fmul_rn((float)(int)(int8_t)tile_code<KYB_FMT_Q8_0>(tile, r, 16 * s + 4 * t + b), d);
+    }
+};
+
+// the non-linear 4-bit grid of IQ4_NL / IQ4_XS (kyojin_mlx/foreign_gguf.py:68), as four little-endian words of int8
+__device__ __forceinline__ float iq4nl_value(uint32_t code) {
+    const uint32_t w = code < 4 ? 0xBFAD9881u : code < 8 ? 0xF6EADDCFu : code < 12 ? 0x26190D01u : 0x71594535u;
+    return (float)(int)(int8_t)((w >> (8 * (code & 3u))) & 255u);
+}
+// 6-bit scale of sub-block ib (0..7) of an IQ4_XS block, still biased by +32: 4 low bits from scales_l, 2 high bits from scales_h (foreign_gguf.py:494-500)
+__device__ __forceinline__ int iq4xs_scale(const uint8_t* meta, int ib) {
+    const uint32_t sh = (uint32_t)meta[2] | ((uint32_t)meta[3] << 8);
+    return (int)(((meta[4 + (ib >> 1)] >> (4 * (ib & 1))) & 15u) | (((sh >> (2 * ib)) & 3u) << 4));
+}
+
+template <>
+struct TileDecode<KYB_FMT_IQ4_XS> {
+    // w[b] = grid[code] * (d * (ls - 32))
+    static __device__ __forceinline__ void row4(const uint8_t* tile, int g, int t, int h, int s, float gscale, float (&w)[4]) {
+        const int r = g + 8 * h;
+        const uint8_t* meta = tile + 2048 + r * 8;
+        const float dl = __fmul_rn(ldh(meta), (float)(iq4xs_scale(meta, s >> 1) - 32));
+#pragma unroll
+        for (int b = 0; b < 4; ++b) w[b] = __fmul_rn(iq4nl_value(tile_code<KYB_FMT_IQ4_XS>(tile, r, 16 * s + 4 * t + b)), dl);
     }
 };
 

@@ -25,7 +25,7 @@ TYPES = {
     22: ("IQ2_S", 256, 82), 23: ("IQ4_XS", 256, 136), 24: ("I8", 1, 1), 25: ("I16", 1, 2), 26: ("I32", 1, 4), 27: ("I64", 1, 8), 28: ("F64", 1, 8),
     29: ("IQ1_M", 256, 56), 30: ("BF16", 1, 2), 34: ("TQ1_0", 256, 54), 35: ("TQ2_0", 256, 66), 39: ("MXFP4", 32, 17), 40: ("NVFP4", 64, 36),
 }
-KERNEL_TYPES = ("Q4_K", "Q3_K", "Q6_K", "NVFP4", "Q5_K", "Q8_0", "Q2_K")          # stored formats the CUDA kernels read (after the lossless T16 repack)
+KERNEL_TYPES = ("Q4_K", "Q3_K", "Q6_K", "NVFP4", "Q5_K", "Q8_0", "Q2_K", "IQ4_XS")          # stored formats the CUDA kernels read (after the lossless T16 repack)
 
 
 class GgufError(ValueError):

@@ -7,6 +7,7 @@ Pack(fmt, n, k, qs, meta, gscale, extra): n output rows, k inputs.
   q3_k    uint8 [n, k/256*110]  stored GGUF Q3_K rows            None
   q5_k    uint8 [n, k/256*176]  stored GGUF Q5_K rows            None
   q2_k    uint8 [n, k/256*84]   stored GGUF Q2_K rows            None
+  iq4_xs  uint8 [n, k/256*136]  stored GGUF IQ4_XS rows          None
   q8_0    uint8 [n, k/32*34]    stored GGUF Q8_0 rows            None
   nvfp4   uint8 [n, k/2]  byte b = input 2b | input 2b+1 << 4    uint16 [n, k/32]: two e4m3 scale bytes (inputs 0-15, 16-31);
                                                                  gscale (float32) multiplies the row result
@@ -22,7 +23,7 @@ import numpy as np
 from . import layout as L
 
 FORMATS = L.FORMATS
-GGUF_TO_FMT = {"Q4_K": "q4_k", "Q6_K": "q6_k", "Q3_K": "q3_k", "NVFP4": "nvfp4", "Q5_K": "q5_k", "Q8_0": "q8_0", "Q2_K": "q2_k"}
+GGUF_TO_FMT = {"Q4_K": "q4_k", "Q6_K": "q6_k", "Q3_K": "q3_k", "NVFP4": "nvfp4", "Q5_K": "q5_k", "Q8_0": "q8_0", "Q2_K": "q2_k", "IQ4_XS": "iq4_xs"}
 
 
 @dataclass

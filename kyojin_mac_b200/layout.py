@@ -29,17 +29,18 @@ Tile contents (offsets in bytes; "word(P, L, i)" = 32-bit word i of the 16-byte 
   q5_k  [0,2048)    the low 4 bits of the 5-bit codes as the q6_k nibble plane   [2048,2560) the fifth bits as the q3_k 1-bit plane
         [2560,2816) row r: the first 16 stored bytes of its block (d, dmin, 12 bytes of 6-bit scales/mins)
   q8_0  [0,4096)    word(P, L, 2p+h): byte b = the int8 of input 16 (2P + p) + 4t + b       [4096,4352) row r: the eight fp16 d of its 32-input blocks
+  iq4_xs [0,2048)   the 4-bit grid indices as the q6_k nibble plane     [2048,2176) row r: the first 8 stored bytes of its block (d, scales_h, scales_l)
   q2_k  [0,1024)    the 2-bit codes as the q3_k 2-bit plane     [1024,1280) row r: the 16 stored scale | min << 4 bytes     [1280,1344) row r: fp16 d, fp16 dmin
 """
 from __future__ import annotations
 
 import numpy as np
 
-FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0", "q2_k")
-FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5, "q2_k": 6}
-TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352, "q2_k": 1344}
-RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34), "q2_k": (256, 84)}     # GGUF block elements / bytes
-GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+FORMATS = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0", "q2_k", "iq4_xs")
+FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5, "q2_k": 6, "iq4_xs": 7}
+TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352, "q2_k": 1344, "iq4_xs": 2176}
+RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34), "q2_k": (256, 84), "iq4_xs": (256, 136)}     # GGUF block elements / bytes
+GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 PREFILL_FUSED = ("q4_k", "q6_k", "q3_k", "nvfp4")       # formats the prefill GEMM decodes inside the kernel; the others are decoded to fp16 first
 ROWS = 16
 KBLOCK = 256
@@ -307,6 +308,10 @@ def raw_to_t16(fmt: str, raw, n: int, k: int) -> np.ndarray:
     elif fmt == "q8_0":
         blk = B.reshape(B.shape[:4] + (8, 34))
         parts = [_byte_plane(np.ascontiguousarray(blk[..., 2:34]).reshape(B.shape[:4] + (256,))), np.ascontiguousarray(blk[..., 0:2]).reshape(nrt, nb, 256)]
+    elif fmt == "iq4_xs":
+        qs = B[..., 8:136].reshape(B.shape[:-1] + (8, 16))
+        codes = np.concatenate([qs & 15, qs >> 4], -1)                                               # [.., sub-block, 32]: element 32 ib + j | 32 ib + 16 + j
+        parts = [_nibble_plane(np.ascontiguousarray(codes).reshape(B.shape[:-1] + (256,))), np.ascontiguousarray(B[..., 0:8]).reshape(nrt, nb, 128)]
     elif fmt == "q2_k":
         qs = B[..., 16:80].reshape(B.shape[:-1] + (2, 32))
         lo = np.stack([(qs >> (2 * j)) & 3 for j in range(4)], -2)                                   # [.., half128, j, l]: element 128 h + 32 j + l
@@ -361,6 +366,10 @@ def t16_to_raw(fmt: str, t16, n: int, k: int) -> np.ndarray:
         blk = B.reshape(nrt, nb, 2, 8, 8, 34)
         blk[..., 2:34] = _byte_plane_inv(T[..., 0:4096]).reshape(nrt, nb, 2, 8, 8, 32)
         blk[..., 0:2] = T[..., 4096:4352].reshape(nrt, nb, 2, 8, 8, 2)
+    elif fmt == "iq4_xs":
+        codes = _nibble_plane_inv(T[..., 0:2048]).reshape(nrt, nb, 2, 8, 8, 2, 16)                   # sub-block, nibble, j
+        B[..., 8:136] = (codes[..., 0, :] | (codes[..., 1, :] << 4)).reshape(nrt, nb, 2, 8, 128)
+        B[..., 0:8] = T[..., 2048:2176].reshape(nrt, nb, 2, 8, 8)
     elif fmt == "q2_k":
         lo = _twobit_plane_inv(T[..., 0:1024]).reshape(nrt, nb, 2, 8, 2, 4, 32)                    # half128, j, l
         qs = np.zeros((nrt, nb, 2, 8, 2, 32), np.uint8)

@@ -12,9 +12,9 @@ import numpy as np
 from .layout import KBLOCK, RAW_BLOCK, TILE_BYTES, padded_rows
 
 # byte offsets of the fp16 scale fields inside a stored block / inside a T16 tile (per row r)
-_RAW_F16 = {"q4_k": (0, 2), "q6_k": (208,), "q3_k": (108,), "q5_k": (0, 2), "q8_0": (0,), "q2_k": (80, 82)}
+_RAW_F16 = {"q4_k": (0, 2), "q6_k": (208,), "q3_k": (108,), "q5_k": (0, 2), "q8_0": (0,), "q2_k": (80, 82), "iq4_xs": (0,)}
 _T16_F16 = {"q4_k": (2048, 16, (0, 2)), "q6_k": (3328, 2, (0,)), "q3_k": (1728, 2, (0,)), "q5_k": (2560, 16, (0, 2)),
-            "q8_0": (4096, 16, (0, 2, 4, 6, 8, 10, 12, 14)), "q2_k": (1280, 4, (0, 2))}     # region offset, row stride, field offsets
+            "q8_0": (4096, 16, (0, 2, 4, 6, 8, 10, 12, 14)), "q2_k": (1280, 4, (0, 2)), "iq4_xs": (2048, 8, (0,))}     # region offset, row stride, field offsets
 
 
 def raw_blocks(fmt: str, n: int, k: int, rng: np.random.Generator, d_sigma: float = 1e-3) -> np.ndarray:

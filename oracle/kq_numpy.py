@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 import numpy as np
 
 # block elements / block bytes (kyojin_mlx/foreign_gguf.py:27-35 TYPES)
-BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36), "Q5_K": (256, 176), "Q8_0": (32, 34), "Q2_K": (256, 84)}
+BLOCK = {"Q4_K": (256, 144), "Q3_K": (256, 110), "Q6_K": (256, 210), "NVFP4": (64, 36), "Q5_K": (256, 176), "Q8_0": (32, 34), "Q2_K": (256, 84), "IQ4_XS": (256, 136)}
 
 # doubled e2m1 magnitudes used with the halved scale of GGUF NVFP4 (foreign_gguf.py:69)
 _FP4_X2 = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
@@ -174,7 +174,24 @@ def _decode_q2k(B):
     return out.reshape(B.shape[:-1] + (256,))
 
 
-_DECODERS = {"Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4, "Q5_K": _decode_q5k, "Q8_0": _decode_q80, "Q2_K": _decode_q2k}
+KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.float32)      # the non-linear 4-bit grid of IQ4_NL / IQ4_XS
+
+
+def _decode_iq4xs(B):
+    """[nr, nb, 136] -> [nr, nb, 256]: w = grid[code] * (d * (ls - 32)); eight 32-element sub-blocks, ls = 4 low bits from scales_l | 2 high bits from scales_h,
+    byte j of sub-block ib = element 32 ib + j (low nibble) and 32 ib + 16 + j (high nibble). (foreign_gguf.py:494-502)"""
+    d = _half_field(B, 0)[..., None]
+    sh = (B[..., 2].astype(np.uint32) | (B[..., 3].astype(np.uint32) << 8))[..., None]
+    sl = B[..., 4:8]
+    ib = np.arange(8)
+    ls = ((sl[..., ib // 2] >> (4 * (ib % 2))) & 15).astype(np.int32) | (((sh >> (2 * ib)) & 3).astype(np.int32) << 4)
+    dl = (d * (ls - 32).astype(np.float32))[..., None]
+    qs = B[..., 8:136].reshape(B.shape[:-1] + (8, 16))
+    y = np.concatenate([KVALUES_IQ4NL[qs & 15], KVALUES_IQ4NL[qs >> 4]], -1) * dl
+    return y.reshape(B.shape[:-1] + (256,)).astype(np.float32)
+
+
+_DECODERS = {"IQ4_XS": _decode_iq4xs, "Q4_K": _decode_q4k, "Q6_K": _decode_q6k, "Q3_K": _decode_q3k, "NVFP4": _decode_nvfp4, "Q5_K": _decode_q5k, "Q8_0": _decode_q80, "Q2_K": _decode_q2k}
 
 
 def _dequant_chunk(tname, raw2, k):

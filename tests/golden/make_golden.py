@@ -3,9 +3,9 @@
 Run once in a container that has the reference source tree (it is NOT needed to run the tests):
     python tests/golden/make_golden.py /path/to/reference
 Writes
-  kquant_ggml.npz  - the Q4_K / Q3_K / Q6_K / Q5_K / Q8_0 / Q2_K entries of the reference's tests/data/gguf_ggml_ref.npz
+  kquant_ggml.npz  - the Q4_K / Q3_K / Q6_K / Q5_K / Q8_0 / Q2_K / IQ4_XS entries of the reference's tests/data/gguf_ggml_ref.npz
                      (raw blocks + ggml's own float32 dequantised values, llama.cpp pin recorded in `pin`)
-  ref_dequant.npz  - seeded random blocks of Q4_K / Q3_K / Q6_K / NVFP4 / Q5_K / Q8_0 / Q2_K with the output of the reference
+  ref_dequant.npz  - seeded random blocks of Q4_K / Q3_K / Q6_K / NVFP4 / Q5_K / Q8_0 / Q2_K / IQ4_XS with the output of the reference
                      decoder kyojin_mlx.foreign_gguf.dequant, the reference's pack-form NVFP4 arrays
                      (foreign_gguf.to_pack) and kyojin_mlx.foreign_pack.dequant of them with a gscale.
 """
@@ -22,12 +22,12 @@ def main(ref_root: str) -> None:
 
     src = np.load(os.path.join(ref_root, "tests", "data", "gguf_ggml_ref.npz"))
     keep = {"pin": src["pin"]}
-    for t in ("Q4_K", "Q3_K", "Q6_K", "Q5_K", "Q8_0", "Q2_K"):
+    for t in ("Q4_K", "Q3_K", "Q6_K", "Q5_K", "Q8_0", "Q2_K", "IQ4_XS"):
         keep[t + "_raw"], keep[t + "_ref"] = src[t + "_raw"], src[t + "_ref"]
     np.savez_compressed(os.path.join(here, "kquant_ggml.npz"), **keep)
 
     out = {}
-    for i, (t, n, k) in enumerate((("Q4_K", 6, 512), ("Q3_K", 6, 512), ("Q6_K", 6, 512), ("NVFP4", 6, 256), ("Q5_K", 6, 512), ("Q8_0", 6, 512), ("Q2_K", 6, 512))):
+    for i, (t, n, k) in enumerate((("Q4_K", 6, 512), ("Q3_K", 6, 512), ("Q6_K", 6, 512), ("NVFP4", 6, 256), ("Q5_K", 6, 512), ("Q8_0", 6, 512), ("Q2_K", 6, 512), ("IQ4_XS", 6, 512))):
         rng = np.random.default_rng(100 + i)
         raw = SY.random_blocks(t, n, k, rng)
         if t == "NVFP4":                                   # also the scale codes the decoder special-cases

@@ -8,7 +8,7 @@ from kyojin_mac_b200 import layout as L, ops, synth
 from oracle import kq_numpy as O
 
 pytestmark = pytest.mark.gpu
-T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 
 
 def _bits(a):
@@ -28,7 +28,7 @@ def test_device_repack_equals_numpy_and_inverts(fmt, n, k):
     np.testing.assert_array_equal(ops.t16_to_raw(fmt, dev, n, k).cpu().numpy(), raw)
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "q3_k", "q6_k", "q5_k", "q8_0", "q2_k"])
+@pytest.mark.parametrize("fmt", ["q4_k", "q3_k", "q6_k", "q5_k", "q8_0", "q2_k", "iq4_xs"])
 def test_dequant_kat_ggml(ggml_golden, fmt):
     raw, ref = ggml_golden[T[fmt] + "_raw"], ggml_golden[T[fmt] + "_ref"]
     if fmt == "q8_0":                                                              # 36 blocks of 32 in the fixture: the first 32 make whole 256-input blocks

@@ -16,7 +16,7 @@ from kyojin_mac_b200.foreign_linear import DevPack, ForeignSwitchGLU
 from oracle import fp4_numpy as F4, kq_numpy as O, moe_numpy as M
 
 pytestmark = pytest.mark.gpu
-T_ = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+T_ = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 
 
 class _Experts(dict):

@@ -9,7 +9,7 @@ from kyojin_mac_b200.foreign_linear import ForeignLinear
 from oracle import kq_numpy as O
 
 pytestmark = pytest.mark.gpu
-T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 128, 256), (256, 512, 1024), (70, 200, 320), (1000, 1300, 2048), (2048, 3072, 3072)])
@@ -43,7 +43,7 @@ def test_gemm_saturates_and_scales():
     torch.testing.assert_close(d2.float(), torch.full((128, 128), 640.0, device="cuda"), rtol=1e-3, atol=0)
 
 
-@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4", "q5_k", "q8_0", "q2_k"])
+@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4", "q5_k", "q8_0", "q2_k", "iq4_xs"])
 @pytest.mark.parametrize("rows", [70, 300])
 def test_linear_prefill_vs_fp64(fmt, rows):
     n, k = 384, 1024

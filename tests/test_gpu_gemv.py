@@ -9,7 +9,7 @@ from kyojin_mac_b200 import layout as L, ops, synth
 from oracle import kq_numpy as O
 
 pytestmark = pytest.mark.gpu
-T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+T = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 REL_FRO = 1e-3          # benchmark contract
 MAX_ABS = 2e-3          # reference's K-class tolerance, relative to max |want|
 

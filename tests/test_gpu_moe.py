@@ -10,7 +10,7 @@ from kyojin_mac_b200.foreign_linear import DevPack, ForeignSwitchGLU
 from oracle import kq_numpy as O, moe_numpy as M
 
 pytestmark = pytest.mark.gpu
-T_ = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K"}
+T_ = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
 
 
 @pytest.mark.parametrize("T,E,K,norm", [(64, 256, 8, True), (7, 64, 4, False), (300, 128, 8, True)])
@@ -75,7 +75,7 @@ def _stack(fmt, E, n, k, seed):
     return DevPack(packs), W
 
 
-@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0", "q2_k"])
+@pytest.mark.parametrize("fmt", ["q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0", "q2_k", "iq4_xs"])
 def test_gather_election_equals_per_expert(fmt):
     """Gathered GEMV with expert election == the expert's own one-matrix GEMV on the same row, bit for bit, and matches fp64."""
     E, n, k, S = 6, 64, 512, 37

@@ -71,4 +71,4 @@ def test_bad_shapes_raise():
     with pytest.raises(ValueError):
         L.t16_nbytes("q4_k", 16, 100)
     with pytest.raises(ValueError):
-        L.t16_nbytes("iq4_xs", 16, 256)
+        L.t16_nbytes("iq3_s", 16, 256)

@@ -10,7 +10,7 @@ def _bits(a):
     return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q3_K", "Q6_K", "Q5_K", "Q8_0", "Q2_K"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q3_K", "Q6_K", "Q5_K", "Q8_0", "Q2_K", "IQ4_XS"])
 def test_bit_equal_to_ggml(ggml_golden, t):
     raw, ref = ggml_golden[t + "_raw"], ggml_golden[t + "_ref"]
     be, bb = O.BLOCK[t]
@@ -21,7 +21,7 @@ def test_bit_equal_to_ggml(ggml_golden, t):
     np.testing.assert_array_equal(_bits(one), _bits(ref))
 
 
-@pytest.mark.parametrize("t", ["Q4_K", "Q3_K", "Q6_K", "NVFP4", "Q5_K", "Q8_0", "Q2_K"])
+@pytest.mark.parametrize("t", ["Q4_K", "Q3_K", "Q6_K", "NVFP4", "Q5_K", "Q8_0", "Q2_K", "IQ4_XS"])
 def test_bit_equal_to_reference_decoder(ref_golden, t):
     k = int(ref_golden[t + "_k"])
     np.testing.assert_array_equal(_bits(O.dequant(t, ref_golden[t + "_raw"], k)), _bits(ref_golden[t + "_f32"]))
