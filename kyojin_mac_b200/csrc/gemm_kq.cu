@@ -694,6 +694,230 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ the dense form by CTA pairs (tcgen05 cta_group::2)
+// A pair of CTAs computes a 256 x 256 tile of D: each CTA holds 128 activation rows (TMA) and decodes ONE HALF of the 256 weight rows (8 row tiles) of a
+// 128-input stage; one MMA of the pair's leader runs on both tensor cores. Per SM and per flop the decode work, the decoder stores and the B operand reads are
+// half of those of a one-CTA item with two activation blocks, which is what bounds that form (shared-memory bandwidth). The 16 decoder warps of a CTA are
+// (row tile w & 7, quarter parity w >> 3): a warp decodes quarters hq and hq + 2 of every T16 tile of its row tile, one per stage (a stage is 128 inputs =
+// two 64-input K-halves; quarter hq or hq + 2 of the tile lands in K-half hq). Barriers as in the NVFP4 pair kernel: full[s] in the leader (the leader's
+// producer with the byte count of both CTAs' activation tiles + the 32 decoder warps of both CTAs, the peer's by remote arrive), empty[s] and acc_full in each
+// CTA (commit to the pair), acc_empty in the leader (8 epilogue warps). Two accumulators alternate. Every wait is bounded.
+// The decoder warps of the peer arrive on the leader's barrier with the plain (CTA-scope release) form of the remote arrive, as the vendor's own pipelines do
+// for remote arrivals: by then the warp's stores sit in its own CTA's shared memory behind a proxy fence, which is where the leader's MMA reads them. With
+// release at cluster scope on each of the 32 arrivals per stage the kernel ran at 950 TFLOP/s instead of 1430.
+constexpr uint32_t KP_A_BYTES = 2 * KQ_A_SUB, KP_B_BYTES = 2 * 128 * KQ_BK * 2, KP_STAGE_BYTES = KP_A_BYTES + KP_B_BYTES;   // 32 K + 32 K per 128-input stage
+constexpr int KP_STAGES = 3;
+
+// registers that only quarter P of the tile used are refilled from the next tile right after P has been computed (this warp uses two quarters of a tile)
+template <int FMT, int P>
+__device__ __forceinline__ void kq_refill_pair(const uint8_t* next, int lane, KqTile<FMT>& tr) {
+    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q6_K) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+        tr.q[4 + (P >> 1)] = ldg128s(next + 2048 + ((P >> 1) * 32 + lane) * 16);
+    } else {
+        tr.q[P >> 1] = ldg128s(next + ((P >> 1) * 32 + lane) * 16);
+        const uint2 hb = ldg64s(next + 1024 + lane * 16 + ((P & 2) ? 8 : 0));
+        if constexpr ((P & 2) == 0) tr.q[2].x = hb.x, tr.q[2].y = hb.y;
+        else tr.q[2].z = hb.x, tr.q[2].w = hb.y;
+    }
+}
+
+struct KpTile {
+    int m0, n0;      // this CTA's first activation row, first weight row of the 256-wide tile
+};
+__device__ __forceinline__ KpTile kp_tile(const KqParams& p, int t, uint32_t rank) {
+    KpTile it;
+    const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;                          // m fastest: the pairs running together share the weight rows
+    it.n0 = tn * KQ_BN, it.m0 = tm * 256 + (int)rank * 128;
+    return it;
+}
+
+template <int FMT, int HQ>
+__device__ __forceinline__ bool kp_decode(const KqParams& p, const int num_items, const int pair, const int pairs, const uint32_t rank, const int rt8, const int lane,
+                                          const uint32_t smem0, const uint32_t scr, const uint32_t full_leader0, const uint32_t empty0) {
+    constexpr int TB = kyb_tile_bytes(FMT);
+    const int g = lane >> 2, tq = lane & 3;
+    const uint32_t row_off = (uint32_t)(2 * rt8) * 1024u + (uint32_t)g * 128u + 8u * (uint32_t)(tq & 1);
+    const bool odd = (g & 1) != 0;
+    uint32_t cx[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cx[i] = (uint32_t)(((2 * (i ^ (odd ? 2 : 0)) + (tq >> 1)) ^ g) * 16);
+    uint32_t parity = 1;
+    int s = 0;
+    bool failed = false;
+    for (int t = pair; t < num_items && !failed; t += pairs) {
+        const KpTile it = kp_tile(p, t, rank);
+        const int rt = min((it.n0 >> 4) + (int)rank * 8 + rt8, p.rt_total - 1);
+        const uint8_t* tp = p.t16 + (size_t)rt * (size_t)p.nb * TB;
+        KqTile<FMT> tr;
+        uint32_t r[16];
+        kq_load<FMT>(tp, lane, tr);
+        kq_prep_scales<FMT>(tr, scr, lane);
+        __syncwarp();
+        if (p.nb > 1) kq_refill_scales<FMT>(tp + TB, lane, tr);
+        kq_compute_quarter<FMT, HQ>(tr, scr, lane, r);
+        if (p.nb > 1) kq_refill_pair<FMT, HQ>(tp + TB, lane, tr);
+#define KYB_KP_STORE()                                                                                            \
+    {                                                                                                             \
+        if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;                                               \
+        const uint32_t b_dst = smem0 + s * KP_STAGE_BYTES + KP_A_BYTES + HQ * 16384u + row_off;                   \
+        kq_store_quarter(b_dst, b_dst + 1024u, cx, odd, r);                                                       \
+    }
+#define KYB_KP_PUBLISH()                                                                                          \
+    {                                                                                                             \
+        fence_proxy_async_smem();                                                                                 \
+        __syncwarp();                                                                                             \
+        if (lane == 0) mbar_arrive_remote(full_leader0 + 8 * s);                                                  \
+        if (++s == KP_STAGES) s = 0, parity ^= 1u;                                                                \
+    }
+        for (int kb = 0; kb < p.nb && !failed; ++kb) {
+            const bool more = kb + 1 < p.nb, more2 = kb + 2 < p.nb;
+            const uint8_t* nx = tp + (size_t)(kb + 1) * TB;
+            KYB_KP_STORE()                                                       // quarter HQ: inputs [0, 128) of the tile
+            kq_compute_quarter<FMT, HQ + 2>(tr, scr, lane, r);
+            if (more) kq_refill_pair<FMT, HQ + 2>(nx, lane, tr);
+            KYB_KP_PUBLISH()                                                     // its warp barrier also ends every lane's reads of this tile's scales
+            if (more) {
+                kq_prep_scales<FMT>(tr, scr, lane);                              // tr.sc holds the next tile's scale bytes
+                __syncwarp();
+                if (more2) kq_refill_scales<FMT>(nx + TB, lane, tr);
+            }
+            KYB_KP_STORE()                                                       // quarter HQ + 2: inputs [128, 256)
+            if (more) {
+                kq_compute_quarter<FMT, HQ>(tr, scr, lane, r);
+                if (more2) kq_refill_pair<FMT, HQ>(nx + TB, lane, tr);
+            }
+            KYB_KP_PUBLISH()
+        }
+#undef KYB_KP_STORE
+#undef KYB_KP_PUBLISH
+    }
+    return failed;
+}
+
+template <int FMT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(KQ_THREADS, 1)
+    gemm_kq_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ KqOutMaps outs, const KqParams p, const int num_items) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t scr0 = smem0 + (uint32_t)KP_STAGES * KP_STAGE_BYTES;
+    const uint32_t stg0 = scr0 + KQ_DW * KQ_SCR;                                    // epilogue staging, 4 warps
+    const uint32_t bars = stg0 + 4 * KQ_STG;                                        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
+    const uint32_t full0 = bars, empty0 = bars + 8 * KP_STAGES, accf0 = bars + 16 * KP_STAGES, acce0 = accf0 + 16, tmem_slot = acce0 + 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = (int)(blockIdx.x >> 1), pairs = (int)(gridDim.x >> 1);
+    const int kstages = p.k / 128;
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < KP_STAGES; ++s) mbar_init_a(full0 + 8 * s, 2 * KQ_DW + 1), mbar_init_a(empty0 + 8 * s, 1);
+        for (int a = 0; a < 2; ++a) mbar_init_a(accf0 + 8 * a, 1), mbar_init_a(acce0 + 8 * a, 8);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tma_a);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    cluster_sync_all();                                                            // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = lds32(tmem_slot);
+    const uint32_t full_leader0 = map_to_rank(full0, 0);
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---- TMA producer: this CTA's 128 activation rows, two 64-input boxes per stage
+        if (elect_one()) {
+            uint32_t parity = 1;
+            int s = 0;
+            for (int t = pair; t < num_items && !failed; t += pairs) {
+                const KpTile it = kp_tile(p, t, rank);
+                for (int ks = 0; ks < kstages && !failed; ++ks) {
+                    if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
+                    const uint32_t a_dst = smem0 + s * KP_STAGE_BYTES;
+                    if (rank == 0) mbar_expect_tx_a(full0 + 8 * s, 2 * KP_A_BYTES);
+                    tma_load_2d_pair(a_dst, &tma_a, ks * 128, it.m0, full_leader0 + 8 * s);
+                    tma_load_2d_pair(a_dst + KQ_A_SUB, &tma_a, ks * 128 + 64, it.m0, full_leader0 + 8 * s);
+                    if (++s == KP_STAGES) s = 0, parity ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer: the pair's leader
+        if (rank == 0 && elect_one()) {
+            constexpr uint32_t idesc = umma_idesc_f16(256, KQ_BN);
+            uint32_t parity = 0;
+            int s = 0;
+            uint32_t cnt = 0;
+            for (int t = pair; t < num_items && !failed; t += pairs, ++cnt) {
+                const uint32_t slot = cnt & 1u;
+                if (!mbar_wait_fast(acce0 + 8 * slot, ((cnt >> 1) & 1u) ^ 1u)) failed = true;           // both CTAs' epilogues have drained the slot
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + slot * KQ_BN;
+                for (int ks = 0; ks < kstages && !failed; ++ks) {
+                    if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
+                    tc_fence_after();
+                    const uint32_t a_src = smem0 + s * KP_STAGE_BYTES, b_src = a_src + KP_A_BYTES;
+#pragma unroll
+                    for (int kh = 0; kh < 2; ++kh) {
+                        const uint64_t adesc = umma_desc_sw128(a_src + kh * KQ_A_SUB), bdesc = umma_desc_sw128(b_src + kh * 16384u);
+#pragma unroll
+                        for (int kk = 0; kk < KQ_BK / 16; ++kk) umma_f16_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (ks | kh | kk) != 0);
+                    }
+                    umma_commit_pair(empty0 + 8 * s);
+                    if (++s == KP_STAGES) s = 0, parity ^= 1u;
+                }
+                umma_commit_pair(accf0 + 8 * slot);
+            }
+        }
+    } else if (warp < 6) {
+        // ---- epilogue: this CTA's 128 rows x 256 columns, staged tiled bulk stores
+        const int q = warp & 3;
+        const uint32_t acce_leader0 = map_to_rank(acce0, 0);
+        uint32_t cnt = 0;
+        for (int t = pair; t < num_items; t += pairs, ++cnt) {
+            const KpTile it = kp_tile(p, t, rank);
+            const uint32_t slot = cnt & 1u;
+            if (!mbar_wait_fast(accf0 + 8 * slot, (cnt >> 1) & 1u)) failed = true;
+            tc_fence_after();
+            const uint32_t stg = stg0 + (uint32_t)q * KQ_STG;
+            const int row0 = it.m0 + q * 32;
+#pragma unroll 1
+            for (int c = 0; c < KQ_BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
+                tmem_ld_wait();
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * j]) * p.gscale), sat_half(__uint_as_float(v[2 * j + 1]) * p.gscale));
+                    w[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                epilogue_stage_store(outs, 1, stg, lane, w, it.n0 + c, row0, !failed && row0 < p.m && it.n0 + c < p.n);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acce_leader0 + 8 * slot);
+        }
+    } else {
+        // ---- decoders
+        const int dw = warp - 6;
+        const uint32_t scr = scr0 + dw * KQ_SCR;
+        if (dw < 8) failed = kp_decode<FMT, 0>(p, num_items, pair, pairs, rank, dw, lane, smem0, scr, full_leader0, empty0);
+        else failed = kp_decode<FMT, 1>(p, num_items, pair, pairs, rank, dw - 8, lane, smem0, scr, full_leader0, empty0);
+    }
+    if (warp >= 2 && warp < 6 && lane == 0) tma_store_wait_all();                      // the staging buffer must outlive its stores
+    if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
+    tc_fence_before();
+    cluster_sync_all();                                                            // neither CTA frees tensor memory or leaves while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 }  // namespace kyb
 
 namespace {
@@ -726,10 +950,48 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
     return kyb_launch_check("gemm_kq");
 }
 
+// the dense form by CTA pairs; KYB_EUNSUPPORTED when the device cannot hold a pair of these CTAs at once (the caller then takes the one-CTA kernel)
+int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqParams p, cudaStream_t st) {
+    static std::mutex mu;
+    static unsigned done[4] = {0, 0, 0, 0};
+    static int pairs_max[4][32] = {};
+    int dev = 0;
+    KYB_CUDA(cudaGetDevice(&dev));
+    const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q4_K>
+                       : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q6_K>
+                       : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q3_K>
+                                             : (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_NVFP4>;
+    constexpr size_t smem = (size_t)kyb::KP_STAGES * kyb::KP_STAGE_BYTES + (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * kyb::KQ_STG + 1024 + 256;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        if (!(done[fmt] & (1u << (dev & 31)))) {
+            KYB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cudaLaunchConfig_t qc = {};
+            qc.gridDim = dim3(2), qc.blockDim = dim3(kyb::KQ_THREADS), qc.dynamicSmemBytes = smem;
+            int nc = 0;
+            if (cudaOccupancyMaxActiveClusters(&nc, kern, &qc) != cudaSuccess || nc <= 0) {
+                (void)cudaGetLastError();
+                nc = 0;
+            }
+            pairs_max[fmt][dev & 31] = nc;
+            done[fmt] |= 1u << (dev & 31);
+        }
+    }
+    const int pm = pairs_max[fmt][dev & 31];
+    if (pm <= 0) return KYB_EUNSUPPORTED;
+    p.msub = 2;
+    p.tiles_m = (p.m + 255) / 256;
+    const int num_items = p.tiles_n * p.tiles_m;
+    const int pairs = std::min(num_items, pm);
+    void* args[] = {(void*)&ta, (void*)&outs, (void*)&p, (void*)&num_items};
+    KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)(2 * pairs)), dim3(kyb::KQ_THREADS), args, smem, st));
+    return kyb_launch_check("gemm_kq_pair");
+}
+
 }  // namespace
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
-                    int64_t col0, int msub, void* stream) {
+                    int64_t col0, int msub, void* stream, bool pair_ok = true) {
     if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
         kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
         return KYB_EUNSUPPORTED;
@@ -775,6 +1037,10 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
         if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
                                       p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
+    if (nout == 1 && p.tma_out && m > 128 && pair_ok) {
+        // one destination and at least two row blocks: CTA pairs (cta_group::2), each CTA decoding half of the 256 weight rows of a tile
+        if (int rc = kq_launch_pair(fmt, ta, outs, p, (cudaStream_t)stream); rc != KYB_EUNSUPPORTED) return rc;
+    }
     return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }
 

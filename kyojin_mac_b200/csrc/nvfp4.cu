@@ -468,31 +468,6 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
 constexpr int NP_STAGES = 5;
 constexpr uint32_t NP_A_BYTES = 128 * NV_BK / 2, NP_B_BYTES = 128 * NV_BK / 2, NP_STAGE_BYTES = NP_A_BYTES + NP_B_BYTES + NV_SFA_BYTES + NV_SFB_BYTES;   // 16 K + 16 K + 2 K + 4 K
 
-__device__ __forceinline__ uint32_t cluster_rank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// tiled load into this CTA's shared memory whose bytes complete on a barrier of the pair's leader (bar: shared::cluster address)
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm), "r"(x),
-                 "r"(y), "r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) { asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory"); }
-__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) { asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory"); }
 __device__ __forceinline__ void tmem_cp_32x128b_x4_pair(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
@@ -503,11 +478,6 @@ __device__ __forceinline__ void umma_nvf4_pair(uint32_t tmem_d, uint64_t adesc, 
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tsfa), "r"(tsfb), "r"(accumulate)
         : "memory");
 }
-// arrives on the barrier at this offset in both CTAs of the pair once every tcgen05 operation issued so far by this thread has completed
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((unsigned short)3) : "memory");
-}
-
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NV_THREADS, 1)
     gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_sfa,
                            const __grid_constant__ CUtensorMap tma_sfb, const __grid_constant__ KybOutMaps outs, const NvGemmParams p, const int tiles_n, const int num_tiles) {
