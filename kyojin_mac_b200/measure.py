@@ -23,7 +23,9 @@ from .foreign_linear import DevPack, ForeignSwitchGLU
 BPW = {"q4_k": 144 / 256, "q6_k": 210 / 256, "q3_k": 110 / 256, "nvfp4": 144 / 256}
 
 
-def timeit(fn, iters=20, warm=3):
+def timeit(fn, iters=20, warm=3, reps=1):
+    """(min, median) microseconds per call over `iters` timings, each of `reps` back-to-back calls between two events (reps > 1 takes the launch gap at the head
+    of an idle stream out of short kernels' figures)."""
     for _ in range(warm):
         fn()
     torch.cuda.synchronize()
@@ -31,10 +33,11 @@ def timeit(fn, iters=20, warm=3):
     for _ in range(iters):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1) * 1e3)
+        ts.append(e0.elapsed_time(e1) * 1e3 / reps)
     return min(ts), statistics.median(ts)
 
 
@@ -104,7 +107,7 @@ def cfg2(extra=False):
         x = torch.randn((m, k), device="cuda").to(torch.float16)
         y = torch.empty((m, n), dtype=torch.float16, device="cuda")
         fl = 2.0 * m * n * k
-        t_a = timeit(lambda: dp.apply(x))[1]
+        t_a = timeit(lambda: dp.apply(x), reps=4)[1]
         rows = torch.randperm(n, device="cuda")[:256]
         w32 = ops.dequant("q3_k", dp.t16, n, k, torch.float32)[rows]
         err = _rel_fro(dp.apply(x)[:, rows], x.double() @ w32.double().T)
@@ -113,9 +116,8 @@ def cfg2(extra=False):
                "parity": {"rel_fro": err, "sample": "256 output columns x all 2048 rows", "against": _PARITY_NOTE}}
         if extra:
             w16 = dp.dequant()
-            rec.update(dequant_us=timeit(lambda: dp.dequant())[1], fp16_gemm_us=timeit(lambda: ops.gemm_f16(x, w16, out=y))[1], staged_us=timeit(lambda: dp._prefill_two_step(x))[1],
-                       fused_msub1_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y, msub=1))[1],
-                       fused_msub2_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y, msub=2))[1])
+            rec.update(dequant_us=timeit(lambda: dp.dequant(), reps=4)[1], fp16_gemm_us=timeit(lambda: ops.gemm_f16(x, w16, out=y), reps=4)[1],
+                       staged_us=timeit(lambda: dp._prefill_two_step(x), reps=4)[1], fused_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y), reps=4)[1])
         out.append(rec)
     return out
 
@@ -146,9 +148,9 @@ def cfg3():
     ac, ap, asw = ops.nvfp4_quant_rows(x, True, True)
     y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     fl = 2.0 * m * n * k
-    t_q = timeit(lambda: ops.nvfp4_quant_rows(x, True, False))[1]
-    t_g = timeit(lambda: ops.gemm_nvfp4(ac, asw, qs, sfb, m, n, k, 1.0, out=y))[1]
-    t_a = timeit(lambda: dp.apply_a4(x, torch.bfloat16))[1]
+    t_q = timeit(lambda: ops.nvfp4_quant_rows(x, True, False), reps=4)[1]
+    t_g = timeit(lambda: ops.gemm_nvfp4(ac, asw, qs, sfb, m, n, k, 1.0, out=y), reps=4)[1]
+    t_a = timeit(lambda: dp.apply_a4(x, torch.bfloat16), reps=4)[1]
     lib = fp4_library_peak()
     peak, src = (lib["TFLOPs_best"], "vendor block-scaled NVFP4 GEMM 8192^3 (torch._scaled_mm) measured in this run") if "TFLOPs_best" in lib else (9000.0, "nominal dense fp4 (vendor GEMM unavailable)")
     rows = torch.randperm(n, device="cuda")[:256]
