@@ -125,7 +125,8 @@ int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const void* b_codes,
  * matrix never exists in HBM. d fp16 [m, n] = sat(gscale * a fp16 [m, k] x W^T). Same call sites as the two entries above
  * (kyojin_mlx/foreign_linear.py:710 / :737 dense, kyojin_mlx/foreign_kqgmm.py:225-239 `gmm` grouped). Weights are rounded to fp16 at the reference's own rounding
  * points for its few-row tensor kernels (block scale and min to fp16, one fp16 fma per weight: kyojin_mlx/foreign_metal.py:1357-1358, :1382-1383); NVFP4 weights
- * are exact in fp16. msub: 128-row blocks of a per work item, 1 or 2 (0 = chosen by the library). The grouped form needs n % 256 == 0 and tb / off from
+ * are exact in fp16. msub = 0: chosen by the library (CTA pairs, tcgen05 cta_group::2, for more than 128 rows and one destination); 1 or 2: the one-CTA
+ * kernel with that many 128-row blocks of a per work item (same bits either way). The grouped form needs n % 256 == 0 and tb / off from
  * kyb_moe_plan with the same mt (128 or 256 rows of one expert per work item). */
 int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub, void* stream);
 int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,

@@ -950,7 +950,8 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
     return kyb_launch_check("gemm_kq");
 }
 
-// the dense form by CTA pairs; KYB_EUNSUPPORTED when the device cannot hold a pair of these CTAs at once (the caller then takes the one-CTA kernel)
+// the dense form by CTA pairs; KYB_EUNSUPPORTED when the device cannot hold a pair of these CTAs at once or the tile count suits the one-CTA kernel better (the
+// caller then takes that kernel)
 int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqParams p, cudaStream_t st) {
     static std::mutex mu;
     static unsigned done[4] = {0, 0, 0, 0};
@@ -982,6 +983,9 @@ int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::
     p.msub = 2;
     p.tiles_m = (p.m + 255) / 256;
     const int num_items = p.tiles_n * p.tiles_m;
+    // more tiles than pairs but no more than SMs: the one-CTA kernel runs them all at once, pairs would need a second, poorly filled wave (12288 -> 3072 at
+    // M = 2048: 96 tiles, 156 us against 170 us)
+    if (num_items > pm && num_items <= 2 * pm) return KYB_EUNSUPPORTED;
     const int pairs = std::min(num_items, pm);
     void* args[] = {(void*)&ta, (void*)&outs, (void*)&p, (void*)&num_items};
     KYB_CUDA(cudaLaunchKernel(kern, dim3((unsigned)(2 * pairs)), dim3(kyb::KQ_THREADS), args, smem, st));
@@ -1003,6 +1007,7 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     KYB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)t16 & 15) == 0, "a and t16 must be 16-byte aligned");
     KYB_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 24), "dimension too large");
     KYB_REQUIRE(msub >= 0 && msub <= 2, "msub is 0 (automatic), 1 or 2");
+    const bool automatic = msub == 0;                                              // a given msub asks for the one-CTA kernel with that many activation blocks per item
     unsigned int* status = kyb_device_status_word();
     KYB_REQUIRE(status, "could not set up the device status word");
     CUtensorMap ta;
@@ -1037,15 +1042,16 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
         if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
                                       p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
-    if (nout == 1 && p.tma_out && m > 128 && pair_ok) {
+    if (nout == 1 && p.tma_out && m > 128 && pair_ok && automatic) {
         // one destination and at least two row blocks: CTA pairs (cta_group::2), each CTA decoding half of the 256 weight rows of a tile
         if (int rc = kq_launch_pair(fmt, ta, outs, p, (cudaStream_t)stream); rc != KYB_EUNSUPPORTED) return rc;
     }
     return kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m, (cudaStream_t)stream);
 }
 
-// D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub: 1 or 2 blocks of 128
-// activation rows per work item (0 = chosen here).
+// D fp16 [m, n] (row stride ldd) = sat(gscale * A fp16 [m, k] (row stride lda) x W^T), W = T16 tiles of an [n, k] matrix of format fmt. msub = 0: the library
+// chooses (CTA pairs for more than 128 rows, else the one-CTA kernel); 1 or 2: the one-CTA kernel with that many blocks of 128 activation rows per work item.
+// All forms give the same bits.
 extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub,
                            void* stream) {
     KYB_REQUIRE(d && ((uintptr_t)d & 1) == 0, "null or odd output pointer");

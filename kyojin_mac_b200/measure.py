@@ -117,7 +117,9 @@ def cfg2(extra=False):
         if extra:
             w16 = dp.dequant()
             rec.update(dequant_us=timeit(lambda: dp.dequant(), reps=4)[1], fp16_gemm_us=timeit(lambda: ops.gemm_f16(x, w16, out=y), reps=4)[1],
-                       staged_us=timeit(lambda: dp._prefill_two_step(x), reps=4)[1], fused_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y), reps=4)[1])
+                       staged_us=timeit(lambda: dp._prefill_two_step(x), reps=4)[1], fused_pair_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y), reps=4)[1],
+                       fused_one_cta_msub1_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y, msub=1), reps=4)[1],
+                       fused_one_cta_msub2_us=timeit(lambda: ops.gemm_kq("q3_k", dp.t16, n, k, x, out=y, msub=2), reps=4)[1])
         out.append(rec)
     return out
 

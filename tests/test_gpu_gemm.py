@@ -62,7 +62,8 @@ def test_linear_prefill_vs_fp64(fmt, rows):
 
 @pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4"])
 def test_fused_decode_gemm_vs_staged(fmt):
-    """Weights decoded inside the GEMM: one and two activation blocks per work item give the same bits; NVFP4 equals the staged form bit for bit (its fp16
+    """Weights decoded inside the GEMM: the CTA-pair kernel (the default for more than 128 rows) and the one-CTA kernel with one and two activation blocks per
+    work item give the same bits; NVFP4 equals the staged form bit for bit (its fp16
     weights are exact), K-quants stay within the accuracy bound and within a few fp16 roundings of the staged form."""
     n, k, m = 1040, 2048, 520                                               # n and m with ragged last tiles
     t16 = synth.t16_random_device(fmt, n, k, seed=11)
@@ -70,8 +71,9 @@ def test_fused_decode_gemm_vs_staged(fmt):
     x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
     y1 = ops.gemm_kq(fmt, t16, n, k, x, msub=1)
     y2 = ops.gemm_kq(fmt, t16, n, k, x, msub=2)
+    y0 = ops.gemm_kq(fmt, t16, n, k, x)
     ops.check_device_status()
-    assert torch.equal(y1, y2)
+    assert torch.equal(y1, y2) and torch.equal(y0, y1)
     w16 = ops.dequant(fmt, t16, n, k, torch.float16)
     staged = ops.gemm_f16(x, w16)
     if fmt == "nvfp4":
