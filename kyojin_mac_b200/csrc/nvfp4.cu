@@ -750,7 +750,9 @@ static int nvfp4_gemm_impl(const void* a_codes, const void* sfa, const void* b_c
             }
         }
         const int pm = pairs_max[dev & 31];
-        if (pm > 0) {
+        const int pair_tiles = (int)(n / kyb::NV_BN) * (int)((m + 255) / 256);
+        // more tiles than pairs but no more than SMs: the one-CTA kernel (twice as many, half as large tiles) fills the device better than a second, short wave of pairs
+        if (pm > 0 && !(pair_tiles > pm && pair_tiles <= 2 * pm)) {
             const int tiles_n = (int)(n / kyb::NV_BN), num_tiles = tiles_n * (int)((m + 255) / 256);
             const int pairs = num_tiles < pm ? num_tiles : pm;
             kyb::gemm_nvfp4_pair_kernel<<<(unsigned)(2 * pairs), kyb::NV_THREADS, psmem, (cudaStream_t)stream>>>(ta, tbh, tsa, tsb, outs, p, tiles_n, num_tiles);
