@@ -170,11 +170,12 @@ class Sweep:
     """The decode sweep over one list of products [(name, fmt, n, k)] at M = 1, 2, 4, 8: two layer copies of seeded synthetic T16 weights alternate (one layer
     exceeds L2), one CUDA graph per copy holds the chained launches of a step, and with more than one rank the step ends with the peer gather of its outputs."""
 
-    def __init__(self, mats, dev, world, rank, seed0, nccl_gather=False):
+    def __init__(self, mats, dev, world, rank, seed0, nccl_gather=False, staged_gather=True):
         import torch
         from kyojin_mac_b200 import synth
         from kyojin_mac_b200.foreign_linear import DevPack
         self.mats, self.dev, self.world, self.rank = mats, dev, world, rank
+        self.staged_gather = staged_gather
         self.copies = 2
         self.layers = [[DevPack.from_t16(f, synth.t16_random_device(f, n, k, seed=seed0 + 1000 * rank + 10 * c + i, device=dev), n, k) for i, (nm, f, n, k) in enumerate(mats)]
                        for c in range(self.copies)]
@@ -193,11 +194,32 @@ class Sweep:
                 if rank == 0:
                     print(f"[bench] symmetric memory unavailable ({type(e).__name__}: {e}); NCCL all-gathers", file=sys.stderr)
         self.graphs = None
+        if self.pg is not None:
+            import torch
+            self.side = torch.cuda.Stream(device=dev)
 
     def one_step(self, c):
         import torch.distributed as dist
         from kyojin_mac_b200 import ops
         layer, works = self.layers[c], []
+        if self.pg is not None and self.staged_gather:
+            # the outputs of a batch size leave for the other ranks on a second stream while the products of the next batch size run; the largest batch goes first,
+            # so what is left exposed at the end of the step is the smallest transfer and the one barrier
+            import torch
+            main = torch.cuda.current_stream()
+            self.pg.begin()
+            for m in sorted(BATCHES, reverse=True):
+                idx = [j for j, (mm, _) in enumerate(self.order) if mm == m]
+                for i, (nm, f, n, k) in enumerate(self.mats):
+                    ops.gemv(f, layer[i].t16, n, k, self.xs[(m, k)], 1.0, out=self.ys[(m, i)], chained=True)
+                ev = torch.cuda.Event()
+                ev.record(main)
+                with torch.cuda.stream(self.side):
+                    self.side.wait_event(ev)
+                    self.pg.store(idx, [self.ys[self.order[j]] for j in idx])
+            main.wait_stream(self.side)
+            self.pg.finish()
+            return
         for m in BATCHES:
             for i, (nm, f, n, k) in enumerate(self.mats):
                 ops.gemv(f, layer[i].t16, n, k, self.xs[(m, k)], 1.0, out=self.ys[(m, i)], chained=True)      # the weights were generated long before: chained launches
@@ -304,7 +326,7 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- value: weak scaling (every rank streams a full layer-sized shard), one CUDA graph per layer copy, device-timed
-    sw = Sweep(mats, dev, world, rank, seed0=0, nccl_gather=args.nccl_gather)
+    sw = Sweep(mats, dev, world, rank, seed0=0, nccl_gather=args.nccl_gather, staged_gather=not args.end_gather)
     sw.capture()
     for s in range(args.warmup):
         sw.run_step(s)
@@ -428,7 +450,7 @@ def run_ours(args):
         else:
             from kyojin_mac_b200.dist import shard_rows
             sharded = [(nm_, f_, shard_rows(n_, world, rank)[1], k_) for nm_, f_, n_, k_ in mats]
-            ss = Sweep(sharded, dev, world, rank, seed0=50000, nccl_gather=args.nccl_gather)
+            ss = Sweep(sharded, dev, world, rank, seed0=50000, nccl_gather=args.nccl_gather, staged_gather=not args.end_gather)
             ss.capture()
             ms_strong = ss.timed(args.steps, args.warmup, barrier)
             strong = {"cfg1": {"case": "the layer at its stated width, every matrix N-sharded by rows, peer gather per step", "ms_per_step": ms_strong,
@@ -455,7 +477,8 @@ def run_ours(args):
                            "launch_list": [f"{nm}:{f}:{n}x{k}" for nm, f, n, k in mats], "same_input_groups": not args.no_group,
                            "l2": "two layer copies alternate; one layer (328 MB) exceeds the 126 MB L2",
                            "timing": ("CUDA graph per step (chained launches), CUDA events, max over ranks" if sw.graphs is not None else "eager launches, CUDA events, max over ranks"),
-                           "parallelism": (f"weak scaling: n-sharded x{world} of an {world}x wider layer + peer-store gather of the step's output slices (one launch + one barrier per step)" if pg is not None
+                           "parallelism": ((f"weak scaling: n-sharded x{world} of an {world}x wider layer + peer-store gather of the output slices: one copy launch per batch size on a second stream (under the next batch size's products), one barrier per step" if sw.staged_gather
+                                             else f"weak scaling: n-sharded x{world} of an {world}x wider layer + peer-store gather of the step's output slices (one launch + one barrier per step)") if pg is not None
                                            else f"weak scaling: n-sharded x{world} of an {world}x wider layer + NCCL all-gather of output slices") if world > 1 else "single GPU",
                            "bytes_per_step": step_bytes},
                 "roofline": roofline, "cpu_baseline": cpu,
@@ -487,6 +510,7 @@ def main():
     ap.add_argument("--no-group", action="store_true", help="launch q, k, v and gate, up separately instead of as same-input groups")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (1 GPU) / the strong-scaling forms (N > 1)")
+    ap.add_argument("--end-gather", action="store_true", help="N > 1: gather all outputs of a step with one copy launch at its end instead of one per batch size on a second stream")
     ap.add_argument("--nccl-gather", action="store_true", help="N > 1: one NCCL all-gather per product instead of the one-launch peer gather of the step")
     ap.add_argument("--e2e-eager", action="store_true", help="end-to-end leg through eager module calls instead of the HostGraph step")
     args = ap.parse_args()

@@ -58,7 +58,8 @@ class ShardedLinear:
 
 class PeerGather:
     """All-gather of the output slices of a whole decode step: every rank stores its (small) local outputs into ALL ranks' gathered buffers with ONE copy launch
-    (plain 16-byte stores to peer-mapped symmetric memory over NVLink) followed by ONE device-side barrier, instead of one NCCL all-gather per product.
+    (plain 16-byte stores to peer-mapped symmetric memory over NVLink) followed by ONE device-side barrier, instead of one NCCL all-gather per product. The
+    staged form (`begin` / `store` / `finish`) sends parts of the step early, on a second stream, and keeps the single barrier.
     shapes[i] = (m, n_local) of product i (the same on every rank; pad uneven shards); dtype float16. gathered(i) is this rank's [world, m, n_local] view, valid
     until the call after next (two buffer sets alternate)."""
 
@@ -94,6 +95,30 @@ class PeerGather:
         ops.gather_flat(srcs, dsts, sizes)
         hdl.barrier()
         self.last = i
+
+    def begin(self) -> None:
+        """Staged form: takes the next buffer set. `store` then sends some of the step's outputs (no barrier), `finish` ends the step with the one barrier.
+        A caller can issue each `store` on a second stream as soon as its outputs exist, so that the NVLink transfers run under the products that follow."""
+        self.last, self.turn = self.turn, self.turn ^ 1
+
+    def store(self, indices, outs) -> None:
+        """Copies this rank's outputs `outs` of the products `indices` into every rank's buffers of the current set (one launch, no barrier)."""
+        from . import ops
+        hdl = self.hdls[self.last]
+        srcs, dsts, sizes = [], [], []
+        for i, o in zip(indices, outs):
+            b = self.bytes[i]
+            if o.numel() * o.element_size() != b or not o.is_contiguous():
+                raise ValueError("output does not match its registered shape")
+            for base in hdl.buffer_ptrs:
+                srcs.append(o)
+                dsts.append(int(base) + self.offs[i] + self.rank * b)
+                sizes.append(b)
+        ops.gather_flat(srcs, dsts, sizes)
+
+    def finish(self) -> None:
+        """One device-side barrier: every rank's stores of the step have landed. (Stream order must put every `store` of the step before this call.)"""
+        self.hdls[self.last].barrier()
 
     def gathered(self, i: int) -> torch.Tensor:
         m, n = self.shapes[i]

@@ -37,6 +37,24 @@ def main():
             got_i = pgather.gathered(i)
             for r in range(world):
                 assert torch.all(got_i[r] == float(r * 10 + i + it)), "peer gather: wrong slice"
+    # ---- the same gather in stages: parts of a step sent early on a second stream, one barrier at the end
+    side = torch.cuda.Stream()
+    for it in range(3):
+        outs = [torch.full(sh, float(rank * 10 + i + it + 100), dtype=torch.float16, device="cuda") for i, sh in enumerate(shapes)]
+        pgather.begin()
+        main = torch.cuda.current_stream()
+        for part in ([2], [0, 1]):
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ev)
+                pgather.store(part, [outs[i] for i in part])
+        main.wait_stream(side)
+        pgather.finish()
+        for i, sh in enumerate(shapes):
+            got_i = pgather.gathered(i)
+            for r in range(world):
+                assert torch.all(got_i[r] == float(r * 10 + i + it + 100)), "staged peer gather: wrong slice"
     # ---- NVFP4 W4A4 shard
     n4 = 512 * world
     full4 = synth.t16_random_device("nvfp4", n4, k, seed=4)
