@@ -1,5 +1,5 @@
 // Prefill GEMM with the dequantisation fused into the operand producer: D[m, n] = sat_f16(gscale * sum_k A[m, k] * W[n, k]), W read as T16 tiles
-// (Q4_K / Q6_K / Q3_K / NVFP4) and never written to HBM as fp16. Replaces the two-step large-row path of kyojin_mlx/foreign_linear.py:710 / :737
+// (Q4_K / Q6_K / Q3_K / NVFP4 / Q5_K / Q8_0) and never written to HBM as fp16. Replaces the two-step large-row path of kyojin_mlx/foreign_linear.py:710 / :737
 // (`x2 @ self.dequant().T`) and, in grouped form, the sorted grouped product of kyojin_mlx/foreign_kqgmm.py:225-239 (`gmm`).
 //
 // One persistent CTA per SM, 22 warps:
@@ -138,7 +138,7 @@ __device__ __forceinline__ uint32_t h2_splat(float v) {
 // of row lane / 2 (half lane % 2) for the scale preparation.
 template <int FMT>
 struct KqTile {
-    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : 4];
+    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : FMT == KYB_FMT_Q5_K ? 5 : FMT == KYB_FMT_Q8_0 ? 8 : 4];
     uint4 sc;
     uint32_t d16;
 };
@@ -150,6 +150,17 @@ __device__ __forceinline__ void kq_load(const uint8_t* tile, int lane, KqTile<FM
 #pragma unroll
         for (int G = 0; G < 4; ++G) tr.q[G] = ldg128s(tile + (G * 32 + lane) * 16);
         tr.sc = ldg128s(tile + 2048 + r * 16);
+        tr.d16 = 0;
+    } else if constexpr (FMT == KYB_FMT_Q5_K) {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
+        tr.q[4] = ldg128s(tile + 2048 + lane * 16);                                           // the fifth bits of all four quarters
+        tr.sc = ldg128s(tile + 2560 + r * 16);
+        tr.d16 = 0;
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
+#pragma unroll
+        for (int P = 0; P < 8; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
+        tr.sc = ldg128s(tile + 4096 + r * 16);                                                // the row's eight fp16 d
         tr.d16 = 0;
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
 #pragma unroll
@@ -192,12 +203,17 @@ __device__ __forceinline__ uint4 kq_scale4(uint32_t codes, uint32_t bias2, uint3
     return make_uint4(prmt(a, 0u, 0x1010u), prmt(a, 0u, 0x3232u), prmt(b, 0u, 0x1010u), prmt(b, 0u, 0x3232u));
 }
 
-// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus min of
-// the eight 32-input sub-blocks); the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte reads of 8 rows on distinct banks).
+// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K / Q5_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus
+// min of the eight 32-input sub-blocks); Q8_0: S[row][8] alone; the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte
+// reads of 8 rows on distinct banks).
 template <int FMT>
 __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t scr, int lane) {
     const int r = lane >> 1, hf = lane & 1;
-    if constexpr (FMT == KYB_FMT_Q4_K) {
+    if constexpr (FMT == KYB_FMT_Q8_0) {
+        // one fp16 d per 32 inputs: S[row][8] as (d, d) pairs at row * 32 (lane half hf covers blocks 4 hf .. 4 hf + 3)
+        const uint32_t w0 = hf ? tr.sc.z : tr.sc.x, w1 = hf ? tr.sc.w : tr.sc.y;
+        sts128(scr + r * 32 + 16 * hf, make_uint4(h2_clamp(prmt(w0, 0u, 0x1010u)), h2_clamp(prmt(w0, 0u, 0x3232u)), h2_clamp(prmt(w1, 0u, 0x1010u)), h2_clamp(prmt(w1, 0u, 0x3232u))));
+    } else if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_Q5_K) {
         const uint4 mt = tr.sc;
         const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const uint32_t mnw = ((hf ? mt.w >> 4 : mt.z) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.z >> 2) & (hf ? 0x30303030u : 0u));
@@ -253,6 +269,39 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
                 r[4 * c + 2 * h] = h2_fma(l01, s_lo, z_lo), r[4 * c + 2 * h + 1] = h2_fma(l23, s_lo, z_lo);
                 r[4 * (2 + c) + 2 * h] = h2_fma(h01, s_hi, z_hi), r[4 * (2 + c) + 2 * h + 1] = h2_fma(h23, s_hi, z_hi);
             }
+        }
+    } else if constexpr (FMT == KYB_FMT_Q5_K) {
+        const uint4 u = tr.q[P], hb = tr.q[4];
+        const uint2 sg = lds64(scr + g * 32 + 8 * P), zg = lds64(scr + 512 + g * 32 + 8 * P);
+        const uint2 sh = lds64(scr + (g + 8) * 32 + 8 * P), zh = lds64(scr + 512 + (g + 8) * 32 + 8 * P);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                                                    // slice s = 4 P + i, sub-block 2 P + i / 2
+            const int p = i >> 1, i8 = 4 * (P & 1) + i;                                      // fifth bit of slice s: bit s & 7 of word s >> 3
+            uint32_t wg = p ? u.z : u.x, wh = p ? u.w : u.y;
+            if (i & 1) wg >>= 4, wh >>= 4;
+            uint32_t bg = (P & 2) ? hb.z : hb.x, bh = (P & 2) ? hb.w : hb.y;
+            if (i8 < 4) bg <<= (4 - i8), bh <<= (4 - i8);
+            else bg >>= (i8 - 4), bh >>= (i8 - 4);
+            const uint32_t vg = and_or(wg, 0x0F0F0F0Fu, bg & 0x10101010u), vh = and_or(wh, 0x0F0F0F0Fu, bh & 0x10101010u);
+            // bytes -> fp16 (1024 + v) - 1024 = v, exact; then one fma per pair with the fp16 scale and minus min of the sub-block
+            const uint32_t sgi = p ? sg.y : sg.x, zgi = p ? zg.y : zg.x, shi = p ? sh.y : sh.x, zhi = p ? zh.y : zh.x;
+            r[4 * i] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64006400u), sgi, zgi);
+            r[4 * i + 1] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64006400u), sgi, zgi);
+            r[4 * i + 2] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64006400u), shi, zhi);
+            r[4 * i + 3] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64006400u), shi, zhi);
+        }
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
+        const uint2 sg = lds64(scr + g * 32 + 8 * P), sh = lds64(scr + (g + 8) * 32 + 8 * P);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                                                    // slice 4 P + i = half i & 1 of unit 2 P + i / 2 (one 32-input block)
+            const uint4 u = tr.q[2 * P + (i >> 1)];
+            const uint32_t vg = ((i & 1) ? u.z : u.x) ^ 0x80808080u, vh = ((i & 1) ? u.w : u.y) ^ 0x80808080u;   // int8 -> value + 128
+            const uint32_t sgi = (i >> 1) ? sg.y : sg.x, shi = (i >> 1) ? sh.y : sh.x;
+            // bytes -> fp16 (1024 + v + 128) - 1152 = v, exact
+            r[4 * i] = h2_mul(h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64806480u), sgi);
+            r[4 * i + 1] = h2_mul(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64806480u), sgi);
+            r[4 * i + 2] = h2_mul(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64806480u), shi);
+            r[4 * i + 3] = h2_mul(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64806480u), shi);
         }
     } else {
         const uint4 sg4 = lds128(scr + g * 80 + 16 * P), sh4 = lds128(scr + (g + 8) * 80 + 16 * P);
@@ -334,6 +383,19 @@ template <int FMT, int P>
 __device__ __forceinline__ void kq_refill(const uint8_t* next, int lane, KqTile<FMT>& tr) {
     if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q5_K) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+        if constexpr (P == 1) {                                                              // fifth bits of quarters 0, 1
+            const uint2 hb = ldg64s(next + 2048 + lane * 16);
+            tr.q[4].x = hb.x, tr.q[4].y = hb.y;
+        }
+        if constexpr (P == 3) {
+            const uint2 hb = ldg64s(next + 2048 + lane * 16 + 8);
+            tr.q[4].z = hb.x, tr.q[4].w = hb.y;
+        }
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
+        tr.q[2 * P] = ldg128s(next + (2 * P * 32 + lane) * 16);
+        tr.q[2 * P + 1] = ldg128s(next + ((2 * P + 1) * 32 + lane) * 16);
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
         if constexpr (P == 1) tr.q[4] = ldg128s(next + 2048 + lane * 16);                    // 2-bit planes of quarters 0, 1
@@ -358,6 +420,10 @@ __device__ __forceinline__ void kq_refill_scales(const uint8_t* tile, int lane, 
     const int r = lane >> 1, hf = lane & 1;
     if constexpr (FMT == KYB_FMT_Q4_K) {
         tr.sc = ldg128s(tile + 2048 + r * 16);
+    } else if constexpr (FMT == KYB_FMT_Q5_K) {
+        tr.sc = ldg128s(tile + 2560 + r * 16);
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
+        tr.sc = ldg128s(tile + 4096 + r * 16);
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         const uint2 s = ldg64s(tile + 3072 + r * 16 + 8 * hf);
         tr.sc.x = s.x, tr.sc.y = s.y;
@@ -714,6 +780,14 @@ template <int FMT, int P>
 __device__ __forceinline__ void kq_refill_pair(const uint8_t* next, int lane, KqTile<FMT>& tr) {
     if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q5_K) {
+        tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+        const uint2 hb = ldg64s(next + 2048 + lane * 16 + ((P & 2) ? 8 : 0));
+        if constexpr ((P & 2) == 0) tr.q[4].x = hb.x, tr.q[4].y = hb.y;
+        else tr.q[4].z = hb.x, tr.q[4].w = hb.y;
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
+        tr.q[2 * P] = ldg128s(next + (2 * P * 32 + lane) * 16);
+        tr.q[2 * P + 1] = ldg128s(next + ((2 * P + 1) * 32 + lane) * 16);
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
         tr.q[4 + (P >> 1)] = ldg128s(next + 2048 + ((P >> 1) * 32 + lane) * 16);
@@ -924,13 +998,15 @@ namespace {
 
 int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqParams p, int num_items, cudaStream_t st) {
     static std::mutex mu;
-    static unsigned done[4] = {0, 0, 0, 0};
+    static unsigned done[KYB_FMT_COUNT] = {};
     static int sms = 0;
     int dev = 0;
     KYB_CUDA(cudaGetDevice(&dev));
     const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q4_K>
                        : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q6_K>
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
+                       : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q5_K>
+                       : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q8_0>
                                              : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
     const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
     const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * (p.wide ? 2 : 1) * kyb::KQ_STG + 1024 + 256 + (p.tb ? 2 * kyb::KQ_TORD : 0);
@@ -954,13 +1030,15 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
 // caller then takes that kernel)
 int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqParams p, cudaStream_t st) {
     static std::mutex mu;
-    static unsigned done[4] = {0, 0, 0, 0};
-    static int pairs_max[4][32] = {};
+    static unsigned done[KYB_FMT_COUNT] = {};
+    static int pairs_max[KYB_FMT_COUNT][32] = {};
     int dev = 0;
     KYB_CUDA(cudaGetDevice(&dev));
     const void* kern = fmt == KYB_FMT_Q4_K   ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q4_K>
                        : fmt == KYB_FMT_Q6_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q6_K>
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q3_K>
+                       : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q5_K>
+                       : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q8_0>
                                              : (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_NVFP4>;
     constexpr size_t smem = (size_t)kyb::KP_STAGES * kyb::KP_STAGE_BYTES + (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * kyb::KQ_STG + 1024 + 256;
     {
@@ -996,11 +1074,11 @@ int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
                     int64_t col0, int msub, void* stream, bool pair_ok = true) {
-    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
-        kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
+    if (fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
+        kyb_set_error("the fused-decode prefill GEMM serves formats 0..5; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
         return KYB_EUNSUPPORTED;
     }
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt <= KYB_FMT_Q8_0, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
@@ -1081,11 +1159,11 @@ static int kq_grouped(int fmt, const void* t16, const void* t16b, int64_t n, int
                       const void* row_map, const void* gs, const void* gsb, float limit, void* d, int64_t ldd, int mt, void* stream) {
     const bool glu = t16b != nullptr;
     KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
-    if (fmt == KYB_FMT_Q5_K || fmt == KYB_FMT_Q8_0 || fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
-        kyb_set_error("the fused-decode prefill GEMM serves formats 0..3; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
+    if (fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
+        kyb_set_error("the fused-decode prefill GEMM serves formats 0..5; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
         return KYB_EUNSUPPORTED;
     }
-    KYB_REQUIRE(fmt >= 0 && fmt <= 3, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt <= KYB_FMT_Q8_0, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
     KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,
                 (long long)k, experts);
