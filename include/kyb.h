@@ -38,9 +38,9 @@ extern "C" {
 #define KYB_FMT_Q3_K  2
 #define KYB_FMT_NVFP4 3
 #define KYB_FMT_Q5_K  4
-#define KYB_FMT_Q8_0  5   /* formats 0..5 are served by every entry point, the fused-decode prefill GEMM (kyb_gemm_kq*) included */
-#define KYB_FMT_Q2_K  6   /* (6 and 7 have no decoder inside the prefill GEMM: it returns KYB_EUNSUPPORTED and prefill runs kyb_dequant_t16 + kyb_gemm_f16_tn) */
-#define KYB_FMT_IQ4_XS 7  /* 4-bit indices into the non-linear IQ4_NL grid, one 6-bit scale per 32 inputs; prefill as format 6 */
+#define KYB_FMT_Q8_0  5
+#define KYB_FMT_Q2_K  6
+#define KYB_FMT_IQ4_XS 7  /* 4-bit indices into the non-linear IQ4_NL grid, one 6-bit scale per 32 inputs; every format is served by every entry point */
 #define KYB_FMT_COUNT 8
 
 #define KYB_DT_F32 0

@@ -1,5 +1,5 @@
 // Prefill GEMM with the dequantisation fused into the operand producer: D[m, n] = sat_f16(gscale * sum_k A[m, k] * W[n, k]), W read as T16 tiles
-// (Q4_K / Q6_K / Q3_K / NVFP4 / Q5_K / Q8_0) and never written to HBM as fp16. Replaces the two-step large-row path of kyojin_mlx/foreign_linear.py:710 / :737
+// (every format of the library) and never written to HBM as fp16. Replaces the two-step large-row path of kyojin_mlx/foreign_linear.py:710 / :737
 // (`x2 @ self.dequant().T`) and, in grouped form, the sorted grouped product of kyojin_mlx/foreign_kqgmm.py:225-239 (`gmm`).
 //
 // One persistent CTA per SM, 22 warps:
@@ -138,7 +138,7 @@ __device__ __forceinline__ uint32_t h2_splat(float v) {
 // of row lane / 2 (half lane % 2) for the scale preparation.
 template <int FMT>
 struct KqTile {
-    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : FMT == KYB_FMT_Q5_K ? 5 : FMT == KYB_FMT_Q8_0 ? 8 : 4];
+    uint4 q[FMT == KYB_FMT_Q6_K ? 6 : FMT == KYB_FMT_Q3_K ? 3 : FMT == KYB_FMT_Q5_K ? 5 : FMT == KYB_FMT_Q8_0 ? 8 : FMT == KYB_FMT_Q2_K ? 2 : 4];
     uint4 sc;
     uint32_t d16;
 };
@@ -161,6 +161,17 @@ __device__ __forceinline__ void kq_load(const uint8_t* tile, int lane, KqTile<FM
 #pragma unroll
         for (int P = 0; P < 8; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
         tr.sc = ldg128s(tile + 4096 + r * 16);                                                // the row's eight fp16 d
+        tr.d16 = 0;
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        tr.q[0] = ldg128s(tile + lane * 16);
+        tr.q[1] = ldg128s(tile + (32 + lane) * 16);
+        tr.sc = ldg128s(tile + 1024 + r * 16);                                                // the row's 16 scale | min << 4 bytes
+        tr.d16 = ldg32s(tile + 1280 + r * 4);                                                 // d | dmin << 16
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+#pragma unroll
+        for (int P = 0; P < 4; ++P) tr.q[P] = ldg128s(tile + (P * 32 + lane) * 16);
+        const uint2 mw = ldg64s(tile + 2048 + r * 8);                                         // d | scales_h << 16, four scales_l bytes
+        tr.sc = make_uint4(mw.x, mw.y, 0, 0);
         tr.d16 = 0;
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
 #pragma unroll
@@ -209,7 +220,25 @@ __device__ __forceinline__ uint4 kq_scale4(uint32_t codes, uint32_t bias2, uint3
 template <int FMT>
 __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t scr, int lane) {
     const int r = lane >> 1, hf = lane & 1;
-    if constexpr (FMT == KYB_FMT_Q8_0) {
+    if constexpr (FMT == KYB_FMT_Q2_K) {
+        // one scale and one minimum per 16 inputs: word (fp16(d sc), fp16(-dmin mn)) per slice at row * 80 + 4 * slice (lane half hf covers slices 8 hf .. 8 hf + 7)
+        const uint32_t d2 = prmt(tr.d16, 0u, 0x1010u), dm2 = prmt(tr.d16, 0u, 0x3232u) ^ 0x80008000u;
+        const uint32_t w0 = hf ? tr.sc.z : tr.sc.x, w1 = hf ? tr.sc.w : tr.sc.y;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const uint32_t w = q ? w1 : w0;
+            const uint32_t sl = w & 0x0F0F0F0Fu, ml = (w >> 4) & 0x0F0F0F0Fu;
+            const uint32_t sa = h2_clamp(h2_mul(h2_sub(prmt(sl, 0x64646464u, 0x4140u), 0x64006400u), d2)), sb = h2_clamp(h2_mul(h2_sub(prmt(sl, 0x64646464u, 0x4342u), 0x64006400u), d2));
+            const uint32_t za = h2_clamp(h2_mul(h2_sub(prmt(ml, 0x64646464u, 0x4140u), 0x64006400u), dm2)), zb = h2_clamp(h2_mul(h2_sub(prmt(ml, 0x64646464u, 0x4342u), 0x64006400u), dm2));
+            sts128(scr + r * 80 + 32 * hf + 16 * q, make_uint4(prmt(sa, za, 0x5410u), prmt(sa, za, 0x7632u), prmt(sb, zb, 0x5410u), prmt(sb, zb, 0x7632u)));
+        }
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+        // 6-bit scales of sub-blocks 4 hf .. 4 hf + 3 (4 low bits from scales_l, 2 high bits from scales_h), minus 32, times d: S[row][8] as (v, v) pairs at row * 32
+        const uint32_t sh = tr.sc.x >> (16 + 8 * hf), sl = tr.sc.y >> (16 * hf);
+        const uint32_t lsw = ((sl & 15u) | ((sh & 3u) << 4)) | ((((sl >> 4) & 15u) | (((sh >> 2) & 3u) << 4)) << 8) | ((((sl >> 8) & 15u) | (((sh >> 4) & 3u) << 4)) << 16) |
+                             ((((sl >> 12) & 15u) | (((sh >> 6) & 3u) << 4)) << 24);
+        sts128(scr + r * 32 + 16 * hf, kq_scale4(lsw, 0x64206420u, prmt(tr.sc.x, 0u, 0x1010u)));
+    } else if constexpr (FMT == KYB_FMT_Q8_0) {
         // one fp16 d per 32 inputs: S[row][8] as (d, d) pairs at row * 32 (lane half hf covers blocks 4 hf .. 4 hf + 3)
         const uint32_t w0 = hf ? tr.sc.z : tr.sc.x, w1 = hf ? tr.sc.w : tr.sc.y;
         sts128(scr + r * 32 + 16 * hf, make_uint4(h2_clamp(prmt(w0, 0u, 0x1010u)), h2_clamp(prmt(w0, 0u, 0x3232u)), h2_clamp(prmt(w1, 0u, 0x1010u)), h2_clamp(prmt(w1, 0u, 0x3232u))));
@@ -289,6 +318,41 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
             r[4 * i + 1] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64006400u), sgi, zgi);
             r[4 * i + 2] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64006400u), shi, zhi);
             r[4 * i + 3] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64006400u), shi, zhi);
+        }
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        const uint4 u = tr.q[P >> 1];
+        const uint4 sg4 = lds128(scr + g * 80 + 16 * P), sh4 = lds128(scr + (g + 8) * 80 + 16 * P);
+        const uint32_t sg[4] = {sg4.x, sg4.y, sg4.z, sg4.w}, sh[4] = {sh4.x, sh4.y, sh4.z, sh4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                                                    // slice 4 P + i: codes at bits 2 i of word (P & 1)
+            const uint32_t vg = (((P & 1) ? u.z : u.x) >> (2 * i)) & 0x03030303u, vh = (((P & 1) ? u.w : u.y) >> (2 * i)) & 0x03030303u;
+            const uint32_t Sg = prmt(sg[i], 0u, 0x1010u), Zg = prmt(sg[i], 0u, 0x3232u), Sh = prmt(sh[i], 0u, 0x1010u), Zh = prmt(sh[i], 0u, 0x3232u);
+            r[4 * i] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64006400u), Sg, Zg);
+            r[4 * i + 1] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64006400u), Sg, Zg);
+            r[4 * i + 2] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64006400u), Sh, Zh);
+            r[4 * i + 3] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64006400u), Sh, Zh);
+        }
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+        const uint4 u = tr.q[P];
+        const uint2 sg = lds64(scr + g * 32 + 8 * P), sh = lds64(scr + (g + 8) * 32 + 8 * P);
+        auto grid4 = [](uint32_t idx) -> uint32_t {                                      // four 4-bit codes (one per byte) -> their grid values + 128
+            const uint32_t x = idx & 0x07070707u, y = x | (x >> 4);
+            const uint32_t sel = prmt(y, 0u, 0x4420u);
+            const uint32_t lo = prmt(0xBFAD9881u, 0xF6EADDCFu, sel), hi = prmt(0x26190D01u, 0x71594535u, sel);
+            const uint32_t m = ((idx >> 3) & 0x01010101u) * 0xFFu;
+            return ((lo & ~m) | (hi & m)) ^ 0x80808080u;
+        };
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                                                    // slice 4 P + i, sub-block 2 P + i / 2
+            const int p = i >> 1;
+            uint32_t wg = p ? u.z : u.x, wh = p ? u.w : u.y;
+            if (i & 1) wg >>= 4, wh >>= 4;
+            const uint32_t vg = grid4(wg & 0x0F0F0F0Fu), vh = grid4(wh & 0x0F0F0F0Fu);
+            const uint32_t sgi = p ? sg.y : sg.x, shi = p ? sh.y : sh.x;
+            r[4 * i] = h2_mul(h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64806480u), sgi);
+            r[4 * i + 1] = h2_mul(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64806480u), sgi);
+            r[4 * i + 2] = h2_mul(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64806480u), shi);
+            r[4 * i + 3] = h2_mul(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64806480u), shi);
         }
     } else if constexpr (FMT == KYB_FMT_Q8_0) {
         const uint2 sg = lds64(scr + g * 32 + 8 * P), sh = lds64(scr + (g + 8) * 32 + 8 * P);
@@ -381,8 +445,11 @@ __device__ __forceinline__ void kq_store_quarter(uint32_t dst_g, uint32_t dst_h,
 // whole tile ahead of its next use). Units shared by two quarters are refilled after the second one.
 template <int FMT, int P>
 __device__ __forceinline__ void kq_refill(const uint8_t* next, int lane, KqTile<FMT>& tr) {
-    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
+    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4 || FMT == KYB_FMT_IQ4_XS) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        if constexpr (P == 1) tr.q[0] = ldg128s(next + lane * 16);                           // 2-bit codes of quarters 0, 1
+        if constexpr (P == 3) tr.q[1] = ldg128s(next + (32 + lane) * 16);
     } else if constexpr (FMT == KYB_FMT_Q5_K) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
         if constexpr (P == 1) {                                                              // fifth bits of quarters 0, 1
@@ -424,6 +491,12 @@ __device__ __forceinline__ void kq_refill_scales(const uint8_t* tile, int lane, 
         tr.sc = ldg128s(tile + 2560 + r * 16);
     } else if constexpr (FMT == KYB_FMT_Q8_0) {
         tr.sc = ldg128s(tile + 4096 + r * 16);
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        tr.sc = ldg128s(tile + 1024 + r * 16);
+        tr.d16 = ldg32s(tile + 1280 + r * 4);
+    } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
+        const uint2 mw = ldg64s(tile + 2048 + r * 8);
+        tr.sc.x = mw.x, tr.sc.y = mw.y;
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         const uint2 s = ldg64s(tile + 3072 + r * 16 + 8 * hf);
         tr.sc.x = s.x, tr.sc.y = s.y;
@@ -778,8 +851,10 @@ constexpr int KP_STAGES = 3;
 // registers that only quarter P of the tile used are refilled from the next tile right after P has been computed (this warp uses two quarters of a tile)
 template <int FMT, int P>
 __device__ __forceinline__ void kq_refill_pair(const uint8_t* next, int lane, KqTile<FMT>& tr) {
-    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4) {
+    if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_NVFP4 || FMT == KYB_FMT_IQ4_XS) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
+    } else if constexpr (FMT == KYB_FMT_Q2_K) {
+        tr.q[P >> 1] = ldg128s(next + ((P >> 1) * 32 + lane) * 16);
     } else if constexpr (FMT == KYB_FMT_Q5_K) {
         tr.q[P] = ldg128s(next + (P * 32 + lane) * 16);
         const uint2 hb = ldg64s(next + 2048 + lane * 16 + ((P & 2) ? 8 : 0));
@@ -1007,6 +1082,8 @@ int kq_launch(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::KqPar
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q3_K>
                        : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q5_K>
                        : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q8_0>
+                       : fmt == KYB_FMT_Q2_K ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_Q2_K>
+                       : fmt == KYB_FMT_IQ4_XS ? (const void*)kyb::gemm_kq_kernel<KYB_FMT_IQ4_XS>
                                              : (const void*)kyb::gemm_kq_kernel<KYB_FMT_NVFP4>;
     const uint32_t stage_bytes = (uint32_t)p.msub * kyb::KQ_A_SUB + kyb::KQ_B_BYTES;
     const size_t fixed = (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * (p.wide ? 2 : 1) * kyb::KQ_STG + 1024 + 256 + (p.tb ? 2 * kyb::KQ_TORD : 0);
@@ -1039,6 +1116,8 @@ int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::
                        : fmt == KYB_FMT_Q3_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q3_K>
                        : fmt == KYB_FMT_Q5_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q5_K>
                        : fmt == KYB_FMT_Q8_0 ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q8_0>
+                       : fmt == KYB_FMT_Q2_K ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_Q2_K>
+                       : fmt == KYB_FMT_IQ4_XS ? (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_IQ4_XS>
                                              : (const void*)kyb::gemm_kq_pair_kernel<KYB_FMT_NVFP4>;
     constexpr size_t smem = (size_t)kyb::KP_STAGES * kyb::KP_STAGE_BYTES + (size_t)kyb::KQ_DW * kyb::KQ_SCR + 4 * kyb::KQ_STG + 1024 + 256;
     {
@@ -1074,11 +1153,7 @@ int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
                     int64_t col0, int msub, void* stream, bool pair_ok = true) {
-    if (fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
-        kyb_set_error("the fused-decode prefill GEMM serves formats 0..5; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
-        return KYB_EUNSUPPORTED;
-    }
-    KYB_REQUIRE(fmt >= 0 && fmt <= KYB_FMT_Q8_0, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
     KYB_REQUIRE(lda >= k && lda % 8 == 0 && ldd >= n, "leading dimensions: lda >= k and a multiple of 8, ldd >= n");
@@ -1159,11 +1234,7 @@ static int kq_grouped(int fmt, const void* t16, const void* t16b, int64_t n, int
                       const void* row_map, const void* gs, const void* gsb, float limit, void* d, int64_t ldd, int mt, void* stream) {
     const bool glu = t16b != nullptr;
     KYB_REQUIRE(mt == 128 || mt == 256, "mt=%d: 128 or 256 rows per work item", mt);
-    if (fmt == KYB_FMT_Q2_K || fmt == KYB_FMT_IQ4_XS) {
-        kyb_set_error("the fused-decode prefill GEMM serves formats 0..5; for format %d run kyb_dequant_t16 + kyb_gemm_f16_tn", fmt);
-        return KYB_EUNSUPPORTED;
-    }
-    KYB_REQUIRE(fmt >= 0 && fmt <= KYB_FMT_Q8_0, "unknown weight format %d", fmt);
+    KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a && d && tb && off, "null pointer");
     KYB_REQUIRE(s > 0 && n > 0 && k > 0 && k % 256 == 0 && experts > 0, "s=%lld n=%lld k=%lld experts=%d: k must be a positive multiple of 256", (long long)s, (long long)n,
                 (long long)k, experts);

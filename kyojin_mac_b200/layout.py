@@ -41,7 +41,7 @@ FMT_ID = {"q4_k": 0, "q6_k": 1, "q3_k": 2, "nvfp4": 3, "q5_k": 4, "q8_0": 5, "q2
 TILE_BYTES = {"q4_k": 2304, "q6_k": 3360, "q3_k": 1760, "nvfp4": 2304, "q5_k": 2816, "q8_0": 4352, "q2_k": 1344, "iq4_xs": 2176}
 RAW_BLOCK = {"q4_k": (256, 144), "q6_k": (256, 210), "q3_k": (256, 110), "nvfp4": (64, 36), "q5_k": (256, 176), "q8_0": (32, 34), "q2_k": (256, 84), "iq4_xs": (256, 136)}     # GGUF block elements / bytes
 GGUF_NAME = {"q4_k": "Q4_K", "q6_k": "Q6_K", "q3_k": "Q3_K", "nvfp4": "NVFP4", "q5_k": "Q5_K", "q8_0": "Q8_0", "q2_k": "Q2_K", "iq4_xs": "IQ4_XS"}
-PREFILL_FUSED = ("q4_k", "q6_k", "q3_k", "nvfp4", "q5_k", "q8_0")       # formats the prefill GEMM decodes inside the kernel; the others are decoded to fp16 first
+PREFILL_FUSED = FORMATS                                 # formats the prefill GEMM decodes inside the kernel (all of them; the staged form stays an option)
 ROWS = 16
 KBLOCK = 256
 

@@ -60,7 +60,7 @@ def test_linear_prefill_vs_fp64(fmt, rows):
     assert np.abs(y.astype(np.float64) - want).max() <= 4e-3 * np.abs(want).max()
 
 
-@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4", "q5_k", "q8_0"])
+@pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4", "q5_k", "q8_0", "q2_k", "iq4_xs"])
 def test_fused_decode_gemm_vs_staged(fmt):
     """Weights decoded inside the GEMM: the CTA-pair kernel (the default for more than 128 rows) and the one-CTA kernel with one and two activation blocks per
     work item give the same bits; NVFP4 equals the staged form bit for bit (its fp16

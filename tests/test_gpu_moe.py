@@ -210,7 +210,7 @@ def test_grouped_gemm_equals_per_expert(mt):
         assert O.rel_fro(yn[rows], want) <= 1e-3
 
 
-@pytest.mark.parametrize("fmt,mt,limit", [("q4_k", 256, None), ("q4_k", 128, 7.0), ("q6_k", 256, None), ("nvfp4", 256, 3.0), ("q5_k", 256, None), ("q8_0", 128, 5.0)])
+@pytest.mark.parametrize("fmt,mt,limit", [("q4_k", 256, None), ("q4_k", 128, 7.0), ("q6_k", 256, None), ("nvfp4", 256, 3.0), ("q5_k", 256, None), ("q8_0", 128, 5.0), ("q2_k", 256, None), ("iq4_xs", 256, 2.0)])
 def test_gated_pair_in_one_grouped_product(fmt, mt, limit):
     """gate | up as ONE grouped product with silu(a) * b in its epilogue == two grouped products + the activation launch, bit for bit (the epilogue rounds both
     products to fp16 first, as the separate launches store them), on ragged segments incl. an empty expert, segments of more than 128 and more than 256 rows,
