@@ -214,9 +214,10 @@ __device__ __forceinline__ uint4 kq_scale4(uint32_t codes, uint32_t bias2, uint3
     return make_uint4(prmt(a, 0u, 0x1010u), prmt(a, 0u, 0x3232u), prmt(b, 0u, 0x1010u), prmt(b, 0u, 0x3232u));
 }
 
-// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K / Q5_K: S[row][8] at row * 32, Z[row][8] at 512 + row * 32 (scale and minus
-// min of the eight 32-input sub-blocks); Q8_0: S[row][8] alone; the others: S[row][16] at row * 80 (one scale per 16 inputs; the 80-byte pitch keeps the 16-byte
-// reads of 8 rows on distinct banks).
+// Block scales of the tile as half2 pairs (value, value) in the warp's scratch. Q4_K / Q5_K: (S, Z)[row][8] at row * 80 (scale and minus min of the eight
+// 32-input sub-blocks, interleaved: one 16-byte read gives both of the two sub-blocks of a quarter); Q8_0 / IQ4_XS: S[row][8] at row * 48; the others: S[row][16]
+// at row * 80 (one scale per 16 inputs). With the 80- and 48-byte pitches the reads of rows g = 0 .. 7 fall on distinct banks: a warp's read costs the minimum
+// number of shared-memory wavefronts (a 32-byte pitch puts rows g and g + 4 on the same banks and doubles them).
 template <int FMT>
 __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t scr, int lane) {
     const int r = lane >> 1, hf = lane & 1;
@@ -237,18 +238,19 @@ __device__ __forceinline__ void kq_prep_scales(const KqTile<FMT>& tr, uint32_t s
         const uint32_t sh = tr.sc.x >> (16 + 8 * hf), sl = tr.sc.y >> (16 * hf);
         const uint32_t lsw = ((sl & 15u) | ((sh & 3u) << 4)) | ((((sl >> 4) & 15u) | (((sh >> 2) & 3u) << 4)) << 8) | ((((sl >> 8) & 15u) | (((sh >> 4) & 3u) << 4)) << 16) |
                              ((((sl >> 12) & 15u) | (((sh >> 6) & 3u) << 4)) << 24);
-        sts128(scr + r * 32 + 16 * hf, kq_scale4(lsw, 0x64206420u, prmt(tr.sc.x, 0u, 0x1010u)));
+        sts128(scr + r * 48 + 16 * hf, kq_scale4(lsw, 0x64206420u, prmt(tr.sc.x, 0u, 0x1010u)));
     } else if constexpr (FMT == KYB_FMT_Q8_0) {
         // one fp16 d per 32 inputs: S[row][8] as (d, d) pairs at row * 32 (lane half hf covers blocks 4 hf .. 4 hf + 3)
         const uint32_t w0 = hf ? tr.sc.z : tr.sc.x, w1 = hf ? tr.sc.w : tr.sc.y;
-        sts128(scr + r * 32 + 16 * hf, make_uint4(h2_clamp(prmt(w0, 0u, 0x1010u)), h2_clamp(prmt(w0, 0u, 0x3232u)), h2_clamp(prmt(w1, 0u, 0x1010u)), h2_clamp(prmt(w1, 0u, 0x3232u))));
+        sts128(scr + r * 48 + 16 * hf, make_uint4(h2_clamp(prmt(w0, 0u, 0x1010u)), h2_clamp(prmt(w0, 0u, 0x3232u)), h2_clamp(prmt(w1, 0u, 0x1010u)), h2_clamp(prmt(w1, 0u, 0x3232u))));
     } else if constexpr (FMT == KYB_FMT_Q4_K || FMT == KYB_FMT_Q5_K) {
         const uint4 mt = tr.sc;
         const uint32_t scw = ((hf ? mt.w : mt.y) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.y >> 2) & (hf ? 0x30303030u : 0u));
         const uint32_t mnw = ((hf ? mt.w >> 4 : mt.z) & (hf ? 0x0f0f0f0fu : 0x3f3f3f3fu)) | ((mt.z >> 2) & (hf ? 0x30303030u : 0u));
         const uint32_t d2 = prmt(mt.x, 0u, 0x1010u), dm2 = prmt(mt.x, 0u, 0x3232u) ^ 0x80008000u;           // (d, d) and (-dmin, -dmin)
-        sts128(scr + r * 32 + 16 * hf, kq_scale4(scw, 0x64006400u, d2));
-        sts128(scr + 512 + r * 32 + 16 * hf, kq_scale4(mnw, 0x64006400u, dm2));
+        const uint4 sv = kq_scale4(scw, 0x64006400u, d2), zv = kq_scale4(mnw, 0x64006400u, dm2);
+        sts128(scr + r * 80 + 32 * hf, make_uint4(sv.x, zv.x, sv.y, zv.y));
+        sts128(scr + r * 80 + 32 * hf + 16, make_uint4(sv.z, zv.z, sv.w, zv.w));
     } else if constexpr (FMT == KYB_FMT_Q6_K) {
         const uint32_t d2 = prmt(tr.d16, 0u, 0x1010u);
         // int8 scale + 128 as an unsigned byte, bias 1024 + 128
@@ -282,14 +284,13 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
     const int g = lane >> 2;
     if constexpr (FMT == KYB_FMT_Q4_K) {
         const uint4 u = tr.q[P];
-        const uint2 sg = lds64(scr + g * 32 + 8 * P), zg = lds64(scr + 512 + g * 32 + 8 * P);
-        const uint2 sh = lds64(scr + (g + 8) * 32 + 8 * P), zh = lds64(scr + 512 + (g + 8) * 32 + 8 * P);
+        const uint4 sg = lds128(scr + g * 80 + 16 * P), sh = lds128(scr + (g + 8) * 80 + 16 * P);   // (scale, minus min) of sub-blocks 2 P and 2 P + 1
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const uint32_t w = h ? (c ? u.w : u.y) : (c ? u.z : u.x);
-                const uint32_t s_lo = h ? sh.x : sg.x, s_hi = h ? sh.y : sg.y, z_lo = h ? zh.x : zg.x, z_hi = h ? zh.y : zg.y;
+                const uint32_t s_lo = h ? sh.x : sg.x, s_hi = h ? sh.z : sg.z, z_lo = h ? sh.y : sg.y, z_hi = h ? sh.w : sg.w;
                 const uint32_t p01 = prmt(w, 0u, 0x4140u), p23 = prmt(w, 0u, 0x4342u);       // bytes (b0, 0, b1, 0), (b2, 0, b3, 0)
                 // low nibbles: 1024 + q, minus 1024; high nibbles: (1024 + 16 q) / 16 - 64; both exact
                 const uint32_t l01 = h2_sub(and_or(p01, 0x000F000Fu, 0x64006400u), 0x64006400u), l23 = h2_sub(and_or(p23, 0x000F000Fu, 0x64006400u), 0x64006400u);
@@ -301,8 +302,7 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
         }
     } else if constexpr (FMT == KYB_FMT_Q5_K) {
         const uint4 u = tr.q[P], hb = tr.q[4];
-        const uint2 sg = lds64(scr + g * 32 + 8 * P), zg = lds64(scr + 512 + g * 32 + 8 * P);
-        const uint2 sh = lds64(scr + (g + 8) * 32 + 8 * P), zh = lds64(scr + 512 + (g + 8) * 32 + 8 * P);
+        const uint4 sg = lds128(scr + g * 80 + 16 * P), sh = lds128(scr + (g + 8) * 80 + 16 * P);   // (scale, minus min) of sub-blocks 2 P and 2 P + 1
 #pragma unroll
         for (int i = 0; i < 4; ++i) {                                                    // slice s = 4 P + i, sub-block 2 P + i / 2
             const int p = i >> 1, i8 = 4 * (P & 1) + i;                                      // fifth bit of slice s: bit s & 7 of word s >> 3
@@ -313,7 +313,7 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
             else bg >>= (i8 - 4), bh >>= (i8 - 4);
             const uint32_t vg = and_or(wg, 0x0F0F0F0Fu, bg & 0x10101010u), vh = and_or(wh, 0x0F0F0F0Fu, bh & 0x10101010u);
             // bytes -> fp16 (1024 + v) - 1024 = v, exact; then one fma per pair with the fp16 scale and minus min of the sub-block
-            const uint32_t sgi = p ? sg.y : sg.x, zgi = p ? zg.y : zg.x, shi = p ? sh.y : sh.x, zhi = p ? zh.y : zh.x;
+            const uint32_t sgi = p ? sg.z : sg.x, zgi = p ? sg.w : sg.y, shi = p ? sh.z : sh.x, zhi = p ? sh.w : sh.y;
             r[4 * i] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4140u), 0x64006400u), sgi, zgi);
             r[4 * i + 1] = h2_fma(h2_sub(prmt(vg, 0x64646464u, 0x4342u), 0x64006400u), sgi, zgi);
             r[4 * i + 2] = h2_fma(h2_sub(prmt(vh, 0x64646464u, 0x4140u), 0x64006400u), shi, zhi);
@@ -334,7 +334,7 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
         }
     } else if constexpr (FMT == KYB_FMT_IQ4_XS) {
         const uint4 u = tr.q[P];
-        const uint2 sg = lds64(scr + g * 32 + 8 * P), sh = lds64(scr + (g + 8) * 32 + 8 * P);
+        const uint2 sg = lds64(scr + g * 48 + 8 * P), sh = lds64(scr + (g + 8) * 48 + 8 * P);
         auto grid4 = [](uint32_t idx) -> uint32_t {                                      // four 4-bit codes (one per byte) -> their grid values + 128
             const uint32_t x = idx & 0x07070707u, y = x | (x >> 4);
             const uint32_t sel = prmt(y, 0u, 0x4420u);
@@ -355,7 +355,7 @@ __device__ __forceinline__ void kq_compute_quarter(const KqTile<FMT>& tr, uint32
             r[4 * i + 3] = h2_mul(h2_sub(prmt(vh, 0x64646464u, 0x4342u), 0x64806480u), shi);
         }
     } else if constexpr (FMT == KYB_FMT_Q8_0) {
-        const uint2 sg = lds64(scr + g * 32 + 8 * P), sh = lds64(scr + (g + 8) * 32 + 8 * P);
+        const uint2 sg = lds64(scr + g * 48 + 8 * P), sh = lds64(scr + (g + 8) * 48 + 8 * P);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {                                                    // slice 4 P + i = half i & 1 of unit 2 P + i / 2 (one 32-input block)
             const uint4 u = tr.q[2 * P + (i >> 1)];
