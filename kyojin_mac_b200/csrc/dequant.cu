@@ -25,7 +25,7 @@ __global__ void dequant_t16_kernel(const uint8_t* __restrict__ t16, int64_t n, i
             if constexpr (sizeof(OUT) == 4) {
                 *reinterpret_cast<float4*>(dst + 16 * s) = make_float4(w[0], w[1], w[2], w[3]);
             } else {
-                __half2 lo = __halves2half2(sat_half(w[0]), sat_half(w[1])), hi = __halves2half2(sat_half(w[2]), sat_half(w[3]));
+                __half2 lo = sat_half2(w[0], w[1]), hi = sat_half2(w[2], w[3]);
                 uint2 v;
                 v.x = *reinterpret_cast<uint32_t*>(&lo);
                 v.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -58,7 +58,7 @@ __global__ void dequant_rows_kernel(const uint8_t* __restrict__ t16, int64_t n, 
         if constexpr (sizeof(OUT) == 4) {
             *reinterpret_cast<float4*>(dst + 16 * s) = make_float4(w[0], w[1], w[2], w[3]);
         } else {
-            __half2 lo = __halves2half2(sat_half(w[0]), sat_half(w[1])), hi = __halves2half2(sat_half(w[2]), sat_half(w[3]));
+            __half2 lo = sat_half2(w[0], w[1]), hi = sat_half2(w[2], w[3]);
             uint2 v;
             v.x = *reinterpret_cast<uint32_t*>(&lo);
             v.y = *reinterpret_cast<uint32_t*>(&hi);

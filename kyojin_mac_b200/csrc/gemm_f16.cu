@@ -172,10 +172,10 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_f16_tn_kernel(const __grid
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             uint4 o;
-                            __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * gscale), sat_half(__uint_as_float(v[j + 1]) * gscale));
-                            __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * gscale), sat_half(__uint_as_float(v[j + 3]) * gscale));
-                            __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * gscale), sat_half(__uint_as_float(v[j + 5]) * gscale));
-                            __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * gscale), sat_half(__uint_as_float(v[j + 7]) * gscale));
+                            __half2 h0 = sat_half2(__uint_as_float(v[j]) * gscale, __uint_as_float(v[j + 1]) * gscale);
+                            __half2 h1 = sat_half2(__uint_as_float(v[j + 2]) * gscale, __uint_as_float(v[j + 3]) * gscale);
+                            __half2 h2 = sat_half2(__uint_as_float(v[j + 4]) * gscale, __uint_as_float(v[j + 5]) * gscale);
+                            __half2 h3 = sat_half2(__uint_as_float(v[j + 6]) * gscale, __uint_as_float(v[j + 7]) * gscale);
                             o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
                             *reinterpret_cast<uint4*>(drow + c + j) = o;
                         }

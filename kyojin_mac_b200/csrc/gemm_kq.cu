@@ -655,7 +655,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                         uint32_t w[16];
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * j]) * gscale), sat_half(__uint_as_float(v[2 * j + 1]) * gscale));
+                            __half2 h = sat_half2(__uint_as_float(v[2 * j]) * gscale, __uint_as_float(v[2 * j + 1]) * gscale);
                             w[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
                         if (p.wide)
@@ -686,7 +686,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * i]) * gscale), sat_half(__uint_as_float(v[2 * i + 1]) * gscale));
+                            __half2 h = sat_half2(__uint_as_float(v[2 * i]) * gscale, __uint_as_float(v[2 * i + 1]) * gscale);
                             w[i] = *reinterpret_cast<uint32_t*>(&h);
                         }
                         if (p.glu) {
@@ -701,7 +701,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                                 float a0 = __low2float(a2), a1 = __high2float(a2);
                                 float b0 = __half2float(sat_half(__uint_as_float(v[2 * i]) * gsb)), b1 = __half2float(sat_half(__uint_as_float(v[2 * i + 1]) * gsb));
                                 if (lim > 0.f) a0 = fminf(a0, lim), a1 = fminf(a1, lim), b0 = fminf(fmaxf(b0, -lim), lim), b1 = fminf(fmaxf(b1, -lim), lim);
-                                __half2 h = __halves2half2(sat_half(a0 * (1.0f / (1.0f + expf(-a0))) * b0), sat_half(a1 * (1.0f / (1.0f + expf(-a1))) * b1));
+                                __half2 h = sat_half2(a0 * (1.0f / (1.0f + expf(-a0))) * b0, a1 * (1.0f / (1.0f + expf(-a1))) * b1);
                                 w[i] = *reinterpret_cast<uint32_t*>(&h);
                             }
                         }
@@ -731,10 +731,10 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
 #pragma unroll
                             for (int j = 0; j < 32; j += 8) {
                                 uint4 o;
-                                __half2 h0 = __halves2half2(sat_half(__uint_as_float(v[j]) * gscale), sat_half(__uint_as_float(v[j + 1]) * gscale));
-                                __half2 h1 = __halves2half2(sat_half(__uint_as_float(v[j + 2]) * gscale), sat_half(__uint_as_float(v[j + 3]) * gscale));
-                                __half2 h2 = __halves2half2(sat_half(__uint_as_float(v[j + 4]) * gscale), sat_half(__uint_as_float(v[j + 5]) * gscale));
-                                __half2 h3 = __halves2half2(sat_half(__uint_as_float(v[j + 6]) * gscale), sat_half(__uint_as_float(v[j + 7]) * gscale));
+                                __half2 h0 = sat_half2(__uint_as_float(v[j]) * gscale, __uint_as_float(v[j + 1]) * gscale);
+                                __half2 h1 = sat_half2(__uint_as_float(v[j + 2]) * gscale, __uint_as_float(v[j + 3]) * gscale);
+                                __half2 h2 = sat_half2(__uint_as_float(v[j + 4]) * gscale, __uint_as_float(v[j + 5]) * gscale);
+                                __half2 h3 = sat_half2(__uint_as_float(v[j + 6]) * gscale, __uint_as_float(v[j + 7]) * gscale);
                                 o.x = *reinterpret_cast<uint32_t*>(&h0), o.y = *reinterpret_cast<uint32_t*>(&h1), o.z = *reinterpret_cast<uint32_t*>(&h2), o.w = *reinterpret_cast<uint32_t*>(&h3);
                                 for (int pr = 0; pr < p.nout; ++pr) *reinterpret_cast<uint4*>(p.d[pr] + doff + c + j) = o;
                             }
@@ -1041,7 +1041,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(KQ_THREADS, 1)
                 uint32_t w[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    __half2 h = __halves2half2(sat_half(__uint_as_float(v[2 * j]) * p.gscale), sat_half(__uint_as_float(v[2 * j + 1]) * p.gscale));
+                    __half2 h = sat_half2(__uint_as_float(v[2 * j]) * p.gscale, __uint_as_float(v[2 * j + 1]) * p.gscale);
                     w[j] = *reinterpret_cast<uint32_t*>(&h);
                 }
                 epilogue_stage_store(outs, 1, stg, lane, w, it.n0 + c, row0, !failed && row0 < p.m && it.n0 + c < p.n);

@@ -206,8 +206,19 @@ __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t b
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) { return __half2float(__ushort_as_half((unsigned short)h16)); }
 
-// float -> fp16 saturated to +-65504 (NaN stays NaN)
-__device__ __forceinline__ __half sat_half(float v) { return __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f)); }
+// float -> fp16, round to nearest even, saturated to +-65504 (infinities too); NaN stays NaN. One conversion instruction: the same bits as clamping first and
+// converting after for every input that is not a NaN (a clamp built from fminf / fmaxf would turn a NaN into -65504).
+__device__ __forceinline__ __half sat_half(float v) {
+    unsigned short d;
+    asm("cvt.rn.satfinite.f16.f32 %0, %1;" : "=h"(d) : "f"(v));
+    return __ushort_as_half(d);
+}
+// two at once: (lo, hi) -> packed pair
+__device__ __forceinline__ __half2 sat_half2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return *reinterpret_cast<__half2*>(&d);
+}
 
 }  // namespace kyb
 #endif

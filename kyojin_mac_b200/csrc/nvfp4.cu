@@ -367,7 +367,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                             __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
                             o[j] = *reinterpret_cast<uint32_t*>(&h);
                         } else {
-                            __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                            __half2 h = sat_half2(f0, f1);
                             o[j] = *reinterpret_cast<uint32_t*>(&h);
                         }
                     }
@@ -418,7 +418,7 @@ __global__ void __launch_bounds__(NV_THREADS, 1) gemm_nvfp4_kernel(const __grid_
                                     __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
                                     w[e] = *reinterpret_cast<uint32_t*>(&h);
                                 } else {
-                                    __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                                    __half2 h = sat_half2(f0, f1);
                                     w[e] = *reinterpret_cast<uint32_t*>(&h);
                                 }
                             }
@@ -579,7 +579,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NV_THREADS, 1)
                         __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
                         o[j] = *reinterpret_cast<uint32_t*>(&h);
                     } else {
-                        __half2 h = __halves2half2(sat_half(f0), sat_half(f1));
+                        __half2 h = sat_half2(f0, f1);
                         o[j] = *reinterpret_cast<uint32_t*>(&h);
                     }
                 }

@@ -41,6 +41,11 @@ def test_gemm_saturates_and_scales():
     assert torch.isfinite(d).all() and (d == 65504).all()
     d2 = ops.gemm_f16(a, b, gscale=1e-3)
     torch.testing.assert_close(d2.float(), torch.full((128, 128), 640.0, device="cuda"), rtol=1e-3, atol=0)
+    d3 = ops.gemm_f16(-a, b)
+    assert (d3 == -65504).all()
+    a[5, 7] = float("nan")                                     # a NaN is not turned into a finite value by the saturation
+    d4 = ops.gemm_f16(a, b)
+    assert torch.isnan(d4[5]).all() and (d4[:5] == 65504).all() and (d4[6:] == 65504).all()
 
 
 @pytest.mark.parametrize("fmt", ["q3_k", "q4_k", "q6_k", "nvfp4", "q5_k", "q8_0", "q2_k", "iq4_xs"])
