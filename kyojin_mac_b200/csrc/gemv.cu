@@ -38,6 +38,7 @@ struct GemvParams {
     int pdl;                 // launched with programmatic stream serialization
     int partial_only;        // every chunk sum goes to `partial` and nothing else is written: form (b), and the two-step entry points with exposed partial sums
     int aligned;             // warps take whole row tiles (no row tile is shared between warps); else runs of whole chunks
+    int local;               // form (c): a CTA owns whole row tiles, its warps share their chunks and the chunk sums meet in shared memory (no workspace, no second launch)
     int warps, stages;
     float gscale;
     float limit;             // gated input: > 0 clamps as the activation kernel does
@@ -569,9 +570,11 @@ __global__ void moe_groups_kernel(const uint32_t* __restrict__ eids, int S, int 
 // Persistent kernel, one CTA per SM. The work of a matrix is cut into UNITS: (16-row tile, canonical k-chunk of kc k-blocks); units are ordered row tile by
 // row tile, which is also their order in memory. CTA c works on k-part c % ksplit (it stages the activations of that part once); the units of a part are dealt
 // to the warps of its CTAs as contiguous, equally long runs, so every warp streams one contiguous range of tiles and all warps finish together. A warp forms the
-// sum of every chunk in registers. Two forms: (a) matrices with many row tiles: a run is whole row tiles, the warp adds the chunk sums in k order and stores y
+// sum of every chunk in registers. Three forms: (a) matrices with many row tiles: a run is whole row tiles, the warp adds the chunk sums in k order and stores y
 // itself; (b) otherwise a run is whole chunks (+-1 over the warps whatever the shape), every chunk sum goes to the workspace and gemv_finalize_kernel adds them in
-// k order. Either way an output is the left-to-right sum of the same chunk sums, so results do not depend on the batch size, the grid or the split.
+// k order; (c) small matrices, where a second launch would cost as much as the product: CTA c owns the row tiles [ntiles c / G, ntiles (c + 1) / G), its warps
+// share the chunks of those row tiles as in (b), the chunk sums go to shared memory and after a CTA barrier the threads add them in k order and store y.
+// Either way an output is the left-to-right sum of the same chunk sums, so results do not depend on the batch size, the grid or the split.
 template <int FMT, int NT, int MST>
 // At most 16 warps per CTA: 128 registers per thread let the compiler keep the unpacked operands of several MMAs in flight (with 24 warps and 80 registers the
 // kernel spilled and its steady rate was 15 % lower).
@@ -588,7 +591,15 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
     const int ntiles = p.npad >> 4;
     const int64_t UP = (int64_t)ntiles * cpk;                                     // units of this part
     // this warp's run: whole row tiles when the plan says so (many row tiles: no row tile is shared, nothing goes through the workspace), else whole chunks
-    const int64_t u0 = p.aligned ? (int64_t)ntiles * ws / WP * cpk : UP * ws / WP, u1 = p.aligned ? (int64_t)ntiles * (ws + 1) / WP * cpk : UP * (ws + 1) / WP;
+    const bool local = p.local != 0;                                              // form (c): one k-part, cpk = nchunks
+    const int rtA = local ? (int)((int64_t)ntiles * blockIdx.x / gridDim.x) : 0, rtB = local ? (int)((int64_t)ntiles * (blockIdx.x + 1) / gridDim.x) : 0;
+    const int64_t UL = (int64_t)(rtB - rtA) * cpk;                                // units of this CTA's row tiles
+    const int64_t u0 = local       ? (int64_t)rtA * cpk + UL * warp / p.warps
+                       : p.aligned ? (int64_t)ntiles * ws / WP * cpk
+                                   : UP * ws / WP,
+                  u1 = local       ? (int64_t)rtA * cpk + UL * (warp + 1) / p.warps
+                       : p.aligned ? (int64_t)ntiles * (ws + 1) / WP * cpk
+                                   : UP * (ws + 1) / WP;
     auto tiles_before = [&](int64_t u) -> int64_t { return (u / cpk) * nblk + (u % cpk) * p.kc; };
     const int total = (int)(tiles_before(u1) - tiles_before(u0));
     const int rt0 = (int)(u0 / cpk), j0 = (int)(u0 % cpk);
@@ -602,6 +613,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
     uint8_t* ring = wbase;
     float* scl = reinterpret_cast<float*>(wbase + (size_t)STAGES * TB);
     uint64_t* bars = reinterpret_cast<uint64_t*>(wbase + (size_t)STAGES * TB + SCL_BYTES);
+    float* cpart = reinterpret_cast<float*>(xaux + (size_t)p.kbp * xaux_bytes_per_block<FMT>(NT) + (size_t)p.warps * warp_bytes);   // form (c): [row tile][chunk][m][16 rows]
 
     // producer state (lane 0): next tile to request. The tiles of a row tile's part are contiguous; the next row tile follows nb - nblk tiles further.
     int p_left = total, p_blk = nblk - j0 * p.kc;             // tiles still to request, tiles left in the current row tile's part
@@ -677,7 +689,7 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
         }
     }
     __syncthreads();
-    if (total == 0) return;
+    if (total == 0 && !local) return;
 
     const int g = lane >> 2, t = lane & 3;
     // lanes whose activation row is not staged read a staged row instead: their output columns are never stored
@@ -723,7 +735,8 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
                             tot.v[nt][q] = 0.f;
                         }
                     } else if (m < p.m) {
-                        p.partial[((size_t)chunk * p.m + m) * p.npad + nrow] = acc.v[nt][q];
+                        if (local) cpart[((size_t)((rt - rtA) * cpk + chunk) * p.m + m) * 16 + g + 8 * (q >> 1)] = acc.v[nt][q];
+                        else p.partial[((size_t)chunk * p.m + m) * p.npad + nrow] = acc.v[nt][q];
                     }
                     acc.v[nt][q] = 0.f;
                 }
@@ -742,6 +755,17 @@ __global__ void __launch_bounds__(NT <= 2 ? 512 : 256, 1) gemv_t16_kernel(const 
     if (i < total) step(0);
     // every requested tile was waited for above (bounded), so no copy of this warp is in flight here
     if (__any_sync(0xffffffffu, failed) && lane == 0) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMV);
+    if (local) {
+        // form (c): the chunk sums of this CTA's row tiles are added in k order, as the finalize kernel of form (b) adds them
+        __syncthreads();
+        const int outs = (rtB - rtA) * 16 * p.m;
+        for (int i = threadIdx.x; i < outs; i += blockDim.x) {
+            const int row = i & 15, m = (i >> 4) % p.m, rtl = (i >> 4) / p.m, nrow = (rtA + rtl) * 16 + row;
+            float s = 0.f;
+            for (int c = 0; c < cpk; ++c) s += cpart[((size_t)(rtl * cpk + c) * p.m + m) * 16 + row];
+            if (nrow < p.n) p.y[(size_t)m * p.ldy + nrow] = sat_half(s * p.gscale);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ routed experts: grouped GEMV with expert election
@@ -923,6 +947,7 @@ struct GemvPlan {
     int nt, mst, warps, stages, kbp, ksplit, grid;
     size_t smem;
     int kc, nchunks, cpp, aligned;
+    int local;
 };
 
 size_t plan_smem(int fmt, int nt, int mst, int kbp, int warps, int stages) {
@@ -993,7 +1018,8 @@ int canonical_chunk(int ntiles, int nb) {
 
 // Warps per CTA, k-parts and the way work is dealt. k is split over CTAs only as far as the staged activations of a part must fit in shared memory next to the
 // warps' rings. For every warp count two ways are scored by how even the busiest warp's share is: whole row tiles per warp (nothing goes through the workspace)
-// or runs of chunks (chunk sums through the workspace and a finalize launch); more warps per SM are mildly preferred.
+// or runs of chunks (chunk sums through the workspace and a finalize launch); more warps per SM are mildly preferred. Small matrices that would take the second
+// way are then moved to whole row tiles per CTA with the chunk sums in shared memory (one launch), see the end of the function.
 GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
     const int sms = device_sms();
     const int nb = (int)(k / 256), ntiles = (int)((n + 15) / 16);
@@ -1022,10 +1048,26 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
                 const double balance = upw / std::ceil(upw);
                 const double shared = aligned && ksplit == 1 ? 1.0 : 0.9;                       // cost of the workspace round trip and the finalize launch
                 const double score = balance * common * shared;
-                if (score > best_score) best_score = score, best = GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, kbp, ksplit, grid, smem, kc, nchunks, cpp, aligned};
+                if (score > best_score) best_score = score, best = GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, kbp, ksplit, grid, smem, kc, nchunks, cpp, aligned, 0};
             }
         }
         if (best_score > 0) break;                                        // the smallest split that fits
+    }
+    // Form (c) instead of form (b) where the second launch costs more than the uneven shares of whole row tiles per CTA: G = min(SMs, row tiles) CTAs own
+    // floor / ceil (row tiles / G) row tiles each, so the product runs as long as its busiest CTA; against that stand about 2 us for the finalize launch of form (b)
+    // (measured inside chained launches: 4096 x 4096 7.4 -> 5.2 us, 10240 x 5120 10.2 -> 9.1 us, 5120 x 8192 9.3 -> 8.7 us at one row; more with 8 rows).
+    // The whole of k is staged in every CTA, so up to 8 activation rows and only while that fits shared memory; at least 64 CTAs must get work.
+    if (best.warps > 0 && !(best.aligned && best.ksplit == 1) && ntiles >= 64 && m <= 8) {
+        const int grid = std::min(sms, ntiles), rpc = (ntiles + grid - 1) / grid;
+        const double t_us = (double)ntiles * nb * (double)kyb_tile_bytes(fmt) / 5.0e6;          // the product at 5 TB/s
+        const double penalty_us = t_us * ((double)rpc * grid / ntiles - 1.0);
+        const size_t cpart = (size_t)rpc * nchunks * (size_t)m * 16 * sizeof(float);
+        if (penalty_us < 2.0) {
+            for (int warps = max_warps; warps >= 8; --warps) {
+                const size_t smem = plan_smem(fmt, nt, mst, nb, warps, kyb::GEMV_DSTAGES) + cpart;
+                if (smem <= smem_cap) return GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, nb, 1, grid, smem, kc, nchunks, nchunks, 0, 1};
+            }
+        }
     }
     return best;
 }
@@ -1070,7 +1112,7 @@ int launch_maybe_chained(const void* kern, dim3 grid, dim3 block, size_t smem, c
     return kyb_launch_check(what);
 }
 
-bool two_step(const GemvPlan& pl) { return !(pl.aligned && pl.ksplit == 1); }     // form (b): chunk sums through the workspace, then the finalize kernel
+bool two_step(const GemvPlan& pl) { return !pl.local && !(pl.aligned && pl.ksplit == 1); }     // form (b): chunk sums through the workspace, then the finalize kernel
 size_t partial_bytes(const GemvPlan& pl, int64_t n, int64_t m) { return (size_t)pl.nchunks * (size_t)m * (size_t)((n + 15) / 16 * 16) * sizeof(float); }
 
 int check_gemv_args(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx) {
@@ -1092,7 +1134,8 @@ int launch_gemv(int fmt, const GemvPlan& pl, const void* t16, int64_t n, int64_t
     p.t16 = (const uint8_t*)t16, p.x = (const __half*)x, p.x2 = (const __half*)x2, p.limit = limit, p.y = (__half*)y, p.partial = partial, p.status = status;
     p.ldx = ldx, p.ldy = ldy, p.n = (int)n, p.npad = (int)((n + 15) / 16 * 16), p.nb = (int)(k / 256), p.m = (int)m, p.mst = pl.mst;
     p.kbp = pl.kbp, p.ksplit = pl.ksplit, p.warps = pl.warps, p.stages = pl.stages, p.gscale = gscale, p.kc = pl.kc, p.nchunks = pl.nchunks, p.cpp = pl.cpp, p.aligned = pl.aligned;
-    p.partial_only = staged ? 1 : 0, p.pdl = chained ? 1 : 0;
+    p.partial_only = (staged || pl.local) ? 1 : 0, p.pdl = chained ? 1 : 0;
+    p.local = (pl.local && !sums_only) ? 1 : 0;                    // chunk sums asked for by the caller go to its buffer as in form (b)
     const void* kern = gemv_kernel_ptr(fmt, variant_of(m));
     if (int rc = ensure_smem_attr(kern)) return rc;
     void* args[] = {(void*)&p};
