@@ -237,8 +237,9 @@ int kyb_gather_flat(const void* const* srcs, void* const* dsts, const int64_t* b
 int kyb_gemv_t16_static(int fmt, const void* t16, int64_t n, int64_t k, const void* x, int64_t m, int64_t ldx, float gscale,
                         void* y, int64_t ldy, int check, void* stream);
 
-/* launch plan the GEMV would use (diagnostics): out8 = {column tiles, 1 if warps take whole row tiles, warps per CTA, k-blocks per canonical chunk,
- * k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. */
+/* launch plan the GEMV would use (diagnostics): out8 = {column tiles, how work is dealt (1: whole row tiles per warp, one launch; 0: runs of chunks per warp,
+ * chunk sums through the workspace and a finalize launch; 2: whole row tiles per CTA, chunk sums added in shared memory, one launch), warps per CTA, k-blocks
+ * per canonical chunk, k-blocks per part, k parts, dynamic shared memory bytes, CTAs}. */
 int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8);
 
 /* device status word of the calling thread's current device: nonzero after a bounded wait expired inside a kernel.

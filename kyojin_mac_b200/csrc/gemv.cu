@@ -1156,7 +1156,7 @@ int launch_gemv(int fmt, const GemvPlan& pl, const void* t16, int64_t n, int64_t
 extern "C" int kyb_gemv_plan(int fmt, int64_t n, int64_t k, int64_t m, int* out8) {
     KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT && n > 0 && k > 0 && k % 256 == 0 && m >= 1 && m <= 32 && out8, "bad arguments");
     const GemvPlan pl = make_plan(fmt, n, k, m);
-    out8[0] = pl.nt, out8[1] = pl.aligned, out8[2] = pl.warps, out8[3] = pl.kc, out8[4] = pl.kbp, out8[5] = pl.ksplit, out8[6] = (int)pl.smem, out8[7] = pl.grid;
+    out8[0] = pl.nt, out8[1] = pl.local ? 2 : pl.aligned, out8[2] = pl.warps, out8[3] = pl.kc, out8[4] = pl.kbp, out8[5] = pl.ksplit, out8[6] = (int)pl.smem, out8[7] = pl.grid;
     return KYB_OK;
 }
 

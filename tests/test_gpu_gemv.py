@@ -136,12 +136,19 @@ def test_full_size_properties(fmt, n, k):
     assert torch.equal(y2, y * 2)
 
 
-@pytest.mark.parametrize("fmt,n,k,m", [("q4_k", 512, 5120, 8), ("q6_k", 1024, 8192, 3), ("q4_k", 10240, 5120, 1), ("q6_k", 5120, 27648, 8), ("q3_k", 48, 3072, 5)])
-def test_product_equals_exposed_partial_sums(fmt, n, k, m):
+FORMS = {"whole row tiles per warp": 1, "runs of chunks + finalize launch": 0, "whole row tiles per CTA, sums in shared memory": 2}
+
+
+@pytest.mark.parametrize("fmt,n,k,m,form", [("q4_k", 512, 5120, 8, 0), ("q6_k", 1024, 8192, 3, 2), ("q4_k", 10240, 5120, 1, 2), ("q6_k", 5120, 27648, 8, 0), ("q3_k", 48, 3072, 5, 0),
+                                            ("q4_k", 4096, 4096, 8, 2), ("q4_k", 5120, 8192, 8, 2), ("q5_k", 1030, 2560, 2, 2), ("q4_k", 55296, 5120, 2, 1)])
+def test_product_equals_exposed_partial_sums(fmt, n, k, m, form):
     """The product == the two-step entry points whose chunk sums are all written out (mma_gemv.partial_mma) and added in k order (finalize_rows), bit for bit,
-    call after call, plain and chained launches, whichever way the library deals the work (whole row tiles per warp or runs of chunks)."""
+    call after call, plain and chained launches, whichever of its three ways the library deals the work (the cases cover all three; n = 1030 ends inside a row
+    tile)."""
     from kyojin_mac_b200 import mma_gemv
     from kyojin_mac_b200.foreign_linear import DevPack
+    assert ops.gemv_plan(fmt, n, k, m)["aligned"] == form, ops.gemv_plan(fmt, n, k, m)
+    assert (ops.gemv_workspace_bytes(fmt, n, k, m) > 0) == (form == 0)
     t16 = synth.t16_random_device(fmt, n, k, seed=3)
     g = torch.Generator(device="cuda").manual_seed(4)
     dev = DevPack.from_t16(fmt, t16, n, k)
