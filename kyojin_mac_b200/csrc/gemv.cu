@@ -1054,7 +1054,7 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
         if (best_score > 0) break;                                        // the smallest split that fits
     }
     // Form (c) instead of form (b) where the second launch costs more than the uneven shares of whole row tiles per CTA: G = min(SMs, row tiles) CTAs own
-    // floor / ceil (row tiles / G) row tiles each, so the product runs as long as its busiest CTA; against that stand about 2 us for the finalize launch of form (b)
+    // floor / ceil (row tiles / G) row tiles each, so the product runs as long as its busiest CTA; against that stand about 2.5 us for the finalize launch of form (b)
     // (measured inside chained launches: 4096 x 4096 7.4 -> 5.2 us, 10240 x 5120 10.2 -> 9.1 us, 5120 x 8192 9.3 -> 8.7 us at one row; more with 8 rows).
     // The whole of k is staged in every CTA, so up to 8 activation rows and only while that fits shared memory; at least 64 CTAs must get work.
     if (best.warps > 0 && !(best.aligned && best.ksplit == 1) && ntiles >= 64 && m <= 8) {
@@ -1062,7 +1062,7 @@ GemvPlan search_plan(int fmt, int64_t n, int64_t k, int64_t m) {
         const double t_us = (double)ntiles * nb * (double)kyb_tile_bytes(fmt) / 5.0e6;          // the product at 5 TB/s
         const double penalty_us = t_us * ((double)rpc * grid / ntiles - 1.0);
         const size_t cpart = (size_t)rpc * nchunks * (size_t)m * 16 * sizeof(float);
-        if (penalty_us < 2.0) {
+        if (penalty_us < 2.5) {
             for (int warps = max_warps; warps >= 8; --warps) {
                 const size_t smem = plan_smem(fmt, nt, mst, nb, warps, kyb::GEMV_DSTAGES) + cpart;
                 if (smem <= smem_cap) return GemvPlan{nt, mst, warps, kyb::GEMV_DSTAGES, nb, 1, grid, smem, kc, nchunks, nchunks, 0, 1};
