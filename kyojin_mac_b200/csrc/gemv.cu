@@ -822,12 +822,21 @@ __global__ void __launch_bounds__(512, 1) gemv_group_kernel(const GroupParams p)
     uint32_t parity = 0;
     int stage = 0;
     bool failed = false;
-    for (uint32_t item = blockIdx.x; item < ngroups * (uint32_t)p.rc * npair; item += gridDim.x) {
-        const uint32_t which = item % npair, it2 = item / npair;              // the two stacks of a pair take neighbouring items
+    // Items go to the CTAs round-robin and all cost the same, so the last round would keep only `rest` of the CTAs busy for a whole item (904 items on 148 CTAs:
+    // six full rounds and a seventh for 16 of them). The items of that last round are therefore cut into `cut` parts of their row tiles each (as many as there are
+    // idle CTAs per item, while every warp still gets a row tile): the round then lasts 1 / cut of an item. A row tile is still computed by one warp over the whole
+    // of k, so no result changes.
+    const uint32_t whole_items = ngroups * (uint32_t)p.rc * npair;
+    const uint32_t even = whole_items / gridDim.x * gridDim.x, rest = whole_items - even;
+    const uint32_t cut = rest ? max(1u, min(gridDim.x / rest, (uint32_t)max(1, tpc / p.warps))) : 1u;
+    for (uint32_t item = blockIdx.x; item < even + rest * cut; item += gridDim.x) {
+        const uint32_t whole = item < even ? item : even + (item - even) / cut, part = item < even ? 0u : (item - even) % cut, parts = item < even ? 1u : cut;
+        const uint32_t which = whole % npair, it2 = whole / npair;            // the two stacks of a pair take neighbouring items
         const uint32_t grp = it2 / (uint32_t)p.rc, rc = it2 % (uint32_t)p.rc;
         const uint32_t e = p.g_expert[grp];
         const uint8_t* stack = which ? p.t16b : p.t16;
-        const int rt0 = (int)rc * tpc + warp, rt_end = min(ntiles, ((int)rc + 1) * tpc);
+        const int c_begin = (int)rc * tpc, c_len = max(0, min(ntiles, ((int)rc + 1) * tpc) - c_begin);
+        const int rt0 = c_begin + (int)((uint32_t)c_len * part / parts) + warp, rt_end = c_begin + (int)((uint32_t)c_len * (part + 1) / parts);
         const int nrt = rt0 < rt_end ? (rt_end - rt0 + p.warps - 1) / p.warps : 0;      // row tiles of this warp: rt0, rt0 + warps, ...
         const int total = nrt * p.nb;
         // ---- producer (lane 0): this item's tiles of this warp
