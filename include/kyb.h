@@ -129,6 +129,15 @@ int kyb_gemm_nvfp4_ag(const void* a_codes, const void* sfa, const void* b_codes,
  * kernel with that many 128-row blocks of a per work item (same bits either way). The grouped form needs n % 256 == 0 and tb / off from
  * kyb_moe_plan with the same mt (128 or 256 rows of one expert per work item). */
 int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int msub, void* stream);
+/* split-k form of kyb_gemm_kq for products with fewer 256 x 256 output tiles than SMs (the reference has no counterpart: its fallback for these row counts is
+ * dequantise + library matmul, kyojin_mlx/foreign_linear.py:710 / :737). The 256-input blocks are cut into `split` equal ranges, (tile, range) items fill the
+ * SMs, every item leaves its fp32 accumulator in the workspace, a second kernel adds the ranges in k order, scales, saturates and stores d. Deterministic; differs
+ * from kyb_gemm_kq by the fp32 summation order only. kyb_gemm_kq_split: the factor the library suggests for a shape (1: do not split; splits keep ranges of at
+ * least 2048 inputs). kyb_gemm_kq_split_bytes: size of the 16-byte aligned workspace = split * (m rounded up to 256) * (n rounded up to 256) * 4. */
+int kyb_gemm_kq_split(int fmt, int64_t n, int64_t k, int64_t m);
+size_t kyb_gemm_kq_split_bytes(int64_t n, int64_t m, int split);
+int kyb_gemm_kq_splitk(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int split,
+                       void* workspace, size_t workspace_bytes, void* stream);
 int kyb_gemm_kq_grouped(int fmt, const void* t16, int64_t n, int64_t k, int experts, const void* a, int64_t lda, int64_t s, const void* tb, const void* off,
                         const void* row_map, const void* gs, void* d, int64_t ldd, int mt, void* stream);
 /* gate and up of a routed SwiGLU layer as ONE grouped product with the gated activation in its epilogue: an item's 256 weight rows are 128 rows of the gate stack

@@ -125,6 +125,9 @@ SIGNATURES = {
     "kyb_gemv_partial_t16": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _vp, _vp]),
     "kyb_gemv_finalize": (_int, [_vp, _int, _i64, _i64, _f32, _vp, _i64, _vp]),
     "kyb_gemm_kq": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
+    "kyb_gemm_kq_split": (_int, [_int, _i64, _i64, _i64]),
+    "kyb_gemm_kq_split_bytes": (C.c_size_t, [_i64, _i64, _int]),
+    "kyb_gemm_kq_splitk": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _vp, _i64, _int, _vp, C.c_size_t, _vp]),
     "kyb_gemm_kq_ag": (_int, [_int, _vp, _i64, _i64, _vp, _i64, _i64, _f32, _pp, _i64, _i64, _int, _vp]),
     "kyb_gemm_nvfp4_ag": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _f32, _int, _pp, _i64, _i64, _vp]),
     "kyb_gemm_kq_grouped": (_int, [_int, _vp, _i64, _i64, _int, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _int, _vp]),

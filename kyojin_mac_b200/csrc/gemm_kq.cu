@@ -50,6 +50,11 @@ struct KqParams {
     int wide;                   // ... in 32 x 64 boxes (4 KB of staging per epilogue warp) instead of 32 x 32: used when the tiles also go to other GPUs
     // gated pair (grouped form): an item's 256 weight rows are 128 rows of the gate stack (t16) and the same 128 rows of the up stack (t16b); the epilogue writes
     // fp16(silu(a) * b) of the two fp16-rounded products, 128 output columns per item (kyojin_mlx/foreign_kqgmm.py:293-314 `mlp`: gmm, gmm, silu_perm in one launch)
+    // split-k (dense form, one destination): the k-blocks are cut into ksplit equal ranges, an item is (tile, range) and writes its fp32 accumulator to
+    // part [range][m][ldp] instead of d; gemm_kq_reduce_kernel adds the ranges in k order, scales, saturates and stores d
+    int ksplit, mpad;           // mpad: rows of a range in part (m rounded up to whole items)
+    float* part;
+    int64_t ldp;
     const uint8_t* t16b;
     const float* gsb;           // per-expert output scale of the up stack (or null)
     int glu;
@@ -58,6 +63,7 @@ struct KqParams {
 
 struct KqItem {
     int m0, m_end, n0, b_rt0, nsub;
+    int tb0, ntb, sp;           // first 256-input block, number of blocks and index of the item's k-range (the whole of k without split-k)
     float gscale, gscale_b;
     bool valid;
 };
@@ -65,7 +71,13 @@ struct KqItem {
 __device__ __forceinline__ KqItem kq_item(const KqParams& p, int t, const uint16_t* tord = nullptr) {
     KqItem it;
     it.valid = true, it.gscale = p.gscale, it.gscale_b = p.gscale, it.m_end = p.m;
+    it.tb0 = 0, it.ntb = p.nb, it.sp = 0;
     if (!p.tb) {
+        if (p.ksplit > 1) {                                                             // tiles fastest, k-ranges slowest
+            const int tiles = p.tiles_m * p.tiles_n;
+            it.sp = t / tiles, t -= it.sp * tiles;
+            it.ntb = p.nb / p.ksplit, it.tb0 = it.sp * it.ntb;
+        }
         const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;                         // m fastest: CTAs running together share the weight rows
         it.n0 = tn * KQ_BN, it.m0 = tm * 128 * p.msub, it.b_rt0 = it.n0 >> 4;
         it.nsub = min(p.msub, (p.m - it.m0 + 127) >> 7);
@@ -527,7 +539,6 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
     const uint32_t bars = stg0 + 4 * stg_bytes;                                     // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], tmem slot
     const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, accf0 = bars + 16 * STAGES, acce0 = accf0 + 16, tmem_slot = acce0 + 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kblocks = p.k / KQ_BK;
     constexpr uint32_t TMEM_COLS = 512;
 
     if (threadIdx.x == 0) {
@@ -585,7 +596,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             for (int t = blockIdx.x; t < num_items && !failed; t += gridDim.x) {
                 const KqItem it = kq_item(p, t, tord);
                 if (!it.valid) continue;
-                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                for (int kb = 4 * it.tb0; kb < 4 * (it.tb0 + it.ntb) && !failed; ++kb) {
                     if (!mbar_wait_fast(empty0 + 8 * s, parity)) failed = true;
                     const uint32_t a_dst = smem0 + s * stage_bytes;
                     mbar_expect_tx_a(full0 + 8 * s, (uint32_t)it.nsub * KQ_A_SUB);
@@ -608,7 +619,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                 // is due, so the first stage of this item overlaps the tail of the previous item's epilogue
                 if (!mbar_wait_fast(acce0 + 8 * (cnt & 1u), ((cnt >> 1) & 1u) ^ 1u)) failed = true;
                 tc_fence_after();
-                for (int kb = 0; kb < kblocks && !failed; ++kb) {
+                for (int kb = 0; kb < 4 * it.ntb && !failed; ++kb) {
                     if (!mbar_wait_fast(full0 + 8 * s, parity)) failed = true;
                     tc_fence_after();
                     const uint32_t a_src = smem0 + s * stage_bytes;
@@ -642,7 +653,25 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
                 if (!mbar_wait_fast(accf0 + 8 * slot, (cnt >> 1) & 1u)) failed = true;
                 tc_fence_after();
                 const float gscale = it.gscale;
-                if (p.tma_out) {
+                if (p.part) {
+                    // ---- split-k: this range's accumulator as it is (fp32) through the staged tiled stores; the tensor map covers part as 16-bit pairs, so a step of
+                    // 32 rows x 16 fp32 columns is the same 32 x 64-byte box as a step of fp16 outputs. Rows past m land in the padding rows of the range.
+                    const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
+                    const int row0 = it.sp * p.mpad + it.m0 + sub * 128 + q * 32;
+#pragma unroll 1
+                    for (int c = 0; c < KQ_BN; c += 32) {
+                        uint32_t v[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + slot * KQ_BN + (uint32_t)c, v);
+                        tmem_ld_wait();
+                        uint32_t w[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) w[j] = v[j];
+                        epilogue_stage_store(outs, 1, stg, lane, w, 2 * (it.n0 + c), row0, !failed);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) w[j] = v[16 + j];
+                        epilogue_stage_store(outs, 1, stg, lane, w, 2 * (it.n0 + c + 16), row0, !failed);
+                    }
+                } else if (p.tma_out) {
                     // ---- staged tiled stores: 32 rows x 32 columns per step go to shared memory (64-byte swizzle, conflict-free 16-byte stores) and leave as one bulk
                     // tensor store per receiving rank: full 64-byte row segments on the wire, rows / columns past the matrix are dropped by the tensor map
                     const uint32_t stg = stg0 + (uint32_t)q * stg_bytes;
@@ -768,7 +797,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             const KqItem it = kq_item(p, t, tord);
             if (!it.valid) continue;
             const int rt = min(it.b_rt0 + (p.glu ? (dw & 7) : dw), p.rt_total - 1);      // gated pair: warps 0-7 decode the gate rows, 8-15 the same rows of the up stack
-            const uint8_t* tp = ((p.glu && dw >= 8) ? p.t16b : p.t16) + (size_t)rt * (size_t)p.nb * TB;
+            const uint8_t* tp = ((p.glu && dw >= 8) ? p.t16b : p.t16) + ((size_t)rt * (size_t)p.nb + (size_t)it.tb0) * TB;
+            const int nbk = it.ntb;                                                      // 256-input blocks of this item
             // Software pipeline over the 64-input quarters: while the stores of quarter q drain into the stage (and before the proxy fence that publishes them), the
             // registers of quarter q + 1 are computed, so the wait for a free stage, the scale loads and the arithmetic overlap the shared-memory traffic.
             KqTile<FMT> tr;
@@ -776,9 +806,9 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
             kq_load<FMT>(tp, lane, tr);
             kq_prep_scales<FMT>(tr, scr, lane);
             __syncwarp();
-            if (p.nb > 1) kq_refill_scales<FMT>(tp + TB, lane, tr);
+            if (nbk > 1) kq_refill_scales<FMT>(tp + TB, lane, tr);
             kq_compute_quarter<FMT, 0>(tr, scr, lane, r);
-            if (p.nb > 1) kq_refill<FMT, 0>(tp + TB, lane, tr);
+            if (nbk > 1) kq_refill<FMT, 0>(tp + TB, lane, tr);
 #define KYB_KQ_PUBLISH()                                                                                          \
     {                                                                                                             \
         fence_proxy_async_smem();                                                                                 \
@@ -792,8 +822,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
         const uint32_t b_dst = smem0 + s * stage_bytes + a_bytes + row_off;                                       \
         kq_store_quarter(b_dst, b_dst + 1024u, cx, odd, r);                                                       \
     }
-            for (int kb = 0; kb < p.nb && !failed; ++kb) {
-                const bool more = kb + 1 < p.nb, more2 = kb + 2 < p.nb;
+            for (int kb = 0; kb < nbk && !failed; ++kb) {
+                const bool more = kb + 1 < nbk, more2 = kb + 2 < nbk;
                 const uint8_t* nx = tp + (size_t)(kb + 1) * TB;                      // the next tile, two tiles ahead for the units already consumed
                 KYB_KQ_STORE()
                 kq_compute_quarter<FMT, 1>(tr, scr, lane, r);
@@ -823,7 +853,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
 #undef KYB_KQ_STORE
         }
     }
-    if (warp >= 2 && warp < 6 && lane == 0 && p.tma_out) tma_store_wait_all();         // the staging buffer must outlive its stores
+    if (warp >= 2 && warp < 6 && lane == 0 && (p.tma_out || p.part)) tma_store_wait_all();   // the staging buffer must outlive its stores
     if (failed) atomicExch(p.status, KYB_DEV_TIMEOUT_GEMM);
     tc_fence_before();
     __syncthreads();
@@ -833,6 +863,31 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) gemm_kq_kernel(const __grid_con
     }
 }
 
+
+// split-k, second step: d [m, n] = sat(gscale * (part[0] + part[1] + ... in k order)), eight columns per thread
+__global__ void gemm_kq_reduce_kernel(const float* __restrict__ part, int ksplit, int m, int mpad, int n, int64_t ldp, float gscale, __half* __restrict__ d, int64_t ldd) {
+    const int n8 = (n + 7) >> 3;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)m * n8) return;
+    const int row = (int)(i / n8), c0 = (int)(i % n8) * 8;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int sp = 0; sp < ksplit; ++sp) {
+        const float4* src = reinterpret_cast<const float4*>(part + ((size_t)sp * (size_t)mpad + (size_t)row) * (size_t)ldp + c0);
+        const float4 a = src[0], b = src[1];                                            // ldp is a multiple of 256: always inside the row
+        acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w, acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+    }
+    __half* dst = d + (size_t)row * (size_t)ldd + c0;
+    if (c0 + 8 <= n && (ldd & 7) == 0 && ((uintptr_t)d & 15) == 0) {
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = sat_half2(acc[2 * j] * gscale, acc[2 * j + 1] * gscale);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+    } else {
+        for (int j = 0; j < 8 && c0 + j < n; ++j) dst[j] = sat_half(acc[j] * gscale);
+    }
+}
 
 // ------------------------------------------------------------------------------------------------ the dense form by CTA pairs (tcgen05 cta_group::2)
 // A pair of CTAs computes a 256 x 256 tile of D: each CTA holds 128 activation rows (TMA) and decodes ONE HALF of the 256 weight rows (8 row tiles) of a
@@ -1152,7 +1207,7 @@ int kq_launch_pair(int fmt, const CUtensorMap& ta, const KybOutMaps& outs, kyb::
 }  // namespace
 
 static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* const* d, int nout, int64_t ldd,
-                    int64_t col0, int msub, void* stream, bool pair_ok = true) {
+                    int64_t col0, int msub, void* stream, bool pair_ok = true, int ksplit = 1, float* part = nullptr) {
     KYB_REQUIRE(fmt >= 0 && fmt < KYB_FMT_COUNT, "unknown weight format %d", fmt);
     KYB_REQUIRE(t16 && a, "null pointer");
     KYB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 256 == 0, "m=%lld n=%lld k=%lld: k must be a positive multiple of 256", (long long)m, (long long)n, (long long)k);
@@ -1171,6 +1226,7 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
     for (int i = 0; i < 8; ++i) p.d[i] = i < nout ? (__half*)d[i] + col0 : nullptr;
     p.gscale = gscale, p.status = status, p.tb = nullptr, p.off = nullptr, p.row_map = nullptr, p.gs = nullptr, p.experts = 0;
     p.tiles_n = (int)((n + kyb::KQ_BN - 1) / kyb::KQ_BN);
+    p.ksplit = ksplit, p.mpad = 0, p.part = ksplit > 1 ? part : nullptr, p.ldp = (int64_t)p.tiles_n * kyb::KQ_BN;
     if (!msub) {
         // two activation blocks per item halve the decode work per flop, but they halve the number of items and keep both accumulators busy (no overlap of
         // the epilogue with the next item): one block when the rows fit one block, when two-block items would leave more than half of the SMs idle, or when the
@@ -1195,6 +1251,19 @@ static int kq_dense(int fmt, const void* t16, int64_t n, int64_t k, const void* 
         if (int rc = kyb_make_tmap_2d(&outs.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, d[i], (uint64_t)m, (uint64_t)(col0 + n), (uint64_t)ldd * 2, 32, p.wide ? 64 : 32,
                                       p.wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B))
             return rc;
+    if (ksplit > 1) {
+        // split-k: the one-CTA kernel over (tile, k-range) items, whose staged stores go to the fp32 ranges (tensor map over part as 16-bit pairs), then the
+        // ranges are added
+        p.mpad = p.tiles_m * 128 * p.msub, p.tma_out = 0, p.wide = 0;
+        memset(&outs, 0, sizeof(outs));
+        if (int rc = kyb_make_tmap_2d(&outs.m[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, part, (uint64_t)ksplit * (uint64_t)p.mpad, (uint64_t)(2 * p.ldp), (uint64_t)p.ldp * 4, 32, 32,
+                                      CU_TENSOR_MAP_SWIZZLE_64B))
+            return rc;
+        if (int rc = kq_launch(fmt, ta, outs, p, p.tiles_n * p.tiles_m * ksplit, (cudaStream_t)stream)) return rc;
+        const int64_t threads = m * ((n + 7) / 8);
+        kyb::gemm_kq_reduce_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(part, ksplit, (int)m, p.mpad, (int)n, p.ldp, gscale, (__half*)d[0], ldd);
+        return kyb_launch_check("gemm_kq_reduce");
+    }
     if (nout == 1 && p.tma_out && m > 128 && pair_ok && automatic) {
         // one destination and at least two row blocks: CTA pairs (cta_group::2), each CTA decoding half of the 256 weight rows of a tile
         if (int rc = kq_launch_pair(fmt, ta, outs, p, (cudaStream_t)stream); rc != KYB_EUNSUPPORTED) return rc;
@@ -1210,6 +1279,48 @@ extern "C" int kyb_gemm_kq(int fmt, const void* t16, int64_t n, int64_t k, const
     KYB_REQUIRE(d && ((uintptr_t)d & 1) == 0, "null or odd output pointer");
     void* outs[1] = {d};
     return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, 1, ldd, 0, msub, stream);
+}
+
+// Split-k for products with fewer output tiles than SMs (e.g. 2048 x 3072 outputs from 12288 inputs: 96 tiles of 256 x 256): the k-blocks are cut into `split`
+// equal ranges, (tile, range) items fill the SMs, every item leaves its fp32 accumulator in the workspace and a second kernel adds the ranges in k order (the result
+// is deterministic; it differs from the unsplit product by fp32 summation order only). kyb_gemm_kq_split: the factor the library suggests (1: do not split);
+// kyb_gemm_kq_split_bytes: bytes of 16-byte aligned workspace the call then needs.
+extern "C" int kyb_gemm_kq_split(int fmt, int64_t n, int64_t k, int64_t m) {
+    if (fmt < 0 || fmt >= KYB_FMT_COUNT || n <= 0 || k <= 0 || k % 256 || m <= 128) return 1;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    (void)cudaGetLastError();
+    const int64_t tiles = ((n + 255) / 256) * ((m + 255) / 256), nb = k / 256;
+    if (tiles >= sms) return 1;                                                       // whole rounds of tiles already fill the SMs
+    // cost in 64-input stages (0.73 us each), fitted to measurements on 3072 x 12288, 1536 x 12288 and 768 x 12288 with 2048 rows: rounds x (stages per item + 8
+    // for its start and its exposed epilogue) + the second pass, which moves (ranges + 0.5) x the fp32 output at about 3 TB/s = 2.2 MB per stage time
+    const double out_mb = (double)(((m + 255) / 256) * 256) * (double)(((n + 255) / 256) * 256) * 4.0 / 1.0e6;
+    const double whole = (double)(4 * nb + 8);                                        // one round of whole-k items
+    int best = 1;
+    double best_cost = 0.95 * whole;                                                    // a split must gain a twentieth at least
+    for (int sp = 2; sp <= 8; ++sp) {
+        if (nb % sp || nb / sp < 8) continue;                                           // equal ranges of at least 2048 inputs
+        const double rounds = (double)((tiles * sp + sms - 1) / sms);
+        const double cost = rounds * (4.0 * (double)(nb / sp) + 8.0) + (sp + 0.5) * out_mb / 2.2;
+        if (cost < best_cost) best = sp, best_cost = cost;
+    }
+    return best;
+}
+extern "C" size_t kyb_gemm_kq_split_bytes(int64_t n, int64_t m, int split) {
+    if (n <= 0 || m <= 0 || split <= 1) return 0;
+    return (size_t)split * (size_t)(((m + 255) / 256) * 256) * (size_t)(((n + 255) / 256) * 256) * sizeof(float);   // rows and columns padded to whole work items
+}
+extern "C" int kyb_gemm_kq_splitk(int fmt, const void* t16, int64_t n, int64_t k, const void* a, int64_t lda, int64_t m, float gscale, void* d, int64_t ldd, int split,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    KYB_REQUIRE(d && ((uintptr_t)d & 1) == 0, "null or odd output pointer");
+    KYB_REQUIRE(split >= 2 && split <= 8 && k > 0 && k % 256 == 0 && (k / 256) % split == 0, "split=%d: 2..8 equal ranges of whole 256-input blocks (k=%lld)", split, (long long)k);
+    const size_t need = kyb_gemm_kq_split_bytes(n, m, split);
+    if (!workspace || workspace_bytes < need || ((uintptr_t)workspace & 15)) {
+        kyb_set_error("split-k needs %zu bytes of 16-byte aligned workspace, got %zu", need, workspace ? workspace_bytes : (size_t)0);
+        return KYB_EWORKSPACE;
+    }
+    void* outs[1] = {d};
+    return kq_dense(fmt, t16, n, k, a, lda, m, gscale, outs, 1, ldd, 0, m > 128 ? 2 : 1, stream, false, split, (float*)workspace);
 }
 
 // The same product with the all-gather of an N-sharded linear folded into the epilogue: every tile goes to the output matrix of every rank, at column col0.
@@ -1258,6 +1369,7 @@ static int kq_grouped(int fmt, const void* t16, const void* t16b, int64_t n, int
     p.rt_total = (int)((int64_t)experts * n / 16);
     p.gscale = 1.0f, p.status = status, p.tb = (const uint32_t*)tb, p.off = (const uint32_t*)off, p.row_map = (const uint32_t*)row_map, p.gs = (const float*)gs, p.experts = experts;
     p.msub = mt / 128;
+    p.ksplit = 1, p.mpad = 0, p.part = nullptr, p.ldp = 0;
     p.t16b = (const uint8_t*)t16b, p.gsb = (const float*)gsb, p.glu = glu ? 1 : 0, p.limit = limit;
     p.tiles_n = (int)(n / (glu ? kyb::KQ_BN / 2 : kyb::KQ_BN)), p.tiles_m = (int)((s + mt - 1) / mt) + experts;
     p.tma_out = 0, p.col0 = 0, p.wide = 0;                                         // rows are scattered (row_map) or end inside a tile: no tensor map fits

@@ -15,3 +15,4 @@ GATHER_PER_EXPERT = _int("KYB_GATHER_PER_EXPERT", 4)   # ... or up to this many 
 PREFILL_TWO_STEP = _int("KYB_PREFILL_TWO_STEP", 0) != 0   # 1: prefill = fp16 copy of the weights in HBM, then the fp16 GEMM (the reference's form); 0: weights decoded inside the GEMM
 GEMV_CHAINED = _int("KYB_GEMV_CHAINED", 1) != 0   # decode products of a module are launched with programmatic stream serialization from their second call on (the weights are settled by then): consecutive products overlap launch and pipeline fill
 ROUTER_TC_MIN_ROWS = _int("KYB_ROUTER_TC_MIN_ROWS", 512)   # fp16 token batches from this size compute the router logits on the tensor cores (gate cut into three fp16 pieces); below it the fp32 kernels run
+GEMM_SPLIT_K = _int("KYB_GEMM_SPLIT_K", 1) != 0   # prefill products with fewer 256 x 256 output tiles than SMs cut k into ranges (fp32 partial sums in a workspace, added in k order); 0: never

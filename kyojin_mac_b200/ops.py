@@ -349,8 +349,11 @@ def gemm_f16_grouped(a: torch.Tensor, b: torch.Tensor, n: int, E: int, tb: torch
     return d
 
 
-def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, msub: int = 0) -> torch.Tensor:
-    """d fp16 [m, n] = a fp16 [m, k] @ W^T with W decoded from its T16 tiles inside the GEMM (no fp16 copy of W in HBM)."""
+def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: float = 1.0, out: torch.Tensor | None = None, msub: int = 0,
+            split: int | None = None) -> torch.Tensor:
+    """d fp16 [m, n] = a fp16 [m, k] @ W^T with W decoded from its T16 tiles inside the GEMM (no fp16 copy of W in HBM).
+    split: number of k-ranges (split-k through an fp32 workspace for products with fewer output tiles than SMs); None = the library's suggestion when msub is 0
+    and `flags.GEMM_SPLIT_K` is on, 1 = never."""
     _need_cuda(t16, a)
     if a.dtype != torch.float16 or a.dim() != 2 or a.shape[1] != k:
         raise ValueError(f"gemm_kq takes float16 [m, {k}], got {a.dtype} {tuple(a.shape)}")
@@ -358,7 +361,16 @@ def gemm_kq(fmt, t16: torch.Tensor, n: int, k: int, a: torch.Tensor, gscale: flo
         a = a.contiguous()
     m = a.shape[0]
     d = out if out is not None else torch.empty((m, n), dtype=torch.float16, device=a.device)
-    _lib.check(_lib.lib().kyb_gemm_kq(_fmt(fmt), t16.data_ptr(), n, k, a.data_ptr(), a.stride(0), m, float(gscale), d.data_ptr(), d.stride(0), msub, _stream()))
+    L = _lib.lib()
+    if split is None:
+        split = L.kyb_gemm_kq_split(_fmt(fmt), n, k, m) if (msub == 0 and F.GEMM_SPLIT_K) else 1
+    if split > 1:
+        need = L.kyb_gemm_kq_split_bytes(n, m, split)
+        ws = workspace(a.device, need)
+        _lib.check(L.kyb_gemm_kq_splitk(_fmt(fmt), t16.data_ptr(), n, k, a.data_ptr(), a.stride(0), m, float(gscale), d.data_ptr(), d.stride(0), split, ws.data_ptr(),
+                                        ws.numel(), _stream()))
+        return d
+    _lib.check(L.kyb_gemm_kq(_fmt(fmt), t16.data_ptr(), n, k, a.data_ptr(), a.stride(0), m, float(gscale), d.data_ptr(), d.stride(0), msub, _stream()))
     return d
 
 

@@ -91,6 +91,36 @@ def test_fused_decode_gemm_vs_staged(fmt):
     assert torch.allclose(ys.float(), y1[:3].float() * 0.5, rtol=2e-3, atol=1e-4)
 
 
+@pytest.mark.parametrize("fmt", ["q4_k", "q3_k", "q6_k", "nvfp4"])
+def test_split_k_adds_the_ranges_in_k_order(fmt):
+    """Split-k (tile, k-range) items + the pass that adds the ranges: deterministic, within the accuracy bound, and within fp32 summation-order distance of the
+    unsplit product; ragged last tiles in both directions; the workspace is checked."""
+    from kyojin_mac_b200 import _lib
+    n, k, m = 1040, 4096, 520
+    t16 = synth.t16_random_device(fmt, n, k, seed=21)
+    g = torch.Generator(device="cuda").manual_seed(22)
+    x = torch.randn((m, k), device="cuda", generator=g).to(torch.float16)
+    y1 = ops.gemm_kq(fmt, t16, n, k, x, split=1)
+    want = x.double() @ ops.dequant(fmt, t16, n, k, torch.float32).double().T
+    err1 = ((y1.double() - want).norm() / want.norm()).item()
+    for sp in (2, 4, 8):
+        ys = ops.gemm_kq(fmt, t16, n, k, x, split=sp)
+        assert torch.equal(ys, ops.gemm_kq(fmt, t16, n, k, x, split=sp))
+        err = ((ys.double() - want).norm() / want.norm()).item()
+        assert err <= 1e-3 and err <= 1.5 * err1 + 1e-6, (sp, err, err1)
+        assert torch.allclose(ys.float(), y1.float(), rtol=2e-3, atol=2e-3 * want.abs().max().item())
+    ops.check_device_status()
+    L = _lib.lib()
+    assert L.kyb_gemm_kq_split(ops._fmt("q3_k"), 3072, 12288, 2048) == 3                      # 96 tiles of 256 x 256 on 148 SMs: two rounds of thirds
+    assert L.kyb_gemm_kq_split(ops._fmt("q3_k"), 12288, 3072, 2048) == 1 and L.kyb_gemm_kq_split(ops._fmt(fmt), n, 2048, m) == 1
+    y = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    small = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    rc = L.kyb_gemm_kq_splitk(ops._fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), x.stride(0), m, 1.0, y.data_ptr(), y.stride(0), 2, small.data_ptr(), small.numel(), 0)
+    assert rc == _lib.EWORKSPACE
+    rc = L.kyb_gemm_kq_splitk(ops._fmt(fmt), t16.data_ptr(), n, k, x.data_ptr(), x.stride(0), m, 1.0, y.data_ptr(), y.stride(0), 3, small.data_ptr(), small.numel(), 0)
+    assert rc != 0                                                                            # 16 blocks do not split into 3 equal ranges
+
+
 def test_gather_epilogue_writes_every_destination():
     """The GEMM + all-gather entry points on one GPU: two 'ranks' (two shards, two output matrices in this process), every shard's tiles land in both matrices
     at the shard's column offset; the result equals the plain GEMM of each shard."""
