@@ -1292,16 +1292,20 @@ extern "C" int kyb_gemm_kq_split(int fmt, int64_t n, int64_t k, int64_t m) {
     (void)cudaGetLastError();
     const int64_t tiles = ((n + 255) / 256) * ((m + 255) / 256), nb = k / 256;
     if (tiles >= sms) return 1;                                                       // whole rounds of tiles already fill the SMs
-    // cost in 64-input stages (0.73 us each), fitted to measurements on 3072 x 12288, 1536 x 12288 and 768 x 12288 with 2048 rows: rounds x (stages per item + 8
-    // for its start and its exposed epilogue) + the second pass, which moves (ranges + 0.5) x the fp32 output at about 3 TB/s = 2.2 MB per stage time
+    // Cost model in microseconds, fitted to measurements with 2048 rows on 3072 x 12288, 1536 x 12288 and 768 x 12288: a 64-input stage of a two-block item of
+    // the one-CTA kernel takes 0.73 us, a 128-input stage of the pair kernel 0.87 us, an item 6 us more (start, exposed epilogue); the split form pays about 10 us
+    // for its second launch and moves (ranges + 0.5) x the fp32 output at about 3 MB per us. The unsplit product is whichever kernel the launcher would take
+    // (pairs unless the tile count lies between the pair count and the SM count). A split must be at least 15 % faster than that.
     const double out_mb = (double)(((m + 255) / 256) * 256) * (double)(((n + 255) / 256) * 256) * 4.0 / 1.0e6;
-    const double whole = (double)(4 * nb + 8);                                        // one round of whole-k items
+    const int64_t pairs = sms / 2;
+    double whole = 4.0 * nb * 0.73 + 6.0;                                              // fewer tiles than SMs: one round
+    if (!(tiles > pairs && tiles <= 2 * pairs)) whole = std::min(whole, (double)((tiles + pairs - 1) / pairs) * (2.0 * nb * 0.87 + 6.0));
     int best = 1;
-    double best_cost = 0.95 * whole;                                                    // a split must gain a twentieth at least
+    double best_cost = 0.85 * whole;
     for (int sp = 2; sp <= 8; ++sp) {
         if (nb % sp || nb / sp < 8) continue;                                           // equal ranges of at least 2048 inputs
         const double rounds = (double)((tiles * sp + sms - 1) / sms);
-        const double cost = rounds * (4.0 * (double)(nb / sp) + 8.0) + (sp + 0.5) * out_mb / 2.2;
+        const double cost = rounds * (4.0 * (double)(nb / sp) * 0.73 + 6.0) + 10.0 + (sp + 0.5) * out_mb / 3.0;
         if (cost < best_cost) best = sp, best_cost = cost;
     }
     return best;

@@ -111,7 +111,7 @@ def test_split_k_adds_the_ranges_in_k_order(fmt):
         assert torch.allclose(ys.float(), y1.float(), rtol=2e-3, atol=2e-3 * want.abs().max().item())
     ops.check_device_status()
     L = _lib.lib()
-    assert L.kyb_gemm_kq_split(ops._fmt("q3_k"), 3072, 12288, 2048) == 3                      # 96 tiles of 256 x 256 on 148 SMs: two rounds of thirds
+    assert L.kyb_gemm_kq_split(ops._fmt("q3_k"), 768, 12288, 2048) == 6                       # 24 tiles of 256 x 256 on 148 SMs: sixths fill one round
     assert L.kyb_gemm_kq_split(ops._fmt("q3_k"), 12288, 3072, 2048) == 1 and L.kyb_gemm_kq_split(ops._fmt(fmt), n, 2048, m) == 1
     y = torch.empty((m, n), dtype=torch.float16, device="cuda")
     small = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
